@@ -1,0 +1,359 @@
+#!/usr/bin/env python
+"""Benchmark of the generation-step hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+Default workload (the headline metric): PSO + Ackley, 1,000,000 particles x 1,000 dimensions, fp32,
+one generation per step, random draws from the in-kernel Philox stream. For N > 1 the same swarm is
+row-sharded over the ranks (strong scaling) and launched with torch.distributed.run.
+
+One JSON line is printed by rank 0. `value` is the device-timed throughput with the state resident
+in HBM; `e2e` is the same metric through StdWorkflow.step() with the step's host inputs (the three
+hyper-parameters) copied from pinned memory and the best fitness read back every step.
+`--impl reference` times the CPU restatement of the reference's eager torch path (oracle/) on the
+host cores instead.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+# Bytes per particle-dimension the fused step must move: read pop, velocity, personal best
+# (12 B), write pop, velocity (8 B). The conditional personal-best write and the per-row
+# vectors are left out, which makes `achieved` conservative.
+PSO_BYTES_PER_ELEM = 20.0
+
+# DRAM traffic per particle-dimension of pso_move_eval_kernel from the ncu capture summarised in
+# profiles/ (dram__bytes_read.sum + dram__bytes_write.sum over the elements of the captured
+# launch); None until a capture exists for the current kernel.
+PSO_NCU_TRAFFIC_BYTES_PER_ELEM = None
+
+WORKLOADS = {
+    # name: (fitness, pop, dim, lb, ub, w, phi_p, phi_g)
+    "pso_ackley_1e6x1000": ("ackley", 1_000_000, 1000, -32.768, 32.768, 0.6, 2.5, 0.8),
+    "pso_rastrigin_1e6x1000": ("rastrigin", 1_000_000, 1000, -5.12, 5.12, 0.7, 1.5, 1.5),
+    "pso_ackley_1e4x500": ("ackley", 10_000, 500, -32.768, 32.768, 0.6, 2.5, 0.8),
+    "pso_ackley_small": ("ackley", 65_536, 1000, -32.768, 32.768, 0.6, 2.5, 0.8),
+}
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle samples taken while the timed region runs."""
+
+    FIELDS = (
+        "index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+        "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+        "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+    )
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.path = None
+
+    def __enter__(self):
+        try:
+            f = tempfile.NamedTemporaryFile("w", suffix=".csv", delete=False)
+            self.path = f.name
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=f, stderr=subprocess.DEVNULL,
+            )
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self) -> dict:
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.path is None or not os.path.exists(self.path):
+            return out
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in open(self.path):
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9 or not parts[0].isdigit() or int(parts[0]) != self.gpu_index:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.path)
+        if sm:
+            # under load = the upper half of the samples (the sampler also sees idle gaps)
+            out["sm_mhz"] = statistics.median(sorted(sm)[len(sm) // 2:])
+            out["sm_max_mhz"] = max(mx)
+            out["samples"] = len(sm)
+        out["reasons"] = sorted(reasons)
+        return out
+
+
+def physical_gpu_index(local: int) -> int:
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        ids = [v for v in vis.split(",") if v.strip()]
+        if local < len(ids) and ids[local].strip().isdigit():
+            return int(ids[local])
+    return local
+
+
+# ---------------------------------------------------------------------------------------------
+# CPU baseline: the oracle's restatement of the reference's eager torch path, on the host cores.
+# ---------------------------------------------------------------------------------------------
+def cpu_pso_gens_per_s(workload: str, budget_s: float, steps: int, warmup: int):
+    """Times oracle.pso.step on a row sample of the workload and scales to the full swarm
+    (the step is linear in the number of particles). Returns (gens/s full-size, sample text, ms/step list)."""
+    from oracle import pso as opso
+
+    fit_name, P, d, lb, ub, w, pp, pg = WORKLOADS[workload]
+    torch.set_num_threads(os.cpu_count() or 1)
+    fitness = opso.FITNESS[fit_name]
+    # calibrate on a small sample, then size the timed sample to the budget
+    probe_rows = min(P, 5_000)
+    s = opso.init_step(opso.make_state(probe_rows, d, lb, ub, w, pp, pg, seed=0), fitness)
+    rg, rp = opso.draws(probe_rows, d, 1)
+    opso.step(s, rg, rp, fitness)
+    t0 = time.perf_counter()
+    opso.step(s, rg, rp, fitness)
+    per_row = (time.perf_counter() - t0) / probe_rows
+    rows = int(budget_s / max(per_row * (steps + warmup), 1e-12))
+    rows = max(min(rows, P, 200_000), min(P, 2_000))
+    s = opso.init_step(opso.make_state(rows, d, lb, ub, w, pp, pg, seed=0), fitness)
+    times = []
+    for g in range(warmup + steps):
+        t0 = time.perf_counter()
+        rg = torch.rand(rows, d)  # the reference draws both inside the step (pso.py:96-97)
+        rp = torch.rand(rows, d)
+        s = opso.step(s, rg, rp, fitness)
+        dt = time.perf_counter() - t0
+        if g >= warmup:
+            times.append(dt)
+    per_gen_full = statistics.mean(times) * (P / rows)
+    sample = f"{rows} of {P} particles x {d} dims, {steps} generations after {warmup} warm-up, scaled linearly"
+    return 1.0 / per_gen_full, sample, [t * 1e3 for t in times]
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    workload = args.workload
+    value, sample, ms = cpu_pso_gens_per_s(workload, budget_s=90.0, steps=args.steps, warmup=args.warmup)
+    fit_name, P, d, *_ = WORKLOADS[workload]
+    line = {
+        "impl": "reference",
+        "metric": "pso_generations_per_s",
+        "value": value,
+        "unit": "gens/s",
+        "n_gpus": args.gpus,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": 1e3 / value,
+        "higher_is_better": True,
+        "scaling": "strong",
+        "vs_baseline": None,
+        "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": workload, "fitness": fit_name, "pop_size": P, "dim": d},
+        "cpu_baseline": {"value": value, "unit": "gens/s", "cores": torch.get_num_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "gens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------------
+def run_ours(args):
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: evox_b200 has no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    from evox_b200 import _cabi
+    from evox_b200.algorithms import PSO
+    from evox_b200.problems.numerical import Ackley, Rastrigin
+    from evox_b200.workflows import StdWorkflow
+
+    fit_name, P, d, lb, ub, w, pp, pg = WORKLOADS[args.workload]
+    torch.manual_seed(0)
+    algo = PSO(P, torch.full((d,), lb), torch.full((d,), ub), w, pp, pg, device=dev, shard=world > 1, seed=2026)
+    # the benchmark configurations start with velocities in +-0.2 * range
+    algo.velocity.mul_(0.2)
+    problem = Ackley() if fit_name == "ackley" else Rastrigin()
+    wf = StdWorkflow(algo, problem, device=dev)
+    assert wf._fused_plan() is not None
+    wf.init_step()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return ms.item()
+
+    for _ in range(max(args.warmup, 3)):
+        wf.step()
+
+    with ClockSampler(physical_gpu_index(local)) as clocks:
+        total_ms = timed(wf.step, args.steps)
+    clock_summary = clocks.summary()
+    launches_per_step = 2 if world == 1 else 3
+    ms_per_step = total_ms / args.steps
+    value = 1e3 / ms_per_step
+
+    # -- end to end: host inputs in, result out, every step ---------------------------------
+    hyper_host = torch.tensor([w, pp, pg], dtype=torch.float32).pin_memory()
+    hyper_dev = torch.empty(3, dtype=torch.float32, device=dev)
+    best_host = torch.empty((), dtype=torch.float32).pin_memory()
+    a = wf.algorithm
+
+    def e2e_step():
+        hyper_dev.copy_(hyper_host, non_blocking=True)
+        a.w.data.copy_(hyper_dev[0])
+        a.phi_p.data.copy_(hyper_dev[1])
+        a.phi_g.data.copy_(hyper_dev[2])
+        wf.step()
+        best_host.copy_(a.global_best_fit, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for _ in range(3):
+        e2e_step()
+    e2e_ms = timed(e2e_step, args.steps) / args.steps
+
+    # -- roofline of the dominant kernel, timed alone on its launch stream -------------------
+    lib = _cabi.lib
+    n_local = a.local_size
+    params = _cabi.host_floats(problem.fused_fitness()[1])
+    fid = problem.fused_fitness()[0]
+
+    def move_only():
+        _cabi.check(
+            lib.evox_pso_move_eval(
+                a.pop.data_ptr(), a.velocity.data_ptr(), a.local_best_location.data_ptr(),
+                a.local_best_fit.data_ptr(), a.fit.data_ptr(), a.global_best_location.data_ptr(),
+                a.lb.data_ptr(), a.ub.data_ptr(), a.w.data_ptr(), a.phi_p.data_ptr(), a.phi_g.data_ptr(),
+                None, None, n_local, d, fid, params, a.seed, a.generation, a.row_start,
+                _cabi.stream_ptr(dev),
+            )
+        )
+        a.generation += 1
+
+    kernel_ms = timed(move_only, args.steps) / args.steps
+    peak, peak_kind = measured_peaks()
+    alg_bytes = PSO_BYTES_PER_ELEM * n_local * d
+    achieved = alg_bytes / (kernel_ms * 1e-3) / 1e9
+    traffic = None if PSO_NCU_TRAFFIC_BYTES_PER_ELEM is None else PSO_NCU_TRAFFIC_BYTES_PER_ELEM * n_local * d
+
+    if rank == 0:
+        line = {
+            "metric": "pso_generations_per_s",
+            "value": value,
+            "unit": "gens/s",
+            "n_gpus": world,
+            "steps": args.steps,
+            "warmup": max(args.warmup, 3),
+            "ms_per_step": ms_per_step,
+            "higher_is_better": True,
+            "scaling": "strong",
+            "vs_baseline": None,
+            "dtype": "f32",
+            "data": "synthetic",
+            "config": {
+                "workload": args.workload, "fitness": fit_name, "pop_size": P, "dim": d,
+                "rows_per_gpu": n_local, "random_draws": "in-kernel Philox4x32-10",
+                "l2": "state per GPU (%.1f GB) is larger than L2, no flush needed" % (12.0 * n_local * d / 1e9)
+                if 12.0 * n_local * d > 4 * 126e6 else "state fits in L2: numbers are L2-resident",
+                "sharding": "rows over ranks, one best-particle allgather per generation" if world > 1 else "single GPU",
+            },
+            "e2e": {
+                "value": 1e3 / e2e_ms, "unit": "gens/s", "h2d_bytes_per_step": 12, "d2h_bytes_per_step": 4,
+                "note": "StdWorkflow.step(); swarm state is device-resident by design, host inputs are the hyper-parameters",
+            },
+            "gpu_launches": launches_per_step * args.steps,
+            "roofline": {
+                "bound": "hbm", "kernel": "pso_move_eval_kernel", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                "frac": achieved / peak, "peak_kind": peak_kind, "traffic": traffic,
+                "bytes_per_launch": alg_bytes, "ms_per_launch": kernel_ms,
+            },
+            "clocks": clock_summary,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            v, sample, _ = cpu_pso_gens_per_s(args.workload, budget_s=15.0, steps=3, warmup=1)
+            line["cpu_baseline"] = {"value": v, "unit": "gens/s", "cores": torch.get_num_threads(), "kind": "port", "sample": sample}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="pso_ackley_1e6x1000", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

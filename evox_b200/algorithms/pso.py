@@ -1,0 +1,218 @@
+"""Particle swarm optimisation with the whole generation in two kernel launches.
+
+Drop-in for the reference's `PSO` (evox/algorithms/so/pso_variants/pso.py:9-115): same
+constructor arguments, same state names (`pop`, `velocity`, `fit`, `local_best_location`,
+`local_best_fit`, `global_best_location`, `global_best_fit`), same update rule. What differs:
+
+* the state tensors are updated in place by the kernels instead of being rebound each step;
+* when the workflow reports that the problem is one the update kernel can evaluate itself
+  (Ackley / Rastrigin / Sphere without shift, affine or transforms) the evaluation is fused
+  into the update and `Problem.evaluate` is not called;
+* the uniform draws come from a Philox4x32-10 stream keyed by (`seed`, generation) unless
+  `step(rg=..., rp=...)` supplies them (pso.py:96-97 draws rg first, then rp);
+* with `shard=True` under an initialised `torch.distributed` group each rank holds only its
+  rows; one allgather of a (dim + 4)-word best-particle record per generation keeps the
+  global best identical on all ranks.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .. import _cabi
+from ..core import Algorithm, Mutable, Parameter
+from ..problems.numerical import FIT_SPHERE
+from ..sharding import allgather_records, group_info, shard_bounds
+
+_INIT_GENERATION = (1 << 64) - 1  # Philox generation slot reserved for the initial swarm
+
+
+class PSO(Algorithm):
+    def __init__(
+        self,
+        pop_size: int,
+        lb: torch.Tensor,
+        ub: torch.Tensor,
+        w: float = 0.6,
+        phi_p: float = 2.5,
+        phi_g: float = 0.8,
+        device: torch.device | None = None,
+        shard: bool = False,
+        group=None,
+        seed: int | None = None,
+    ):
+        """
+        :param pop_size: number of particles (of the WHOLE swarm when `shard=True`).
+        :param lb, ub: 1-D lower / upper position bounds of equal shape and dtype float32.
+        :param w, phi_p, phi_g: inertia, cognitive and social weights.
+        :param device: where the state lives; must be a CUDA device to step.
+        :param shard: split the particles over the ranks of `group`.
+        :param seed: key of the in-kernel random stream; drawn from torch's CPU generator if None,
+            so `torch.manual_seed` makes runs repeatable (and equal on every rank).
+        """
+        super().__init__()
+        device = torch.get_default_device() if device is None else torch.device(device)
+        assert lb.shape == ub.shape and lb.ndim == 1 and ub.ndim == 1 and lb.dtype == ub.dtype
+        assert lb.dtype == torch.float32, "the PSO kernels compute in float32"
+        self.pop_size = pop_size
+        self.dim = lb.shape[0]
+        self.group = group
+        self.rank, self.world_size = group_info(group) if shard else (0, 1)
+        self.row_start, self.row_end = shard_bounds(pop_size, self.world_size, self.rank)
+        self.local_size = self.row_end - self.row_start
+        assert self.local_size > 0, "every rank needs at least one particle"
+        self.seed = int(torch.randint(0, 2**62, (), device="cpu")) if seed is None else int(seed)
+        self.generation = 0
+        # hyper-parameters stay 0-d device tensors: the kernels read them without a host sync
+        self.w = Parameter(w, dtype=torch.float32, device=device)
+        self.phi_p = Parameter(phi_p, dtype=torch.float32, device=device)
+        self.phi_g = Parameter(phi_g, dtype=torch.float32, device=device)
+        lb = lb[None, :].to(device=device).contiguous()
+        ub = ub[None, :].to(device=device).contiguous()
+        length = ub - lb
+        n, d = self.local_size, self.dim
+        if device.type == "cuda":
+            u_pop = torch.empty(n, d, dtype=torch.float32, device=device)
+            u_vel = torch.empty(n, d, dtype=torch.float32, device=device)
+            for which, out in ((0, u_pop), (1, u_vel)):
+                _cabi.check(
+                    _cabi.lib.evox_pso_fill_uniform(
+                        _cabi.ptr(out), n, d, self.seed, _INIT_GENERATION, which, self.row_start, _cabi.stream_ptr(device)
+                    )
+                )
+        else:  # host-only construction (state inspection, checkpoints); stepping needs CUDA
+            u_pop = torch.rand(n, d, device=device)
+            u_vel = torch.rand(n, d, device=device)
+        pop = length * u_pop + lb
+        velocity = 2 * length * u_vel - length
+        self.lb = lb
+        self.ub = ub
+        self.pop = Mutable(pop)
+        self.velocity = Mutable(velocity)
+        self.fit = Mutable(torch.full((n,), torch.inf, device=device))
+        self.local_best_location = Mutable(pop.clone())
+        self.local_best_fit = Mutable(torch.full((n,), torch.inf, device=device))
+        self.global_best_location = Mutable(pop[0].clone())
+        self.global_best_fit = Mutable(torch.tensor(torch.inf, device=device))
+        self._scratch: dict[str, torch.Tensor] = {}
+
+    # -- checkpointing of the random stream position ------------------------------------------
+    def get_extra_state(self):
+        return {"seed": self.seed, "generation": self.generation}
+
+    def set_extra_state(self, state):
+        self.seed = int(state["seed"])
+        self.generation = int(state["generation"])
+
+    def load_state_dict(self, state_dict, strict: bool = True, assign: bool = False):
+        # a state_dict written by the reference has no random-stream entry: keep ours
+        if "_extra_state" not in state_dict:
+            state_dict = dict(state_dict)
+            state_dict["_extra_state"] = self.get_extra_state()
+        return super().load_state_dict(state_dict, strict=strict, assign=assign)
+
+    # -- kernel plumbing -----------------------------------------------------------------------
+    def _buffers_ready(self) -> torch.device:
+        dev = self.pop.device
+        if dev.type != "cuda":
+            raise _cabi.EvoxKernelError("PSO.step needs its state on a CUDA device; evox_b200 has no CPU path")
+        for name in ("pop", "velocity", "local_best_location", "local_best_fit", "fit", "global_best_location", "global_best_fit"):
+            t = getattr(self, name)
+            if not t.is_contiguous() or t.dtype != torch.float32:
+                setattr(self, name, t.to(torch.float32).contiguous())
+        if self.local_best_location.data_ptr() == self.pop.data_ptr():
+            # a loaded reference state may alias the two (pso.py:63-66 wraps the same tensor twice)
+            self.local_best_location = self.local_best_location.clone()
+        if "ws" not in self._scratch or self._scratch["ws"].device != dev:
+            nbytes = _cabi.lib.evox_pso_workspace_bytes(self.local_size, self.dim)
+            self._scratch["ws"] = torch.zeros(nbytes, dtype=torch.uint8, device=dev)
+            words = _cabi.lib.evox_pso_candidate_words(self.dim)
+            self._scratch["cand"] = torch.zeros(words, dtype=torch.int32, device=dev)
+        return dev
+
+    def _fused_plan(self):
+        planner = getattr(self, "_workflow_fused_plan", None)
+        return planner() if planner is not None else None
+
+    def _update_global_best(self, dev: torch.device, have_previous: bool) -> None:
+        ws, cand = self._scratch["ws"], self._scratch["cand"]
+        lib, s = _cabi.lib, _cabi.stream_ptr(dev)
+        _cabi.check(
+            lib.evox_pso_local_best(
+                _cabi.ptr(self.fit), _cabi.ptr(self.pop), self.local_size, self.dim, self.row_start,
+                _cabi.ptr(cand), _cabi.ptr(ws), ws.numel(), s,
+            )
+        )
+        records = allgather_records(cand, self.group)
+        _cabi.check(
+            lib.evox_pso_merge_best(
+                _cabi.ptr(records), self.world_size, self.dim, int(have_previous),
+                _cabi.ptr(self.global_best_location), _cabi.ptr(self.global_best_fit), s,
+            )
+        )
+
+    def step(self, rg: torch.Tensor | None = None, rp: torch.Tensor | None = None):
+        """One generation (pso.py:71-106). `rg`, `rp`: optional (local_size, dim) uniform draws."""
+        dev = self._buffers_ready()
+        plan = self._fused_plan()
+        fitness_id, params = plan if plan is not None else (FIT_SPHERE, (0.0, 0.0, 0.0))
+        if (rg is None) != (rp is None):
+            raise _cabi.EvoxKernelError("rg and rp must be given together")
+        if rg is not None:
+            rg, rp = rg.contiguous(), rp.contiguous()
+            assert rg.shape == self.pop.shape and rp.shape == self.pop.shape
+        lib, s = _cabi.lib, _cabi.stream_ptr(dev)
+        ws = self._scratch["ws"]
+        args = (
+            _cabi.ptr(self.lb, torch.float32, "lb"), _cabi.ptr(self.ub, torch.float32, "ub"),
+            _cabi.ptr(self.w, torch.float32, "w"), _cabi.ptr(self.phi_p, torch.float32, "phi_p"),
+            _cabi.ptr(self.phi_g, torch.float32, "phi_g"),
+            _cabi.ptr(rg, torch.float32, "rg"), _cabi.ptr(rp, torch.float32, "rp"),
+            self.local_size, self.dim, fitness_id, _cabi.host_floats(params), self.seed, self.generation,
+        )
+        if self.world_size == 1:
+            _cabi.check(
+                lib.evox_pso_step(
+                    _cabi.ptr(self.pop), _cabi.ptr(self.velocity), _cabi.ptr(self.local_best_location),
+                    _cabi.ptr(self.local_best_fit), _cabi.ptr(self.fit), _cabi.ptr(self.global_best_location),
+                    _cabi.ptr(self.global_best_fit), *args, _cabi.ptr(ws), ws.numel(), s,
+                )
+            )
+        else:
+            self._update_global_best(dev, have_previous=True)
+            _cabi.check(
+                lib.evox_pso_move_eval(
+                    _cabi.ptr(self.pop), _cabi.ptr(self.velocity), _cabi.ptr(self.local_best_location),
+                    _cabi.ptr(self.local_best_fit), _cabi.ptr(self.fit), _cabi.ptr(self.global_best_location),
+                    *args, self.row_start, s,
+                )
+            )
+        self.generation += 1
+        if plan is None:
+            self.fit = self.evaluate(self.pop)
+        else:
+            self._workflow_notify(self.pop, self.fit)
+
+    def init_step(self):
+        """First generation (pso.py:108-115): evaluate, seed the personal and global bests."""
+        dev = self._buffers_ready()
+        plan = self._fused_plan()
+        if plan is None:
+            self.fit = self.evaluate(self.pop)
+            self._buffers_ready()
+        else:
+            fitness_id, params = plan
+            _cabi.check(
+                _cabi.lib.evox_eval_fitness(
+                    _cabi.ptr(self.pop), self.local_size, self.dim, fitness_id, _cabi.host_floats(params),
+                    _cabi.ptr(self.fit), _cabi.stream_ptr(dev),
+                )
+            )
+            self._workflow_notify(self.pop, self.fit)
+        self.local_best_fit.copy_(self.fit)
+        self._update_global_best(dev, have_previous=False)
+
+    def _workflow_notify(self, pop: torch.Tensor, fit: torch.Tensor) -> None:
+        notify = getattr(self, "_workflow_fused_notify", None)
+        if notify is not None:
+            notify(pop, fit)

@@ -1,0 +1,617 @@
+// P1: particle swarm generation step fused with the fitness evaluation.
+//
+// Reference semantics: PSO.step / PSO.init_step (evox/algorithms/so/pso_variants/pso.py:71-115),
+// min_by (pso_variants/utils.py:6-25), clamp (evox/utils/jit_fix_operator.py:24-44),
+// ackley_func / rastrigin_func (evox/problems/numerical/basic.py:66-69, 115-116).
+//
+// One generation is two launches on one stream:
+//   1. pso_local_best_kernel  — argmin over fit (4 bytes per particle), finished by the last
+//      block to arrive; it also folds the result into the running global best (single GPU) or
+//      writes a candidate record for an allgather (sharded swarm).
+//   2. pso_move_eval_kernel   — one warp per particle, 128-bit loads: personal-best update,
+//      velocity / position update, relu-form clamps and the fitness of the moved particle, with
+//      a fixed-order shuffle reduction so results do not depend on scheduling.
+// HBM traffic per particle-dimension: 12 B read (pop, velocity, personal best) + 8 B written
+// (pop, velocity), + 8 B read when rg / rp are supplied as tensors instead of Philox.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace evox {
+
+namespace {
+
+constexpr int kWarpsPerBlock = 8;
+constexpr int kThreads = kWarpsPerBlock * 32;
+constexpr int kMaxPartials = 2048;
+
+struct FitParams {
+  float a, b, c;
+};
+
+// --------------------------------------------------------------------------------------------
+// Fitness functors: per-element accumulation + per-row finalisation. Every elementwise
+// operation is rounded separately, as the reference's eager torch ops are.
+// --------------------------------------------------------------------------------------------
+template <int FIT>
+struct Fitness;
+
+template <>
+struct Fitness<EVOX_FIT_ACKLEY> {
+  float s_sq = 0.f, s_cos = 0.f;
+  __device__ __forceinline__ void add(float x, const FitParams& p) {
+    s_sq += __fmul_rn(x, x);
+    s_cos += cosf(__fmul_rn(p.c, x));
+  }
+  __device__ __forceinline__ void reduce() {
+    s_sq = warp_sum(s_sq);
+    s_cos = warp_sum(s_cos);
+  }
+  __device__ __forceinline__ float finish(int d, const FitParams& p) const {
+    const float fd = (float)d;
+    const float m_sq = __fdiv_rn(s_sq, fd);
+    const float m_cos = __fdiv_rn(s_cos, fd);
+    const float t1 = __fmul_rn(-p.a, expf(__fmul_rn(-p.b, sqrtf(m_sq))));
+    const float t2 = expf(m_cos);
+    return __fadd_rn(__fadd_rn(__fsub_rn(t1, t2), p.a), 2.718281828459045f);
+  }
+};
+
+template <>
+struct Fitness<EVOX_FIT_RASTRIGIN> {
+  float s = 0.f;
+  __device__ __forceinline__ void add(float x, const FitParams&) {
+    const float t = __fmul_rn(6.283185307179586f, x);
+    s += __fsub_rn(__fmul_rn(x, x), __fmul_rn(10.0f, cosf(t)));
+  }
+  __device__ __forceinline__ void reduce() { s = warp_sum(s); }
+  __device__ __forceinline__ float finish(int d, const FitParams&) const {
+    return __fadd_rn((float)(10 * (long long)d), s);
+  }
+};
+
+template <>
+struct Fitness<EVOX_FIT_SPHERE> {
+  float s = 0.f;
+  __device__ __forceinline__ void add(float x, const FitParams&) { s += __fmul_rn(x, x); }
+  __device__ __forceinline__ void reduce() { s = warp_sum(s); }
+  __device__ __forceinline__ float finish(int, const FitParams&) const { return s; }
+};
+
+// --------------------------------------------------------------------------------------------
+// Uniform stream of the in-kernel generator. One Philox call covers 4 consecutive columns of
+// one row for one of the two draws: counter = (q lo, q hi, generation lo, which + 2*generation hi)
+// with q = global_row * ceil(dim/4) + column/4, key = (seed lo, seed hi).
+// --------------------------------------------------------------------------------------------
+__device__ __forceinline__ float4 pso_uniform4(uint64_t q, uint64_t generation, uint32_t which,
+                                               uint64_t seed) {
+  const uint4 r = philox4x32_10((uint32_t)q, (uint32_t)(q >> 32), (uint32_t)generation,
+                                which + 2u * (uint32_t)(generation >> 32), (uint32_t)seed,
+                                (uint32_t)(seed >> 32));
+  return make_float4(u24_to_unit(r.x), u24_to_unit(r.y), u24_to_unit(r.z), u24_to_unit(r.w));
+}
+
+__device__ __forceinline__ float pick(const float4& v, int k) {
+  return k == 0 ? v.x : (k == 1 ? v.y : (k == 2 ? v.z : v.w));
+}
+
+struct MoveArgs {
+  float* pop;
+  float* vel;
+  float* pbest_loc;
+  float* pbest_fit;
+  float* fit;
+  const float* gbest_loc;
+  const float* lb;
+  const float* ub;
+  const float* w;
+  const float* phi_p;
+  const float* phi_g;
+  const float* rg;
+  const float* rp;
+  long long P;
+  int d;
+  FitParams fp;
+  uint64_t seed;
+  uint64_t generation;
+  long long row_offset;
+};
+
+// One particle-dimension of PSO.step (pso.py:98-105). Returns the clamped position.
+__device__ __forceinline__ float move_one(float x, float& v, float pb, float gb, float lb, float ub,
+                                          float rg, float rp, float w, float phi_p, float phi_g) {
+  const float inertia = __fmul_rn(w, v);
+  const float cognitive = __fmul_rn(__fmul_rn(phi_p, rp), __fsub_rn(pb, x));
+  const float social = __fmul_rn(__fmul_rn(phi_g, rg), __fsub_rn(gb, x));
+  const float vn = __fadd_rn(__fadd_rn(inertia, cognitive), social);
+  const float xn = __fadd_rn(x, vn);
+  v = relu_clamp(vn, lb, ub);
+  return relu_clamp(xn, lb, ub);
+}
+
+template <int VEC, bool PHILOX, int FIT>
+__global__ void __launch_bounds__(kThreads) pso_move_eval_kernel(const MoveArgs a) {
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = (long long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  const long long n_warps = (long long)gridDim.x * kWarpsPerBlock;
+  const float w = *a.w, phi_p = *a.phi_p, phi_g = *a.phi_g;
+  const int d = a.d;
+  const int n_call = (d + 3) >> 2;  // Philox calls per row and draw
+
+  for (long long row = warp0; row < a.P; row += n_warps) {
+    const float f_old = a.fit[row];
+    const float pbf = a.pbest_fit[row];
+    const bool better = pbf > f_old;  // pso.py:89
+    const size_t base = (size_t)row * (size_t)d;
+    Fitness<FIT> acc;
+
+    if constexpr (VEC == 4) {
+      float4* pop4 = reinterpret_cast<float4*>(a.pop + base);
+      float4* vel4 = reinterpret_cast<float4*>(a.vel + base);
+      float4* pb4 = reinterpret_cast<float4*>(a.pbest_loc + base);
+      const float4* gb4 = reinterpret_cast<const float4*>(a.gbest_loc);
+      const float4* lb4 = reinterpret_cast<const float4*>(a.lb);
+      const float4* ub4 = reinterpret_cast<const float4*>(a.ub);
+      const float4* rg4 = PHILOX ? nullptr : reinterpret_cast<const float4*>(a.rg + base);
+      const float4* rp4 = PHILOX ? nullptr : reinterpret_cast<const float4*>(a.rp + base);
+      const uint64_t q0 = (uint64_t)(a.row_offset + row) * (uint64_t)n_call;
+#pragma unroll 2
+      for (int c = lane; c < n_call; c += 32) {
+        const float4 x = __ldcs(pop4 + c);
+        float4 v = __ldcs(vel4 + c);
+        float4 pb;
+        if (better) {
+          pb = x;  // pso.py:90 — the particle's own position becomes its personal best
+        } else {
+          pb = __ldcs(pb4 + c);
+        }
+        float4 rg, rp;
+        if constexpr (PHILOX) {
+          rg = pso_uniform4(q0 + c, a.generation, 0u, a.seed);
+          rp = pso_uniform4(q0 + c, a.generation, 1u, a.seed);
+        } else {
+          rg = __ldcs(rg4 + c);
+          rp = __ldcs(rp4 + c);
+        }
+        const float4 gb = __ldg(gb4 + c);
+        const float4 lb = __ldg(lb4 + c);
+        const float4 ub = __ldg(ub4 + c);
+        float4 xo;
+        xo.x = move_one(x.x, v.x, pb.x, gb.x, lb.x, ub.x, rg.x, rp.x, w, phi_p, phi_g);
+        xo.y = move_one(x.y, v.y, pb.y, gb.y, lb.y, ub.y, rg.y, rp.y, w, phi_p, phi_g);
+        xo.z = move_one(x.z, v.z, pb.z, gb.z, lb.z, ub.z, rg.z, rp.z, w, phi_p, phi_g);
+        xo.w = move_one(x.w, v.w, pb.w, gb.w, lb.w, ub.w, rg.w, rp.w, w, phi_p, phi_g);
+        if (better) __stcs(pb4 + c, x);
+        __stcs(pop4 + c, xo);
+        __stcs(vel4 + c, v);
+        acc.add(xo.x, a.fp);
+        acc.add(xo.y, a.fp);
+        acc.add(xo.z, a.fp);
+        acc.add(xo.w, a.fp);
+      }
+    } else {
+      const uint64_t q0 = (uint64_t)(a.row_offset + row) * (uint64_t)n_call;
+      for (int e = lane; e < d; e += 32) {
+        const float x = a.pop[base + e];
+        float v = a.vel[base + e];
+        const float pb = better ? x : a.pbest_loc[base + e];
+        float rg, rp;
+        if constexpr (PHILOX) {
+          rg = pick(pso_uniform4(q0 + (e >> 2), a.generation, 0u, a.seed), e & 3);
+          rp = pick(pso_uniform4(q0 + (e >> 2), a.generation, 1u, a.seed), e & 3);
+        } else {
+          rg = a.rg[base + e];
+          rp = a.rp[base + e];
+        }
+        const float xo = move_one(x, v, pb, a.gbest_loc[e], a.lb[e], a.ub[e], rg, rp, w, phi_p, phi_g);
+        if (better) a.pbest_loc[base + e] = x;
+        a.pop[base + e] = xo;
+        a.vel[base + e] = v;
+        acc.add(xo, a.fp);
+      }
+    }
+    acc.reduce();
+    if (lane == 0) {
+      a.fit[row] = acc.finish(d, a.fp);     // pso.py:106
+      if (better) a.pbest_fit[row] = f_old;  // pso.py:91
+    }
+  }
+}
+
+template <int VEC, int FIT>
+__global__ void __launch_bounds__(kThreads)
+    eval_fitness_kernel(const float* __restrict__ pop, long long P, int d, FitParams fp, float* __restrict__ fit) {
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = (long long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  const long long n_warps = (long long)gridDim.x * kWarpsPerBlock;
+  for (long long row = warp0; row < P; row += n_warps) {
+    const size_t base = (size_t)row * (size_t)d;
+    Fitness<FIT> acc;
+    if constexpr (VEC == 4) {
+      const float4* p4 = reinterpret_cast<const float4*>(pop + base);
+      const int n4 = d >> 2;
+#pragma unroll 4
+      for (int c = lane; c < n4; c += 32) {
+        const float4 x = __ldg(p4 + c);
+        acc.add(x.x, fp);
+        acc.add(x.y, fp);
+        acc.add(x.z, fp);
+        acc.add(x.w, fp);
+      }
+    } else {
+      for (int e = lane; e < d; e += 32) acc.add(pop[base + e], fp);
+    }
+    acc.reduce();
+    if (lane == 0) fit[row] = acc.finish(d, fp);
+  }
+}
+
+// --------------------------------------------------------------------------------------------
+// argmin over the shard + optional fold into the running global best.
+// Workspace layout: [0] uint32 ticket | [64 ..) MinIdx partials[kMaxPartials].
+// --------------------------------------------------------------------------------------------
+struct BestArgs {
+  const float* fit;
+  const float* pop;
+  long long P;
+  int d;
+  long long row_offset;
+  uint32_t* candidate;  // record out, or nullptr when folding directly
+  float* gbest_loc;     // used when candidate == nullptr
+  float* gbest_fit;
+  int have_previous;
+  unsigned int* ticket;
+  MinIdx* partials;
+};
+
+__device__ __forceinline__ MinIdx block_min_idx(MinIdx m, MinIdx* smem) {
+  m = warp_min_idx(m);
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  if (lane == 0) smem[wid] = m;
+  __syncthreads();
+  if (wid == 0) {
+    MinIdx t = (lane < (int)(blockDim.x >> 5)) ? smem[lane] : MinIdx{INFINITY, 0x7fffffffffffffffLL};
+    t = warp_min_idx(t);
+    if (lane == 0) smem[0] = t;
+  }
+  __syncthreads();
+  MinIdx r = smem[0];
+  __syncthreads();
+  return r;
+}
+
+__global__ void __launch_bounds__(kThreads) pso_local_best_kernel(const BestArgs a) {
+  __shared__ MinIdx smem[32];
+  __shared__ bool is_last;
+  // +inf with the largest index loses against every real entry (an all-+inf shard still
+  // reports index 0 because equal keys resolve to the lower index).
+  MinIdx m{INFINITY, 0x7fffffffffffffffLL};
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < a.P; i += (long long)gridDim.x * blockDim.x) {
+    m = min_idx_combine(m, MinIdx{a.fit[i], i});
+  }
+  m = block_min_idx(m, smem);
+  if (threadIdx.x == 0) {
+    a.partials[blockIdx.x] = m;
+    __threadfence();
+    const unsigned int t = atomicAdd(a.ticket, 1u);
+    is_last = (t == gridDim.x - 1);
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  MinIdx f{INFINITY, 0x7fffffffffffffffLL};
+  for (int i = threadIdx.x; i < (int)gridDim.x; i += blockDim.x) {
+    const volatile MinIdx* p = a.partials + i;
+    f = min_idx_combine(f, MinIdx{p->v, p->i});
+  }
+  f = block_min_idx(f, smem);
+  if (threadIdx.x == 0) *a.ticket = 0u;  // ready for the next launch
+  const float* row = a.pop + (size_t)f.i * (size_t)a.d;
+  if (a.candidate != nullptr) {
+    if (threadIdx.x == 0) {
+      const long long g = f.i + a.row_offset;
+      a.candidate[0] = __float_as_uint(f.v);
+      a.candidate[1] = (uint32_t)((unsigned long long)g & 0xffffffffull);
+      a.candidate[2] = (uint32_t)((unsigned long long)g >> 32);
+      a.candidate[3] = 0u;
+    }
+    for (int e = threadIdx.x; e < a.d; e += blockDim.x) a.candidate[4 + e] = __float_as_uint(row[e]);
+  } else {
+    // torch.argmin over cat([old best, fit]): the old best sits at index 0 and wins ties.
+    const bool take = !a.have_previous || key_less(f.v, *a.gbest_fit);
+    if (take) {
+      for (int e = threadIdx.x; e < a.d; e += blockDim.x) a.gbest_loc[e] = row[e];
+      __syncthreads();
+      if (threadIdx.x == 0) *a.gbest_fit = f.v;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kThreads)
+    pso_merge_best_kernel(const uint32_t* __restrict__ cands, int n, int d, int have_previous,
+                          float* gbest_loc, float* gbest_fit) {
+  __shared__ int winner;
+  const int words = 4 + d;
+  if (threadIdx.x == 0) {
+    MinIdx best{INFINITY, 0x7fffffffffffffffLL};
+    int bi = 0;
+    for (int r = 0; r < n; ++r) {
+      const uint32_t* c = cands + (size_t)r * words;
+      const MinIdx m{__uint_as_float(c[0]), (long long)(((unsigned long long)c[2] << 32) | c[1])};
+      const bool wins = r == 0 || key_less(m.v, best.v) || (!key_less(best.v, m.v) && m.i < best.i);
+      if (wins) {
+        best = m;
+        bi = r;
+      }
+    }
+    const bool take = !have_previous || key_less(best.v, *gbest_fit);
+    winner = take ? bi : -1;
+    if (take) *gbest_fit = best.v;
+  }
+  __syncthreads();
+  if (winner < 0) return;
+  const uint32_t* c = cands + (size_t)winner * words + 4;
+  for (int e = threadIdx.x; e < d; e += blockDim.x) gbest_loc[e] = __uint_as_float(c[e]);
+}
+
+template <int VEC>
+__global__ void __launch_bounds__(kThreads)
+    pso_fill_uniform_kernel(float* __restrict__ out, long long P, int d, uint64_t seed, uint64_t generation,
+                            uint32_t which, long long row_offset) {
+  const int n_call = (d + 3) >> 2;
+  const long long total = P * (long long)n_call;
+  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
+    const long long row = t / n_call;
+    const int c = (int)(t - row * n_call);
+    const uint64_t q = (uint64_t)(row_offset + row) * (uint64_t)n_call + (uint64_t)c;
+    const float4 u = pso_uniform4(q, generation, which, seed);
+    float* o = out + (size_t)row * (size_t)d + 4 * (size_t)c;
+    if constexpr (VEC == 4) {
+      *reinterpret_cast<float4*>(o) = u;
+    } else {
+      const int rem = d - 4 * c;
+      o[0] = u.x;
+      if (rem > 1) o[1] = u.y;
+      if (rem > 2) o[2] = u.z;
+      if (rem > 3) o[3] = u.w;
+    }
+  }
+}
+
+// --------------------------------------------------------------------------------------------
+// Host-side helpers
+// --------------------------------------------------------------------------------------------
+struct Workspace {
+  unsigned int* ticket;
+  MinIdx* partials;
+};
+
+constexpr size_t kWsBytes = 64 + sizeof(MinIdx) * kMaxPartials;
+
+int carve(void* ws, size_t bytes, Workspace* out) {
+  EVOX_REQUIRE(ws != nullptr, EVOX_ERR_WORKSPACE, "pso: workspace is NULL");
+  EVOX_REQUIRE(bytes >= kWsBytes, EVOX_ERR_WORKSPACE, "pso: workspace of %zu bytes is smaller than %zu", bytes, kWsBytes);
+  EVOX_REQUIRE(aligned16(ws), EVOX_ERR_INVALID, "pso: workspace must be 16-byte aligned");
+  out->ticket = reinterpret_cast<unsigned int*>(ws);
+  out->partials = reinterpret_cast<MinIdx*>(reinterpret_cast<char*>(ws) + 64);
+  return EVOX_OK;
+}
+
+int row_grid(long long P) {
+  // persistent grid: enough resident warps to cover HBM latency, never more rows than exist
+  const long long want = (P + kWarpsPerBlock - 1) / kWarpsPerBlock;
+  const long long cap = (long long)sm_count() * 8;  // 8 blocks x 8 warps = 64 warps per SM
+  return (int)(want < cap ? (want < 1 ? 1 : want) : cap);
+}
+
+int check_fit(int fitness_id, const float* params, FitParams* fp) {
+  EVOX_REQUIRE(fitness_id >= EVOX_FIT_ACKLEY && fitness_id <= EVOX_FIT_SPHERE, EVOX_ERR_INVALID,
+               "unknown fitness_id %d", fitness_id);
+  fp->a = fp->b = fp->c = 0.f;
+  if (fitness_id == EVOX_FIT_ACKLEY) {
+    EVOX_REQUIRE(params != nullptr, EVOX_ERR_INVALID, "Ackley needs params {a, b, c}");
+    fp->a = params[0];
+    fp->b = params[1];
+    fp->c = params[2];
+  }
+  return EVOX_OK;
+}
+
+template <int VEC, bool PHILOX>
+void launch_move(int fitness_id, int grid, cudaStream_t s, const MoveArgs& a) {
+  switch (fitness_id) {
+    case EVOX_FIT_ACKLEY:
+      pso_move_eval_kernel<VEC, PHILOX, EVOX_FIT_ACKLEY><<<grid, kThreads, 0, s>>>(a);
+      break;
+    case EVOX_FIT_RASTRIGIN:
+      pso_move_eval_kernel<VEC, PHILOX, EVOX_FIT_RASTRIGIN><<<grid, kThreads, 0, s>>>(a);
+      break;
+    default:
+      pso_move_eval_kernel<VEC, PHILOX, EVOX_FIT_SPHERE><<<grid, kThreads, 0, s>>>(a);
+      break;
+  }
+}
+
+int launch_local_best(const float* fit, const float* pop, long long P, int d, long long row_offset,
+                      uint32_t* candidate, float* gbest_loc, float* gbest_fit, int have_previous,
+                      const Workspace& ws, cudaStream_t s) {
+  BestArgs b;
+  b.fit = fit;
+  b.pop = pop;
+  b.P = P;
+  b.d = d;
+  b.row_offset = row_offset;
+  b.candidate = candidate;
+  b.gbest_loc = gbest_loc;
+  b.gbest_fit = gbest_fit;
+  b.have_previous = have_previous;
+  b.ticket = ws.ticket;
+  b.partials = ws.partials;
+  long long want = (P + (long long)kThreads * 8 - 1) / ((long long)kThreads * 8);
+  long long cap = (long long)sm_count() * 2;
+  if (cap > kMaxPartials) cap = kMaxPartials;
+  int grid = (int)(want < 1 ? 1 : (want < cap ? want : cap));
+  pso_local_best_kernel<<<grid, kThreads, 0, s>>>(b);
+  EVOX_LAUNCH_CHECK();
+  return EVOX_OK;
+}
+
+int check_shape(long long P, int d) {
+  EVOX_REQUIRE(P > 0, EVOX_ERR_INVALID, "pop_size must be positive, got %lld", P);
+  EVOX_REQUIRE(d > 0, EVOX_ERR_INVALID, "dim must be positive, got %d", d);
+  return EVOX_OK;
+}
+
+}  // namespace
+}  // namespace evox
+
+using namespace evox;
+
+extern "C" size_t evox_pso_workspace_bytes(int64_t, int32_t) { return kWsBytes; }
+
+extern "C" int32_t evox_pso_candidate_words(int32_t dim) { return 4 + dim; }
+
+extern "C" int evox_eval_fitness(const float* pop, int64_t pop_size, int32_t dim, int32_t fitness_id,
+                                 const float* params, float* fit, void* stream) {
+  if (int rc = check_shape(pop_size, dim)) return rc;
+  EVOX_REQUIRE(pop && fit, EVOX_ERR_INVALID, "eval_fitness: NULL pointer");
+  FitParams fp;
+  if (int rc = check_fit(fitness_id, params, &fp)) return rc;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const int grid = row_grid(pop_size);
+  const bool vec = (dim % 4 == 0) && aligned16(pop);
+#define EVOX_EVAL(V, F) eval_fitness_kernel<V, F><<<grid, kThreads, 0, s>>>(pop, pop_size, dim, fp, fit)
+  if (vec) {
+    if (fitness_id == EVOX_FIT_ACKLEY) EVOX_EVAL(4, EVOX_FIT_ACKLEY);
+    else if (fitness_id == EVOX_FIT_RASTRIGIN) EVOX_EVAL(4, EVOX_FIT_RASTRIGIN);
+    else EVOX_EVAL(4, EVOX_FIT_SPHERE);
+  } else {
+    if (fitness_id == EVOX_FIT_ACKLEY) EVOX_EVAL(1, EVOX_FIT_ACKLEY);
+    else if (fitness_id == EVOX_FIT_RASTRIGIN) EVOX_EVAL(1, EVOX_FIT_RASTRIGIN);
+    else EVOX_EVAL(1, EVOX_FIT_SPHERE);
+  }
+#undef EVOX_EVAL
+  EVOX_LAUNCH_CHECK();
+  return EVOX_OK;
+}
+
+extern "C" int evox_pso_local_best(const float* fit, const float* pop, int64_t pop_size, int32_t dim,
+                                   int64_t row_offset, uint32_t* candidate, void* workspace,
+                                   size_t workspace_bytes, void* stream) {
+  if (int rc = check_shape(pop_size, dim)) return rc;
+  EVOX_REQUIRE(fit && pop && candidate, EVOX_ERR_INVALID, "pso_local_best: NULL pointer");
+  Workspace ws;
+  if (int rc = carve(workspace, workspace_bytes, &ws)) return rc;
+  return launch_local_best(fit, pop, pop_size, dim, row_offset, candidate, nullptr, nullptr, 0, ws,
+                           reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" int evox_pso_merge_best(const uint32_t* candidates, int32_t n_candidates, int32_t dim,
+                                   int32_t have_previous, float* global_best_location,
+                                   float* global_best_fit, void* stream) {
+  EVOX_REQUIRE(candidates && global_best_location && global_best_fit, EVOX_ERR_INVALID, "pso_merge_best: NULL pointer");
+  EVOX_REQUIRE(n_candidates > 0 && dim > 0, EVOX_ERR_INVALID, "pso_merge_best: n_candidates and dim must be positive");
+  pso_merge_best_kernel<<<1, kThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      candidates, n_candidates, dim, have_previous, global_best_location, global_best_fit);
+  EVOX_LAUNCH_CHECK();
+  return EVOX_OK;
+}
+
+extern "C" int evox_pso_move_eval(float* pop, float* velocity, float* local_best_location,
+                                  float* local_best_fit, float* fit, const float* global_best_location,
+                                  const float* lb, const float* ub, const float* w, const float* phi_p,
+                                  const float* phi_g, const float* rg, const float* rp, int64_t pop_size,
+                                  int32_t dim, int32_t fitness_id, const float* params, uint64_t seed,
+                                  uint64_t generation, int64_t row_offset, void* stream) {
+  if (int rc = check_shape(pop_size, dim)) return rc;
+  EVOX_REQUIRE(pop && velocity && local_best_location && local_best_fit && fit && global_best_location && lb &&
+                   ub && w && phi_p && phi_g,
+               EVOX_ERR_INVALID, "pso_move_eval: NULL pointer");
+  EVOX_REQUIRE((rg == nullptr) == (rp == nullptr), EVOX_ERR_INVALID,
+               "pso_move_eval: rg and rp must both be given or both be NULL");
+  MoveArgs a;
+  if (int rc = check_fit(fitness_id, params, &a.fp)) return rc;
+  a.pop = pop;
+  a.vel = velocity;
+  a.pbest_loc = local_best_location;
+  a.pbest_fit = local_best_fit;
+  a.fit = fit;
+  a.gbest_loc = global_best_location;
+  a.lb = lb;
+  a.ub = ub;
+  a.w = w;
+  a.phi_p = phi_p;
+  a.phi_g = phi_g;
+  a.rg = rg;
+  a.rp = rp;
+  a.P = pop_size;
+  a.d = dim;
+  a.seed = seed;
+  a.generation = generation;
+  a.row_offset = row_offset;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const int grid = row_grid(pop_size);
+  const bool philox = (rg == nullptr);
+  bool vec = (dim % 4 == 0) && aligned16(pop) && aligned16(velocity) && aligned16(local_best_location) &&
+             aligned16(global_best_location) && aligned16(lb) && aligned16(ub);
+  if (!philox) vec = vec && aligned16(rg) && aligned16(rp);
+  if (vec) {
+    if (philox) launch_move<4, true>(fitness_id, grid, s, a);
+    else launch_move<4, false>(fitness_id, grid, s, a);
+  } else {
+    if (philox) launch_move<1, true>(fitness_id, grid, s, a);
+    else launch_move<1, false>(fitness_id, grid, s, a);
+  }
+  EVOX_LAUNCH_CHECK();
+  return EVOX_OK;
+}
+
+extern "C" int evox_pso_step(float* pop, float* velocity, float* local_best_location, float* local_best_fit,
+                             float* fit, float* global_best_location, float* global_best_fit,
+                             const float* lb, const float* ub, const float* w, const float* phi_p,
+                             const float* phi_g, const float* rg, const float* rp, int64_t pop_size,
+                             int32_t dim, int32_t fitness_id, const float* params, uint64_t seed,
+                             uint64_t generation, void* workspace, size_t workspace_bytes, void* stream) {
+  if (int rc = check_shape(pop_size, dim)) return rc;
+  EVOX_REQUIRE(fit && pop && global_best_location && global_best_fit, EVOX_ERR_INVALID, "pso_step: NULL pointer");
+  Workspace ws;
+  if (int rc = carve(workspace, workspace_bytes, &ws)) return rc;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (int rc = launch_local_best(fit, pop, pop_size, dim, 0, nullptr, global_best_location, global_best_fit, 1, ws, s))
+    return rc;
+  return evox_pso_move_eval(pop, velocity, local_best_location, local_best_fit, fit, global_best_location, lb, ub,
+                            w, phi_p, phi_g, rg, rp, pop_size, dim, fitness_id, params, seed, generation, 0, stream);
+}
+
+extern "C" int evox_pso_init_step(const float* pop, float* fit, float* local_best_fit,
+                                  float* global_best_location, float* global_best_fit, int64_t pop_size,
+                                  int32_t dim, int32_t fitness_id, const float* params, void* workspace,
+                                  size_t workspace_bytes, void* stream) {
+  if (int rc = check_shape(pop_size, dim)) return rc;
+  EVOX_REQUIRE(pop && fit && local_best_fit && global_best_location && global_best_fit, EVOX_ERR_INVALID,
+               "pso_init_step: NULL pointer");
+  Workspace ws;
+  if (int rc = carve(workspace, workspace_bytes, &ws)) return rc;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (int rc = evox_eval_fitness(pop, pop_size, dim, fitness_id, params, fit, stream)) return rc;
+  EVOX_CUDA(cudaMemcpyAsync(local_best_fit, fit, sizeof(float) * (size_t)pop_size, cudaMemcpyDeviceToDevice, s));
+  return launch_local_best(fit, pop, pop_size, dim, 0, nullptr, global_best_location, global_best_fit, 0, ws, s);
+}
+
+extern "C" int evox_pso_fill_uniform(float* out, int64_t pop_size, int32_t dim, uint64_t seed,
+                                     uint64_t generation, int32_t which, int64_t row_offset, void* stream) {
+  if (int rc = check_shape(pop_size, dim)) return rc;
+  EVOX_REQUIRE(out != nullptr, EVOX_ERR_INVALID, "pso_fill_uniform: NULL pointer");
+  EVOX_REQUIRE(which == 0 || which == 1, EVOX_ERR_INVALID, "pso_fill_uniform: which must be 0 (rg) or 1 (rp)");
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const long long total = pop_size * (long long)((dim + 3) / 4);
+  long long want = (total + kThreads - 1) / kThreads;
+  const long long cap = (long long)sm_count() * 16;
+  const int grid = (int)(want < cap ? want : cap);
+  if (dim % 4 == 0 && aligned16(out))
+    pso_fill_uniform_kernel<4><<<grid, kThreads, 0, s>>>(out, pop_size, dim, seed, generation, (uint32_t)which, row_offset);
+  else
+    pso_fill_uniform_kernel<1><<<grid, kThreads, 0, s>>>(out, pop_size, dim, seed, generation, (uint32_t)which, row_offset);
+  EVOX_LAUNCH_CHECK();
+  return EVOX_OK;
+}

@@ -1,0 +1,118 @@
+/*
+ * evox_b200 — C-ABI of the B200 (sm_100a) kernels behind the population-batched
+ * generation step of EvoX (PSO step, NSGA-II / RVEA environmental selection,
+ * virtual-LoRA ES forward and update).
+ *
+ * Conventions
+ *  - Every pointer named in a signature is a DEVICE pointer unless its comment says
+ *    "host". Arrays are dense row-major. Nothing here allocates device memory unless
+ *    its comment says so: outputs and scratch ("workspace") are supplied by the caller,
+ *    who asks the matching *_workspace_bytes() function for the size.
+ *  - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream).
+ *    Calls only enqueue work; none of them synchronises the device.
+ *  - Return value: 0 on success, a negative EVOX_ERR_* code otherwise;
+ *    evox_last_error() returns the message of the calling thread's last failure.
+ *  - File and line citations name the function of the reference implementation
+ *    (EMI-Group/evox, paths relative to its src/evox/) that the entry point replaces.
+ */
+#ifndef EVOX_B200_H_
+#define EVOX_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define EVOX_OK 0
+#define EVOX_ERR_INVALID (-1)   /* bad argument (shape, alignment, null pointer, unsupported size) */
+#define EVOX_ERR_CUDA (-2)      /* a CUDA runtime call or kernel launch failed */
+#define EVOX_ERR_WORKSPACE (-3) /* workspace too small */
+#define EVOX_ERR_TIMEOUT (-4)   /* a bounded device-side wait gave up (status word reported it) */
+
+/* Fitness functions fused into the PSO step (problems/numerical/basic.py). */
+#define EVOX_FIT_ACKLEY 0    /* basic.py:66-69, params = {a, b, c} */
+#define EVOX_FIT_RASTRIGIN 1 /* basic.py:115-116, no params */
+#define EVOX_FIT_SPHERE 2    /* sum(x^2), no params */
+
+const char* evox_last_error(void);
+int evox_version(void);
+
+/* ------------------------------------------------------------------------------------------
+ * P1. Particle swarm step fused with the fitness evaluation.
+ * ------------------------------------------------------------------------------------------ */
+
+/* Evaluate a numerical test function on every row of `pop` (pop_size x dim, fp32) into
+ * `fit` (pop_size). Replaces ShiftAffineNumericalProblem.evaluate with shift = affine = None
+ * (problems/numerical/basic.py:52-63) for ackley_func (:66-69) and rastrigin_func (:115-116).
+ * `params` is a HOST array of 3 floats (Ackley: a, b, c; ignored otherwise). */
+int evox_eval_fitness(const float* pop, int64_t pop_size, int32_t dim, int32_t fitness_id,
+                      const float* params, float* fit, void* stream);
+
+/* Bytes of scratch the PSO entry points need for a shard of `pop_size` rows of `dim` columns.
+ * The workspace must be zero-filled once before its first use and then left alone. */
+size_t evox_pso_workspace_bytes(int64_t pop_size, int32_t dim);
+
+/* Number of 4-byte words of one best-particle candidate record (see evox_pso_local_best). */
+int32_t evox_pso_candidate_words(int32_t dim);
+
+/* First half of PSO.step (algorithms/so/pso_variants/pso.py:92-95 with
+ * pso_variants/utils.py:18-25): argmin of `fit` over this shard's rows and the row of `pop`
+ * it points at, written as one candidate record
+ *   word 0: fitness (fp32) | word 1,2: GLOBAL row index (int64 = row_offset + local row)
+ *   word 3: 0 | words 4..4+dim-1: the row
+ * so that the records of several shards can be exchanged with one allgather. Ties resolve to
+ * the lowest index and NaN counts as the minimum, as torch.argmin does. */
+int evox_pso_local_best(const float* fit, const float* pop, int64_t pop_size, int32_t dim,
+                        int64_t row_offset, uint32_t* candidate, void* workspace,
+                        size_t workspace_bytes, void* stream);
+
+/* Second half of min_by: fold `n_candidates` records (n_candidates * evox_pso_candidate_words
+ * words, in rank order) into the running global best. The old global best wins ties, then the
+ * lowest global row index (torch.cat puts the old best at index 0, pso.py:92-95).
+ * With `have_previous` == 0 the old best is ignored (PSO.init_step, pso.py:108-115). */
+int evox_pso_merge_best(const uint32_t* candidates, int32_t n_candidates, int32_t dim,
+                        int32_t have_previous, float* global_best_location,
+                        float* global_best_fit, void* stream);
+
+/* Rest of PSO.step (pso.py:89-91 and :96-106) fused with the fitness evaluation of the moved
+ * swarm: personal-best update from (fit, pop), velocity and position update with the relu-form
+ * clamp (utils/jit_fix_operator.py:42-44; the velocity is clamped with the POSITION bounds,
+ * pso.py:105), then fit = f(pop). pop, velocity, local_best_location, local_best_fit and fit
+ * are updated in place. w, phi_p, phi_g are DEVICE scalars (the reference keeps them as 0-d
+ * Parameters, pso.py:46-50). rg and rp are either both (pop_size x dim) uniform draws, in the
+ * order the reference draws them (pso.py:96-97), or both NULL: then they are generated inside
+ * the kernel from Philox4x32-10 with key = seed and counter = (global row, column/4,
+ * generation, stream) — exactly the numbers evox_pso_fill_uniform() writes. */
+int evox_pso_move_eval(float* pop, float* velocity, float* local_best_location,
+                       float* local_best_fit, float* fit, const float* global_best_location,
+                       const float* lb, const float* ub, const float* w, const float* phi_p,
+                       const float* phi_g, const float* rg, const float* rp, int64_t pop_size,
+                       int32_t dim, int32_t fitness_id, const float* params, uint64_t seed,
+                       uint64_t generation, int64_t row_offset, void* stream);
+
+/* One whole single-GPU generation: local_best + merge_best + move_eval (PSO.step, pso.py:71-106). */
+int evox_pso_step(float* pop, float* velocity, float* local_best_location, float* local_best_fit,
+                  float* fit, float* global_best_location, float* global_best_fit,
+                  const float* lb, const float* ub, const float* w, const float* phi_p,
+                  const float* phi_g, const float* rg, const float* rp, int64_t pop_size,
+                  int32_t dim, int32_t fitness_id, const float* params, uint64_t seed,
+                  uint64_t generation, void* workspace, size_t workspace_bytes, void* stream);
+
+/* PSO.init_step (pso.py:108-115): fit = f(pop); local_best_fit = fit; global best = min_by. */
+int evox_pso_init_step(const float* pop, float* fit, float* local_best_fit,
+                       float* global_best_location, float* global_best_fit, int64_t pop_size,
+                       int32_t dim, int32_t fitness_id, const float* params, void* workspace,
+                       size_t workspace_bytes, void* stream);
+
+/* Materialise the uniform draws the in-kernel generator of evox_pso_move_eval uses:
+ * which = 0 -> rg, 1 -> rp. out is (pop_size x dim) fp32 in [0, 1) with 24 random bits,
+ * (u >> 8) * 2^-24 as in triton_kernels/kernels/philox.py:108-110. */
+int evox_pso_fill_uniform(float* out, int64_t pop_size, int32_t dim, uint64_t seed,
+                          uint64_t generation, int32_t which, int64_t row_offset, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* EVOX_B200_H_ */

@@ -1,0 +1,104 @@
+"""Generate the golden vectors under tests/golden/ by running the REFERENCE implementation.
+
+Run in a container that has the reference checkout:
+    python tests/golden/make_golden.py --reference /root/reference/src [--only pso,...]
+The reference is imported from that path, run in eager mode on CPU (torch's own CPU kernels),
+and its inputs / outputs are saved as small .npz files. The tests never import the reference;
+they only read these files. Random draws the reference takes from torch's global generator
+(`torch.rand` inside `PSO.step`) are replaced by recorded tensors so that the same draws can
+be fed to the oracle and to the CUDA kernels.
+"""
+
+from __future__ import annotations
+
+import argparse
+import sys
+from pathlib import Path
+
+import numpy as np
+import torch
+
+HERE = Path(__file__).resolve().parent
+
+
+def _np(t):
+    return t.detach().cpu().numpy() if isinstance(t, torch.Tensor) else np.asarray(t)
+
+
+def golden_pso(out: dict):
+    """PSO.init_step + 3 teacher-forced steps on Ackley and Rastrigin, dims 12 (vector path)
+    and 10 (scalar path); every state tensor before and after each step is stored."""
+    from evox.algorithms import PSO
+    from evox.problems.numerical import Ackley, Rastrigin
+    from evox.workflows import StdWorkflow
+
+    import evox.algorithms.so.pso_variants.pso as pso_mod
+
+    names = ["pop", "velocity", "fit", "local_best_location", "local_best_fit", "global_best_location", "global_best_fit"]
+    for prob_name, prob_cls, lo, hi, hyper in (
+        ("ackley", Ackley, -32.768, 32.768, (0.6, 2.5, 0.8)),
+        ("rastrigin", Rastrigin, -5.12, 5.12, (0.7, 1.5, 1.5)),
+    ):
+        for dim in (12, 10):
+            pop_size = 37
+            torch.manual_seed(1234 + dim)
+            lb = torch.full((dim,), lo)
+            ub = torch.full((dim,), hi)
+            algo = PSO(pop_size, lb, ub, *hyper)
+            # the benchmark configurations start with velocities in +-0.2 * range
+            algo.velocity = 0.2 * algo.velocity
+            wf = StdWorkflow(algo, prob_cls())
+            tag = f"pso_{prob_name}_d{dim}"
+            out[f"{tag}_hyper"] = np.asarray(hyper, dtype=np.float32)
+            out[f"{tag}_bounds"] = np.asarray([lo, hi], dtype=np.float32)
+            state0 = {k: v.clone() for k, v in wf.algorithm.state_dict().items()}
+            for n in names:
+                out[f"{tag}_s0_{n}"] = _np(state0[n])
+            wf.init_step()
+            for n in names:
+                out[f"{tag}_s1_{n}"] = _np(wf.algorithm.state_dict()[n])
+            gen = torch.Generator().manual_seed(99 + dim)
+            for g in range(3):
+                rg = torch.rand(pop_size, dim, generator=gen)
+                rp = torch.rand(pop_size, dim, generator=gen)
+                queue = [rg, rp]
+                real_rand = torch.rand
+
+                def fake_rand(*a, **k):
+                    return queue.pop(0)
+
+                pso_mod.torch.rand = fake_rand
+                try:
+                    wf.step()
+                finally:
+                    pso_mod.torch.rand = real_rand
+                assert not queue
+                out[f"{tag}_g{g}_rg"] = _np(rg)
+                out[f"{tag}_g{g}_rp"] = _np(rp)
+                for n in names:
+                    out[f"{tag}_s{g + 2}_{n}"] = _np(wf.algorithm.state_dict()[n])
+
+
+GENERATORS = {"pso": golden_pso}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", default="/root/reference/src")
+    ap.add_argument("--only", default="")
+    args = ap.parse_args()
+    sys.path.insert(0, args.reference)
+    torch.set_default_device("cpu")
+    only = [s for s in args.only.split(",") if s]
+    for name, fn in GENERATORS.items():
+        if only and name not in only:
+            continue
+        data: dict = {}
+        fn(data)
+        path = HERE / f"{name}.npz"
+        np.savez_compressed(path, **data)
+        print(f"wrote {path} ({path.stat().st_size} bytes, {len(data)} arrays)")
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,292 @@
+"""Parity of the CUDA particle-swarm path with the reference's recorded states and the oracle.
+
+Tolerances: elementwise state (pop, velocity, personal / global best locations) must be
+bit-exact, because the kernel performs the same separately rounded fp32 operations as the
+reference. Fitness values differ only by summation order and device libm: relative 1e-5, and
+for Rastrigin |diff| <= 1e-5 * max(|ref|, 10 * dim) because 10*d + sum(...) cancels near the optimum.
+"""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import pso as opso
+
+pytestmark = pytest.mark.gpu
+
+NAMES = ["pop", "velocity", "fit", "local_best_location", "local_best_fit", "global_best_location", "global_best_fit"]
+FIT_ID = {"ackley": 0, "rastrigin": 1, "sphere": 2}
+PARAMS = {"ackley": (20.0, 0.2, 2 * math.pi), "rastrigin": (0.0, 0.0, 0.0), "sphere": (0.0, 0.0, 0.0)}
+
+
+def assert_fitness_close(got, ref, prob, dim):
+    got, ref = got.double().cpu(), ref.double().cpu()
+    scale = ref.abs()
+    if prob == "rastrigin":
+        scale = torch.maximum(scale, torch.tensor(10.0 * dim, dtype=torch.float64))
+    finite = torch.isfinite(ref)
+    assert torch.equal(torch.isfinite(got), finite)
+    err = ((got - ref).abs() / scale.clamp_min(1e-30))[finite]
+    assert err.numel() == 0 or err.max().item() <= 1e-5, f"max rel err {err.max().item():.3e}"
+
+
+class Swarm:
+    """Device copy of a reference-format state + the raw C-ABI calls on it."""
+
+    def __init__(self, state: dict, dev):
+        from evox_b200 import _cabi
+
+        self.c = _cabi
+        self.dev = dev
+        self.t = {k: v.to(dev).contiguous().clone() for k, v in state.items()}
+        self.P, self.d = self.t["pop"].shape
+        n = _cabi.lib.evox_pso_workspace_bytes(self.P, self.d)
+        self.ws = torch.zeros(n, dtype=torch.uint8, device=dev)
+
+    def p(self, k):
+        return self.c.ptr(self.t[k], torch.float32, k)
+
+    def step(self, prob, rg=None, rp=None, seed=0, generation=0):
+        c = self.c
+        rg_d = None if rg is None else rg.to(self.dev).contiguous()
+        rp_d = None if rp is None else rp.to(self.dev).contiguous()
+        c.check(
+            c.lib.evox_pso_step(
+                self.p("pop"), self.p("velocity"), self.p("local_best_location"), self.p("local_best_fit"),
+                self.p("fit"), self.p("global_best_location"), self.p("global_best_fit"), self.p("lb"), self.p("ub"),
+                self.p("w"), self.p("phi_p"), self.p("phi_g"), c.ptr(rg_d), c.ptr(rp_d), self.P, self.d,
+                FIT_ID[prob], c.host_floats(PARAMS[prob]), seed, generation, c.ptr(self.ws), self.ws.numel(),
+                c.stream_ptr(self.dev),
+            )
+        )
+        torch.cuda.synchronize()
+
+    def init_step(self, prob):
+        c = self.c
+        c.check(
+            c.lib.evox_pso_init_step(
+                self.p("pop"), self.p("fit"), self.p("local_best_fit"), self.p("global_best_location"),
+                self.p("global_best_fit"), self.P, self.d, FIT_ID[prob], c.host_floats(PARAMS[prob]),
+                c.ptr(self.ws), self.ws.numel(), c.stream_ptr(self.dev),
+            )
+        )
+        torch.cuda.synchronize()
+
+
+def load_state(g, tag, k):
+    s = {n: torch.from_numpy(g[f"{tag}_s{k}_{n}"]) for n in NAMES}
+    lo, hi = g[f"{tag}_bounds"]
+    dim = s["pop"].shape[1]
+    s["lb"] = torch.full((1, dim), float(lo))
+    s["ub"] = torch.full((1, dim), float(hi))
+    w, pp, pg = g[f"{tag}_hyper"]
+    s["w"], s["phi_p"], s["phi_g"] = torch.tensor(w), torch.tensor(pp), torch.tensor(pg)
+    return s
+
+
+def compare_states(got: dict, want: dict, prob: str, exact_fit_inputs=True):
+    dim = want["pop"].shape[1]
+    for n in ("pop", "velocity", "local_best_location", "global_best_location"):
+        assert torch.equal(got[n].cpu(), want[n]), f"{n} differs"
+    for n in ("fit", "local_best_fit", "global_best_fit"):
+        assert_fitness_close(got[n], want[n], prob, dim)
+
+
+@pytest.mark.parametrize("prob", ["ackley", "rastrigin"])
+@pytest.mark.parametrize("dim", [12, 10])
+def test_golden_states(golden, cuda, prob, dim):
+    """init_step and three teacher-forced steps against states recorded from the reference."""
+    g = golden("pso")
+    tag = f"pso_{prob}_d{dim}"
+    sw = Swarm(load_state(g, tag, 0), cuda)
+    sw.init_step(prob)
+    compare_states(sw.t, load_state(g, tag, 1), prob)
+    for gen in range(3):
+        sw = Swarm(load_state(g, tag, gen + 1), cuda)
+        rg = torch.from_numpy(g[f"{tag}_g{gen}_rg"])
+        rp = torch.from_numpy(g[f"{tag}_g{gen}_rp"])
+        sw.step(prob, rg, rp)
+        compare_states(sw.t, load_state(g, tag, gen + 2), prob)
+
+
+@pytest.mark.parametrize("shape", [(3, 4), (65, 10), (257, 500), (33, 1001), (1, 1)])
+@pytest.mark.parametrize("which", [0, 1])
+def test_fill_uniform_bit_exact(cuda, shape, which):
+    from evox_b200 import _cabi
+
+    P, d = shape
+    out = torch.empty(P, d, device=cuda)
+    seed, gen, off = 0x1234567890ABCDEF, (5 << 32) + 17, 1000003
+    _cabi.check(_cabi.lib.evox_pso_fill_uniform(_cabi.ptr(out), P, d, seed, gen, which, off, _cabi.stream_ptr(cuda)))
+    ref = opso.pso_uniform(P, d, seed, gen, which, off)
+    assert torch.equal(out.cpu(), ref)
+
+
+@pytest.mark.parametrize("prob", ["ackley", "rastrigin", "sphere"])
+@pytest.mark.parametrize("shape", [(1000, 500), (128, 1000), (77, 10), (5, 3)])
+def test_eval_fitness(cuda, prob, shape):
+    from evox_b200.problems import numerical
+
+    P, d = shape
+    lo, hi = (-32.768, 32.768) if prob == "ackley" else (-5.12, 5.12)
+    x = lo + (hi - lo) * torch.rand(P, d, generator=torch.Generator().manual_seed(3))
+    x[0] = 0.0  # the optimum, where Rastrigin cancels completely
+    cls = {"ackley": numerical.Ackley, "rastrigin": numerical.Rastrigin, "sphere": numerical.Sphere}[prob]
+    got = cls().evaluate(x.to(cuda))
+    assert_fitness_close(got, opso.FITNESS[prob](x), prob, d)
+
+
+@pytest.mark.parametrize("prob,P,d", [("ackley", 10_000, 500), ("rastrigin", 4096, 1000), ("ackley", 999, 10)])
+def test_step_vs_oracle(cuda, prob, P, d):
+    """One teacher-forced generation at benchmark shapes: tensor mode, then Philox mode fed
+    with the tensors evox_pso_fill_uniform materialises."""
+    lo, hi = (-32.768, 32.768) if prob == "ackley" else (-5.12, 5.12)
+    hyper = (0.6, 2.5, 0.8) if prob == "ackley" else (0.7, 1.5, 1.5)
+    fitness = opso.FITNESS[prob]
+    s0 = opso.init_step(opso.make_state(P, d, lo, hi, *hyper, seed=0), fitness)
+    rg, rp = opso.draws(P, d, 1000)
+    s1 = opso.step(s0, rg, rp, fitness)  # state with a non-trivial personal best
+    rg, rp = opso.draws(P, d, 1001)
+    want = opso.step(s1, rg, rp, fitness)
+    sw = Swarm(s1, cuda)
+    sw.step(prob, rg, rp)
+    compare_states(sw.t, want, prob)
+    # in-kernel Philox == the same draws read from memory
+    seed, gen = 42, 7
+    rg2 = opso.pso_uniform(P, d, seed, gen, 0)
+    rp2 = opso.pso_uniform(P, d, seed, gen, 1)
+    a, b = Swarm(s1, cuda), Swarm(s1, cuda)
+    a.step(prob, None, None, seed=seed, generation=gen)
+    b.step(prob, rg2, rp2)
+    for n in NAMES:
+        assert torch.equal(a.t[n], b.t[n]), n
+
+
+def test_global_best_tie_and_nan_rules(cuda):
+    """min_by puts the old best first: it wins ties; among particles the lowest index wins;
+    NaN counts as the minimum (torch.argmin)."""
+    P, d = 300, 8
+    s = opso.make_state(P, d, -1.0, 1.0, 0.6, 2.5, 0.8, seed=5)
+    s["fit"] = torch.full((P,), 3.0)
+    s["fit"][[17, 200]] = 1.0
+    s["local_best_fit"] = s["fit"].clone()
+    s["global_best_fit"] = torch.tensor(1.0)  # tie with particles 17 and 200 -> old best stays
+    s["global_best_location"] = torch.full((d,), 0.25)
+    rg, rp = opso.draws(P, d, 1)
+    sw = Swarm(s, cuda)
+    sw.step("sphere", rg, rp)
+    want = opso.step(s, rg, rp, opso.sphere)
+    assert torch.equal(sw.t["global_best_location"].cpu(), want["global_best_location"])
+    assert torch.equal(sw.t["global_best_location"].cpu(), torch.full((d,), 0.25))
+    s["global_best_fit"] = torch.tensor(2.0)  # now particle 17 (the first of the two) wins
+    sw = Swarm(s, cuda)
+    sw.step("sphere", rg, rp)
+    want = opso.step(s, rg, rp, opso.sphere)
+    assert torch.equal(sw.t["global_best_location"].cpu(), s["pop"][17])
+    assert torch.equal(sw.t["global_best_location"].cpu(), want["global_best_location"])
+    s["fit"][250] = float("nan")
+    sw = Swarm(s, cuda)
+    sw.step("sphere", rg, rp)
+    want = opso.step(s, rg, rp, opso.sphere)
+    assert torch.equal(sw.t["global_best_location"].cpu(), want["global_best_location"])
+    assert math.isnan(sw.t["global_best_fit"].item()) and math.isnan(want["global_best_fit"].item())
+
+
+def test_sharded_candidates_match_single(cuda):
+    """Two shards emulated on one GPU: local_best per shard + merge == the single-GPU result."""
+    from evox_b200 import _cabi as c
+
+    P, d = 5001, 40
+    s = opso.init_step(opso.make_state(P, d, -5.12, 5.12, 0.7, 1.5, 1.5, seed=9), opso.rastrigin)
+    s["global_best_fit"] = torch.tensor(float("inf"))
+    single = Swarm(s, cuda)
+    rg, rp = opso.draws(P, d, 2)
+    single.step("rastrigin", rg, rp)
+    words = c.lib.evox_pso_candidate_words(d)
+    bounds = [(0, 2501), (2501, P)]
+    recs = torch.zeros(2 * words, dtype=torch.int32, device=cuda)
+    shards = []
+    for r, (a, b) in enumerate(bounds):
+        part = {k: (v[a:b] if (v.ndim >= 1 and v.shape[0] == P) else v) for k, v in s.items()}
+        sh = Swarm(part, cuda)
+        shards.append(sh)
+        c.check(c.lib.evox_pso_local_best(sh.p("fit"), sh.p("pop"), b - a, d, a, recs[r * words:].data_ptr(),
+                                          c.ptr(sh.ws), sh.ws.numel(), c.stream_ptr(cuda)))
+    for r, (a, b) in enumerate(bounds):
+        sh = shards[r]
+        c.check(c.lib.evox_pso_merge_best(c.ptr(recs), 2, d, 1, sh.p("global_best_location"), sh.p("global_best_fit"),
+                                          c.stream_ptr(cuda)))
+        c.check(c.lib.evox_pso_move_eval(sh.p("pop"), sh.p("velocity"), sh.p("local_best_location"),
+                                         sh.p("local_best_fit"), sh.p("fit"), sh.p("global_best_location"),
+                                         sh.p("lb"), sh.p("ub"), sh.p("w"), sh.p("phi_p"), sh.p("phi_g"),
+                                         c.ptr(rg[a:b].to(cuda).contiguous()), c.ptr(rp[a:b].to(cuda).contiguous()),
+                                         b - a, d, 1, c.host_floats((0, 0, 0)), 0, 0, a, c.stream_ptr(cuda)))
+    torch.cuda.synchronize()
+    for n in ("pop", "velocity", "fit", "local_best_location", "local_best_fit"):
+        assert torch.equal(torch.cat([sh.t[n] for sh in shards]), single.t[n]), n
+    for sh in shards:
+        assert torch.equal(sh.t["global_best_location"], single.t["global_best_location"])
+        assert torch.equal(sh.t["global_best_fit"], single.t["global_best_fit"])
+
+
+def test_workflow_fused_equals_unfused(cuda):
+    """StdWorkflow(PSO, Ackley): the fused step and the path through Problem.evaluate agree,
+    and the swarm improves."""
+    from evox_b200.algorithms import PSO
+    from evox_b200.core import Monitor
+    from evox_b200.problems.numerical import Ackley
+    from evox_b200.workflows import StdWorkflow
+
+    class Count(Monitor):
+        def __init__(self):
+            super().__init__()
+            self.calls = []
+
+        def post_ask(self, x):
+            self.calls.append("post_ask")
+
+        def pre_tell(self, f):
+            self.calls.append("pre_tell")
+
+    d = 100
+    lb, ub = torch.full((d,), -32.768), torch.full((d,), 32.768)
+    runs = []
+    for fused in (True, False):
+        algo = PSO(512, lb, ub, device=cuda, seed=11)
+        mon = Count()
+        wf = StdWorkflow(algo, Ackley(), monitor=mon, device=cuda,
+                         fitness_transform=None if fused else torch.nn.Identity())
+        assert (wf._fused_plan() is not None) == fused
+        wf.init_step()
+        first = wf.algorithm.global_best_fit.item()
+        for _ in range(20):
+            wf.step()
+        assert mon.calls == ["post_ask", "pre_tell"] * 21
+        assert wf.algorithm.global_best_fit.item() < first
+        runs.append({k: v.clone() for k, v in wf.algorithm.state_dict().items() if isinstance(v, torch.Tensor)})
+    for k in runs[0]:
+        assert torch.equal(runs[0][k], runs[1][k]), k
+
+
+def test_reference_state_dict_loads(golden, cuda):
+    """A state_dict with the reference's keys loads into the drop-in class, and one step through
+    the public API lands on the reference's next state."""
+    from evox_b200.algorithms import PSO
+    from evox_b200.problems.numerical import Ackley
+    from evox_b200.workflows import StdWorkflow
+
+    g = golden("pso")
+    tag = "pso_ackley_d12"
+    lo, hi = g[f"{tag}_bounds"]
+    algo = PSO(37, torch.full((12,), float(lo)), torch.full((12,), float(hi)), device=cuda)
+    wf = StdWorkflow(algo, Ackley(), device=cuda)
+    sd = {n: torch.from_numpy(g[f"{tag}_s2_{n}"]) for n in NAMES}
+    w, pp, pg = g[f"{tag}_hyper"]
+    sd.update({"w": torch.tensor(w), "phi_p": torch.tensor(pp), "phi_g": torch.tensor(pg)})
+    wf.algorithm.load_state_dict(sd)
+    rg = torch.from_numpy(g[f"{tag}_g1_rg"]).to(cuda)
+    rp = torch.from_numpy(g[f"{tag}_g1_rp"]).to(cuda)
+    wf.algorithm.step(rg=rg, rp=rp)
+    got = {k: v for k, v in wf.algorithm.state_dict().items() if isinstance(v, torch.Tensor)}
+    compare_states(got, load_state(g, tag, 3), "ackley")
