@@ -245,12 +245,13 @@ def run_ours(args):
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return ms.item()
 
+    # the sampler runs from the warm-up to the last timed loop (all of it is under load): the
+    # timed region alone can be shorter than one nvidia-smi sampling period
+    clocks = ClockSampler(physical_gpu_index(local))
+    clocks.__enter__()
     for _ in range(max(args.warmup, 3)):
         wf.step()
-
-    with ClockSampler(physical_gpu_index(local)) as clocks:
-        total_ms = timed(wf.step, args.steps)
-    clock_summary = clocks.summary()
+    total_ms = timed(wf.step, args.steps)
     launches_per_step = 2 if world == 1 else 3
     ms_per_step = total_ms / args.steps
     value = 1e3 / ms_per_step
@@ -293,6 +294,8 @@ def run_ours(args):
         a.generation += 1
 
     kernel_ms = timed(move_only, args.steps) / args.steps
+    clocks.__exit__(None, None, None)
+    clock_summary = clocks.summary()
     peak, peak_kind = measured_peaks()
     alg_bytes = PSO_BYTES_PER_ELEM * n_local * d
     achieved = alg_bytes / (kernel_ms * 1e-3) / 1e9

@@ -59,10 +59,13 @@ PROTOTYPES = _parse_header(HEADER)
 def _load() -> ctypes.CDLL:
     path = _build.LIB_PATH
     if not path.exists():
-        raise ImportError(
-            f"{path} is missing: the evox_b200 CUDA kernels are not built. "
-            "Run `python -m evox_b200._build` (needs nvcc); there is no CPU fallback."
-        )
+        try:
+            _build.build()  # first import of a fresh checkout: compile once (needs nvcc)
+        except Exception as exc:
+            raise ImportError(
+                f"{path} is missing and could not be built ({exc}). The evox_b200 CUDA kernels are "
+                "required; there is no CPU fallback."
+            ) from exc
     lib = ctypes.CDLL(str(path))
     for name, (restype, argtypes) in PROTOTYPES.items():
         fn = getattr(lib, name)  # AttributeError if the library lacks a declared symbol

@@ -79,7 +79,54 @@ def golden_pso(out: dict):
                     out[f"{tag}_s{g + 2}_{n}"] = _np(wf.algorithm.state_dict()[n])
 
 
-GENERATORS = {"pso": golden_pso}
+def nds_cases():
+    """Inputs of the NSGA-II selection goldens (shared with the tests through the .npz)."""
+    g = torch.Generator().manual_seed(7)
+    cases = {}
+    x = torch.rand(300, 12, generator=g)
+    from evox.problems.numerical import DTLZ2
+
+    cases["dtlz2"] = (DTLZ2(d=12, m=3).evaluate(x), 150)
+    cases["ties_m2"] = (torch.round(torch.rand(257, 2, generator=g) * 8) / 8, 100)
+    f = torch.rand(130, 5, generator=g)
+    f[3, 1] = float("nan")
+    f[77] = float("nan")
+    f[12, 0] = float("inf")
+    f[13, 4] = float("-inf")
+    cases["nan_m5"] = (f, 64)
+    f = torch.rand(64, 3, generator=g)
+    f[:, 1] = 0.5
+    cases["flat_objective"] = (f, 20)
+    cases["single_front"] = (torch.stack([torch.linspace(0, 1, 40), torch.linspace(1, 0, 40)], dim=1), 17)
+    cases["tiny"] = (torch.tensor([[1.0, 2.0], [2.0, 1.0], [3.0, 3.0]]), 2)
+    return cases
+
+
+def golden_nds(out: dict):
+    """non_dominate_rank, crowding_distance on the last selected front and
+    nd_environmental_selection (x = row index, so the selected order is visible)."""
+    from evox.operators.selection import crowding_distance, nd_environmental_selection, non_dominate_rank
+
+    for name, (f, topk) in nds_cases().items():
+        n = f.shape[0]
+        rank = non_dominate_rank(f)
+        worst = torch.topk(rank, topk, largest=False)[0][-1]
+        mask = rank == worst
+        crowd = crowding_distance(f, mask)
+        x = torch.arange(n, dtype=torch.float32)[:, None].repeat(1, 2)
+        sx, sf, srank, scrowd = nd_environmental_selection(x, f, topk)
+        out[f"{name}_f"] = _np(f)
+        out[f"{name}_topk"] = np.asarray(topk)
+        out[f"{name}_rank"] = _np(rank)
+        out[f"{name}_mask"] = _np(mask)
+        out[f"{name}_crowd"] = _np(crowd)
+        out[f"{name}_sel_index"] = _np(sx[:, 0].to(torch.int64))
+        out[f"{name}_sel_f"] = _np(sf)
+        out[f"{name}_sel_rank"] = _np(srank)
+        out[f"{name}_sel_crowd"] = _np(scrowd)
+
+
+GENERATORS = {"pso": golden_pso, "nds": golden_nds}
 
 
 def main():

@@ -213,14 +213,17 @@ def test_sharded_candidates_match_single(cuda):
         shards.append(sh)
         c.check(c.lib.evox_pso_local_best(sh.p("fit"), sh.p("pop"), b - a, d, a, recs[r * words:].data_ptr(),
                                           c.ptr(sh.ws), sh.ws.numel(), c.stream_ptr(cuda)))
+    keep = []  # device slices must outlive the asynchronous launches that read them
     for r, (a, b) in enumerate(bounds):
         sh = shards[r]
+        rg_s, rp_s = rg[a:b].to(cuda).contiguous(), rp[a:b].to(cuda).contiguous()
+        keep += [rg_s, rp_s]
         c.check(c.lib.evox_pso_merge_best(c.ptr(recs), 2, d, 1, sh.p("global_best_location"), sh.p("global_best_fit"),
                                           c.stream_ptr(cuda)))
         c.check(c.lib.evox_pso_move_eval(sh.p("pop"), sh.p("velocity"), sh.p("local_best_location"),
                                          sh.p("local_best_fit"), sh.p("fit"), sh.p("global_best_location"),
                                          sh.p("lb"), sh.p("ub"), sh.p("w"), sh.p("phi_p"), sh.p("phi_g"),
-                                         c.ptr(rg[a:b].to(cuda).contiguous()), c.ptr(rp[a:b].to(cuda).contiguous()),
+                                         c.ptr(rg_s), c.ptr(rp_s),
                                          b - a, d, 1, c.host_floats((0, 0, 0)), 0, 0, a, c.stream_ptr(cuda)))
     torch.cuda.synchronize()
     for n in ("pop", "velocity", "fit", "local_best_location", "local_best_fit"):
