@@ -58,9 +58,9 @@ PROTOTYPES = _parse_header(HEADER)
 
 def _load() -> ctypes.CDLL:
     path = _build.LIB_PATH
-    if not path.exists():
+    if not _build.is_current():
         try:
-            _build.build()  # first import of a fresh checkout: compile once (needs nvcc)
+            _build.build()  # fresh checkout or edited sources: compile once (needs nvcc)
         except Exception as exc:
             raise ImportError(
                 f"{path} is missing and could not be built ({exc}). The evox_b200 CUDA kernels are "

@@ -1,0 +1,831 @@
+// P2: NSGA-II environmental selection — non-dominated rank, crowding distance, truncation.
+//
+// Reference semantics: dominate_relation, the front-peeling loop of non_dominate_rank,
+// crowding_distance and nd_environmental_selection
+// (evox/operators/selection/non_dominate.py:6-26, 151-195, 198-231, 234-254) and the stable
+// lexsort they use (evox/utils/jit_fix_operator.py:216-252).
+//
+// Rank:
+//   1. nds_transpose_kernel    objectives to structure-of-arrays, padded with NaN (a NaN never
+//                              dominates and is never dominated, as in the reference's comparisons).
+//   2. nds_dominance_kernel    bit-packed dominance matrix Dt: bit i of row j is set iff i
+//                              dominates j. A warp holds 32 dominators per word in registers,
+//                              walks the columns of a shared-memory tile and turns 32 comparisons
+//                              into one word with a ballot; tiles leave through shared memory as
+//                              128-byte rows. n^2 / 8 bytes are written once.
+//   3. nds_peel_kernel         persistent cooperative kernel. Front k = the unranked columns whose
+//                              row of Dt has no bit left in the unranked mask. Every column keeps a
+//                              witness position: the scan of its row resumes where it last found an
+//                              unranked dominator and never goes back, so each row of Dt is read
+//                              once in total (n^2 / 8 bytes), not once per front as the reference
+//                              does. Fronts are separated by a bounded grid barrier.
+// Selection: histogram of ranks -> last admitted front -> per-objective stable radix sort of that
+// front -> neighbour gaps / range -> stable sorts by (rank) and (-crowding) -> gather.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace evox {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kSortThreads = 1024;
+constexpr int kTileJ = 128;      // columns (dominated candidates) per dominance tile
+constexpr int kPad = 1024;       // population padded to a multiple of this (32 words = 128 B rows)
+constexpr unsigned kSpinLimit = 1u << 22;  // grid-barrier polls before giving up (~ seconds)
+
+// ---------------------------------------------------------------------------------------------
+// Workspace
+// ---------------------------------------------------------------------------------------------
+struct Ctrl {
+  unsigned bar_count;
+  unsigned bar_gen;
+  unsigned remaining[2];
+  int status;        // 0 ok, 1 barrier timed out, 2 no progress
+  int n_fronts;
+  int worst_rank;    // last admitted front
+  int n_before;      // rows with rank < worst_rank
+  int n_last;        // rows with rank == worst_rank
+  int pad[7];
+};
+
+struct Layout {
+  size_t fs, dt, unranked, newfront, ptr, ctrl, hist, idx_a, key_a, idx_l, sortbuf, contrib, boundary, crowd, order, rank, total;
+  long long npad;
+  int wp;
+};
+
+size_t align_up(size_t x, size_t a = 256) { return (x + a - 1) / a * a; }
+
+Layout make_layout(long long n, int m, bool with_matrix) {
+  Layout L;
+  L.npad = (n + kPad - 1) / kPad * kPad;
+  L.wp = (int)(L.npad / 32);
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    size_t at = off;
+    off = align_up(off + bytes);
+    return at;
+  };
+  L.ctrl = take(sizeof(Ctrl));
+  L.fs = take(sizeof(float) * (size_t)m * L.npad);
+  L.unranked = take(sizeof(uint32_t) * L.wp);
+  L.newfront = take(sizeof(uint32_t) * L.wp);
+  L.ptr = take(sizeof(int) * (size_t)n);
+  L.hist = take(sizeof(int) * (size_t)(n + 1));
+  L.idx_a = take(sizeof(uint32_t) * (size_t)n);
+  L.key_a = take(sizeof(uint32_t) * (size_t)n);
+  L.idx_l = take(sizeof(uint32_t) * (size_t)n);
+  L.sortbuf = take(sizeof(uint32_t) * 4 * (size_t)n * (size_t)(m + 2));  // per sort: keys, vals, 2 x temp
+  L.contrib = take(sizeof(float) * (size_t)m * (size_t)n);
+  L.boundary = take(sizeof(uint32_t) * (size_t)n);
+  L.crowd = take(sizeof(float) * (size_t)n);
+  L.order = take(sizeof(uint32_t) * (size_t)n);
+  L.rank = take(sizeof(int) * (size_t)n);
+  L.dt = with_matrix ? take(sizeof(uint32_t) * (size_t)n * (size_t)L.wp) : off;
+  L.total = off;
+  return L;
+}
+
+template <class T>
+T* at(void* ws, size_t off) {
+  return reinterpret_cast<T*>(reinterpret_cast<char*>(ws) + off);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Rank
+// ---------------------------------------------------------------------------------------------
+__global__ void nds_transpose_kernel(const float* __restrict__ f, long long n, int m, long long npad,
+                                     float* __restrict__ fs) {
+  const long long total = (long long)m * npad;
+  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
+    const int k = (int)(t / npad);
+    const long long i = t - (long long)k * npad;
+    fs[t] = (i < n) ? f[i * m + k] : __int_as_float(0x7fc00000);
+  }
+}
+
+// i dominates j: all(f_i <= f_j) and any(f_i < f_j) (non_dominate.py:20-24).
+template <int M>
+__device__ __forceinline__ bool dominates(const float (&a)[M], const float (&b)[M]) {
+  bool le = true, lt = false;
+#pragma unroll
+  for (int k = 0; k < M; ++k) {
+    le = le && (a[k] <= b[k]);
+    lt = lt || (a[k] < b[k]);
+  }
+  return le && lt;
+}
+
+template <int M, int R>
+__global__ void __launch_bounds__(kThreads)
+    nds_dominance_kernel(const float* __restrict__ fs, long long npad, long long n, uint32_t* __restrict__ Dt, int wp) {
+  constexpr int kWords = 8 * R;  // words of dominators per block (8 warps x R)
+  __shared__ float sfj[M][kTileJ];
+  __shared__ uint32_t sout[kTileJ][kWords];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long i0 = (long long)blockIdx.y * (32 * kWords);
+  const long long j0 = (long long)blockIdx.x * kTileJ;
+
+  float fi[R][M];
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const long long i = i0 + (long long)(warp * R + r) * 32 + lane;
+#pragma unroll
+    for (int k = 0; k < M; ++k) fi[r][k] = (i < npad) ? fs[(long long)k * npad + i] : __int_as_float(0x7fc00000);
+  }
+  for (int t = threadIdx.x; t < M * kTileJ; t += kThreads) {
+    const int k = t / kTileJ, jj = t - k * kTileJ;
+    const long long j = j0 + jj;
+    sfj[k][jj] = (j < n) ? fs[(long long)k * npad + j] : __int_as_float(0x7fc00000);
+  }
+  __syncthreads();
+#pragma unroll 4
+  for (int jj = 0; jj < kTileJ; ++jj) {
+    float fj[M];
+#pragma unroll
+    for (int k = 0; k < M; ++k) fj[k] = sfj[k][jj];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const uint32_t word = __ballot_sync(0xffffffffu, dominates<M>(fi[r], fj));
+      if (lane == 0) sout[jj][warp * R + r] = word;
+    }
+  }
+  __syncthreads();
+  const int w0 = (int)(i0 >> 5);
+  for (int t = threadIdx.x; t < kTileJ * kWords; t += kThreads) {
+    const int jj = t / kWords, w = t - jj * kWords;
+    const long long j = j0 + jj;
+    if (j < n && w0 + w < wp) Dt[j * wp + w0 + w] = sout[jj][w];
+  }
+}
+
+// Generic number of objectives (slow path, > 16): one thread per (word, column).
+__global__ void __launch_bounds__(kThreads)
+    nds_dominance_generic_kernel(const float* __restrict__ fs, long long npad, long long n, int m,
+                                 uint32_t* __restrict__ Dt, int wp) {
+  const long long total = n * (long long)wp;
+  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
+    const long long j = t / wp;
+    const int w = (int)(t - j * wp);
+    uint32_t word = 0;
+    for (int b = 0; b < 32; ++b) {
+      const long long i = (long long)w * 32 + b;
+      bool le = true, lt = false;
+      for (int k = 0; k < m; ++k) {
+        const float a = fs[(long long)k * npad + i], c = fs[(long long)k * npad + j];
+        le = le && (a <= c);
+        lt = lt || (a < c);
+      }
+      word |= (uint32_t)(le && lt) << b;
+    }
+    Dt[t] = word;
+  }
+}
+
+__global__ void nds_peel_init_kernel(long long n, int wp, uint32_t* unranked, uint32_t* newfront, int* ptr, int* rank,
+                                     Ctrl* ctrl) {
+  const long long t0 = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long w = t0; w < wp; w += stride) {
+    const long long lo = w * 32;
+    uint32_t bits = 0;
+    if (lo + 32 <= n) bits = 0xffffffffu;
+    else if (lo < n) bits = (1u << (int)(n - lo)) - 1u;
+    unranked[w] = bits;
+    newfront[w] = 0;
+  }
+  for (long long j = t0; j < n; j += stride) {
+    ptr[j] = 0;
+    rank[j] = -1;
+  }
+  if (t0 == 0) {
+    ctrl->bar_count = 0;
+    ctrl->bar_gen = 0;
+    ctrl->remaining[0] = 0;
+    ctrl->remaining[1] = 0;
+    ctrl->status = 0;
+    ctrl->n_fronts = 0;
+  }
+}
+
+// Grid-wide barrier for a cooperative (co-resident) launch. The wait is bounded: a block that
+// polls kSpinLimit times records status 1 and every block leaves at its next check.
+__device__ __forceinline__ bool grid_barrier(Ctrl* ctrl, unsigned n_blocks) {
+  __shared__ int ok;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    volatile unsigned* gen_p = &ctrl->bar_gen;
+    volatile int* status_p = &ctrl->status;
+    const unsigned gen = *gen_p;
+    __threadfence();
+    const unsigned arrived = atomicAdd(&ctrl->bar_count, 1u) + 1u;
+    if (arrived == n_blocks) {
+      ctrl->bar_count = 0;
+      __threadfence();
+      atomicAdd(&ctrl->bar_gen, 1u);
+    } else {
+      unsigned spins = 0;
+      while (*gen_p == gen && *status_p == 0) {
+        __nanosleep(64);
+        if (++spins > kSpinLimit) {
+          atomicExch(&ctrl->status, 1);
+          break;
+        }
+      }
+    }
+    __threadfence();
+    ok = (*status_p == 0);
+  }
+  __syncthreads();
+  return ok != 0;
+}
+
+__global__ void __launch_bounds__(kThreads)
+    nds_peel_kernel(const uint32_t* __restrict__ Dt, int wp, long long n, uint32_t* unranked, uint32_t* newfront,
+                    int* ptr, int* rank, Ctrl* ctrl) {
+  __shared__ unsigned s_cnt[kThreads / 32];
+  const int lane = threadIdx.x & 31;
+  const long long gwarp = ((long long)blockIdx.x * kThreads + threadIdx.x) >> 5;
+  const long long n_warps = ((long long)gridDim.x * kThreads) >> 5;
+  const long long gtid = (long long)blockIdx.x * kThreads + threadIdx.x;
+  const long long n_threads = (long long)gridDim.x * kThreads;
+  const int n_chunks = (wp + 31) / 32;
+  unsigned prev_remaining = (unsigned)n + 1u;
+
+  for (int k = 0; k <= n; ++k) {
+    // ---- phase A: which unranked columns have no unranked dominator left? -------------------
+    for (long long j = gwarp; j < n; j += n_warps) {
+      int r = 0, c = 0;
+      if (lane == 0) {
+        r = __ldcg(rank + j);
+        c = __ldcg(ptr + j);
+      }
+      r = __shfl_sync(0xffffffffu, r, 0);
+      if (r >= 0) continue;
+      c = __shfl_sync(0xffffffffu, c, 0);
+      const uint32_t* row = Dt + j * wp;
+      bool blocked = false;
+      for (; c < n_chunks; ++c) {
+        const int w = c * 32 + lane;
+        uint32_t word = 0;
+        if (w < wp) word = __ldg(row + w) & __ldcg(unranked + w);
+        if (__any_sync(0xffffffffu, word != 0)) {
+          blocked = true;
+          break;
+        }
+      }
+      if (lane == 0) {
+        if (blocked) {
+          ptr[j] = c;
+        } else {
+          rank[j] = k;
+          atomicOr(newfront + (j >> 5), 1u << (int)(j & 31));
+        }
+      }
+    }
+    if (!grid_barrier(ctrl, gridDim.x)) return;
+    // ---- phase B: retire the front, count what is left ---------------------------------------
+    unsigned cnt = 0;
+    for (long long w = gtid; w < wp; w += n_threads) {
+      const uint32_t u = __ldcg(unranked + w) & ~__ldcg(newfront + w);
+      unranked[w] = u;
+      newfront[w] = 0;
+      cnt += __popc(u);
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, off);
+    if (lane == 0) s_cnt[threadIdx.x >> 5] = cnt;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      unsigned tot = 0;
+      for (int i = 0; i < kThreads / 32; ++i) tot += s_cnt[i];
+      if (tot) atomicAdd(&ctrl->remaining[k & 1], tot);
+      if (blockIdx.x == 0) ctrl->remaining[(k + 1) & 1] = 0;
+    }
+    if (!grid_barrier(ctrl, gridDim.x)) return;
+    const unsigned rem = *((volatile unsigned*)&ctrl->remaining[k & 1]);
+    if (rem == 0) {
+      if (gtid == 0) ctrl->n_fronts = k + 1;
+      return;
+    }
+    if (rem >= prev_remaining) {  // dominance is a strict partial order: every pass must rank someone
+      if (gtid == 0) atomicExch(&ctrl->status, 2);
+      return;
+    }
+    prev_remaining = rem;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Stable least-significant-digit radix sort of (key, value) pairs by one thread block.
+// 8-bit digits; within a tile of blockDim.x elements the order among equal digits is kept with
+// match_any + per-warp digit counts, so equal keys stay in input order (what torch.argsort(stable)
+// guarantees). Result ends in (keys, vals); (tk, tv) are scratch.
+// ---------------------------------------------------------------------------------------------
+struct SortSmem {
+  unsigned base[256];
+  unsigned tile_total[256];
+  unsigned wcnt[kSortThreads / 32][256];
+};
+
+__device__ void block_radix_sort(uint32_t* keys, uint32_t* vals, uint32_t* tk, uint32_t* tv, int n, int bits,
+                                 SortSmem& sm) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int n_warps = blockDim.x >> 5;
+  uint32_t *src_k = keys, *src_v = vals, *dst_k = tk, *dst_v = tv;
+  const int passes = (bits + 7) / 8;
+  for (int pass = 0; pass < passes; ++pass) {
+    const int shift = pass * 8;
+    for (int i = tid; i < 256; i += blockDim.x) sm.base[i] = 0;
+    __syncthreads();
+    for (int i = tid; i < n; i += blockDim.x) atomicAdd(&sm.base[(src_k[i] >> shift) & 255u], 1u);
+    __syncthreads();
+    if (warp == 0) {  // exclusive scan of 256 counts by one warp, 8 per lane
+      unsigned local[8], sum = 0;
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        local[q] = sm.base[lane * 8 + q];
+        sum += local[q];
+      }
+      unsigned incl = sum;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const unsigned t = __shfl_up_sync(0xffffffffu, incl, off);
+        if (lane >= off) incl += t;
+      }
+      unsigned run = incl - sum;
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        sm.base[lane * 8 + q] = run;
+        run += local[q];
+      }
+    }
+    __syncthreads();
+    for (int s = 0; s < n; s += blockDim.x) {
+      const int i = s + tid;
+      const bool valid = i < n;
+      uint32_t key = 0, val = 0;
+      unsigned dg = 256u + (unsigned)lane;  // invalid lanes match nobody
+      if (valid) {
+        key = src_k[i];
+        val = src_v[i];
+        dg = (key >> shift) & 255u;
+      }
+      for (int q = tid; q < n_warps * 256; q += blockDim.x) (&sm.wcnt[0][0])[q] = 0;
+      __syncthreads();
+      const unsigned peers = __match_any_sync(0xffffffffu, dg);
+      const unsigned before = __popc(peers & ((1u << lane) - 1u));
+      if (valid && before == 0) sm.wcnt[warp][dg] = __popc(peers);
+      __syncthreads();
+      if (tid < 256) {
+        unsigned run = 0;
+        for (int w = 0; w < n_warps; ++w) {
+          const unsigned c = sm.wcnt[w][tid];
+          sm.wcnt[w][tid] = run;
+          run += c;
+        }
+        sm.tile_total[tid] = run;
+      }
+      __syncthreads();
+      if (valid) {
+        const unsigned dest = sm.base[dg] + sm.wcnt[warp][dg] + before;
+        dst_k[dest] = key;
+        dst_v[dest] = val;
+      }
+      __syncthreads();
+      if (tid < 256) sm.base[tid] += sm.tile_total[tid];
+      __syncthreads();
+    }
+    uint32_t* t = src_k; src_k = dst_k; dst_k = t;
+    t = src_v; src_v = dst_v; dst_v = t;
+    __threadfence_block();
+    __syncthreads();
+  }
+  if (src_k != keys) {
+    for (int i = tid; i < n; i += blockDim.x) {
+      keys[i] = src_k[i];
+      vals[i] = src_v[i];
+    }
+    __syncthreads();
+  }
+}
+
+// float -> uint32 whose unsigned order is torch's ascending sort order: -inf < ... < -0 = +0 < ...
+// < +inf < NaN (all NaNs equal, both zeros equal, so a stable sort keeps their input order).
+__device__ __forceinline__ uint32_t float_order_key(float x) {
+  if (x != x) return 0xffffffffu;
+  if (x == 0.0f) x = 0.0f;
+  const uint32_t b = __float_as_uint(x);
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Selection
+// ---------------------------------------------------------------------------------------------
+__global__ void nds_hist_kernel(const int* __restrict__ rank, long long n, int* hist) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const int r = rank[i];
+    if (r >= 0 && r <= n) atomicAdd(hist + r, 1);
+  }
+}
+
+// One block: k-th smallest rank (torch.topk(rank, k, largest=False)[0][-1], non_dominate.py:250),
+// then index-ordered lists of the rows before the last admitted front and of that front.
+__global__ void __launch_bounds__(kSortThreads)
+    nds_partition_kernel(const int* __restrict__ rank, const int* __restrict__ hist, long long n, long long topk,
+                         Ctrl* ctrl, uint32_t* idx_a, uint32_t* key_a, uint32_t* idx_l) {
+  __shared__ int s_worst;
+  __shared__ unsigned s_worst_u;
+  __shared__ unsigned s_wsum[kSortThreads / 32][2];
+  __shared__ unsigned s_base[2];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  // smallest r with hist[0] + ... + hist[r] >= topk, found a tile of 1024 ranks at a time
+  __shared__ unsigned long long s_run;
+  __shared__ unsigned s_scan[kSortThreads / 32];
+  if (tid == 0) {
+    s_worst = -1;
+    s_worst_u = 0xffffffffu;
+    s_run = 0;
+    s_base[0] = s_base[1] = 0;
+  }
+  __syncthreads();
+  for (long long b = 0; b <= n; b += kSortThreads) {
+    const long long r = b + tid;
+    const unsigned h = (r <= n) ? (unsigned)hist[r] : 0u;
+    unsigned incl = h;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const unsigned t = __shfl_up_sync(0xffffffffu, incl, off);
+      if (lane >= off) incl += t;
+    }
+    if (lane == 31) s_scan[warp] = incl;
+    __syncthreads();
+    unsigned long long before = s_run;
+    for (int w = 0; w < warp; ++w) before += s_scan[w];
+    const bool hit = (r <= n) && (before + incl >= (unsigned long long)topk);
+    if (hit) atomicMin(&s_worst_u, (unsigned)r);
+    __syncthreads();
+    if (tid == 0) {
+      unsigned long long t = 0;
+      for (int w = 0; w < kSortThreads / 32; ++w) t += s_scan[w];
+      s_run += t;
+    }
+    __syncthreads();
+    if (s_worst_u != 0xffffffffu) break;
+  }
+  if (tid == 0) s_worst = (s_worst_u == 0xffffffffu) ? (int)n : (int)s_worst_u;
+  __syncthreads();
+  const int worst = s_worst;
+  for (long long s = 0; s < n; s += kSortThreads) {
+    const long long i = s + tid;
+    const int r = (i < n) ? rank[i] : 0x7fffffff;
+    const bool in_a = r < worst, in_l = r == worst;
+    const unsigned ma = __ballot_sync(0xffffffffu, in_a), ml = __ballot_sync(0xffffffffu, in_l);
+    if (lane == 0) {
+      s_wsum[warp][0] = __popc(ma);
+      s_wsum[warp][1] = __popc(ml);
+    }
+    __syncthreads();
+    unsigned off_a = s_base[0], off_l = s_base[1];
+    for (int w = 0; w < warp; ++w) {
+      off_a += s_wsum[w][0];
+      off_l += s_wsum[w][1];
+    }
+    const unsigned lt = (1u << lane) - 1u;
+    if (in_a) {
+      const unsigned p = off_a + __popc(ma & lt);
+      idx_a[p] = (uint32_t)i;
+      key_a[p] = (uint32_t)r;
+    }
+    if (in_l) idx_l[off_l + __popc(ml & lt)] = (uint32_t)i;
+    __syncthreads();
+    if (tid == 0) {
+      unsigned ta = 0, tl = 0;
+      for (int w = 0; w < kSortThreads / 32; ++w) {
+        ta += s_wsum[w][0];
+        tl += s_wsum[w][1];
+      }
+      s_base[0] += ta;
+      s_base[1] += tl;
+    }
+    __syncthreads();
+  }
+  if (tid == 0) {
+    ctrl->worst_rank = worst;
+    ctrl->n_before = (int)s_base[0];
+    ctrl->n_last = (int)s_base[1];
+  }
+}
+
+// Index-ordered list of the rows with mask != 0 (crowding_distance called on its own).
+__global__ void __launch_bounds__(kSortThreads)
+    nds_mask_list_kernel(const uint8_t* __restrict__ mask, long long n, Ctrl* ctrl, uint32_t* idx_l) {
+  __shared__ unsigned s_wsum[kSortThreads / 32];
+  __shared__ unsigned s_base;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (tid == 0) s_base = 0;
+  __syncthreads();
+  for (long long s = 0; s < n; s += kSortThreads) {
+    const long long i = s + tid;
+    const bool in = (i < n) && mask[i] != 0;
+    const unsigned m = __ballot_sync(0xffffffffu, in);
+    if (lane == 0) s_wsum[warp] = __popc(m);
+    __syncthreads();
+    unsigned off = s_base;
+    for (int w = 0; w < warp; ++w) off += s_wsum[w];
+    if (in) idx_l[off + __popc(m & ((1u << lane) - 1u))] = (uint32_t)i;
+    __syncthreads();
+    if (tid == 0) {
+      unsigned t = 0;
+      for (int w = 0; w < kSortThreads / 32; ++w) t += s_wsum[w];
+      s_base += t;
+    }
+    __syncthreads();
+  }
+  if (tid == 0) ctrl->n_last = (int)s_base;
+}
+
+// Block k sorts the front by objective k (stable) and writes each member's neighbour gap divided
+// by the objective's range over the front (non_dominate.py:221-225). Members that come first or
+// last in ANY objective are flagged: the reference sets their whole row to +inf (:226-227).
+__global__ void __launch_bounds__(kSortThreads)
+    nds_crowding_sort_kernel(const float* __restrict__ costs, int m, long long n, const Ctrl* ctrl,
+                             const uint32_t* __restrict__ idx_l, uint32_t* sortbuf, float* contrib, uint32_t* boundary) {
+  __shared__ SortSmem sm;
+  const int k = blockIdx.x;
+  const int nl = ctrl->n_last;
+  uint32_t* keys = sortbuf + (size_t)k * 4 * n;
+  uint32_t* vals = keys + n;
+  uint32_t* tk = vals + n;
+  uint32_t* tv = tk + n;
+  for (int t = threadIdx.x; t < nl; t += blockDim.x) {
+    keys[t] = float_order_key(costs[(size_t)idx_l[t] * m + k]);
+    vals[t] = (uint32_t)t;
+  }
+  __syncthreads();
+  block_radix_sort(keys, vals, tk, tv, nl, 32, sm);
+  if (nl == 0) return;
+  const float c_first = costs[(size_t)idx_l[vals[0]] * m + k];
+  const float c_last = costs[(size_t)idx_l[vals[nl - 1]] * m + k];
+  const float span = __fsub_rn(c_last, c_first);
+  for (int p = threadIdx.x; p < nl; p += blockDim.x) {
+    const uint32_t t = vals[p];
+    if (p == 0 || p == nl - 1) {
+      boundary[t] = 1u;
+      contrib[(size_t)k * n + t] = INFINITY;
+    } else {
+      const float hi = costs[(size_t)idx_l[vals[p + 1]] * m + k];
+      const float lo = costs[(size_t)idx_l[vals[p - 1]] * m + k];
+      contrib[(size_t)k * n + t] = __fdiv_rn(__fsub_rn(hi, lo), span);
+    }
+  }
+}
+
+// Sum of m per-objective terms in the order torch.sum(dim=1) uses on the reference's CPU path
+// for a contiguous inner dimension (ATen SumKernel: vectors of 8 floats accumulated lane-wise,
+// scalar remainder with 4 interleaved partial sums, lanes added last in index order). For
+// m <= 4 and m == 8 this is plain left-to-right order.
+__device__ float aten_row_sum(const float* __restrict__ v, int m, size_t stride) {
+  auto scalar_sum = [&](int begin, int end) {
+    const int size = end - begin, groups = size / 4;
+    float ps[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int g = 0; g < groups; ++g)
+      for (int q = 0; q < 4; ++q) ps[q] = __fadd_rn(ps[q], v[(size_t)(begin + 4 * g + q) * stride]);
+    for (int i = begin + groups * 4; i < end; ++i) ps[0] = __fadd_rn(ps[0], v[(size_t)i * stride]);
+    ps[0] = __fadd_rn(ps[0], ps[1]);
+    ps[0] = __fadd_rn(ps[0], ps[2]);
+    ps[0] = __fadd_rn(ps[0], ps[3]);
+    return ps[0];
+  };
+  if (m < 8) return scalar_sum(0, m);
+  const int nvec = m / 8, groups = nvec / 4;
+  float lanes[8];
+  for (int l = 0; l < 8; ++l) {
+    float ps[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int g = 0; g < groups; ++g)
+      for (int q = 0; q < 4; ++q) ps[q] = __fadd_rn(ps[q], v[(size_t)((4 * g + q) * 8 + l) * stride]);
+    for (int i = groups * 4; i < nvec; ++i) ps[0] = __fadd_rn(ps[0], v[(size_t)(i * 8 + l) * stride]);
+    ps[0] = __fadd_rn(ps[0], ps[1]);
+    ps[0] = __fadd_rn(ps[0], ps[2]);
+    ps[0] = __fadd_rn(ps[0], ps[3]);
+    lanes[l] = ps[0];
+  }
+  float acc = scalar_sum(nvec * 8, m);
+  for (int l = 0; l < 8; ++l) acc = __fadd_rn(acc, lanes[l]);
+  return acc;
+}
+
+__global__ void nds_crowding_finish_kernel(int m, long long n, const Ctrl* ctrl, const uint32_t* __restrict__ idx_l,
+                                           const float* __restrict__ contrib, const uint32_t* __restrict__ boundary,
+                                           float* __restrict__ crowd) {
+  const int nl = ctrl->n_last;
+  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < nl; t += (long long)gridDim.x * blockDim.x) {
+    crowd[idx_l[t]] = boundary[t] ? INFINITY : aten_row_sum(contrib + t, m, (size_t)n);
+  }
+}
+
+__global__ void nds_fill_kernel(float* p, long long n, float v) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) p[i] = v;
+}
+
+// Block 0: rows before the last admitted front by (rank, index). Block 1: the last front by
+// (-crowding, index) — together lexsort([-crowd, rank])[:topk] (non_dominate.py:253).
+__global__ void __launch_bounds__(kSortThreads)
+    nds_order_kernel(long long n, long long topk, const Ctrl* ctrl, uint32_t* idx_a, uint32_t* key_a,
+                     const uint32_t* __restrict__ idx_l, const float* __restrict__ crowd, uint32_t* sortbuf, int m,
+                     uint32_t* order) {
+  __shared__ SortSmem sm;
+  const int na = ctrl->n_before, nl = ctrl->n_last;
+  uint32_t* scratch = sortbuf + (size_t)(m + blockIdx.x) * 4 * n;
+  if (blockIdx.x == 0) {
+    int bits = 1;
+    while (bits < 32 && (ctrl->worst_rank >> bits) != 0) ++bits;
+    block_radix_sort(key_a, idx_a, scratch, scratch + n, na, bits, sm);
+    for (int t = threadIdx.x; t < na && t < topk; t += blockDim.x) order[t] = idx_a[t];
+  } else {
+    uint32_t* keys = scratch;
+    uint32_t* vals = scratch + n;
+    for (int t = threadIdx.x; t < nl; t += blockDim.x) {
+      keys[t] = float_order_key(-crowd[idx_l[t]]);
+      vals[t] = idx_l[t];
+    }
+    __syncthreads();
+    block_radix_sort(keys, vals, scratch + 2 * n, scratch + 3 * n, nl, 32, sm);
+    for (long long t = threadIdx.x; t < nl && na + t < topk; t += blockDim.x) order[na + t] = vals[t];
+  }
+}
+
+__global__ void nds_gather_kernel(const uint32_t* __restrict__ order, long long topk, const float* __restrict__ x,
+                                  long long dx, const float* __restrict__ f, int m, const int* __restrict__ rank,
+                                  const float* __restrict__ crowd, float* out_x, float* out_f, int* out_rank,
+                                  float* out_crowd, long long* out_index) {
+  const long long per = dx + m + 1;
+  const long long total = topk * per;
+  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
+    const long long row = t / per, c = t - row * per;
+    const long long src = order[row];
+    if (c < dx) {
+      out_x[row * dx + c] = x[src * dx + c];
+    } else if (c < dx + m) {
+      out_f[row * m + (c - dx)] = f[src * m + (c - dx)];
+    } else {
+      out_rank[row] = rank[src];
+      out_crowd[row] = crowd[src];
+      if (out_index) out_index[row] = src;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------------
+template <int M>
+void launch_dominance(const float* fs, long long npad, long long n, uint32_t* Dt, int wp, cudaStream_t s) {
+  constexpr int R = (M <= 4) ? 4 : ((M <= 8) ? 2 : 1);
+  dim3 grid((unsigned)((n + kTileJ - 1) / kTileJ), (unsigned)((npad + 256 * R - 1) / (256 * R)));
+  nds_dominance_kernel<M, R><<<grid, kThreads, 0, s>>>(fs, npad, n, Dt, wp);
+}
+
+int grid_1d(long long work, int per_block = kThreads) {
+  long long want = (work + per_block - 1) / per_block;
+  const long long cap = (long long)sm_count() * 8;
+  return (int)(want < 1 ? 1 : (want < cap ? want : cap));
+}
+
+int run_rank(const float* f, long long n, int m, int* rank, void* ws, const Layout& L, cudaStream_t s) {
+  float* fs = at<float>(ws, L.fs);
+  uint32_t* Dt = at<uint32_t>(ws, L.dt);
+  Ctrl* ctrl = at<Ctrl>(ws, L.ctrl);
+  uint32_t* unranked = at<uint32_t>(ws, L.unranked);
+  uint32_t* newfront = at<uint32_t>(ws, L.newfront);
+  int* ptr = at<int>(ws, L.ptr);
+  nds_transpose_kernel<<<grid_1d((long long)m * L.npad), kThreads, 0, s>>>(f, n, m, L.npad, fs);
+  EVOX_LAUNCH_CHECK();
+  switch (m) {
+#define EVOX_DOM(MM) case MM: launch_dominance<MM>(fs, L.npad, n, Dt, L.wp, s); break;
+    EVOX_DOM(1) EVOX_DOM(2) EVOX_DOM(3) EVOX_DOM(4) EVOX_DOM(5) EVOX_DOM(6) EVOX_DOM(7) EVOX_DOM(8)
+    EVOX_DOM(9) EVOX_DOM(10) EVOX_DOM(11) EVOX_DOM(12) EVOX_DOM(13) EVOX_DOM(14) EVOX_DOM(15) EVOX_DOM(16)
+#undef EVOX_DOM
+    default:
+      nds_dominance_generic_kernel<<<grid_1d(n * (long long)L.wp), kThreads, 0, s>>>(fs, L.npad, n, m, Dt, L.wp);
+  }
+  EVOX_LAUNCH_CHECK();
+  nds_peel_init_kernel<<<grid_1d(n), kThreads, 0, s>>>(n, L.wp, unranked, newfront, ptr, rank, ctrl);
+  EVOX_LAUNCH_CHECK();
+  // persistent cooperative grid: every block must be resident for the grid barrier
+  int per_sm = 0;
+  EVOX_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, nds_peel_kernel, kThreads, 0));
+  EVOX_REQUIRE(per_sm > 0, EVOX_ERR_CUDA, "nds_peel_kernel cannot be made resident");
+  if (per_sm > 4) per_sm = 4;
+  long long blocks = (long long)sm_count() * per_sm;
+  const long long useful = (n * 32 + kThreads - 1) / kThreads;  // one warp per column
+  if (blocks > useful) blocks = useful < 1 ? 1 : useful;
+  const uint32_t* Dt_c = Dt;
+  int wp = L.wp;
+  long long nn = n;
+  void* args[] = {(void*)&Dt_c, (void*)&wp, (void*)&nn, (void*)&unranked, (void*)&newfront, (void*)&ptr, (void*)&rank, (void*)&ctrl};
+  EVOX_CUDA(cudaLaunchCooperativeKernel((const void*)nds_peel_kernel, dim3((unsigned)blocks), dim3(kThreads), args, 0, s));
+  return EVOX_OK;
+}
+
+int check_ws(const char* who, void* ws, size_t bytes, const Layout& L) {
+  EVOX_REQUIRE(ws != nullptr, EVOX_ERR_WORKSPACE, "%s: workspace is NULL", who);
+  EVOX_REQUIRE(((uintptr_t)ws & 255u) == 0, EVOX_ERR_INVALID, "%s: workspace must be 256-byte aligned", who);
+  EVOX_REQUIRE(bytes >= L.total, EVOX_ERR_WORKSPACE, "%s: workspace of %zu bytes is smaller than %zu", who, bytes, L.total);
+  return EVOX_OK;
+}
+
+int check_nm(const char* who, long long n, int m) {
+  EVOX_REQUIRE(n > 0 && n < (1ll << 31) - kPad, EVOX_ERR_INVALID, "%s: n must be in [1, 2^31), got %lld", who, n);
+  EVOX_REQUIRE(m > 0 && m <= 1024, EVOX_ERR_INVALID, "%s: number of objectives must be in [1, 1024], got %d", who, m);
+  return EVOX_OK;
+}
+
+int run_crowding(const float* costs, long long n, int m, void* ws, const Layout& L, float* crowd, cudaStream_t s) {
+  Ctrl* ctrl = at<Ctrl>(ws, L.ctrl);
+  uint32_t* idx_l = at<uint32_t>(ws, L.idx_l);
+  uint32_t* sortbuf = at<uint32_t>(ws, L.sortbuf);
+  float* contrib = at<float>(ws, L.contrib);
+  uint32_t* boundary = at<uint32_t>(ws, L.boundary);
+  EVOX_CUDA(cudaMemsetAsync(boundary, 0, sizeof(uint32_t) * (size_t)n, s));
+  nds_fill_kernel<<<grid_1d(n), kThreads, 0, s>>>(crowd, n, -INFINITY);
+  EVOX_LAUNCH_CHECK();
+  nds_crowding_sort_kernel<<<m, kSortThreads, 0, s>>>(costs, m, n, ctrl, idx_l, sortbuf, contrib, boundary);
+  EVOX_LAUNCH_CHECK();
+  nds_crowding_finish_kernel<<<grid_1d(n), kThreads, 0, s>>>(m, n, ctrl, idx_l, contrib, boundary, crowd);
+  EVOX_LAUNCH_CHECK();
+  return EVOX_OK;
+}
+
+}  // namespace
+}  // namespace evox
+
+using namespace evox;
+
+extern "C" size_t evox_nds_workspace_bytes(int64_t n, int32_t m) {
+  if (n <= 0 || m <= 0) return 0;
+  return make_layout(n, m, true).total;
+}
+
+extern "C" int evox_nd_rank(const float* f, int64_t n, int32_t m, int32_t* rank, int32_t* status,
+                            void* workspace, size_t workspace_bytes, void* stream) {
+  if (int rc = check_nm("nd_rank", n, m)) return rc;
+  EVOX_REQUIRE(f && rank, EVOX_ERR_INVALID, "nd_rank: NULL pointer");
+  const Layout L = make_layout(n, m, true);
+  if (int rc = check_ws("nd_rank", workspace, workspace_bytes, L)) return rc;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (int rc = run_rank(f, n, m, rank, workspace, L, s)) return rc;
+  if (status) {
+    EVOX_CUDA(cudaMemcpyAsync(status, &at<Ctrl>(workspace, L.ctrl)->status, 2 * sizeof(int), cudaMemcpyDeviceToDevice, s));
+  }
+  return EVOX_OK;
+}
+
+extern "C" int evox_crowding_distance(const float* costs, const uint8_t* mask, int64_t n, int32_t m,
+                                      float* distance, void* workspace, size_t workspace_bytes, void* stream) {
+  if (int rc = check_nm("crowding_distance", n, m)) return rc;
+  EVOX_REQUIRE(costs && mask && distance, EVOX_ERR_INVALID, "crowding_distance: NULL pointer");
+  const Layout L = make_layout(n, m, true);
+  if (int rc = check_ws("crowding_distance", workspace, workspace_bytes, L)) return rc;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  nds_mask_list_kernel<<<1, kSortThreads, 0, s>>>(mask, n, at<Ctrl>(workspace, L.ctrl), at<uint32_t>(workspace, L.idx_l));
+  EVOX_LAUNCH_CHECK();
+  return run_crowding(costs, n, m, workspace, L, distance, s);
+}
+
+extern "C" int evox_nd_environmental_selection(const float* x, int64_t dx, const float* f, int64_t n, int32_t m,
+                                               int64_t topk, float* out_x, float* out_f, int32_t* out_rank,
+                                               float* out_crowd, int64_t* out_index, int32_t* status,
+                                               void* workspace, size_t workspace_bytes, void* stream) {
+  if (int rc = check_nm("nd_environmental_selection", n, m)) return rc;
+  EVOX_REQUIRE(x && f && out_x && out_f && out_rank && out_crowd, EVOX_ERR_INVALID, "nd_environmental_selection: NULL pointer");
+  EVOX_REQUIRE(topk > 0 && topk <= n, EVOX_ERR_INVALID, "nd_environmental_selection: topk must be in [1, n], got %lld", (long long)topk);
+  EVOX_REQUIRE(dx > 0, EVOX_ERR_INVALID, "nd_environmental_selection: dx must be positive");
+  const Layout L = make_layout(n, m, true);
+  if (int rc = check_ws("nd_environmental_selection", workspace, workspace_bytes, L)) return rc;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  void* ws = workspace;
+  int* rank = at<int>(ws, L.rank);
+  Ctrl* ctrl = at<Ctrl>(ws, L.ctrl);
+  if (int rc = run_rank(f, n, m, rank, ws, L, s)) return rc;
+  int* hist = at<int>(ws, L.hist);
+  EVOX_CUDA(cudaMemsetAsync(hist, 0, sizeof(int) * (size_t)(n + 1), s));
+  nds_hist_kernel<<<grid_1d(n), kThreads, 0, s>>>(rank, n, hist);
+  EVOX_LAUNCH_CHECK();
+  uint32_t* idx_a = at<uint32_t>(ws, L.idx_a);
+  uint32_t* key_a = at<uint32_t>(ws, L.key_a);
+  uint32_t* idx_l = at<uint32_t>(ws, L.idx_l);
+  nds_partition_kernel<<<1, kSortThreads, 0, s>>>(rank, hist, n, topk, ctrl, idx_a, key_a, idx_l);
+  EVOX_LAUNCH_CHECK();
+  float* crowd = at<float>(ws, L.crowd);
+  if (int rc = run_crowding(f, n, m, ws, L, crowd, s)) return rc;
+  uint32_t* order = at<uint32_t>(ws, L.order);
+  nds_order_kernel<<<2, kSortThreads, 0, s>>>(n, topk, ctrl, idx_a, key_a, idx_l, crowd, at<uint32_t>(ws, L.sortbuf), m, order);
+  EVOX_LAUNCH_CHECK();
+  nds_gather_kernel<<<grid_1d(topk * (dx + m + 1)), kThreads, 0, s>>>(order, topk, x, dx, f, m, rank, crowd, out_x, out_f,
+                                                                      out_rank, out_crowd, (long long*)out_index);
+  EVOX_LAUNCH_CHECK();
+  if (status) EVOX_CUDA(cudaMemcpyAsync(status, &ctrl->status, 2 * sizeof(int), cudaMemcpyDeviceToDevice, s));
+  return EVOX_OK;
+}

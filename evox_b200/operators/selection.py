@@ -1,0 +1,115 @@
+"""Environmental selection operators backed by the CUDA kernels.
+
+Function names, argument order, dtypes and return values follow the reference
+(evox/operators/selection/non_dominate.py:172-254, rvea_selection.py:32-99).
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .. import _cabi
+
+__all__ = ["non_dominate_rank", "crowding_distance", "nd_environmental_selection"]
+
+_workspaces: dict[tuple[str, torch.device], torch.Tensor] = {}
+
+
+def _workspace(kind: str, device: torch.device, nbytes: int) -> torch.Tensor:
+    """A per-device scratch buffer that only grows; kernels using it are ordered by the stream."""
+    key = (kind, device)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def _check_objectives(f: torch.Tensor, name: str) -> torch.Tensor:
+    if f.ndim != 2:
+        raise _cabi.EvoxKernelError(f"{name} must be 2-D (n, m), got shape {tuple(f.shape)}")
+    return f.to(torch.float32).contiguous()
+
+
+def _raise_on_status(status: torch.Tensor) -> None:
+    code = int(status[0])
+    if code != 0:
+        raise _cabi.EvoxKernelError(
+            "non-dominated sort did not finish: " + ("a grid-barrier wait timed out" if code == 1 else "no progress")
+        )
+
+
+def non_dominate_rank(x: torch.Tensor, check: bool = False) -> torch.Tensor:
+    """Non-domination rank (int32, 0 = non-dominated) of each row of `x` (n, m).
+
+    `check=True` reads the kernel's status word back (one host synchronisation) and raises if the
+    bounded device-side waits gave up; the default leaves the call asynchronous."""
+    f = _check_objectives(x, "x")
+    n, m = f.shape
+    rank = torch.empty(n, dtype=torch.int32, device=f.device)
+    if n == 0:
+        return rank
+    nbytes = _cabi.lib.evox_nds_workspace_bytes(n, m)
+    ws = _workspace("nds", f.device, nbytes)
+    status = torch.zeros(2, dtype=torch.int32, device=f.device)
+    _cabi.check(
+        _cabi.lib.evox_nd_rank(
+            _cabi.ptr(f), n, m, _cabi.ptr(rank), _cabi.ptr(status), _cabi.ptr(ws), ws.numel(), _cabi.stream_ptr(f.device)
+        )
+    )
+    if check:
+        _raise_on_status(status)
+    return rank
+
+
+def crowding_distance(costs: torch.Tensor, mask: torch.Tensor | None = None) -> torch.Tensor:
+    """Crowding distance of the rows selected by `mask` (all rows if None); -inf elsewhere."""
+    f = _check_objectives(costs, "costs")
+    n, m = f.shape
+    if mask is None:
+        mask = torch.ones(n, dtype=torch.bool, device=f.device)
+    mask_u8 = mask.to(torch.uint8).contiguous()
+    out = torch.empty(n, dtype=torch.float32, device=f.device)
+    if n == 0:
+        return out
+    nbytes = _cabi.lib.evox_nds_workspace_bytes(n, m)
+    ws = _workspace("nds", f.device, nbytes)
+    _cabi.check(
+        _cabi.lib.evox_crowding_distance(
+            _cabi.ptr(f), _cabi.ptr(mask_u8), n, m, _cabi.ptr(out), _cabi.ptr(ws), ws.numel(), _cabi.stream_ptr(f.device)
+        )
+    )
+    return out
+
+
+def nd_environmental_selection(x: torch.Tensor, f: torch.Tensor, topk: int, return_index: bool = False, check: bool = False):
+    """Keep the best `topk` rows by (non-domination rank, then crowding distance).
+
+    Returns (x, f, rank, crowding_distance) of the selected rows like the reference; with
+    `return_index=True` a fifth tensor holds their row numbers."""
+    fo = _check_objectives(f, "f")
+    xo = x.to(torch.float32).contiguous()
+    n, m = fo.shape
+    if xo.ndim != 2 or xo.shape[0] != n:
+        raise _cabi.EvoxKernelError(f"x must be (n, d) with n = {n}, got {tuple(x.shape)}")
+    dx = xo.shape[1]
+    dev = fo.device
+    out_x = torch.empty(topk, dx, dtype=torch.float32, device=dev)
+    out_f = torch.empty(topk, m, dtype=torch.float32, device=dev)
+    out_rank = torch.empty(topk, dtype=torch.int32, device=dev)
+    out_crowd = torch.empty(topk, dtype=torch.float32, device=dev)
+    out_index = torch.empty(topk, dtype=torch.int64, device=dev)
+    status = torch.zeros(2, dtype=torch.int32, device=dev)
+    nbytes = _cabi.lib.evox_nds_workspace_bytes(n, m)
+    ws = _workspace("nds", dev, nbytes)
+    _cabi.check(
+        _cabi.lib.evox_nd_environmental_selection(
+            _cabi.ptr(xo), dx, _cabi.ptr(fo), n, m, topk, _cabi.ptr(out_x), _cabi.ptr(out_f), _cabi.ptr(out_rank),
+            _cabi.ptr(out_crowd), _cabi.ptr(out_index), _cabi.ptr(status), _cabi.ptr(ws), ws.numel(), _cabi.stream_ptr(dev),
+        )
+    )
+    if check:
+        _raise_on_status(status)
+    if return_index:
+        return out_x, out_f, out_rank, out_crowd, out_index
+    return out_x, out_f, out_rank, out_crowd

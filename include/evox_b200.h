@@ -112,6 +112,40 @@ int evox_pso_init_step(const float* pop, float* fit, float* local_best_fit,
 int evox_pso_fill_uniform(float* out, int64_t pop_size, int32_t dim, uint64_t seed,
                           uint64_t generation, int32_t which, int64_t row_offset, void* stream);
 
+/* ------------------------------------------------------------------------------------------
+ * P2. NSGA-II environmental selection.
+ * ------------------------------------------------------------------------------------------ */
+
+/* Scratch bytes for the three entry points below (dominated by the bit-packed dominance
+ * matrix, n * ceil(n / 1024) * 128 bytes). The workspace needs no initialisation and must be
+ * 256-byte aligned. */
+size_t evox_nds_workspace_bytes(int64_t n, int32_t m);
+
+/* Non-domination rank of every row of f (n x m, fp32): rank 0 = non-dominated, rank r = non-
+ * dominated once ranks < r are removed. Replaces non_dominate_rank
+ * (operators/selection/non_dominate.py:172-195: dominate_relation :6-26 + the front-peeling
+ * loop :151-169); rank is int32 like the reference's. NaN objectives compare false both ways.
+ * `status` (optional, device int32[2]) receives {0 = ok | 1 = a bounded grid-barrier wait gave
+ * up | 2 = no progress, number of fronts}. */
+int evox_nd_rank(const float* f, int64_t n, int32_t m, int32_t* rank, int32_t* status,
+                 void* workspace, size_t workspace_bytes, void* stream);
+
+/* Crowding distance of the rows selected by `mask` (n bytes, non-zero = selected), -inf for
+ * the others. Replaces crowding_distance (non_dominate.py:198-231) including its stable
+ * tie-breaking (utils/jit_fix_operator.py:216-252) and its treatment of rows that are first or
+ * last in any objective (+inf). */
+int evox_crowding_distance(const float* costs, const uint8_t* mask, int64_t n, int32_t m,
+                           float* distance, void* workspace, size_t workspace_bytes, void* stream);
+
+/* rank -> last admitted front -> crowding distance on it -> the first `topk` rows in the order
+ * lexsort([-crowding, rank]) -> gathered x (topk x dx), f (topk x m), rank, crowding distance.
+ * Replaces nd_environmental_selection (non_dominate.py:234-254). `out_index` (optional, int64)
+ * receives the selected row numbers, `status` as in evox_nd_rank. */
+int evox_nd_environmental_selection(const float* x, int64_t dx, const float* f, int64_t n, int32_t m,
+                                    int64_t topk, float* out_x, float* out_f, int32_t* out_rank,
+                                    float* out_crowd, int64_t* out_index, int32_t* status,
+                                    void* workspace, size_t workspace_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
