@@ -137,3 +137,31 @@ def pso_uniform(pop_size: int, dim: int, seed: int, generation: int, which: int,
     k1 = torch.full_like(q, (seed >> 32) & _MASK)
     out = torch.stack(philox4x32_10(c0, c1, c2, c3, k0, k1), dim=2).reshape(pop_size, n_call * 4)[:, :dim]
     return ((out & _MASK) >> 8).to(torch.float32) * (1.0 / (1 << 24))
+
+
+# ---------------------------------------------------------------------------------------------
+# Sharded swarm: the best-particle record each rank contributes and how the records are merged.
+# Layout as in include/evox_b200.h (evox_pso_local_best): word 0 fitness bits, words 1-2 global
+# row index (int64), word 3 zero, then the row. min_by's tie rules (utils.py:18-25) decide.
+# ---------------------------------------------------------------------------------------------
+def candidate_record(fit: torch.Tensor, pop: torch.Tensor, row_offset: int) -> torch.Tensor:
+    i = int(torch.argmin(fit))
+    d = pop.shape[1]
+    rec = torch.zeros(4 + d, dtype=torch.int32)
+    rec[0] = fit[i : i + 1].view(torch.int32)[0]
+    rec[1:3] = torch.tensor([i + row_offset], dtype=torch.int64).view(torch.int32)  # little endian: lo, hi
+    rec[4:] = pop[i].view(torch.int32)
+    return rec
+
+
+def merge_records(records: torch.Tensor, world: int, d: int, gbest_loc: torch.Tensor, gbest_fit: torch.Tensor, have_previous: bool = True):
+    """Pick the winner the way argmin over cat([old best, all particles]) would."""
+    recs = records.view(world, 4 + d)
+    fits = recs[:, 0].contiguous().view(torch.float32)
+    idx = (recs[:, 1].to(torch.int64) & 0xFFFFFFFF) | (recs[:, 2].to(torch.int64) << 32)
+    order = sorted(range(world), key=lambda r: int(idx[r]))  # global row order = concatenation order
+    keys = torch.stack([fits[r] for r in order])
+    rows = torch.stack([recs[r, 4:].contiguous().view(torch.float32) for r in order])
+    if have_previous:
+        return min_by([gbest_loc[None], rows], [gbest_fit[None], keys])
+    return min_by([rows], [keys])
