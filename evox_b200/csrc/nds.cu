@@ -23,6 +23,8 @@
 // front -> neighbour gaps / range -> stable sorts by (rank) and (-crowding) -> gather.
 #include <math.h>
 
+#include <mutex>
+
 #include "common.cuh"
 
 namespace evox {
@@ -827,5 +829,74 @@ extern "C" int evox_nd_environmental_selection(const float* x, int64_t dx, const
                                                                       out_rank, out_crowd, (long long*)out_index);
   EVOX_LAUNCH_CHECK();
   if (status) EVOX_CUDA(cudaMemcpyAsync(status, &ctrl->status, 2 * sizeof(int), cudaMemcpyDeviceToDevice, s));
+  return EVOX_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free rank for small populations.
+//
+// Some hosts of this library may not allocate device memory at the point where they need a
+// rank: code running between fixed-size arenas handed out at start-up, plug-ins that are given
+// input and output buffers by their host application and nothing else, and loops that must not
+// disturb an allocator's bookkeeping while they run. For them the scratch of evox_nd_rank lives
+// in a fixed array inside the library image. Every GPU that loads the library carries those
+// kStaticBytes until the process exits, which is why the population is capped.
+// ---------------------------------------------------------------------------------------------
+namespace evox {
+namespace {
+
+constexpr long long kStaticMaxN = 4096;
+constexpr int kStaticMaxM = 16;
+constexpr size_t kStaticBytes = 4u << 20;  // >= make_layout(kStaticMaxN, kStaticMaxM).total, checked at set-up
+
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticBytes];
+
+// In host code `g_static_scratch` is only a handle for the runtime, not a device address: the
+// address has to be asked for, once per device, while that device is current.
+std::mutex g_static_mutex;
+void* g_static_address[64] = {nullptr};
+bool g_static_ready[64] = {false};
+
+int static_scratch_address(void** out) {
+  int dev = -1;
+  EVOX_CUDA(cudaGetDevice(&dev));
+  EVOX_REQUIRE(dev >= 0 && dev < 64, EVOX_ERR_INVALID, "nd_rank_static: device ordinal %d is not supported", dev);
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  if (!g_static_ready[dev]) {
+    EVOX_REQUIRE(make_layout(kStaticMaxN, kStaticMaxM, true).total <= kStaticBytes, EVOX_ERR_INVALID,
+                 "nd_rank_static: built-in scratch of %zu bytes cannot hold the maximum problem", kStaticBytes);
+    void* p = nullptr;
+    EVOX_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
+    EVOX_REQUIRE(p != nullptr && ((uintptr_t)p & 255u) == 0, EVOX_ERR_CUDA, "nd_rank_static: bad scratch address");
+    g_static_address[dev] = p;
+    g_static_ready[dev] = true;
+  }
+  *out = g_static_address[dev];
+  return EVOX_OK;
+}
+
+}  // namespace
+}  // namespace evox
+
+extern "C" int evox_nd_rank_static(const float* f, int64_t n, int32_t m, int32_t* rank, int32_t* status,
+                                   void* stream) {
+  if (int rc = check_nm("nd_rank_static", n, m)) return rc;
+  EVOX_REQUIRE(f && rank, EVOX_ERR_INVALID, "nd_rank_static: NULL pointer");
+  EVOX_REQUIRE(n <= kStaticMaxN, EVOX_ERR_INVALID,
+               "nd_rank_static: n = %lld exceeds the built-in scratch (at most %lld rows); use evox_nd_rank with a workspace",
+               (long long)n, kStaticMaxN);
+  EVOX_REQUIRE(m <= kStaticMaxM, EVOX_ERR_INVALID,
+               "nd_rank_static: m = %d exceeds the built-in scratch (at most %d objectives); use evox_nd_rank with a workspace",
+               m, kStaticMaxM);
+  void* scratch = nullptr;
+  if (int rc = static_scratch_address(&scratch)) return rc;
+  const Layout L = make_layout(n, m, true);
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  // run_rank rewrites every scratch region it later reads (objectives, matrix rows, masks,
+  // witness positions, control block), so what an earlier call left behind is never seen
+  if (int rc = run_rank(f, n, m, rank, scratch, L, s)) return rc;
+  if (status) {
+    EVOX_CUDA(cudaMemcpyAsync(status, &at<Ctrl>(scratch, L.ctrl)->status, 2 * sizeof(int), cudaMemcpyDeviceToDevice, s));
+  }
   return EVOX_OK;
 }

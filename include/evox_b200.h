@@ -146,6 +146,23 @@ int evox_nd_environmental_selection(const float* x, int64_t dx, const float* f, 
                                     float* out_crowd, int64_t* out_index, int32_t* status,
                                     void* workspace, size_t workspace_bytes, void* stream);
 
+/* evox_nd_rank for callers that cannot allocate device memory: no workspace argument, and the
+ * call itself allocates nothing (no cudaMalloc / cudaFree, no allocating library routine). It
+ * has no counterpart in the reference. It is meant for hosts that only own the buffers they
+ * were handed — a plug-in inside another application's memory arena, a loop that must leave
+ * the allocator untouched while it runs. The scratch (objectives, dominance bits, masks) is a
+ * fixed 4 MiB array inside the library image, present on every GPU that loads the library
+ * until the process exits; hence the limits n <= 4096 rows and m <= 16 objectives, beyond which
+ * the call fails with EVOX_ERR_INVALID and evox_nd_rank must be used. Same results as
+ * evox_nd_rank; `f`, `rank` and the optional `status` are still the caller's buffers.
+ * The first call on each device looks up the array's device address (with that device
+ * current); make that first call before starting any stream capture. All calls on a device
+ * share the one array and it keeps the previous call's contents (everything that is read is
+ * rewritten first), so two calls must not overlap on the GPU: issue them on one stream, or
+ * order them with events. */
+int evox_nd_rank_static(const float* f, int64_t n, int32_t m, int32_t* rank, int32_t* status,
+                        void* stream);
+
 #ifdef __cplusplus
 }
 #endif
