@@ -343,16 +343,61 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_nds(args):
+    """Secondary workload: non-dominated rank / full environmental selection on DTLZ2-shaped
+    objectives (BASELINE configs[1] at 2N = 20,000 and the metric's 2N = 100,000)."""
+    from evox_b200.operators.selection import nd_environmental_selection, non_dominate_rank
+    from oracle import nds as onds
+
+    dev = torch.device("cuda", 0)
+    n = {"nds_rank_2e4": 20_000, "nds_rank_1e5": 100_000}[args.workload]
+    gen = torch.Generator().manual_seed(0)
+    x = torch.rand(n, 12, generator=gen)
+    f = onds.dtlz2_objectives(x, 3)
+    xd, fd = x.to(dev), f.to(dev)
+
+    def timed(fn, reps):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+
+    rank_ms = timed(lambda: non_dominate_rank(fd), args.steps)
+    sel_ms = timed(lambda: nd_environmental_selection(xd, fd, n // 2), args.steps)
+    rank = non_dominate_rank(fd, check=True)
+    line = {
+        "metric": "nds_rank_ms", "value": rank_ms, "unit": "ms", "n_gpus": 1, "steps": args.steps, "warmup": 3,
+        "ms_per_step": rank_ms, "higher_is_better": False, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "n": n, "m": 3, "fronts": int(rank.max()) + 1},
+        "selection_ms": sel_ms,
+        "pairs_per_s": n * n / (rank_ms * 1e-3),
+    }
+    if not args.no_cpu_baseline and n <= 20_000:
+        t0 = time.perf_counter()
+        onds.non_dominate_rank(f)
+        line["cpu_baseline"] = {"value": (time.perf_counter() - t0) * 1e3, "unit": "ms", "cores": torch.get_num_threads(),
+                                "kind": "port", "sample": "whole workload, one run"}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="pso_ackley_1e6x1000", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="pso_ackley_1e6x1000", choices=sorted(WORKLOADS) + ["nds_rank_2e4", "nds_rank_1e5"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.workload.startswith("nds_"):
+        run_nds(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
