@@ -1,0 +1,280 @@
+// P3: RVEA reference-vector-guided selection as one association + APD pass.
+//
+// Reference semantics: ref_vec_guided and apd_fn (evox/operators/selection/rvea_selection.py:7-99)
+// with the relu-form helpers nanmin / maximum / clamp_float (evox/utils/jit_fix_operator.py).
+// The reference materialises an (n, nv, m) product and about ten (n, nv) temporaries; here each
+// objective row is read once:
+//   1. rvea_ideal_kernel   column minima ignoring NaN (ordered-integer atomicMin).
+//   2. rvea_vectors_kernel unit reference vectors and gamma_j = min over k of the angle between
+//                          v_j and v_k, the diagonal counted as cosine 0 (rvea_selection.py:63-71).
+//   3. rvea_assign_kernel  4 lanes per individual: translate, normalise, cosine against every
+//                          vector from shared memory, arccos, first-minimum association, APD, and
+//                          a 64-bit atomicMin of (APD bits, row) per vector — APD is positive, so
+//                          its bit pattern orders like the value and the lowest row wins ties, as
+//                          torch.argmin does.
+//   4. rvea_gather_kernel  rows of x and f for every vector, NaN for vectors nobody joined.
+// Bytes that must move: n*m*4 (objectives) + nv*(dx+m)*4 (outputs); the pass is latency-bound at
+// the benchmark's 2 MB input.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace evox {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kLanesPerRow = 4;
+constexpr float kEps = 1e-8f;  // torch.nn.functional.cosine_similarity's eps
+
+__device__ __forceinline__ uint32_t order_key(float x) {
+  const uint32_t b = __float_as_uint(x);
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+__device__ __forceinline__ float order_key_inv(uint32_t k) {
+  return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
+}
+
+__device__ __forceinline__ float relu_clamp01(float a) {
+  const float lo = fmaxf(__fsub_rn(0.0f, a), 0.0f);
+  const float hi = fmaxf(__fsub_rn(a, 1.0f), 0.0f);
+  return __fsub_rn(__fadd_rn(a, lo), hi);
+}
+
+__global__ void rvea_init_kernel(uint32_t* zmin_key, int m, unsigned long long* best, int nv) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t < m) zmin_key[t] = order_key(INFINITY);
+  if (t < nv) best[t] = 0xffffffffffffffffull;
+}
+
+// nanmin over rows (jit_fix_operator.py:289-292): NaN counts as +inf.
+__global__ void __launch_bounds__(kThreads)
+    rvea_ideal_kernel(const float* __restrict__ f, long long n, int m, uint32_t* zmin_key) {
+  // thread t handles column t % m of rows t / m, t / m + stride, ... (coalesced over the row-major matrix)
+  const long long total = n * (long long)m;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  const long long step = stride - (stride % m);  // keep each thread on one column
+  long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= step) return;
+  const int col = (int)(t % m);
+  float mn = INFINITY;
+  for (; t < total; t += step) {
+    const float v = f[t];
+    if (v == v) mn = fminf(mn, v);
+  }
+  atomicMin(zmin_key + col, order_key(mn));
+}
+
+// One block. vn = v / max(|v|, eps); gamma_j = min_k acos(clamp01(cos(v_j, v_k))) with cos_jj := 0.
+__global__ void __launch_bounds__(kThreads)
+    rvea_vectors_kernel(const float* __restrict__ v, int nv, int m, float* __restrict__ vn, float* __restrict__ gamma) {
+  for (int j = threadIdx.x; j < nv; j += blockDim.x) {
+    float s = 0.f;
+    for (int k = 0; k < m; ++k) s = __fmaf_rn(v[j * m + k], v[j * m + k], s);
+    const float nrm = fmaxf(sqrtf(s), kEps);
+    for (int k = 0; k < m; ++k) vn[j * m + k] = __fdiv_rn(v[j * m + k], nrm);
+  }
+  __syncthreads();
+  for (int j = threadIdx.x; j < nv; j += blockDim.x) {
+    float g = acosf(0.0f);  // the diagonal entry, set to cosine 0 by the reference
+    for (int k = 0; k < nv; ++k) {
+      if (k == j) continue;
+      float c = 0.f;
+      for (int q = 0; q < m; ++q) c = __fmaf_rn(vn[j * m + q], vn[k * m + q], c);
+      g = fminf(g, acosf(relu_clamp01(c)));
+    }
+    gamma[j] = g;
+  }
+}
+
+template <int MP>
+__global__ void __launch_bounds__(kThreads)
+    rvea_assign_kernel(const float* __restrict__ f, long long n, int m, const uint32_t* __restrict__ zmin_key,
+                       const float* __restrict__ vn, const float* __restrict__ gamma, int nv,
+                       const float* __restrict__ theta_p, unsigned long long* best, int* __restrict__ associate) {
+  extern __shared__ float s_vn[];  // nv x MP, zero padded
+  for (int t = threadIdx.x; t < nv * MP; t += blockDim.x) {
+    const int j = t / MP, k = t - j * MP;
+    s_vn[t] = (k < m) ? vn[j * m + k] : 0.0f;
+  }
+  __syncthreads();
+  const float m_theta = __fmul_rn((float)m, *theta_p);  // rvea_selection.py:26: obj.size(1) * theta
+  const int sub = threadIdx.x & (kLanesPerRow - 1);
+  const long long rows_per_pass = (long long)gridDim.x * (kThreads / kLanesPerRow);
+  const long long n_pad = (n + rows_per_pass - 1) / rows_per_pass * rows_per_pass;  // keep whole warps in the shuffles
+  for (long long row = (long long)blockIdx.x * (kThreads / kLanesPerRow) + (threadIdx.x / kLanesPerRow); row < n_pad;
+       row += rows_per_pass) {
+    const bool live = row < n;
+    float obj[MP];
+    bool has_nan = false;
+    float sq = 0.f;
+#pragma unroll
+    for (int k = 0; k < MP; ++k) {
+      float o = 0.f;
+      if (live && k < m) {
+        o = __fsub_rn(f[row * m + k], order_key_inv(zmin_key[k]));
+        o = __fadd_rn(o, fmaxf(__fsub_rn(1e-32f, o), 0.0f));  // maximum(obj, 1e-32), relu form
+        has_nan = has_nan || (o != o);
+        sq = __fmaf_rn(o, o, sq);
+      }
+      obj[k] = o;
+    }
+    const float norm = sqrtf(sq);
+    const float inv_den = fmaxf(norm, kEps);
+#pragma unroll
+    for (int k = 0; k < MP; ++k) obj[k] = __fdiv_rn(obj[k], inv_den);
+    float best_angle = INFINITY;
+    int best_j = 0x7fffffff;
+    for (int j = sub; j < nv; j += kLanesPerRow) {
+      const float* vj = s_vn + j * MP;
+      float c = 0.f;
+#pragma unroll
+      for (int k = 0; k < MP; ++k) c = __fmaf_rn(obj[k], vj[k], c);
+      const float a = acosf(relu_clamp01(c));
+      if (a < best_angle) {
+        best_angle = a;
+        best_j = j;
+      }
+    }
+#pragma unroll
+    for (int off = 1; off < kLanesPerRow; off <<= 1) {
+      const float oa = __shfl_xor_sync(0xffffffffu, best_angle, off);
+      const int oj = __shfl_xor_sync(0xffffffffu, best_j, off);
+      if (oa < best_angle || (oa == best_angle && oj < best_j)) {
+        best_angle = oa;
+        best_j = oj;
+      }
+    }
+    if (live && sub == 0) {
+      if (has_nan || best_j >= nv) {
+        associate[row] = -1;  // rvea_selection.py:81-83
+      } else {
+        associate[row] = best_j;
+        // rvea_selection.py:25-29: (1 + m * theta * angle) / gamma * |obj|
+        const float left = __fdiv_rn(__fadd_rn(1.0f, __fmul_rn(m_theta, best_angle)), gamma[best_j]);
+        const float apd = __fmul_rn(left, norm);
+        // NaN sorts first (torch.argmin); +inf keeps its bit pattern and is resolved at gather time
+        const unsigned long long key =
+            (apd != apd) ? (unsigned long long)row
+                         : (((unsigned long long)__float_as_uint(apd) << 32) | (unsigned long long)(uint32_t)row);
+        atomicMin(best + best_j, key);
+      }
+    }
+  }
+}
+
+__global__ void rvea_gather_kernel(const unsigned long long* __restrict__ best, int nv, const float* __restrict__ x,
+                                   long long dx, const float* __restrict__ f, int m, float* __restrict__ next_x,
+                                   float* __restrict__ next_f, long long* __restrict__ next_index) {
+  const long long per = dx + m;
+  const long long total = (long long)nv * per;
+  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
+    const int j = (int)(t / per);
+    const long long c = t - (long long)j * per;
+    const unsigned long long key = best[j];
+    const bool empty = key == 0xffffffffffffffffull;
+    // a vector whose members all have APD = +inf: argmin over an all-inf column is row 0
+    const bool all_inf = !empty && (uint32_t)(key >> 32) == 0x7f800000u;
+    const long long src = all_inf ? 0 : (long long)(uint32_t)key;
+    const float nanv = __int_as_float(0x7fc00000);
+    if (c < dx) next_x[(long long)j * dx + c] = empty ? nanv : x[src * dx + c];
+    else next_f[(long long)j * m + (c - dx)] = empty ? nanv : f[src * m + (c - dx)];
+    if (c == 0 && next_index) next_index[j] = empty ? -1 : src;
+  }
+}
+
+struct Layout {
+  size_t zmin, best, vn, gamma, associate, total;
+};
+
+Layout make_layout(long long n, int m, int nv) {
+  Layout L;
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    const size_t at = off;
+    off = (off + bytes + 255) / 256 * 256;
+    return at;
+  };
+  L.zmin = take(sizeof(uint32_t) * (size_t)m);
+  L.best = take(sizeof(unsigned long long) * (size_t)nv);
+  L.vn = take(sizeof(float) * (size_t)nv * m);
+  L.gamma = take(sizeof(float) * (size_t)nv);
+  L.associate = take(sizeof(int) * (size_t)n);
+  L.total = off;
+  return L;
+}
+
+template <int MP>
+int launch_assign(const float* f, long long n, int m, const uint32_t* zmin, const float* vn, const float* gamma, int nv,
+                  const float* theta, unsigned long long* best, int* associate, cudaStream_t s) {
+  const size_t smem = sizeof(float) * (size_t)nv * MP;
+  EVOX_REQUIRE(smem <= 200 * 1024, EVOX_ERR_INVALID, "ref_vec_guided: %d reference vectors x %d objectives do not fit in shared memory", nv, m);
+  if (smem > 48 * 1024) {
+    EVOX_CUDA(cudaFuncSetAttribute(rvea_assign_kernel<MP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  }
+  const long long rows_per_block = kThreads / kLanesPerRow;
+  long long blocks = (n + rows_per_block - 1) / rows_per_block;
+  const long long cap = (long long)sm_count() * 8;
+  if (blocks > cap) blocks = cap;
+  rvea_assign_kernel<MP><<<(unsigned)blocks, kThreads, smem, s>>>(f, n, m, zmin, vn, gamma, nv, theta, best, associate);
+  EVOX_LAUNCH_CHECK();
+  return EVOX_OK;
+}
+
+}  // namespace
+}  // namespace evox
+
+using namespace evox;
+
+extern "C" size_t evox_rvea_workspace_bytes(int64_t n, int32_t m, int32_t nv) {
+  if (n <= 0 || m <= 0 || nv <= 0) return 0;
+  return make_layout(n, m, nv).total;
+}
+
+extern "C" int evox_ref_vec_guided(const float* x, int64_t dx, const float* f, int64_t n, int32_t m,
+                                   const float* v, int32_t nv, const float* theta, float* next_x,
+                                   float* next_f, int64_t* next_index, void* workspace,
+                                   size_t workspace_bytes, void* stream) {
+  EVOX_REQUIRE(x && f && v && theta && next_x && next_f, EVOX_ERR_INVALID, "ref_vec_guided: NULL pointer");
+  EVOX_REQUIRE(n > 0 && n < (1ll << 32), EVOX_ERR_INVALID, "ref_vec_guided: n must be in [1, 2^32), got %lld", (long long)n);
+  EVOX_REQUIRE(m > 0 && m <= 32, EVOX_ERR_INVALID, "ref_vec_guided: number of objectives must be in [1, 32], got %d", m);
+  EVOX_REQUIRE(nv > 0 && dx > 0, EVOX_ERR_INVALID, "ref_vec_guided: nv and dx must be positive");
+  const Layout L = make_layout(n, m, nv);
+  EVOX_REQUIRE(workspace != nullptr && workspace_bytes >= L.total, EVOX_ERR_WORKSPACE,
+               "ref_vec_guided: workspace of %zu bytes is smaller than %zu", workspace_bytes, L.total);
+  EVOX_REQUIRE(((uintptr_t)workspace & 255u) == 0, EVOX_ERR_INVALID, "ref_vec_guided: workspace must be 256-byte aligned");
+  char* ws = reinterpret_cast<char*>(workspace);
+  uint32_t* zmin = reinterpret_cast<uint32_t*>(ws + L.zmin);
+  unsigned long long* best = reinterpret_cast<unsigned long long*>(ws + L.best);
+  float* vn = reinterpret_cast<float*>(ws + L.vn);
+  float* gamma = reinterpret_cast<float*>(ws + L.gamma);
+  int* associate = reinterpret_cast<int*>(ws + L.associate);
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const int init_n = m > nv ? m : nv;
+  rvea_init_kernel<<<(init_n + kThreads - 1) / kThreads, kThreads, 0, s>>>(zmin, m, best, nv);
+  EVOX_LAUNCH_CHECK();
+  {
+    long long want = (n * m + kThreads * 8 - 1) / (kThreads * 8);
+    const long long cap = (long long)sm_count() * 4;
+    const int grid = (int)(want < 1 ? 1 : (want < cap ? want : cap));
+    rvea_ideal_kernel<<<grid, kThreads, 0, s>>>(f, n, m, zmin);
+    EVOX_LAUNCH_CHECK();
+  }
+  rvea_vectors_kernel<<<1, kThreads, 0, s>>>(v, nv, m, vn, gamma);
+  EVOX_LAUNCH_CHECK();
+  int rc;
+  if (m <= 4) rc = launch_assign<4>(f, n, m, zmin, vn, gamma, nv, theta, best, associate, s);
+  else if (m <= 8) rc = launch_assign<8>(f, n, m, zmin, vn, gamma, nv, theta, best, associate, s);
+  else if (m <= 12) rc = launch_assign<12>(f, n, m, zmin, vn, gamma, nv, theta, best, associate, s);
+  else if (m <= 16) rc = launch_assign<16>(f, n, m, zmin, vn, gamma, nv, theta, best, associate, s);
+  else rc = launch_assign<32>(f, n, m, zmin, vn, gamma, nv, theta, best, associate, s);
+  if (rc) return rc;
+  {
+    const long long total = (long long)nv * (dx + m);
+    const long long cap = (long long)sm_count() * 8;
+    long long want = (total + kThreads - 1) / kThreads;
+    rvea_gather_kernel<<<(unsigned)(want < cap ? want : cap), kThreads, 0, s>>>(best, nv, x, dx, f, m, next_x, next_f,
+                                                                                 (long long*)next_index);
+    EVOX_LAUNCH_CHECK();
+  }
+  return EVOX_OK;
+}

@@ -10,7 +10,7 @@ import torch
 
 from .. import _cabi
 
-__all__ = ["non_dominate_rank", "crowding_distance", "nd_environmental_selection"]
+__all__ = ["non_dominate_rank", "crowding_distance", "nd_environmental_selection", "ref_vec_guided"]
 
 _workspaces: dict[tuple[str, torch.device], torch.Tensor] = {}
 
@@ -113,3 +113,34 @@ def nd_environmental_selection(x: torch.Tensor, f: torch.Tensor, topk: int, retu
     if return_index:
         return out_x, out_f, out_rank, out_crowd, out_index
     return out_x, out_f, out_rank, out_crowd
+
+
+def ref_vec_guided(x: torch.Tensor, f: torch.Tensor, v: torch.Tensor, theta: torch.Tensor | float, return_index: bool = False):
+    """RVEA selection: per reference vector the associated individual with the smallest
+    angle-penalised distance. Returns (next_x, next_f) with NaN rows for empty vectors, like the
+    reference; `return_index=True` adds the chosen row numbers (-1 for empty vectors)."""
+    fo = _check_objectives(f, "f")
+    n, m = fo.shape
+    dev = fo.device
+    xo = x.to(torch.float32).contiguous()
+    vo = v.to(device=dev, dtype=torch.float32).contiguous()
+    if xo.ndim != 2 or xo.shape[0] != n:
+        raise _cabi.EvoxKernelError(f"x must be (n, d) with n = {n}, got {tuple(x.shape)}")
+    if vo.ndim != 2 or vo.shape[1] != m:
+        raise _cabi.EvoxKernelError(f"v must be (nv, {m}), got {tuple(v.shape)}")
+    nv, dx = vo.shape[0], xo.shape[1]
+    th = torch.as_tensor(theta, dtype=torch.float32, device=dev).reshape(())
+    next_x = torch.empty(nv, dx, dtype=torch.float32, device=dev)
+    next_f = torch.empty(nv, m, dtype=torch.float32, device=dev)
+    next_index = torch.empty(nv, dtype=torch.int64, device=dev)
+    nbytes = _cabi.lib.evox_rvea_workspace_bytes(n, m, nv)
+    ws = _workspace("rvea", dev, nbytes)
+    _cabi.check(
+        _cabi.lib.evox_ref_vec_guided(
+            _cabi.ptr(xo), dx, _cabi.ptr(fo), n, m, _cabi.ptr(vo), nv, _cabi.ptr(th), _cabi.ptr(next_x), _cabi.ptr(next_f),
+            _cabi.ptr(next_index), _cabi.ptr(ws), ws.numel(), _cabi.stream_ptr(dev),
+        )
+    )
+    if return_index:
+        return next_x, next_f, next_index
+    return next_x, next_f

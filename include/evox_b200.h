@@ -146,6 +146,26 @@ int evox_nd_environmental_selection(const float* x, int64_t dx, const float* f, 
                                     float* out_crowd, int64_t* out_index, int32_t* status,
                                     void* workspace, size_t workspace_bytes, void* stream);
 
+/* ------------------------------------------------------------------------------------------
+ * P3. RVEA reference-vector-guided selection.
+ * ------------------------------------------------------------------------------------------ */
+
+size_t evox_rvea_workspace_bytes(int64_t n, int32_t m, int32_t nv);
+
+/* For every reference vector v_j (nv x m) the individual with the smallest angle-penalised
+ * distance among those associated with it; rows of x (n x dx) and f (n x m) are gathered into
+ * next_x (nv x dx) and next_f (nv x m), NaN rows for vectors nobody is associated with.
+ * Replaces ref_vec_guided (operators/selection/rvea_selection.py:32-99, apd_fn :7-29): ideal
+ * point by nanmin, objectives floored at 1e-32, cosine similarity with eps 1e-8, relu-form
+ * clamp to [0,1], arccos, first-minimum association (individuals with a NaN objective join no
+ * vector), APD = (1 + m * theta * angle) / gamma_j * |f - z|, first-minimum per vector.
+ * `theta` is a DEVICE scalar (the reference passes a 0-d tensor). `next_index` (optional,
+ * int64[nv]) receives the chosen row numbers, -1 for empty vectors. m <= 32. */
+int evox_ref_vec_guided(const float* x, int64_t dx, const float* f, int64_t n, int32_t m,
+                        const float* v, int32_t nv, const float* theta, float* next_x,
+                        float* next_f, int64_t* next_index, void* workspace,
+                        size_t workspace_bytes, void* stream);
+
 /* evox_nd_rank for callers that cannot allocate device memory: no workspace argument, and the
  * call itself allocates nothing (no cudaMalloc / cudaFree, no allocating library routine). It
  * has no counterpart in the reference. It is meant for hosts that only own the buffers they

@@ -126,7 +126,29 @@ def golden_nds(out: dict):
         out[f"{name}_sel_crowd"] = _np(scrowd)
 
 
-GENERATORS = {"pso": golden_pso, "nds": golden_nds}
+def golden_rvea(out: dict):
+    """ref_vec_guided on (a) the shape of the reference's own unit test (12 x 4, 5 vectors, one
+    NaN row), (b) 10 objectives with the 275 two-layer lattice vectors, (c) 3 objectives."""
+    from evox.operators.sampling import uniform_sampling
+    from evox.operators.selection import ref_vec_guided
+
+    g = torch.Generator().manual_seed(21)
+    cases = {}
+    f = torch.rand(12, 4, generator=g)
+    f[5] = float("nan")
+    cases["unit"] = (torch.rand(12, 6, generator=g), f, torch.rand(5, 4, generator=g), torch.tensor(0.5))
+    f = torch.rand(600, 10, generator=g) + 0.05 * torch.randn(600, 10, generator=g).abs()
+    cases["m10"] = (torch.rand(600, 19, generator=g), f, uniform_sampling(275, 10)[0], torch.tensor(0.25))
+    f = torch.rand(400, 3, generator=g)
+    f[17, 1] = float("nan")
+    cases["m3"] = (torch.rand(400, 5, generator=g), f, uniform_sampling(28, 3)[0], torch.tensor(0.81))
+    for name, (x, f, v, theta) in cases.items():
+        nx, nf = ref_vec_guided(x, f, v, theta)
+        out[f"{name}_x"], out[f"{name}_f"], out[f"{name}_v"], out[f"{name}_theta"] = _np(x), _np(f), _np(v), _np(theta)
+        out[f"{name}_next_x"], out[f"{name}_next_f"] = _np(nx), _np(nf)
+
+
+GENERATORS = {"pso": golden_pso, "nds": golden_nds, "rvea": golden_rvea}
 
 
 def main():
