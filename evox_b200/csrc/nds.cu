@@ -18,7 +18,8 @@
 //                              witness position: the scan of its row resumes where it last found an
 //                              unranked dominator and never goes back, so each row of Dt is read
 //                              once in total (n^2 / 8 bytes), not once per front as the reference
-//                              does. Fronts are separated by a bounded grid barrier.
+//                              does. A warp owns 32 columns; the mask is double buffered so one
+//                              bounded grid barrier separates two fronts.
 // Selection: histogram of ranks -> last admitted front -> per-objective stable radix sort of that
 // front -> neighbour gaps / range -> stable sorts by (rank) and (-crowding) -> gather.
 #include <math.h>
@@ -42,13 +43,13 @@ constexpr unsigned kSpinLimit = 1u << 22;  // grid-barrier polls before giving u
 struct Ctrl {
   unsigned bar_count;
   unsigned bar_gen;
-  unsigned remaining[2];
+  unsigned ranked[4];  // columns ranked in pass k, slot k & 3
   int status;        // 0 ok, 1 barrier timed out, 2 no progress
   int n_fronts;
   int worst_rank;    // last admitted front
   int n_before;      // rows with rank < worst_rank
   int n_last;        // rows with rank == worst_rank
-  int pad[7];
+  int pad[5];
 };
 
 struct Layout {
@@ -185,7 +186,7 @@ __global__ void __launch_bounds__(kThreads)
   }
 }
 
-__global__ void nds_peel_init_kernel(long long n, int wp, uint32_t* unranked, uint32_t* newfront, int* ptr, int* rank,
+__global__ void nds_peel_init_kernel(long long n, int wp, uint32_t* unranked, uint32_t* unranked_alt, int* ptr, int* rank,
                                      Ctrl* ctrl) {
   const long long t0 = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long stride = (long long)gridDim.x * blockDim.x;
@@ -195,7 +196,7 @@ __global__ void nds_peel_init_kernel(long long n, int wp, uint32_t* unranked, ui
     if (lo + 32 <= n) bits = 0xffffffffu;
     else if (lo < n) bits = (1u << (int)(n - lo)) - 1u;
     unranked[w] = bits;
-    newfront[w] = 0;
+    unranked_alt[w] = bits;
   }
   for (long long j = t0; j < n; j += stride) {
     ptr[j] = 0;
@@ -204,8 +205,7 @@ __global__ void nds_peel_init_kernel(long long n, int wp, uint32_t* unranked, ui
   if (t0 == 0) {
     ctrl->bar_count = 0;
     ctrl->bar_gen = 0;
-    ctrl->remaining[0] = 0;
-    ctrl->remaining[1] = 0;
+    for (int i = 0; i < 4; ++i) ctrl->ranked[i] = 0;
     ctrl->status = 0;
     ctrl->n_fronts = 0;
   }
@@ -229,7 +229,7 @@ __device__ __forceinline__ bool grid_barrier(Ctrl* ctrl, unsigned n_blocks) {
     } else {
       unsigned spins = 0;
       while (*gen_p == gen && *status_p == 0) {
-        __nanosleep(64);
+        __nanosleep(32);
         if (++spins > kSpinLimit) {
           atomicExch(&ctrl->status, 1);
           break;
@@ -243,79 +243,120 @@ __device__ __forceinline__ bool grid_barrier(Ctrl* ctrl, unsigned n_blocks) {
   return ok != 0;
 }
 
+// The mask snapshot lives in shared memory when it fits; otherwise it is read from L2 (never
+// through L1, which may hold the same buffer's contents of two passes ago).
+__device__ __forceinline__ uint32_t mask_word(const uint32_t* m, int i, int in_smem) {
+  return in_smem ? m[i] : __ldcg(m + i);
+}
+__device__ __forceinline__ uint4 mask_quad(const uint32_t* m, int i, int in_smem) {
+  return in_smem ? *reinterpret_cast<const uint4*>(m + i) : __ldcg(reinterpret_cast<const uint4*>(m + i));
+}
+
+__device__ __forceinline__ int first_nonzero(const uint4& v) {
+  return v.x ? 0 : (v.y ? 1 : (v.z ? 2 : (v.w ? 3 : -1)));
+}
+
+// Front k = unranked columns j whose row of Dt has no bit left under the unranked mask U.
+// A warp owns 32 consecutive columns (one word of U). Two copies of U alternate: pass k reads
+// U[k & 1] as a snapshot and the owner of a word writes its successor into U[(k + 1) & 1], so one
+// grid barrier per front is enough and no atomics touch the masks. Each lane first re-tests its
+// column's witness word (where the last scan stopped); only columns whose witness cleared are
+// scanned on, 1024 words per step with 128-bit loads, and never backwards: over all fronts a row of
+// Dt is read once.
 __global__ void __launch_bounds__(kThreads)
-    nds_peel_kernel(const uint32_t* __restrict__ Dt, int wp, long long n, uint32_t* unranked, uint32_t* newfront,
-                    int* ptr, int* rank, Ctrl* ctrl) {
+    nds_peel_kernel(const uint32_t* __restrict__ Dt, int wp, long long n, uint32_t* U0, uint32_t* U1, int* ptr,
+                    int* rank, Ctrl* ctrl, int mask_in_smem) {
+  extern __shared__ __align__(16) uint32_t s_mask[];
   __shared__ unsigned s_cnt[kThreads / 32];
   const int lane = threadIdx.x & 31;
   const long long gwarp = ((long long)blockIdx.x * kThreads + threadIdx.x) >> 5;
   const long long n_warps = ((long long)gridDim.x * kThreads) >> 5;
-  const long long gtid = (long long)blockIdx.x * kThreads + threadIdx.x;
-  const long long n_threads = (long long)gridDim.x * kThreads;
-  const int n_chunks = (wp + 31) / 32;
-  unsigned prev_remaining = (unsigned)n + 1u;
+  const long long n_words = (n + 31) >> 5;
+  long long remaining = n;
 
   for (int k = 0; k <= n; ++k) {
-    // ---- phase A: which unranked columns have no unranked dominator left? -------------------
-    for (long long j = gwarp; j < n; j += n_warps) {
-      int r = 0, c = 0;
-      if (lane == 0) {
-        r = __ldcg(rank + j);
-        c = __ldcg(ptr + j);
-      }
-      r = __shfl_sync(0xffffffffu, r, 0);
-      if (r >= 0) continue;
-      c = __shfl_sync(0xffffffffu, c, 0);
-      const uint32_t* row = Dt + j * wp;
+    const uint32_t* R = (k & 1) ? U1 : U0;
+    uint32_t* W = (k & 1) ? U0 : U1;
+    // this pass's snapshot of the unranked mask, staged in shared memory when it fits
+    const uint32_t* Rs = R;
+    if (mask_in_smem) {
+      for (int w = threadIdx.x * 4; w < wp; w += kThreads * 4)
+        *reinterpret_cast<uint4*>(s_mask + w) = __ldcg(reinterpret_cast<const uint4*>(R + w));
+      __syncthreads();
+      Rs = s_mask;
+    }
+    unsigned ranked_here = 0;
+    for (long long wj = gwarp; wj < n_words; wj += n_warps) {
+      const uint32_t own = mask_word(Rs, (int)wj, mask_in_smem);
+      const long long j = wj * 32 + lane;
+      const bool open = (own >> lane) & 1u;  // this lane's column is still unranked
+      int c = 0;
       bool blocked = false;
-      for (; c < n_chunks; ++c) {
-        const int w = c * 32 + lane;
-        uint32_t word = 0;
-        if (w < wp) word = __ldg(row + w) & __ldcg(unranked + w);
-        if (__any_sync(0xffffffffu, word != 0)) {
-          blocked = true;
-          break;
-        }
+      if (open) {
+        c = __ldcg(ptr + j);
+        blocked = (__ldg(Dt + j * wp + c) & mask_word(Rs, c, mask_in_smem)) != 0u;
       }
-      if (lane == 0) {
-        if (blocked) {
-          ptr[j] = c;
-        } else {
-          rank[j] = k;
-          atomicOr(newfront + (j >> 5), 1u << (int)(j & 31));
-        }
-      }
-    }
-    if (!grid_barrier(ctrl, gridDim.x)) return;
-    // ---- phase B: retire the front, count what is left ---------------------------------------
-    unsigned cnt = 0;
-    for (long long w = gtid; w < wp; w += n_threads) {
-      const uint32_t u = __ldcg(unranked + w) & ~__ldcg(newfront + w);
-      unranked[w] = u;
-      newfront[w] = 0;
-      cnt += __popc(u);
-    }
+      unsigned todo = __ballot_sync(0xffffffffu, open && !blocked);
+      unsigned newly = 0;
+      while (todo) {
+        const int l = __ffs(todo) - 1;
+        todo &= todo - 1;
+        const long long jl = wj * 32 + l;
+        const int cl = __shfl_sync(0xffffffffu, c, l);
+        const uint4* row4 = reinterpret_cast<const uint4*>(Dt + jl * wp);
+        int found = -1;
+        // 1024 words per step: eight independent 128-bit loads per lane are in flight together
+        for (int base = (cl & ~1023); base < wp && found < 0; base += 1024) {
+          uint4 d[8];
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, off);
-    if (lane == 0) s_cnt[threadIdx.x >> 5] = cnt;
+          for (int q = 0; q < 8; ++q) {
+            const int w = base + q * 128 + lane * 4;
+            d[q] = (w < wp) ? __ldg(row4 + (w >> 2)) : make_uint4(0, 0, 0, 0);
+          }
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            const int w = base + q * 128 + lane * 4;
+            int f = -1;
+            if (w < wp) {
+              const uint4 u = mask_quad(Rs, w, mask_in_smem);
+              f = first_nonzero(make_uint4(d[q].x & u.x, d[q].y & u.y, d[q].z & u.z, d[q].w & u.w));
+            }
+            const unsigned m = __ballot_sync(0xffffffffu, f >= 0);
+            if (m && found < 0) {
+              const int src = __ffs(m) - 1;
+              found = base + q * 128 + src * 4 + __shfl_sync(0xffffffffu, f, src);
+            }
+          }
+        }
+        if (found >= 0) {
+          if (lane == 0) ptr[jl] = found;
+        } else {
+          newly |= 1u << l;
+          if (lane == 0) rank[jl] = k;
+        }
+      }
+      if (lane == 0) W[wj] = own & ~newly;
+      ranked_here += __popc(newly);
+    }
+    if (lane == 0) s_cnt[threadIdx.x >> 5] = ranked_here;
     __syncthreads();
     if (threadIdx.x == 0) {
       unsigned tot = 0;
       for (int i = 0; i < kThreads / 32; ++i) tot += s_cnt[i];
-      if (tot) atomicAdd(&ctrl->remaining[k & 1], tot);
-      if (blockIdx.x == 0) ctrl->remaining[(k + 1) & 1] = 0;
+      if (tot) atomicAdd(&ctrl->ranked[k & 3], tot);
+      if (blockIdx.x == 0) ctrl->ranked[(k + 2) & 3] = 0;  // last read two barriers ago
     }
     if (!grid_barrier(ctrl, gridDim.x)) return;
-    const unsigned rem = *((volatile unsigned*)&ctrl->remaining[k & 1]);
-    if (rem == 0) {
-      if (gtid == 0) ctrl->n_fronts = k + 1;
+    const unsigned got = *((volatile unsigned*)&ctrl->ranked[k & 3]);
+    remaining -= got;
+    if (remaining <= 0) {
+      if (blockIdx.x == 0 && threadIdx.x == 0) ctrl->n_fronts = k + 1;
       return;
     }
-    if (rem >= prev_remaining) {  // dominance is a strict partial order: every pass must rank someone
-      if (gtid == 0) atomicExch(&ctrl->status, 2);
+    if (got == 0) {  // dominance is a strict partial order: every pass must rank someone
+      if (blockIdx.x == 0 && threadIdx.x == 0) atomicExch(&ctrl->status, 2);
       return;
     }
-    prev_remaining = rem;
   }
 }
 
@@ -717,17 +758,24 @@ int run_rank(const float* f, long long n, int m, int* rank, void* ws, const Layo
   EVOX_LAUNCH_CHECK();
   // persistent cooperative grid: every block must be resident for the grid barrier
   int per_sm = 0;
-  EVOX_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, nds_peel_kernel, kThreads, 0));
+  size_t mask_bytes = sizeof(uint32_t) * (size_t)L.wp;
+  int mask_in_smem = mask_bytes <= 64 * 1024 ? 1 : 0;  // larger masks are read through L2
+  if (!mask_in_smem) mask_bytes = 0;
+  if (mask_bytes > 40 * 1024) {
+    EVOX_CUDA(cudaFuncSetAttribute(nds_peel_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
+  }
+  EVOX_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, nds_peel_kernel, kThreads, mask_bytes));
   EVOX_REQUIRE(per_sm > 0, EVOX_ERR_CUDA, "nds_peel_kernel cannot be made resident");
   if (per_sm > 4) per_sm = 4;
   long long blocks = (long long)sm_count() * per_sm;
-  const long long useful = (n * 32 + kThreads - 1) / kThreads;  // one warp per column
+  const long long useful = ((n + 31) / 32 + kThreads / 32 - 1) / (kThreads / 32);  // one warp per 32 columns
   if (blocks > useful) blocks = useful < 1 ? 1 : useful;
   const uint32_t* Dt_c = Dt;
   int wp = L.wp;
   long long nn = n;
-  void* args[] = {(void*)&Dt_c, (void*)&wp, (void*)&nn, (void*)&unranked, (void*)&newfront, (void*)&ptr, (void*)&rank, (void*)&ctrl};
-  EVOX_CUDA(cudaLaunchCooperativeKernel((const void*)nds_peel_kernel, dim3((unsigned)blocks), dim3(kThreads), args, 0, s));
+  void* args[] = {(void*)&Dt_c, (void*)&wp, (void*)&nn, (void*)&unranked, (void*)&newfront, (void*)&ptr, (void*)&rank, (void*)&ctrl,
+                  (void*)&mask_in_smem};
+  EVOX_CUDA(cudaLaunchCooperativeKernel((const void*)nds_peel_kernel, dim3((unsigned)blocks), dim3(kThreads), args, mask_bytes, s));
   return EVOX_OK;
 }
 

@@ -148,7 +148,77 @@ def golden_rvea(out: dict):
         out[f"{name}_next_x"], out[f"{name}_next_f"] = _np(nx), _np(nf)
 
 
-GENERATORS = {"pso": golden_pso, "nds": golden_nds, "rvea": golden_rvea}
+def golden_es(out: dict):
+    """Philox streams, LoRA factors / delta / gradient, one VirtualLoRAES step and one OpenES step."""
+    from evox.algorithms import OpenES
+    from evox.algorithms.so.es_variants.virtual_lora_es import VirtualLoRAES
+    from evox.triton_kernels.kernels.lora_noise import (
+        compute_counter_offsets, generate_lora_factors, lora_delta_output, lora_gradient)
+    from evox.triton_kernels.kernels.philox import philox_normal, philox_uniform
+
+    g = torch.Generator().manual_seed(5)
+    seeds = torch.randint(0, 2**31, (6,), generator=g, dtype=torch.int64)
+    seeds[1] = (3 << 32) + 12345  # exercises the high key word
+    out["seeds"] = _np(seeds)
+    for n, counter in ((10, 0), (7, 5), (64, (1 << 31) - 40), (33, (7 << 32) + 9)):
+        out[f"uniform_n{n}_c{counter}"] = _np(philox_uniform(seeds, n, counter))
+        out[f"normal_n{n}_c{counter}"] = _np(philox_normal(seeds, n, counter))
+    shapes = [(10,), (4, 3), (2, 5)]
+    out["offsets_kat"] = np.asarray(compute_counter_offsets(shapes, 2))  # == [0, 12, 28] in the reference's test
+    a, b = generate_lora_factors(seeds, (12, 20), 4, 40)
+    out["factors_A"], out["factors_B"] = _np(a), _np(b)
+    x = torch.randn(6, 5, 20, generator=g)
+    out["delta_x"] = _np(x)
+    out["delta_out"] = _np(lora_delta_output(x, a, b, 0.1))
+    fit = torch.randn(6, generator=g)
+    out["grad_fitness"] = _np(fit)
+    out["grad_out"] = _np(lora_gradient(fit, a, b, 6, 0.1, (12, 20)))
+    noise = generate_lora_factors(seeds, (9,), 4, 3)
+    out["bias_noise"] = _np(noise)
+    out["grad_bias"] = _np(lora_gradient(fit, noise, None, 6, 0.1, (9,)))
+
+    # VirtualLoRAES.step with the seeds fixed and a quadratic fitness on the perturbed weights
+    import evox.algorithms.so.es_variants.virtual_lora_es as vmod
+
+    shapes = [(8, 6), (8,), (3, 8), (3,)]
+    dim = sum(int(np.prod(s)) for s in shapes)
+    for opt in (None, "adam"):
+        center = torch.randn(dim, generator=g) * 0.3
+        algo = VirtualLoRAES(shapes, 2, 10, center.clone(), 0.05, 0.1, optimizer=opt)
+        step_seeds = torch.randint(0, 2**31, (10,), generator=g, dtype=torch.int64)
+        fitness = torch.randn(10, generator=g)
+        algo.evaluate = lambda payload, fitness=fitness: fitness
+        real = vmod.torch.randint
+        vmod.torch.randint = lambda *a, **k: step_seeds
+        try:
+            algo.step()
+        finally:
+            vmod.torch.randint = real
+        tag = f"vlora_{opt}"
+        out[f"{tag}_center0"], out[f"{tag}_seeds"], out[f"{tag}_fitness"] = _np(center), _np(step_seeds), _np(fitness)
+        out[f"{tag}_center1"] = _np(algo.center)
+        if opt:
+            out[f"{tag}_exp_avg"], out[f"{tag}_exp_avg_sq"] = _np(algo.exp_avg), _np(algo.exp_avg_sq)
+
+    # OpenES.step with the normal draws fixed, sphere fitness
+    import evox.algorithms.so.es_variants.open_es as omod
+
+    for opt in (None, "adam"):
+        center = torch.randn(12, generator=g)
+        algo = OpenES(8, center.clone(), 0.05, 0.1, optimizer=opt)
+        noise = torch.randn(4, 12, generator=g)
+        algo.evaluate = lambda pop: (pop**2).sum(dim=1)
+        real = omod.torch.randn
+        omod.torch.randn = lambda *a, **k: noise
+        try:
+            algo.step()
+        finally:
+            omod.torch.randn = real
+        tag = f"openes_{opt}"
+        out[f"{tag}_center0"], out[f"{tag}_noise"], out[f"{tag}_center1"] = _np(center), _np(noise), _np(algo.center)
+
+
+GENERATORS = {"pso": golden_pso, "nds": golden_nds, "rvea": golden_rvea, "es": golden_es}
 
 
 def main():
