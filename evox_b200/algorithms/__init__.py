@@ -1,3 +1,4 @@
+from .es import OpenES, VirtualLoRAES
 from .pso import PSO
 
-__all__ = ["PSO"]
+__all__ = ["PSO", "OpenES", "VirtualLoRAES"]

@@ -1,0 +1,141 @@
+"""OpenES and VirtualLoRAES with the reference's constructor arguments and state names
+(evox/algorithms/so/es_variants/open_es.py:10-86, virtual_lora_es.py:18-138)."""
+
+from __future__ import annotations
+
+from typing import Literal
+
+import torch
+
+from .. import _cabi
+from ..core import Algorithm, Mutable, Parameter
+from ..lora_kernels import compute_counter_offsets, generate_lora_factors, lora_gradient
+
+
+def _update_center(algo, grad: torch.Tensor) -> None:
+    dev = algo.center.device
+    adam = algo.optimizer == "adam"
+    _cabi.check(
+        _cabi.lib.evox_es_update(
+            _cabi.ptr(algo.center, torch.float32, "center"), _cabi.ptr(grad, torch.float32, "grad"),
+            _cabi.ptr(algo.learning_rate, torch.float32, "learning_rate"),
+            _cabi.ptr(algo.exp_avg) if adam else None, _cabi.ptr(algo.exp_avg_sq) if adam else None,
+            _cabi.ptr(algo.beta1) if adam else None, _cabi.ptr(algo.beta2) if adam else None,
+            1e-8, algo.center.numel(), _cabi.stream_ptr(dev),
+        )
+    )
+
+
+class _ESBase(Algorithm):
+    def _common_init(self, pop_size, center_init, learning_rate, noise_stdev, optimizer, device):
+        assert noise_stdev > 0, "noise_stdev must be greater than 0."
+        assert learning_rate > 0, "learning_rate must be greater than 0."
+        assert pop_size > 0, "pop_size must be greater than 0."
+        assert optimizer in [None, "adam"], "optimizer must be None or 'adam'."
+        self.learning_rate = Parameter(learning_rate, dtype=torch.float32, device=device)
+        self.noise_stdev = Parameter(noise_stdev, dtype=torch.float32, device=device)
+        self._sigma_host = float(noise_stdev)
+        self.pop_size = pop_size
+        self.optimizer = optimizer
+        self.center = Mutable(center_init.to(device=device, dtype=torch.float32).contiguous().clone())
+        if optimizer == "adam":
+            self.exp_avg = Mutable(torch.zeros_like(self.center))
+            self.exp_avg_sq = Mutable(torch.zeros_like(self.center))
+            self.beta1 = Parameter(0.9, dtype=torch.float32, device=device)
+            self.beta2 = Parameter(0.999, dtype=torch.float32, device=device)
+
+    def sigma(self) -> float:
+        """Host copy of noise_stdev; refreshed (one sync) only when the parameter was modified."""
+        ver = self.noise_stdev._version
+        if getattr(self, "_sigma_version", None) != ver:
+            self._sigma_host = float(self.noise_stdev)
+            self._sigma_version = ver
+        return self._sigma_host
+
+    def record_step(self):
+        return {"center": self.center}
+
+
+class OpenES(_ESBase):
+    """OpenAI-ES: mirrored Gaussian sampling, score-function gradient, SGD or Adam."""
+
+    def __init__(
+        self,
+        pop_size: int,
+        center_init: torch.Tensor,
+        learning_rate: float,
+        noise_stdev: float,
+        optimizer: Literal["adam"] | None = None,
+        mirrored_sampling: bool = True,
+        device: torch.device | None = None,
+    ):
+        super().__init__()
+        device = torch.get_default_device() if device is None else torch.device(device)
+        if mirrored_sampling is True:
+            assert pop_size % 2 == 0, "When mirrored_sampling is True, pop_size must be a multiple of 2."
+        self._common_init(pop_size, center_init, learning_rate, noise_stdev, optimizer, device)
+        self.dim = center_init.shape[0]
+        self.mirrored_sampling = mirrored_sampling
+
+    def step(self, noise: torch.Tensor | None = None):
+        """One generation (open_es.py:60-83). `noise`: optional (pop/2 or pop, dim) standard-normal
+        draws; by default they come from torch.randn like the reference's."""
+        dev = self.center.device
+        rows = self.pop_size // 2 if self.mirrored_sampling else self.pop_size
+        if noise is None:
+            noise = torch.randn(rows, self.dim, device=dev)
+        noise = noise.to(torch.float32).contiguous()
+        assert noise.shape == (rows, self.dim)
+        pop = torch.empty(self.pop_size, self.dim, dtype=torch.float32, device=dev)
+        lib, s = _cabi.lib, _cabi.stream_ptr(dev)
+        _cabi.check(lib.evox_openes_ask(_cabi.ptr(self.center), _cabi.ptr(noise), _cabi.ptr(self.noise_stdev), self.pop_size, self.dim, rows, _cabi.ptr(pop), s))
+        fitness = self.evaluate(pop).to(torch.float32).contiguous()
+        grad = torch.empty(self.dim, dtype=torch.float32, device=dev)
+        _cabi.check(lib.evox_openes_gradient(_cabi.ptr(noise), _cabi.ptr(fitness), self.pop_size, self.dim, rows, self.sigma(), _cabi.ptr(grad), s))
+        _update_center(self, grad)
+
+
+class VirtualLoRAES(_ESBase):
+    """ES over a virtual population: only the centre and one int64 seed per individual exist;
+    perturbations are rank-r factors regenerated from the seeds."""
+
+    def __init__(
+        self,
+        param_shapes: list[tuple],
+        lora_rank: int,
+        pop_size: int,
+        center_init: torch.Tensor,
+        learning_rate: float,
+        noise_stdev: float,
+        optimizer: Literal["adam"] | None = None,
+        device: torch.device | None = None,
+    ):
+        super().__init__()
+        device = torch.get_default_device() if device is None else torch.device(device)
+        assert lora_rank > 0, "lora_rank must be greater than 0."
+        self._common_init(pop_size, center_init, learning_rate, noise_stdev, optimizer, device)
+        self.param_shapes = [tuple(s) for s in param_shapes]
+        self.lora_rank = lora_rank
+        self.dim = sum(int(torch.tensor(s).prod()) for s in self.param_shapes)
+        self.counter_offsets = compute_counter_offsets(self.param_shapes, lora_rank)
+        assert center_init.shape[0] == self.dim, (
+            "center_init length must equal the total number of parameters (sum of element counts over param_shapes)."
+        )
+        self.seeds = Mutable(torch.randint(0, 2**31, (pop_size,), device=device, dtype=torch.int64))
+
+    def step(self, seeds: torch.Tensor | None = None):
+        """One generation (virtual_lora_es.py:90-135). `seeds`: optional int64 (pop,) to use
+        instead of fresh torch.randint draws."""
+        dev = self.center.device
+        self.seeds = torch.randint(0, 2**31, (self.pop_size,), device=dev, dtype=torch.int64) if seeds is None else seeds.to(dev)
+        sigma = self.sigma()
+        fitness = self.evaluate((self.center, self.seeds, sigma)).to(torch.float32).contiguous()
+        parts = []
+        for shape, offset in zip(self.param_shapes, self.counter_offsets):
+            factors = generate_lora_factors(self.seeds, shape, self.lora_rank, offset)
+            if isinstance(factors, tuple):
+                a, b = factors
+                parts.append(lora_gradient(fitness, a, b, self.pop_size, sigma, shape).reshape(-1))
+            else:
+                parts.append(lora_gradient(fitness, factors, None, self.pop_size, sigma, shape).reshape(-1))
+        _update_center(self, torch.cat(parts))

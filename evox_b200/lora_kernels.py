@@ -1,0 +1,112 @@
+"""Philox streams and virtual-LoRA operators on the CUDA kernels.
+
+Same function names, argument order and shapes as the reference's `evox.triton_kernels`
+(kernels/philox.py:274-311, kernels/lora_noise.py:58-196).
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import _cabi
+
+__all__ = [
+    "philox_uniform", "philox_normal", "compute_counter_offsets", "generate_lora_factors",
+    "lora_delta_output", "lora_gradient",
+]
+
+
+def _seeds(seeds: torch.Tensor) -> torch.Tensor:
+    if seeds.ndim != 1 or seeds.dtype != torch.int64:
+        raise _cabi.EvoxKernelError("seeds must be a 1-D int64 tensor")
+    return seeds.contiguous()
+
+
+def _fill(fn, seeds: torch.Tensor, n: int, counter: int) -> torch.Tensor:
+    seeds = _seeds(seeds)
+    out = torch.empty(seeds.shape[0], n, dtype=torch.float32, device=seeds.device)
+    if out.numel():
+        _cabi.check(fn(_cabi.ptr(seeds), seeds.shape[0], n, counter & (2**64 - 1), _cabi.ptr(out), _cabi.stream_ptr(seeds.device)))
+    return out
+
+
+def philox_uniform(seeds: torch.Tensor, n: int, counter: int = 0) -> torch.Tensor:
+    """(pop, n) uniforms in [0, 1) from per-individual Philox4x32-10 streams."""
+    return _fill(_cabi.lib.evox_philox_uniform, seeds, n, counter)
+
+
+def philox_normal(seeds: torch.Tensor, n: int, counter: int = 0) -> torch.Tensor:
+    """(pop, n) standard normals (Box-Muller on the uniform stream)."""
+    return _fill(_cabi.lib.evox_philox_normal, seeds, n, counter)
+
+
+def _ceil4(x: int) -> int:
+    return (x + 3) // 4 * 4
+
+
+def _as_2d(shape) -> tuple[int, int]:
+    return int(math.prod(shape[:-1])), int(shape[-1])
+
+
+def compute_counter_offsets(param_shapes: list[tuple], lora_rank: int) -> list[int]:
+    """Disjoint Philox counter ranges for a list of parameter blocks (host arithmetic)."""
+    offsets, cur = [], 0
+    for shape in param_shapes:
+        offsets.append(cur)
+        if len(shape) == 1:
+            n = shape[0]
+        else:
+            d, k = _as_2d(shape)
+            n = lora_rank * k + d * lora_rank
+        cur += _ceil4(n)
+    return offsets
+
+
+def generate_lora_factors(seeds: torch.Tensor, weight_shape: tuple, rank: int, counter: int):
+    """Flat noise (pop, n) for a 1-D block; (A (pop, r, k), B (pop, d, r)) otherwise."""
+    pop = seeds.shape[0]
+    if len(weight_shape) == 1:
+        return philox_normal(seeds, weight_shape[0], counter)
+    d, k = _as_2d(weight_shape)
+    a = philox_normal(seeds, rank * k, counter).reshape(pop, rank, k)
+    b = philox_normal(seeds, d * rank, counter + _ceil4(rank * k)).reshape(pop, d, rank)
+    return a, b
+
+
+def lora_delta_output(x: torch.Tensor, A: torch.Tensor, B: torch.Tensor, sigma: float) -> torch.Tensor:
+    """sigma * (x @ A^T) @ B^T for x (pop, batch, k), A (pop, r, k), B (pop, d, r)."""
+    x, A, B = x.float().contiguous(), A.float().contiguous(), B.float().contiguous()
+    pop, batch, k = x.shape
+    r, d = A.shape[1], B.shape[1]
+    if A.shape != (pop, r, k) or B.shape != (pop, d, r):
+        raise _cabi.EvoxKernelError(f"shape mismatch: x {tuple(x.shape)}, A {tuple(A.shape)}, B {tuple(B.shape)}")
+    out = torch.empty(pop, batch, d, dtype=torch.float32, device=x.device)
+    t = torch.empty(pop, batch, r, dtype=torch.float32, device=x.device)
+    _cabi.check(
+        _cabi.lib.evox_lora_delta_output(
+            _cabi.ptr(x), _cabi.ptr(A), _cabi.ptr(B), float(sigma), pop, batch, k, r, d, _cabi.ptr(out), _cabi.ptr(t),
+            _cabi.stream_ptr(x.device),
+        )
+    )
+    return out
+
+
+def lora_gradient(fitness: torch.Tensor, A: torch.Tensor, B: torch.Tensor | None, pop_size: int, sigma, weight_shape: tuple) -> torch.Tensor:
+    """Population gradient of one parameter block, reshaped to `weight_shape`."""
+    fitness = fitness.float().contiguous()
+    A = A.float().contiguous()
+    sigma = float(sigma)
+    dev = fitness.device
+    if B is None:
+        n = A.shape[1]
+        grad = torch.empty(n, dtype=torch.float32, device=dev)
+        _cabi.check(_cabi.lib.evox_lora_gradient(_cabi.ptr(fitness), _cabi.ptr(A), None, pop_size, sigma, 1, n, 1, _cabi.ptr(grad), _cabi.stream_ptr(dev)))
+    else:
+        B = B.float().contiguous()
+        r, k = A.shape[1], A.shape[2]
+        d = B.shape[1]
+        grad = torch.empty(d, k, dtype=torch.float32, device=dev)
+        _cabi.check(_cabi.lib.evox_lora_gradient(_cabi.ptr(fitness), _cabi.ptr(A), _cabi.ptr(B), pop_size, sigma, d, k, r, _cabi.ptr(grad), _cabi.stream_ptr(dev)))
+    return grad.reshape(weight_shape)

@@ -1,3 +1,4 @@
 from . import numerical
+from .virtual_lora_problem import VirtualLoRAProblem
 
-__all__ = ["numerical"]
+__all__ = ["numerical", "VirtualLoRAProblem"]

@@ -1,0 +1,142 @@
+"""Fitness of a virtual LoRA-perturbed population of an `nn.Sequential` of Linear layers.
+
+Same constructor and payload protocol as the reference's `VirtualLoRAProblem`
+(evox/problems/neuroevolution/virtual_lora_problem.py:33-272): `evaluate` receives
+`(center_flat, seeds, sigma)`; weights are slices of the flat centre in `named_parameters()`
+order; per layer `h <- act(h W^T + b + sigma (h A^T) B^T + sigma * bias_noise)` with the factors
+regenerated from the seeds. Inputs may be one shared batch (batch, in) as in the reference, or one
+batch per individual (pop, batch, in).
+"""
+
+from __future__ import annotations
+
+import warnings
+
+import torch
+from torch import nn
+
+from .. import _cabi
+from ..core import Problem
+from ..lora_kernels import compute_counter_offsets, generate_lora_factors
+
+__all__ = ["VirtualLoRAProblem"]
+
+_ACTIVATIONS = (nn.ReLU, nn.Tanh, nn.Sigmoid, nn.GELU, nn.LeakyReLU, nn.ELU, nn.Softmax, nn.Identity)
+
+
+class VirtualLoRAProblem(Problem):
+    def __init__(self, model: nn.Sequential, data_loader, criterion, lora_rank: int, n_batch_per_eval: int = 1,
+                 device: torch.device | None = None, reduction: str = "mean"):
+        super().__init__()
+        if not isinstance(model, nn.Sequential):
+            raise TypeError(f"VirtualLoRAProblem requires an nn.Sequential model, got {type(model).__name__}.")
+        self.device = torch.get_default_device() if device is None else torch.device(device)
+        self.model = model
+        self.data_loader = data_loader
+        self.data_loader_iter = iter(data_loader)
+        self.criterion = criterion
+        self.lora_rank = lora_rank
+        self.n_batch_per_eval = n_batch_per_eval
+        self.reduction = reduction
+        named = list(model.named_parameters())
+        self.param_names = [n for n, _ in named]
+        self.param_shapes = [tuple(p.shape) for _, p in named]
+        self.counter_offsets = compute_counter_offsets(self.param_shapes, lora_rank)
+        starts, cur = [], 0
+        for shape in self.param_shapes:
+            starts.append(cur)
+            cur += int(torch.tensor(shape).prod())
+        self._starts = starts
+        self.dim = cur
+        for module in model.children():
+            if not isinstance(module, (nn.Linear, *_ACTIVATIONS)):
+                raise NotImplementedError(
+                    f"Layer type {type(module).__name__} is not supported by VirtualLoRAProblem. Supported types: "
+                    "nn.Linear and common activation modules (ReLU, Tanh, Sigmoid, GELU, LeakyReLU, ELU, Softmax, Identity)."
+                )
+
+    def _param(self, center: torch.Tensor, name: str) -> tuple[torch.Tensor, int]:
+        i = self.param_names.index(name)
+        n = int(torch.tensor(self.param_shapes[i]).prod())
+        return center[self._starts[i] : self._starts[i] + n].view(self.param_shapes[i]), i
+
+    def _virtual_forward(self, inputs: torch.Tensor, center: torch.Tensor, seeds: torch.Tensor, sigma: float, pop_size: int) -> torch.Tensor:
+        dev = center.device
+        shared = inputs.ndim == 2
+        h = inputs.to(device=dev, dtype=torch.float32).contiguous()
+        batch = h.shape[-2]
+        children = list(self.model.named_children())
+        lib, s = _cabi.lib, _cabi.stream_ptr(dev)
+        skip = False
+        for pos, (name, module) in enumerate(children):
+            if skip:
+                skip = False
+                continue
+            if isinstance(module, nn.Linear):
+                weight, wi = self._param(center, f"{name}.weight")
+                d, k = weight.shape
+                a, b = generate_lora_factors(seeds, (d, k), self.lora_rank, self.counter_offsets[wi])
+                bias = bias_noise = None
+                if module.bias is not None:
+                    bias, bi = self._param(center, f"{name}.bias")
+                    bias_noise = generate_lora_factors(seeds, (d,), self.lora_rank, self.counter_offsets[bi])
+                t = torch.empty(pop_size, batch, self.lora_rank, dtype=torch.float32, device=dev)
+                _cabi.check(lib.evox_lora_down(_cabi.ptr(h), int(shared), _cabi.ptr(a), pop_size, batch, k, self.lora_rank, _cabi.ptr(t), s))
+                relu = pos + 1 < len(children) and isinstance(children[pos + 1][1], nn.ReLU)
+                out = torch.empty(pop_size, batch, d, dtype=torch.float32, device=dev)
+                _cabi.check(
+                    lib.evox_lora_linear_forward(
+                        _cabi.ptr(h), int(shared), _cabi.ptr(weight.contiguous()), _cabi.ptr(bias), _cabi.ptr(t), _cabi.ptr(b),
+                        _cabi.ptr(bias_noise), float(sigma), pop_size, batch, k, d, self.lora_rank, int(relu), _cabi.ptr(out), s,
+                    )
+                )
+                h, shared, skip = out, False, relu
+            else:
+                if shared:
+                    h = h.unsqueeze(0).expand(pop_size, -1, -1).contiguous()
+                    shared = False
+                h = module(h)
+        if shared:
+            h = h.unsqueeze(0).expand(pop_size, -1, -1).contiguous()
+        return h
+
+    def evaluate(self, payload) -> torch.Tensor:
+        center_flat, seeds, sigma = payload
+        pop_size = seeds.shape[0]
+        center = center_flat.to(torch.float32).contiguous()
+        if self.n_batch_per_eval == -1:
+            batches = list(self.data_loader)
+        else:
+            batches = []
+            for _ in range(self.n_batch_per_eval):
+                try:
+                    batches.append(next(self.data_loader_iter))
+                except StopIteration:
+                    self.data_loader_iter = iter(self.data_loader)
+                    batches.append(next(self.data_loader_iter))
+        per_individual = []
+        for inputs, labels in batches:
+            inputs = inputs.to(device=self.device, non_blocking=True)
+            labels = labels.to(device=self.device, non_blocking=True)
+            logits = self._virtual_forward(inputs, center, seeds, sigma, pop_size)
+            batch = logits.shape[1]
+            flat_logits = logits.reshape(pop_size * batch, -1)
+            if labels.ndim == 1:  # class labels shared by the population (virtual_lora_problem.py:247)
+                flat_labels = labels.unsqueeze(0).expand(pop_size, -1).reshape(-1)
+            else:  # regression targets (batch, out) shared by the population
+                flat_labels = labels.unsqueeze(0).expand(pop_size, *labels.shape).reshape(pop_size * batch, -1)
+            flat_loss = self.criterion(flat_logits, flat_labels)
+            if flat_loss.ndim == 0:
+                warnings.warn(
+                    "Criterion output is a scalar. We recommend setting `reduction` to 'none' "
+                    "for the criterion and letting VirtualLoRAProblem handle the reduction."
+                )
+                loss = flat_loss.expand(pop_size)
+            else:
+                if flat_loss.ndim == 2:
+                    flat_loss = flat_loss.mean(dim=1)
+                per_sample = flat_loss.reshape(pop_size, batch)
+                loss = per_sample.mean(dim=1) if self.reduction == "mean" else per_sample.sum(dim=1)
+            per_individual.append(loss)
+        losses = torch.stack(per_individual, dim=1)
+        return losses.mean(dim=1) if self.reduction == "mean" else losses.sum(dim=1)

@@ -166,6 +166,67 @@ int evox_ref_vec_guided(const float* x, int64_t dx, const float* f, int64_t n, i
                         float* next_f, int64_t* next_index, void* workspace,
                         size_t workspace_bytes, void* stream);
 
+/* ------------------------------------------------------------------------------------------
+ * P4. Evolution strategies: Philox streams, virtual LoRA population, OpenES.
+ * ------------------------------------------------------------------------------------------ */
+
+/* out (pop x n, fp32): per-individual Philox4x32-10 streams, key = int64 seed split low / high,
+ * counter low word + call index (no carry into the high word), 24-bit uniforms in [0, 1).
+ * Replaces philox_uniform (triton_kernels/kernels/philox.py:52-84, Triton kernel :134-246). */
+int evox_philox_uniform(const int64_t* seeds, int64_t pop, int64_t n, uint64_t counter, float* out,
+                        void* stream);
+
+/* Standard normals by Box-Muller on consecutive uniform pairs of the same streams.
+ * Replaces philox_normal (philox.py:87-112). */
+int evox_philox_normal(const int64_t* seeds, int64_t pop, int64_t n, uint64_t counter, float* out,
+                       void* stream);
+
+/* t (pop x batch x r) = x A^T per individual; x is (pop x batch x k), or (batch x k) shared by
+ * all individuals when x_is_shared != 0; A is (pop x r x k). First half of lora_delta_output
+ * (triton_kernels/kernels/lora_noise.py:151). */
+int evox_lora_down(const float* x, int32_t x_is_shared, const float* A, int64_t pop, int64_t batch,
+                   int64_t k, int32_t r, float* t, void* stream);
+
+/* out (pop x batch x d) = sigma * (x A^T) B^T with B (pop x d x r). Replaces lora_delta_output
+ * (lora_noise.py:130-154). t_scratch: pop * batch * r floats. sigma is a host value, as in the
+ * reference's signature. */
+int evox_lora_delta_output(const float* x, const float* A, const float* B, float sigma, int64_t pop,
+                           int64_t batch, int64_t k, int32_t r, int64_t d, float* out,
+                           float* t_scratch, void* stream);
+
+/* grad (d x k) = sum_i fitness_i B_i A_i / (pop * sigma); with B == NULL, A is the (pop x k)
+ * noise of a 1-D block and grad (k) = fitness A / (pop * sigma). Replaces lora_gradient
+ * (lora_noise.py:157-196). */
+int evox_lora_gradient(const float* fitness, const float* A, const float* B, int64_t pop, float sigma,
+                       int64_t d, int64_t k, int32_t r, float* grad, void* stream);
+
+/* One Linear layer of the virtual-population forward pass, fp32
+ * (problems/neuroevolution/virtual_lora_problem.py:160-193):
+ *   out = act(h W^T + bias + sigma * t B^T + sigma * bias_noise), act = ReLU if relu != 0.
+ * h: (pop x batch x k) or shared (batch x k); W: (d x k); bias, bias_noise (pop x d): optional;
+ * t (pop x batch x r) = h A^T from evox_lora_down and B (pop x d x r): both or neither. */
+int evox_lora_linear_forward(const float* h, int32_t h_is_shared, const float* W, const float* bias,
+                             const float* t, const float* B, const float* bias_noise, float sigma,
+                             int64_t pop, int64_t batch, int64_t k, int64_t d, int32_t r, int32_t relu,
+                             float* out, void* stream);
+
+/* population (pop x dim) = center + sigma * noise, where noise is (noise_rows x dim) and rows
+ * noise_rows.. reuse it negated when noise_rows == pop / 2 (mirrored sampling).
+ * First half of OpenES.step (algorithms/so/es_variants/open_es.py:62-68). sigma: device scalar. */
+int evox_openes_ask(const float* center, const float* noise, const float* sigma, int64_t pop,
+                    int64_t dim, int64_t noise_rows, float* population, void* stream);
+
+/* grad (dim) = noise^T fitness / pop / sigma (open_es.py:70), same mirrored convention. */
+int evox_openes_gradient(const float* noise, const float* fitness, int64_t pop, int64_t dim,
+                         int64_t noise_rows, float sigma, float* grad, void* stream);
+
+/* center -= lr * grad (open_es.py:71-72, virtual_lora_es.py:123-124), or with exp_avg /
+ * exp_avg_sq given the reference's Adam (es_variants/adam_step.py:4-26: no bias correction).
+ * learning_rate, beta1, beta2 are device scalars; the state is updated in place. */
+int evox_es_update(float* center, const float* grad, const float* learning_rate, float* exp_avg,
+                   float* exp_avg_sq, const float* beta1, const float* beta2, float eps, int64_t dim,
+                   void* stream);
+
 /* evox_nd_rank for callers that cannot allocate device memory: no workspace argument, and the
  * call itself allocates nothing (no cudaMalloc / cudaFree, no allocating library routine). It
  * has no counterpart in the reference. It is meant for hosts that only own the buffers they

@@ -134,5 +134,6 @@ def open_es_step(center, noise_half, fitness_fn, lr, sigma, mirrored=True, adam_
     grad = noise.T @ fitness / noise.shape[0] / sigma
     if adam_state is None:
         return center - lr * grad, fitness, grad
-    new_center, m, v = adam_single_tensor(center, grad, adam_state[0], adam_state[1], lr=lr)
+    # the reference holds beta1 / beta2 as float32 tensors (open_es.py:57-58), so 1 - beta is rounded in fp32
+    new_center, m, v = adam_single_tensor(center, grad, adam_state[0], adam_state[1], torch.tensor(0.9), torch.tensor(0.999), lr)
     return new_center, fitness, grad, (m, v)
