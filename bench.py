@@ -386,17 +386,87 @@ def run_nds(args):
     print(json.dumps(line), flush=True)
 
 
+def run_lora_es(args):
+    """Secondary workload: BASELINE configs[3] — VirtualLoRAES over a 3 x (4096 -> 4096) bf16 MLP,
+    1,024 individuals with their own 64 x 4096 batch, rank-8 factors, sigma 0.02, lr 0.01, centred
+    ranks, SGD. One step = seeds -> forward (tensor cores) -> fitness -> gradient -> centre update,
+    through StdWorkflow.step()."""
+    from torch import nn
+
+    from evox_b200.algorithms import VirtualLoRAES
+    from evox_b200.problems import VirtualLoRAProblem
+    from evox_b200.transforms import CenteredRank
+    from evox_b200.workflows import StdWorkflow
+
+    dev = torch.device("cuda", 0)
+    pop, batch, width, layers, rank = args.lora_pop, 64, 4096, 3, 8
+    gen = torch.Generator().manual_seed(0)
+    mods = []
+    for i in range(layers):
+        lin = nn.Linear(width, width, bias=False)
+        with torch.no_grad():
+            lin.weight.copy_(torch.randn(width, width, generator=gen) / width**0.5)
+        mods.append(lin)
+        if i + 1 < layers:
+            mods.append(nn.ReLU())
+    model = nn.Sequential(*mods)
+    x = torch.randn(pop, batch, width, generator=gen).bfloat16().to(dev)
+    target = torch.randn(batch, width, generator=gen).to(dev)
+    prob = VirtualLoRAProblem(model, [(x, target)], nn.MSELoss(reduction="none"), rank, device=dev, compute_dtype=torch.bfloat16)
+    center = torch.cat([p.detach().reshape(-1) for p in model.parameters()])
+    algo = VirtualLoRAES(prob.param_shapes, rank, pop, center, 0.01, 0.02, device=dev)
+    wf = StdWorkflow(algo, prob, device=dev, fitness_transform=CenteredRank())
+
+    def timed(fn, reps):
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+
+    for _ in range(2):
+        wf.step()
+    step_ms = timed(wf.step, args.steps)
+    seeds = wf.algorithm.seeds
+    fwd_ms = timed(lambda: prob.evaluate((wf.algorithm.center, seeds, 0.02)), args.steps)
+    m = pop * batch
+    flop_fwd = layers * (2.0 * m * width * width + 2.0 * m * rank * 2 * width)
+    flop_grad = layers * 2.0 * width * (pop * rank) * width
+    from evox_b200.lora_kernels import lora_layer_bf16
+
+    peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
+    peak = float(peaks.get("bf16_tflops_sustained", 1400.0))
+    line = {
+        "metric": "lora_es_generations_per_s", "value": 1e3 / step_ms, "unit": "gens/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": 2, "ms_per_step": step_ms, "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "lora_es_config3", "pop": pop, "batch": batch, "width": width, "layers": layers, "rank": rank},
+        "forward_ms": fwd_ms,
+        "roofline": {"bound": "tensor", "kernel": "lora_gemm_kernel (forward, 3 layers)", "achieved": flop_fwd / (fwd_ms * 1e-3) / 1e12,
+                     "peak": peak, "unit": "TFLOP/s", "frac": flop_fwd / (fwd_ms * 1e-3) / 1e12 / peak,
+                     "peak_kind": "measured sustained" if peaks else "fallback", "traffic": None},
+        "generation_tflops": (flop_fwd + flop_grad) / (step_ms * 1e-3) / 1e12,
+        "gemm_error_flag": int(lora_layer_bf16.last_error_flag),
+    }
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="pso_ackley_1e6x1000", choices=sorted(WORKLOADS) + ["nds_rank_2e4", "nds_rank_1e5"])
+    ap.add_argument("--workload", default="pso_ackley_1e6x1000", choices=sorted(WORKLOADS) + ["nds_rank_2e4", "nds_rank_1e5", "lora_es_config3"])
+    ap.add_argument("--lora-pop", type=int, default=1024)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     if args.workload.startswith("nds_"):
         run_nds(args)
+    elif args.workload == "lora_es_config3":
+        run_lora_es(args)
     elif args.impl == "reference":
         run_reference(args)
     else:

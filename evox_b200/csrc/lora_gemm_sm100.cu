@@ -1,0 +1,559 @@
+// P4 (part 2): one Linear layer of the virtual-LoRA population forward on the 5th-generation
+// tensor cores (sm_100a): Y = act(H W^T + bias + sigma * (H A_p^T) B_p^T + sigma * bias_noise_p).
+//
+// Reference semantics: VirtualLoRAProblem._virtual_forward
+// (evox/problems/neuroevolution/virtual_lora_problem.py:160-193) with the factors of
+// generate_lora_factors (evox/triton_kernels/kernels/lora_noise.py:86-127); the reference does
+// the base product as an fp32 cuBLAS SGEMM and the correction as two batched matmuls over
+// materialised factors (lora_noise.py:151-153).
+//
+// lora_gemm_kernel — persistent, one CTA per SM, warp specialised:
+//   warp 0    TMA producer: 128 x 64 tile of H and 256 x 64 tile of W (bf16, 128-byte swizzle)
+//             per k-block into a 4-stage shared-memory ring.
+//   warp 1    issues tcgen05.mma (M = 128, N = 256, K = 16, bf16 x bf16 -> fp32) from one lane into
+//             one of two 256-column TMEM accumulators; tcgen05.commit releases ring stages and
+//             hands finished accumulators to the epilogue.
+//   warps 2-5 epilogue: regenerate the tile's slice of B_p (and bias noise) from the individuals'
+//             Philox streams into shared memory, read the accumulator with tcgen05.ld, add bias,
+//             the rank-r correction sigma * t B_p^T (t = H A_p^T from lora_down_bf16_kernel), ReLU,
+//             and store bf16 / fp32 — or, for the last layer, reduce (y - target)^2 per row.
+//             The second accumulator lets the next tile's products run underneath.
+// Every mbarrier wait is bounded by a wall-clock limit; on expiry the kernel raises an error flag,
+// all roles leave their loops, outstanding copies are drained with the same bound and TMEM is freed.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <math.h>
+
+#include <mutex>
+
+#include "common.cuh"
+
+namespace evox {
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4, RANK = 8;
+constexpr int kGemmThreads = 192;
+constexpr uint32_t kBytesA = BM * BK * 2, kBytesB = BN * BK * 2, kStageBytes = kBytesA + kBytesB;
+constexpr uint32_t kMaxInd = 2;  // individuals per 128-row tile (batch is a multiple of 64)
+constexpr uint32_t kOffBfac = STAGES * kStageBytes;                  // float [kMaxInd][BN][RANK]
+constexpr uint32_t kOffBnoise = kOffBfac + kMaxInd * BN * RANK * 4;  // float [kMaxInd][BN]
+constexpr uint32_t kOffBars = kOffBnoise + kMaxInd * BN * 4;         // mbarriers + tmem base
+constexpr uint32_t kSmemBytes = kOffBars + 256 + 1024;               // + alignment slack
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;           // 2 s per wait
+
+struct GemmArgs {
+  long long M, N, K;     // rows = pop * batch, out features, in features
+  long long batch;       // rows per individual
+  const float* bias;     // [N] or null
+  const float* t;        // [M][RANK] = H A_p^T, or null (no LoRA correction)
+  const long long* seeds;  // [pop]
+  unsigned long long b_counter;      // Philox counter of the B stream of this weight block
+  unsigned long long noise_counter;  // Philox counter of the bias-noise block
+  int has_bias_noise;
+  float sigma;
+  int relu;
+  __nv_bfloat16* out_bf16;  // [M][N] or null
+  float* out_f32;           // [M][N] or null
+  const float* target;      // [batch][N] or null: write row_partial instead of the output
+  float* row_partial;       // [M][N / BN]
+  int* error_flag;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+// Bounded wait. Returns false when the limit expired or another role already reported an error.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* error_flag, int code) {
+  if (mbar_try(bar, parity)) return true;
+  const unsigned long long t0 = global_timer_ns();
+  for (uint32_t it = 1;; ++it) {
+    if (mbar_try(bar, parity)) return true;
+    if ((it & 255u) == 0) {
+      if (*((volatile int*)error_flag) != 0) return false;
+      if (global_timer_ns() - t0 > kWaitLimitNs) {
+        atomicCAS(error_flag, 0, code);
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"((unsigned long long)map), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+
+// Shared-memory operand descriptor: K-major tile, rows of 128 bytes, 128-byte swizzle, 8-row groups
+// 1024 bytes apart (descriptor version 1 of sm_100).
+__device__ __forceinline__ unsigned long long umma_desc(uint32_t smem_addr) {
+  unsigned long long d = 0;
+  d |= (unsigned long long)((smem_addr & 0x3ffffu) >> 4);  // start address
+  d |= (unsigned long long)(1024u >> 4) << 32;             // stride byte offset
+  d |= 1ull << 46;                                         // version
+  d |= 2ull << 61;                                         // SWIZZLE_128B
+  return d;
+}
+
+// kind::f16 instruction descriptor: D = fp32, A = B = bf16, both K-major, N = 256, M = 128.
+constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, unsigned long long a, unsigned long long b, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+      ::"r"(d_tmem), "l"(a), "l"(b), "r"(kIdesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+        "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+        "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// Four standard normals of Philox call `call` of one individual's stream (same arithmetic as
+// philox_normal, evox/triton_kernels/kernels/philox.py:87-112).
+__device__ __forceinline__ float4 normal4(unsigned long long seed, unsigned long long counter, uint32_t call) {
+  const uint4 r = philox4x32_10((uint32_t)counter + call, (uint32_t)(counter >> 32), 0u, 0u, (uint32_t)seed,
+                                (uint32_t)(seed >> 32));
+  const float u0 = u24_to_unit(r.x), u1 = u24_to_unit(r.y), u2 = u24_to_unit(r.z), u3 = u24_to_unit(r.w);
+  const float r0 = sqrtf(__fmul_rn(-2.0f, logf(fmaxf(u0, 1e-10f))));
+  const float r1 = sqrtf(__fmul_rn(-2.0f, logf(fmaxf(u2, 1e-10f))));
+  float s0, c0, s1, c1;
+  sincosf(__fmul_rn(6.283185307179586f, u1), &s0, &c0);
+  sincosf(__fmul_rn(6.283185307179586f, u3), &s1, &c1);
+  return make_float4(__fmul_rn(r0, c0), __fmul_rn(r0, s0), __fmul_rn(r1, c1), __fmul_rn(r1, s1));
+}
+
+__global__ void __launch_bounds__(kGemmThreads, 1)
+    lora_gemm_kernel(const __grid_constant__ CUtensorMap map_h, const __grid_constant__ CUtensorMap map_w, const GemmArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~(uintptr_t)1023u);
+  const uint32_t smem_base = smem_u32(smem);
+  float* bfac = reinterpret_cast<float*>(smem + kOffBfac);
+  float* bnoise = reinterpret_cast<float*>(smem + kOffBnoise);
+  const uint32_t bars = smem_base + kOffBars;
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int b) { return bars + 8u * (2 * STAGES + b); };
+  auto tempty_bar = [&](int b) { return bars + 8u * (2 * STAGES + 2 + b); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kOffBars + 8 * (2 * STAGES + 4));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long n_tiles_n = a.N / BN;
+  const long long n_tiles = (a.M / BM) * n_tiles_n;
+  const int k_blocks = (int)(a.K / BK);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(tfull_bar(b), 1);
+      mbar_init(tempty_bar(b), 128);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(tmem_slot)) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem_base = *((volatile uint32_t*)tmem_slot);
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer ------------------------------------------
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      uint32_t issued = 0;  // bit s: a copy into stage s may still be in flight
+      bool ok = true;
+      for (long long tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+        const int m0 = (int)((tile / n_tiles_n) * BM), n0 = (int)((tile % n_tiles_n) * BN);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(empty_bar(s), ph ^ 1u, a.error_flag, 1)) {
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(full_bar(s), kStageBytes);
+          tma_load_2d(smem_base + s * kStageBytes, &map_h, full_bar(s), kb * BK, m0);
+          tma_load_2d(smem_base + s * kStageBytes + kBytesA, &map_w, full_bar(s), kb * BK, n0);
+          issued |= 1u << s;
+          if (++s == STAGES) {
+            s = 0;
+            ph ^= 1u;
+          }
+        }
+      }
+      if (!ok) {
+        // drain: the last copy issued into each stage must land before shared memory is released
+        for (int q = 0; q < STAGES; ++q) {
+          if (!(issued & (1u << q))) continue;
+          // stage q was last filled in phase (ph if q < s else ph ^ 1)
+          const uint32_t last = (q < s) ? ph : (ph ^ 1u);
+          const unsigned long long t0 = global_timer_ns();
+          while (!mbar_try(full_bar(q), last) && !mbar_try(full_bar(q), last ^ 1u)) {
+            if (global_timer_ns() - t0 > kWaitLimitNs) break;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer --------------------------------------------
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      long long it = 0;
+      bool ok = true;
+      for (long long tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++it) {
+        const int buf = (int)(it & 1);
+        const uint32_t acc_ph = (uint32_t)((it >> 1) & 1);
+        if (!mbar_wait(tempty_bar(buf), acc_ph ^ 1u, a.error_flag, 2)) break;
+        fence_after_sync();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(full_bar(s), ph, a.error_flag, 3)) {
+            ok = false;
+            break;
+          }
+          fence_after_sync();
+          const uint32_t sa = smem_base + s * kStageBytes, sb = sa + kBytesA;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            umma_bf16(d_tmem, umma_desc(sa + k * 32), umma_desc(sb + k * 32), (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(empty_bar(s));  // stage reusable once these products have read it
+          if (++s == STAGES) {
+            s = 0;
+            ph ^= 1u;
+          }
+        }
+        if (ok) umma_commit(tfull_bar(buf));  // accumulator complete
+      }
+    }
+  } else {
+    // ------------------------------- epilogue (128 threads) --------------------------------
+    const int quarter = warp & 3;           // TMEM lanes this warp may read
+    const int row_in_tile = quarter * 32 + lane;
+    const int et = threadIdx.x - 64;        // 0..127 within the epilogue group
+    const int inds_per_tile = (a.batch >= BM) ? 1 : (int)(BM / a.batch);
+    long long it = 0;
+    bool ok = true;
+    for (long long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++it) {
+      const long long m0 = (tile / n_tiles_n) * BM;
+      const int n_blk = (int)(tile % n_tiles_n);
+      const long long n0 = (long long)n_blk * BN;
+      const int buf = (int)(it & 1);
+      const uint32_t acc_ph = (uint32_t)((it >> 1) & 1);
+      const long long p_first = m0 / a.batch;
+      // all epilogue threads are done with the previous tile's factors
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (a.t != nullptr) {
+        // B_p[n][q], q = 0..7: elements n * 8 + q of the stream -> Philox calls 2n and 2n + 1
+        for (int idx = et; idx < inds_per_tile * BN * 2; idx += 128) {
+          const int ind = idx / (BN * 2), rest = idx - ind * (BN * 2);
+          const int col = rest >> 1, half = rest & 1;
+          const unsigned long long seed = (unsigned long long)a.seeds[p_first + ind];
+          const float4 z = normal4(seed, a.b_counter, (uint32_t)(((n0 + col) * RANK) / 4 + half));
+          *reinterpret_cast<float4*>(bfac + ((size_t)(ind * BN + col) * RANK + half * 4)) = z;
+        }
+      }
+      if (a.has_bias_noise) {
+        for (int idx = et; idx < inds_per_tile * (BN / 4); idx += 128) {
+          const int ind = idx / (BN / 4), c4 = idx - ind * (BN / 4);
+          const unsigned long long seed = (unsigned long long)a.seeds[p_first + ind];
+          const float4 z = normal4(seed, a.noise_counter, (uint32_t)((n0 >> 2) + c4));
+          *reinterpret_cast<float4*>(bnoise + (size_t)ind * BN + c4 * 4) = z;
+        }
+      }
+      const long long row = m0 + row_in_tile;
+      const int my_ind = (int)(row / a.batch - p_first);
+      float tr[RANK];
+#pragma unroll
+      for (int q = 0; q < RANK; ++q) tr[q] = 0.f;
+      if (a.t != nullptr) {
+        const float4 t0 = *reinterpret_cast<const float4*>(a.t + row * RANK);
+        const float4 t1 = *reinterpret_cast<const float4*>(a.t + row * RANK + 4);
+        tr[0] = t0.x; tr[1] = t0.y; tr[2] = t0.z; tr[3] = t0.w;
+        tr[4] = t1.x; tr[5] = t1.y; tr[6] = t1.z; tr[7] = t1.w;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (ok && !mbar_wait(tfull_bar(buf), acc_ph, a.error_flag, 4)) ok = false;
+      if (!ok) continue;  // keep the named barriers balanced, skip the work
+      fence_after_sync();
+      const float* bf = bfac + (size_t)my_ind * BN * RANK;
+      const float* bn = bnoise + (size_t)my_ind * BN;
+      const float* target_row = a.target ? a.target + (row % a.batch) * a.N + n0 : nullptr;
+      float sq_sum = 0.f;
+      for (int c = 0; c < BN; c += 32) {
+        uint32_t v[32];
+        tmem_ld32(tmem_base + (uint32_t)(buf * BN + c) + ((uint32_t)(quarter * 32) << 16), v);
+        tmem_ld_wait();
+        float y[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          float acc = __uint_as_float(v[j]);
+          if (a.bias) acc += __ldg(a.bias + n0 + c + j);
+          if (a.t != nullptr) {
+            const float4 b0 = *reinterpret_cast<const float4*>(bf + (size_t)(c + j) * RANK);
+            const float4 b1 = *reinterpret_cast<const float4*>(bf + (size_t)(c + j) * RANK + 4);
+            float dl = tr[0] * b0.x;
+            dl = fmaf(tr[1], b0.y, dl);
+            dl = fmaf(tr[2], b0.z, dl);
+            dl = fmaf(tr[3], b0.w, dl);
+            dl = fmaf(tr[4], b1.x, dl);
+            dl = fmaf(tr[5], b1.y, dl);
+            dl = fmaf(tr[6], b1.z, dl);
+            dl = fmaf(tr[7], b1.w, dl);
+            acc = fmaf(a.sigma, dl, acc);
+          }
+          if (a.has_bias_noise) acc = fmaf(a.sigma, bn[c + j], acc);
+          y[j] = a.relu ? fmaxf(acc, 0.f) : acc;
+        }
+        if (target_row) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float dlt = y[j] - __ldg(target_row + c + j);
+            sq_sum = fmaf(dlt, dlt, sq_sum);
+          }
+        } else if (a.out_bf16) {
+          __nv_bfloat16* o = a.out_bf16 + row * a.N + n0 + c;
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            uint4 pk;
+            __nv_bfloat162 h0 = __floats2bfloat162_rn(y[j], y[j + 1]), h1 = __floats2bfloat162_rn(y[j + 2], y[j + 3]);
+            __nv_bfloat162 h2 = __floats2bfloat162_rn(y[j + 4], y[j + 5]), h3 = __floats2bfloat162_rn(y[j + 6], y[j + 7]);
+            pk.x = *reinterpret_cast<uint32_t*>(&h0);
+            pk.y = *reinterpret_cast<uint32_t*>(&h1);
+            pk.z = *reinterpret_cast<uint32_t*>(&h2);
+            pk.w = *reinterpret_cast<uint32_t*>(&h3);
+            *reinterpret_cast<uint4*>(o + j) = pk;
+          }
+        } else {
+          float* o = a.out_f32 + row * a.N + n0 + c;
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(o + j) = make_float4(y[j], y[j + 1], y[j + 2], y[j + 3]);
+        }
+      }
+      if (target_row) a.row_partial[row * n_tiles_n + n_blk] = sq_sum;
+      fence_before_sync();
+      mbar_arrive(tempty_bar(buf));  // this thread no longer reads the accumulator
+    }
+  }
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    fence_after_sync();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
+  }
+}
+
+// t[p][b][q] = sum_k H[p][b][k] * A_p[q][k] with A_p regenerated from the seed (never stored).
+// One block per individual; 256 threads; K is walked in chunks of 256 columns staged in shared memory.
+__global__ void __launch_bounds__(256)
+    lora_down_bf16_kernel(const __nv_bfloat16* __restrict__ h, const long long* __restrict__ seeds, unsigned long long a_counter,
+                          long long batch, long long K, float* __restrict__ t) {
+  constexpr int KC = 256;
+  __shared__ float sA[RANK][KC + 4];
+  extern __shared__ float sH[];  // [batch][KC + 1]
+  const long long p = blockIdx.x;
+  const unsigned long long seed = (unsigned long long)seeds[p];
+  const int tid = threadIdx.x;
+  const int n_out = (int)batch * RANK;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};  // outputs tid, tid + 256, ... (batch * RANK <= 1024)
+  for (long long k0 = 0; k0 < K; k0 += KC) {
+    // A_p[q][k]: element q * K + k -> call (q * K + k) / 4 (K is a multiple of 4)
+    for (int idx = tid; idx < RANK * (KC / 4); idx += 256) {
+      const int q = idx / (KC / 4), c4 = idx - q * (KC / 4);
+      const float4 z = normal4(seed, a_counter, (uint32_t)(((long long)q * K + k0) / 4 + c4));
+      sA[q][c4 * 4 + 0] = z.x;
+      sA[q][c4 * 4 + 1] = z.y;
+      sA[q][c4 * 4 + 2] = z.z;
+      sA[q][c4 * 4 + 3] = z.w;
+    }
+    for (int idx = tid; idx < (int)batch * KC; idx += 256) {
+      const int b = idx / KC, c = idx - b * KC;
+      sH[b * (KC + 1) + c] = __bfloat162float(h[(p * batch + b) * K + k0 + c]);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int o = tid + u * 256;
+      if (o < n_out) {
+        const int b = o / RANK, q = o - b * RANK;
+        float s = acc[u];
+        for (int c = 0; c < KC; ++c) s = fmaf(sH[b * (KC + 1) + c], sA[q][c], s);
+        acc[u] = s;
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const int o = tid + u * 256;
+    if (o < n_out) t[p * n_out + o] = acc[u];
+  }
+}
+
+// fitness[p] = -(sum of row partials of individual p) / (batch * N): negative mean squared error.
+__global__ void neg_mse_kernel(const float* __restrict__ row_partial, long long batch, long long tiles_n, long long N,
+                               long long pop, float* __restrict__ fitness) {
+  const long long p = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (p >= pop) return;
+  float s = 0.f;
+  const float* rp = row_partial + p * batch * tiles_n;
+  for (long long i = 0; i < batch * tiles_n; ++i) s += rp[i];
+  fitness[p] = -s / (float)(batch * N);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+int encode_fn(EncodeTiledFn* out) {
+  static EncodeTiledFn fn = nullptr;
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lock(mu);
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    EVOX_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q));
+    EVOX_REQUIRE(p != nullptr && q == cudaDriverEntryPointSuccess, EVOX_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
+    fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  *out = fn;
+  return EVOX_OK;
+}
+
+int make_map(CUtensorMap* map, const void* base, long long rows, long long K, int box_rows) {
+  EncodeTiledFn fn;
+  if (int rc = encode_fn(&fn)) return rc;
+  const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  EVOX_REQUIRE(r == CUDA_SUCCESS, EVOX_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+  return EVOX_OK;
+}
+
+}  // namespace
+}  // namespace evox
+
+using namespace evox;
+
+extern "C" int evox_lora_gemm_supported(int64_t pop, int64_t batch, int64_t k, int64_t d, int32_t r) {
+  return (pop > 0 && batch % 64 == 0 && (batch <= 128 ? 128 % batch == 0 : batch % 128 == 0) && (pop * batch) % BM == 0 &&
+          k % BK == 0 && k >= BK && d % BN == 0 && r == RANK && batch * RANK <= 1024)
+             ? 1
+             : 0;
+}
+
+extern "C" int evox_lora_down_bf16(const void* h, const int64_t* seeds, uint64_t a_counter, int64_t pop, int64_t batch,
+                                   int64_t k, int32_t r, float* t, void* stream) {
+  EVOX_REQUIRE(h && seeds && t, EVOX_ERR_INVALID, "lora_down_bf16: NULL pointer");
+  EVOX_REQUIRE(r == RANK && k % 256 == 0 && batch > 0 && batch * RANK <= 1024 && pop > 0, EVOX_ERR_INVALID,
+               "lora_down_bf16: needs rank 8, k a multiple of 256 and batch <= 128");
+  const size_t smem = sizeof(float) * (size_t)batch * 257;
+  EVOX_CUDA(cudaFuncSetAttribute(lora_down_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  lora_down_bf16_kernel<<<(unsigned)pop, 256, smem, reinterpret_cast<cudaStream_t>(stream)>>>(
+      (const __nv_bfloat16*)h, (const long long*)seeds, a_counter, batch, k, t);
+  EVOX_LAUNCH_CHECK();
+  return EVOX_OK;
+}
+
+extern "C" int evox_lora_gemm_bf16(const void* h, const void* w, const float* bias, const float* t, const int64_t* seeds,
+                                   uint64_t b_counter, int32_t has_bias_noise, uint64_t noise_counter, float sigma,
+                                   int64_t pop, int64_t batch, int64_t k, int64_t d, int32_t r, int32_t relu,
+                                   void* out_bf16, float* out_f32, const float* target, float* row_partial,
+                                   int32_t* error_flag, void* stream) {
+  EVOX_REQUIRE(h && w && seeds && error_flag, EVOX_ERR_INVALID, "lora_gemm_bf16: NULL pointer");
+  EVOX_REQUIRE(evox_lora_gemm_supported(pop, batch, k, d, r), EVOX_ERR_INVALID,
+               "lora_gemm_bf16: shape (pop %lld, batch %lld, k %lld, d %lld, r %d) is not supported by the tensor-core path",
+               (long long)pop, (long long)batch, (long long)k, (long long)d, r);
+  EVOX_REQUIRE((target != nullptr) ? (row_partial != nullptr) : ((out_bf16 != nullptr) != (out_f32 != nullptr)),
+               EVOX_ERR_INVALID, "lora_gemm_bf16: give exactly one of out_bf16 / out_f32, or target + row_partial");
+  EVOX_REQUIRE(((uintptr_t)h & 15u) == 0 && ((uintptr_t)w & 15u) == 0, EVOX_ERR_INVALID, "lora_gemm_bf16: operands must be 16-byte aligned");
+  GemmArgs a;
+  a.M = pop * batch;
+  a.N = d;
+  a.K = k;
+  a.batch = batch;
+  a.bias = bias;
+  a.t = t;
+  a.seeds = (const long long*)seeds;
+  a.b_counter = b_counter;
+  a.noise_counter = noise_counter;
+  a.has_bias_noise = has_bias_noise;
+  a.sigma = sigma;
+  a.relu = relu;
+  a.out_bf16 = (__nv_bfloat16*)out_bf16;
+  a.out_f32 = out_f32;
+  a.target = target;
+  a.row_partial = row_partial;
+  a.error_flag = error_flag;
+  CUtensorMap map_h, map_w;
+  if (int rc = make_map(&map_h, h, a.M, k, BM)) return rc;
+  if (int rc = make_map(&map_w, w, d, k, BN)) return rc;
+  EVOX_CUDA(cudaFuncSetAttribute(lora_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+  const long long n_tiles = (a.M / BM) * (a.N / BN);
+  long long grid = sm_count();
+  if (grid > n_tiles) grid = n_tiles;
+  lora_gemm_kernel<<<(unsigned)grid, kGemmThreads, kSmemBytes, reinterpret_cast<cudaStream_t>(stream)>>>(map_h, map_w, a);
+  EVOX_LAUNCH_CHECK();
+  return EVOX_OK;
+}
+
+extern "C" int evox_neg_mse_from_partials(const float* row_partial, int64_t pop, int64_t batch, int64_t d, float* fitness,
+                                          void* stream) {
+  EVOX_REQUIRE(row_partial && fitness, EVOX_ERR_INVALID, "neg_mse_from_partials: NULL pointer");
+  EVOX_REQUIRE(pop > 0 && batch > 0 && d > 0 && d % BN == 0, EVOX_ERR_INVALID, "neg_mse_from_partials: bad sizes");
+  neg_mse_kernel<<<(unsigned)((pop + 127) / 128), 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(row_partial, batch, d / BN, d, pop,
+                                                                                                 fitness);
+  EVOX_LAUNCH_CHECK();
+  return EVOX_OK;
+}

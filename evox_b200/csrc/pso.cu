@@ -24,6 +24,9 @@ namespace {
 constexpr int kWarpsPerBlock = 8;
 constexpr int kThreads = kWarpsPerBlock * 32;
 constexpr int kMaxPartials = 2048;
+#ifndef MOVE_BLOCKS_PER_SM
+#define MOVE_BLOCKS_PER_SM 4
+#endif
 
 struct FitParams {
   float a, b, c;
@@ -111,14 +114,13 @@ __device__ __forceinline__ float4 pso_uniform4(uint64_t q, uint64_t generation, 
   uint32_t c3 = which + 2u * (uint32_t)(generation >> 32);
 #pragma unroll
   for (int r = 0; r < 10; ++r) {
-    const uint32_t hi0 = __umulhi(EVOX_PHILOX_M0, c0);
-    const uint32_t lo0 = EVOX_PHILOX_M0 * c0;
-    const uint32_t hi1 = __umulhi(EVOX_PHILOX_M1, c2);
-    const uint32_t lo1 = EVOX_PHILOX_M1 * c2;
-    c0 = hi1 ^ c1 ^ rk.k[2 * r];
-    c1 = lo1;
-    c2 = hi0 ^ c3 ^ rk.k[2 * r + 1];
-    c3 = lo0;
+    // one 32 x 32 -> 64 bit multiply per half instead of separate high / low products
+    const unsigned long long p0 = (unsigned long long)EVOX_PHILOX_M0 * (unsigned long long)c0;
+    const unsigned long long p1 = (unsigned long long)EVOX_PHILOX_M1 * (unsigned long long)c2;
+    c0 = (uint32_t)(p1 >> 32) ^ c1 ^ rk.k[2 * r];
+    c1 = (uint32_t)p1;
+    c2 = (uint32_t)(p0 >> 32) ^ c3 ^ rk.k[2 * r + 1];
+    c3 = (uint32_t)p0;
   }
   return make_float4(u24_to_unit(c0), u24_to_unit(c1), u24_to_unit(c2), u24_to_unit(c3));
 }
@@ -174,7 +176,7 @@ __device__ __forceinline__ float move_one(float x, float& v, float pb, float gb,
 }
 
 template <int VEC, bool PHILOX, int FIT>
-__global__ void __launch_bounds__(kThreads, 4) pso_move_eval_kernel(const MoveArgs a) {
+__global__ void __launch_bounds__(kThreads, MOVE_BLOCKS_PER_SM) pso_move_eval_kernel(const MoveArgs a) {
   const int lane = threadIdx.x & 31;
   const long long warp0 = (long long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
   const long long n_warps = (long long)gridDim.x * kWarpsPerBlock;
@@ -604,7 +606,7 @@ extern "C" int evox_pso_move_eval(float* pop, float* velocity, float* local_best
   a.generation = generation;
   a.row_offset = row_offset;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  const int grid = row_grid(pop_size, 4);  // __launch_bounds__(256, 4)
+  const int grid = row_grid(pop_size, MOVE_BLOCKS_PER_SM);
   const bool philox = (rg == nullptr);
   bool vec = (dim % 4 == 0) && aligned16(pop) && aligned16(velocity) && aligned16(local_best_location) &&
              aligned16(global_best_location) && aligned16(lb) && aligned16(ub);

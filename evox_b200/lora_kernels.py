@@ -110,3 +110,50 @@ def lora_gradient(fitness: torch.Tensor, A: torch.Tensor, B: torch.Tensor | None
         grad = torch.empty(d, k, dtype=torch.float32, device=dev)
         _cabi.check(_cabi.lib.evox_lora_gradient(_cabi.ptr(fitness), _cabi.ptr(A), _cabi.ptr(B), pop_size, sigma, d, k, r, _cabi.ptr(grad), _cabi.stream_ptr(dev)))
     return grad.reshape(weight_shape)
+
+
+def lora_layer_bf16(h: torch.Tensor, w: torch.Tensor, seeds: torch.Tensor, counter: int, sigma: float, *,
+                    bias: torch.Tensor | None = None, bias_counter: int | None = None, relu: bool = False,
+                    out_dtype: torch.dtype = torch.bfloat16, target: torch.Tensor | None = None, lora: bool = True):
+    """One virtual-LoRA Linear layer on the tensor cores: h (pop, batch, k) bf16, w (d, k) bf16.
+
+    Returns y (pop, batch, d) in `out_dtype`, or, with `target` (batch, d) given, the per-individual
+    fitness -mean((y - target)^2) without ever writing y. `counter` is the weight block's Philox
+    counter (A at `counter`, B at `counter + ceil4(8 k)`), `bias_counter` the bias block's."""
+    rank = 8
+    pop, batch, k = h.shape
+    d = w.shape[0]
+    dev = h.device
+    if h.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise _cabi.EvoxKernelError("lora_layer_bf16 needs bf16 activations and weights")
+    if not _cabi.lib.evox_lora_gemm_supported(pop, batch, k, d, rank):
+        raise _cabi.EvoxKernelError(f"layer shape (pop {pop}, batch {batch}, k {k}, d {d}) is not supported by the tensor-core path")
+    h, w, seeds = h.contiguous(), w.contiguous(), _seeds(seeds)
+    lib, s = _cabi.lib, _cabi.stream_ptr(dev)
+    t = None
+    if lora:
+        t = torch.empty(pop, batch, rank, dtype=torch.float32, device=dev)
+        _cabi.check(lib.evox_lora_down_bf16(_cabi.ptr(h), _cabi.ptr(seeds), counter, pop, batch, k, rank, _cabi.ptr(t), s))
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    out_bf16 = out_f32 = partial = None
+    if target is not None:
+        target = target.to(device=dev, dtype=torch.float32).contiguous()
+        partial = torch.empty(pop * batch, d // 256, dtype=torch.float32, device=dev)
+    elif out_dtype == torch.bfloat16:
+        out_bf16 = torch.empty(pop, batch, d, dtype=torch.bfloat16, device=dev)
+    else:
+        out_f32 = torch.empty(pop, batch, d, dtype=torch.float32, device=dev)
+    bias_f = None if bias is None else bias.to(device=dev, dtype=torch.float32).contiguous()
+    _cabi.check(
+        lib.evox_lora_gemm_bf16(
+            _cabi.ptr(h), _cabi.ptr(w), _cabi.ptr(bias_f), _cabi.ptr(t), _cabi.ptr(seeds), counter + _ceil4(rank * k),
+            int(bias is not None and bias_counter is not None and lora), bias_counter or 0, float(sigma), pop, batch, k, d, rank,
+            int(relu), _cabi.ptr(out_bf16), _cabi.ptr(out_f32), _cabi.ptr(target), _cabi.ptr(partial), _cabi.ptr(err), s,
+        )
+    )
+    lora_layer_bf16.last_error_flag = err
+    if target is not None:
+        fitness = torch.empty(pop, dtype=torch.float32, device=dev)
+        _cabi.check(lib.evox_neg_mse_from_partials(_cabi.ptr(partial), pop, batch, d, _cabi.ptr(fitness), s))
+        return fitness
+    return out_bf16 if out_bf16 is not None else out_f32

@@ -17,7 +17,7 @@ from torch import nn
 
 from .. import _cabi
 from ..core import Problem
-from ..lora_kernels import compute_counter_offsets, generate_lora_factors
+from ..lora_kernels import compute_counter_offsets, generate_lora_factors, lora_layer_bf16
 
 __all__ = ["VirtualLoRAProblem"]
 
@@ -26,8 +26,12 @@ _ACTIVATIONS = (nn.ReLU, nn.Tanh, nn.Sigmoid, nn.GELU, nn.LeakyReLU, nn.ELU, nn.
 
 class VirtualLoRAProblem(Problem):
     def __init__(self, model: nn.Sequential, data_loader, criterion, lora_rank: int, n_batch_per_eval: int = 1,
-                 device: torch.device | None = None, reduction: str = "mean"):
+                 device: torch.device | None = None, reduction: str = "mean", compute_dtype: torch.dtype = torch.float32):
+        """`compute_dtype=torch.bfloat16` runs every Linear layer whose shape the tensor-core kernel
+        supports (rank 8, batch 64 or 128 per individual, feature sizes multiples of 256) with bf16
+        operands and fp32 accumulation; other layers and the default use the fp32 kernels."""
         super().__init__()
+        self.compute_dtype = compute_dtype
         if not isinstance(model, nn.Sequential):
             raise TypeError(f"VirtualLoRAProblem requires an nn.Sequential model, got {type(model).__name__}.")
         self.device = torch.get_default_device() if device is None else torch.device(device)
@@ -63,7 +67,9 @@ class VirtualLoRAProblem(Problem):
     def _virtual_forward(self, inputs: torch.Tensor, center: torch.Tensor, seeds: torch.Tensor, sigma: float, pop_size: int) -> torch.Tensor:
         dev = center.device
         shared = inputs.ndim == 2
-        h = inputs.to(device=dev, dtype=torch.float32).contiguous()
+        h = inputs.to(device=dev).contiguous()
+        if self.compute_dtype != torch.bfloat16 or h.dtype != torch.bfloat16:
+            h = h.to(torch.float32)
         batch = h.shape[-2]
         children = list(self.model.named_children())
         lib, s = _cabi.lib, _cabi.stream_ptr(dev)
@@ -75,14 +81,28 @@ class VirtualLoRAProblem(Problem):
             if isinstance(module, nn.Linear):
                 weight, wi = self._param(center, f"{name}.weight")
                 d, k = weight.shape
+                relu = pos + 1 < len(children) and isinstance(children[pos + 1][1], nn.ReLU)
+                if (self.compute_dtype == torch.bfloat16 and not shared
+                        and lib.evox_lora_gemm_supported(pop_size, batch, k, d, self.lora_rank)):
+                    bias = bias_counter = None
+                    if module.bias is not None:
+                        bias, bi = self._param(center, f"{name}.bias")
+                        bias_counter = self.counter_offsets[bi]
+                    last = pos + (2 if relu else 1) >= len(children)
+                    h = lora_layer_bf16(
+                        h.to(torch.bfloat16), weight.to(torch.bfloat16), seeds, self.counter_offsets[wi], sigma, bias=bias,
+                        bias_counter=bias_counter, relu=relu, out_dtype=torch.float32 if last else torch.bfloat16,
+                    )
+                    skip = relu
+                    continue
                 a, b = generate_lora_factors(seeds, (d, k), self.lora_rank, self.counter_offsets[wi])
                 bias = bias_noise = None
                 if module.bias is not None:
                     bias, bi = self._param(center, f"{name}.bias")
                     bias_noise = generate_lora_factors(seeds, (d,), self.lora_rank, self.counter_offsets[bi])
                 t = torch.empty(pop_size, batch, self.lora_rank, dtype=torch.float32, device=dev)
+                h = h.to(torch.float32)
                 _cabi.check(lib.evox_lora_down(_cabi.ptr(h), int(shared), _cabi.ptr(a), pop_size, batch, k, self.lora_rank, _cabi.ptr(t), s))
-                relu = pos + 1 < len(children) and isinstance(children[pos + 1][1], nn.ReLU)
                 out = torch.empty(pop_size, batch, d, dtype=torch.float32, device=dev)
                 _cabi.check(
                     lib.evox_lora_linear_forward(
@@ -98,7 +118,7 @@ class VirtualLoRAProblem(Problem):
                 h = module(h)
         if shared:
             h = h.unsqueeze(0).expand(pop_size, -1, -1).contiguous()
-        return h
+        return h.to(torch.float32)
 
     def evaluate(self, payload) -> torch.Tensor:
         center_flat, seeds, sigma = payload

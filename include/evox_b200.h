@@ -227,6 +227,36 @@ int evox_es_update(float* center, const float* grad, const float* learning_rate,
                    float* exp_avg_sq, const float* beta1, const float* beta2, float eps, int64_t dim,
                    void* stream);
 
+/* 1 if evox_lora_gemm_bf16 / evox_lora_down_bf16 accept this layer shape: batch 64 or 128,
+ * pop * batch a multiple of 128, k a multiple of 256, d a multiple of 256, rank 8. */
+int evox_lora_gemm_supported(int64_t pop, int64_t batch, int64_t k, int64_t d, int32_t r);
+
+/* t (pop x batch x 8, fp32) = h A_p^T for bf16 activations h (pop x batch x k); A_p (8 x k) is
+ * regenerated in the kernel from seeds / a_counter exactly as generate_lora_factors would
+ * (lora_noise.py:118-125) and never written to memory. */
+int evox_lora_down_bf16(const void* h, const int64_t* seeds, uint64_t a_counter, int64_t pop,
+                        int64_t batch, int64_t k, int32_t r, float* t, void* stream);
+
+/* One Linear layer of the virtual-population forward pass on the tensor cores
+ * (virtual_lora_problem.py:160-193): bf16 h (pop*batch x k) and W (d x k), fp32 accumulation,
+ *   y = act(h W^T + bias + sigma * t B_p^T + sigma * bias_noise_p)
+ * with B_p (d x 8) and the bias noise regenerated in the epilogue from the Philox streams
+ * (b_counter = block counter + ceil4(8 k); noise_counter = the bias block's counter).
+ * t = NULL skips the correction. Exactly one sink: out_bf16 (pop*batch x d), out_f32, or
+ * target (batch x d, fp32, shared by all individuals) + row_partial (pop*batch x d/256) which
+ * receives per-row sums of (y - target)^2 instead of y. error_flag: device int32, zero on
+ * entry; non-zero afterwards means a bounded wait expired (1 producer, 2/3 issuer, 4 epilogue). */
+int evox_lora_gemm_bf16(const void* h, const void* w, const float* bias, const float* t,
+                        const int64_t* seeds, uint64_t b_counter, int32_t has_bias_noise,
+                        uint64_t noise_counter, float sigma, int64_t pop, int64_t batch, int64_t k,
+                        int64_t d, int32_t r, int32_t relu, void* out_bf16, float* out_f32,
+                        const float* target, float* row_partial, int32_t* error_flag, void* stream);
+
+/* fitness (pop) = -(sum of an individual's row_partial entries) / (batch * d): negative mean
+ * squared error of the last layer, summed in a fixed order. */
+int evox_neg_mse_from_partials(const float* row_partial, int64_t pop, int64_t batch, int64_t d,
+                               float* fitness, void* stream);
+
 /* evox_nd_rank for callers that cannot allocate device memory: no workspace argument, and the
  * call itself allocates nothing (no cudaMalloc / cudaFree, no allocating library routine). It
  * has no counterpart in the reference. It is meant for hosts that only own the buffers they

@@ -1,0 +1,82 @@
+"""The tensor-core (tcgen05) virtual-LoRA layer against fp32 math on the same bf16-rounded inputs.
+
+Tolerance: 2e-2 relative to the largest output magnitude (bf16 operands, fp32 accumulation, bf16
+output rounding). The kernel's error flag must stay zero (no bounded wait expired).
+"""
+import pytest
+import torch
+
+from oracle import lora
+
+pytestmark = pytest.mark.gpu
+
+
+def reference_layer(h, w, seeds, counter, sigma, bias, bias_counter, relu, rank=8):
+    pop, batch, k = h.shape
+    d = w.shape[0]
+    a, b = lora.generate_lora_factors(seeds, (d, k), rank, counter)
+    y = h.float() @ w.float().t() + lora.lora_delta_output(h.float(), a, b, sigma)
+    if bias is not None:
+        y = y + bias
+        if bias_counter is not None:
+            y = y + sigma * lora.generate_lora_factors(seeds, (d,), rank, bias_counter).unsqueeze(1)
+    return torch.relu(y) if relu else y
+
+
+def rel_err(got, want):
+    return float((got.double().cpu() - want.double()).abs().max() / want.double().abs().max())
+
+
+@pytest.mark.parametrize("pop,batch,k,d,bias,relu", [
+    (2, 64, 256, 256, False, False),
+    (4, 64, 512, 512, True, True),
+    (3, 128, 256, 768, False, True),
+    (128, 64, 256, 2048, False, True),   # 512 tiles: every CTA walks several tiles and both accumulators
+])
+def test_layer_vs_fp32(cuda, pop, batch, k, d, bias, relu):
+    from evox_b200.lora_kernels import lora_layer_bf16
+
+    g = torch.Generator().manual_seed(pop * 1000 + k)
+    h = torch.randn(pop, batch, k, generator=g).bfloat16()
+    w = (torch.randn(d, k, generator=g) / k**0.5).bfloat16()
+    seeds = torch.randint(0, 2**31, (pop,), generator=g, dtype=torch.int64)
+    b = torch.randn(d, generator=g) * 0.1 if bias else None
+    counter, bias_counter, sigma = 40, (4096 if bias else None), 0.05
+    want = reference_layer(h, w, seeds, counter, sigma, b, bias_counter, relu)
+    for out_dtype in (torch.float32, torch.bfloat16):
+        got = lora_layer_bf16(h.to(cuda), w.to(cuda), seeds.to(cuda), counter, sigma, bias=None if b is None else b.to(cuda),
+                              bias_counter=bias_counter, relu=relu, out_dtype=out_dtype)
+        torch.cuda.synchronize()
+        assert int(lora_layer_bf16.last_error_flag) == 0
+        assert got.dtype == out_dtype
+        err = rel_err(got.float(), want)
+        assert err <= (2e-2 if out_dtype == torch.bfloat16 else 5e-3), err
+    # without the correction: the plain product
+    plain = lora_layer_bf16(h.to(cuda), w.to(cuda), seeds.to(cuda), counter, 0.0, out_dtype=torch.float32, lora=False)
+    assert rel_err(plain, h.float() @ w.float().t()) <= 1e-3
+
+
+def test_fused_negative_mse(cuda):
+    from evox_b200.lora_kernels import lora_layer_bf16
+
+    g = torch.Generator().manual_seed(5)
+    pop, batch, k, d = 6, 64, 256, 512
+    h = torch.randn(pop, batch, k, generator=g).bfloat16()
+    w = (torch.randn(d, k, generator=g) / k**0.5).bfloat16()
+    seeds = torch.randint(0, 2**31, (pop,), generator=g, dtype=torch.int64)
+    target = torch.randn(batch, d, generator=g)
+    want = -((reference_layer(h, w, seeds, 8, 0.02, None, None, False) - target) ** 2).mean(dim=(1, 2))
+    got = lora_layer_bf16(h.to(cuda), w.to(cuda), seeds.to(cuda), 8, 0.02, target=target.to(cuda))
+    torch.cuda.synchronize()
+    assert int(lora_layer_bf16.last_error_flag) == 0
+    assert rel_err(got, want) <= 2e-3
+
+
+def test_unsupported_shape_is_rejected(cuda):
+    from evox_b200 import _cabi
+    from evox_b200.lora_kernels import lora_layer_bf16
+
+    h = torch.zeros(2, 48, 256, dtype=torch.bfloat16, device=cuda)
+    w = torch.zeros(256, 256, dtype=torch.bfloat16, device=cuda)
+    with pytest.raises(_cabi.EvoxKernelError):
+        lora_layer_bf16(h, w, torch.zeros(2, dtype=torch.int64, device=cuda), 0, 0.1)
