@@ -9,7 +9,7 @@ import torch
 
 from .. import _cabi
 from ..core import Algorithm, Mutable, Parameter
-from ..lora_kernels import compute_counter_offsets, generate_lora_factors, lora_gradient
+from ..lora_kernels import compute_counter_offsets, lora_gradient_from_seeds
 
 
 def _update_center(algo, grad: torch.Tensor) -> None:
@@ -130,12 +130,10 @@ class VirtualLoRAES(_ESBase):
         self.seeds = torch.randint(0, 2**31, (self.pop_size,), device=dev, dtype=torch.int64) if seeds is None else seeds.to(dev)
         sigma = self.sigma()
         fitness = self.evaluate((self.center, self.seeds, sigma)).to(torch.float32).contiguous()
-        parts = []
+        grad = torch.empty(self.dim, dtype=torch.float32, device=dev)
+        start = 0
         for shape, offset in zip(self.param_shapes, self.counter_offsets):
-            factors = generate_lora_factors(self.seeds, shape, self.lora_rank, offset)
-            if isinstance(factors, tuple):
-                a, b = factors
-                parts.append(lora_gradient(fitness, a, b, self.pop_size, sigma, shape).reshape(-1))
-            else:
-                parts.append(lora_gradient(fitness, factors, None, self.pop_size, sigma, shape).reshape(-1))
-        _update_center(self, torch.cat(parts))
+            n = int(torch.tensor(shape).prod())
+            lora_gradient_from_seeds(fitness, self.seeds, shape, self.lora_rank, offset, self.pop_size, sigma, out=grad[start : start + n])
+            start += n
+        _update_center(self, grad)

@@ -57,6 +57,18 @@ struct GemmArgs {
   const float* target;      // [batch][N] or null: write row_partial instead of the output
   float* row_partial;       // [M][N / BN]
   int* error_flag;
+  // K schedule: the product is summed over n_combo passes; pass c reads the K range of length K that
+  // starts at column a_piece[c] * K of the first operand and b_piece[c] * K of the second (split-
+  // precision products); the plain layer uses one pass over piece 0.
+  int n_combo;
+  int a_piece[6];
+  int b_piece[6];
+  float out_scale;
+  long long ld_out;         // row stride of out_f32 (elements)
+  // The tensor core adds each K = 16 product into the fp32 accumulator with truncation, a bias that
+  // grows with the number of accumulations. With chunk_kblocks > 0 an accumulator only collects that
+  // many k-blocks; the epilogue then adds the chunks into out_f32 in round-to-nearest fp32.
+  int chunk_kblocks;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -179,6 +191,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   const long long n_tiles_n = a.N / BN;
   const long long n_tiles = (a.M / BM) * n_tiles_n;
   const int k_blocks = (int)(a.K / BK);
+  const int total_kb = k_blocks * a.n_combo;
+  const int chunk_kb = a.chunk_kblocks > 0 ? a.chunk_kblocks : total_kb;
+  const int n_chunks = (total_kb + chunk_kb - 1) / chunk_kb;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -209,14 +224,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       bool ok = true;
       for (long long tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
         const int m0 = (int)((tile / n_tiles_n) * BM), n0 = (int)((tile % n_tiles_n) * BN);
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        for (int kb = 0; kb < k_blocks * a.n_combo; ++kb) {
           if (!mbar_wait(empty_bar(s), ph ^ 1u, a.error_flag, 1)) {
             ok = false;
             break;
           }
+          const int combo = kb / k_blocks, kk = kb - combo * k_blocks;
           mbar_expect_tx(full_bar(s), kStageBytes);
-          tma_load_2d(smem_base + s * kStageBytes, &map_h, full_bar(s), kb * BK, m0);
-          tma_load_2d(smem_base + s * kStageBytes + kBytesA, &map_w, full_bar(s), kb * BK, n0);
+          tma_load_2d(smem_base + s * kStageBytes, &map_h, full_bar(s), (int)(a.a_piece[combo] * a.K) + kk * BK, m0);
+          tma_load_2d(smem_base + s * kStageBytes + kBytesA, &map_w, full_bar(s), (int)(a.b_piece[combo] * a.K) + kk * BK, n0);
           issued |= 1u << s;
           if (++s == STAGES) {
             s = 0;
@@ -244,30 +260,36 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       uint32_t ph = 0;
       long long it = 0;
       bool ok = true;
-      for (long long tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++it) {
-        const int buf = (int)(it & 1);
-        const uint32_t acc_ph = (uint32_t)((it >> 1) & 1);
-        if (!mbar_wait(tempty_bar(buf), acc_ph ^ 1u, a.error_flag, 2)) break;
-        fence_after_sync();
-        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
-        for (int kb = 0; kb < k_blocks; ++kb) {
-          if (!mbar_wait(full_bar(s), ph, a.error_flag, 3)) {
+      for (long long tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+        for (int chunk = 0; chunk < n_chunks && ok; ++chunk, ++it) {
+          const int buf = (int)(it & 1);
+          const uint32_t acc_ph = (uint32_t)((it >> 1) & 1);
+          if (!mbar_wait(tempty_bar(buf), acc_ph ^ 1u, a.error_flag, 2)) {
             ok = false;
             break;
           }
           fence_after_sync();
-          const uint32_t sa = smem_base + s * kStageBytes, sb = sa + kBytesA;
+          const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
+          const int kb0 = chunk * chunk_kb, kb1 = min(kb0 + chunk_kb, total_kb);
+          for (int kb = kb0; kb < kb1; ++kb) {
+            if (!mbar_wait(full_bar(s), ph, a.error_flag, 3)) {
+              ok = false;
+              break;
+            }
+            fence_after_sync();
+            const uint32_t sa = smem_base + s * kStageBytes, sb = sa + kBytesA;
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k) {
-            umma_bf16(d_tmem, umma_desc(sa + k * 32), umma_desc(sb + k * 32), (kb > 0 || k > 0) ? 1u : 0u);
+            for (int k = 0; k < BK / 16; ++k) {
+              umma_bf16(d_tmem, umma_desc(sa + k * 32), umma_desc(sb + k * 32), (kb > kb0 || k > 0) ? 1u : 0u);
+            }
+            umma_commit(empty_bar(s));  // stage reusable once these products have read it
+            if (++s == STAGES) {
+              s = 0;
+              ph ^= 1u;
+            }
           }
-          umma_commit(empty_bar(s));  // stage reusable once these products have read it
-          if (++s == STAGES) {
-            s = 0;
-            ph ^= 1u;
-          }
+          if (ok) umma_commit(tfull_bar(buf));  // accumulator complete
         }
-        if (ok) umma_commit(tfull_bar(buf));  // accumulator complete
       }
     }
   } else {
@@ -278,12 +300,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     const int inds_per_tile = (a.batch >= BM) ? 1 : (int)(BM / a.batch);
     long long it = 0;
     bool ok = true;
-    for (long long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++it) {
+    for (long long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
       const long long m0 = (tile / n_tiles_n) * BM;
       const int n_blk = (int)(tile % n_tiles_n);
       const long long n0 = (long long)n_blk * BN;
-      const int buf = (int)(it & 1);
-      const uint32_t acc_ph = (uint32_t)((it >> 1) & 1);
       const long long p_first = m0 / a.batch;
       // all epilogue threads are done with the previous tile's factors
       asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -317,6 +337,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         tr[4] = t1.x; tr[5] = t1.y; tr[6] = t1.z; tr[7] = t1.w;
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");
+      for (int chunk = 0; chunk < n_chunks; ++chunk, ++it) {
+      const int buf = (int)(it & 1);
+      const uint32_t acc_ph = (uint32_t)((it >> 1) & 1);
       if (ok && !mbar_wait(tfull_bar(buf), acc_ph, a.error_flag, 4)) ok = false;
       if (!ok) continue;  // keep the named barriers balanced, skip the work
       fence_after_sync();
@@ -331,7 +354,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         float y[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
-          float acc = __uint_as_float(v[j]);
+          float acc = __uint_as_float(v[j]) * a.out_scale;
           if (a.bias) acc += __ldg(a.bias + n0 + c + j);
           if (a.t != nullptr) {
             const float4 b0 = *reinterpret_cast<const float4*>(bf + (size_t)(c + j) * RANK);
@@ -369,14 +392,22 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             *reinterpret_cast<uint4*>(o + j) = pk;
           }
         } else {
-          float* o = a.out_f32 + row * a.N + n0 + c;
+          float* o = a.out_f32 + row * a.ld_out + n0 + c;
 #pragma unroll
-          for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(o + j) = make_float4(y[j], y[j + 1], y[j + 2], y[j + 3]);
+          for (int j = 0; j < 32; j += 4) {
+            float4 r = make_float4(y[j], y[j + 1], y[j + 2], y[j + 3]);
+            if (chunk > 0) {  // later chunks of the same tile: fp32 round-to-nearest accumulation
+              const float4 prev = *reinterpret_cast<const float4*>(o + j);
+              r = make_float4(prev.x + r.x, prev.y + r.y, prev.z + r.z, prev.w + r.w);
+            }
+            *reinterpret_cast<float4*>(o + j) = r;
+          }
         }
       }
       if (target_row) a.row_partial[row * n_tiles_n + n_blk] = sq_sum;
       fence_before_sync();
       mbar_arrive(tempty_bar(buf));  // this thread no longer reads the accumulator
+      }
     }
   }
   fence_before_sync();
@@ -443,6 +474,61 @@ __global__ void neg_mse_kernel(const float* __restrict__ row_partial, long long 
   const float* rp = row_partial + p * batch * tiles_n;
   for (long long i = 0; i < batch * tiles_n; ++i) s += rp[i];
   fitness[p] = -s / (float)(batch * N);
+}
+
+// fp32 -> three bf16 pieces with x = hi + mid + lo (each piece rounds what the previous ones left).
+__device__ __forceinline__ void split3(float x, __nv_bfloat16& hi, __nv_bfloat16& mid, __nv_bfloat16& lo) {
+  hi = __float2bfloat16_rn(x);
+  const float r1 = x - __bfloat162float(hi);
+  mid = __float2bfloat16_rn(r1);
+  lo = __float2bfloat16_rn(r1 - __bfloat162float(mid));
+}
+
+// Operands of the population gradient sum_i f_i B_i A_i as two K-major matrices over K = pop * 8:
+//   bf3[j][piece * K + i * 8 + q] = piece of (f_i * B_i[j][q]),   j < d
+//   at3[l][piece * K + i * 8 + q] = piece of A_i[q][l],            l < k
+// with the factors regenerated from the seeds (lora_noise.py:118-125) and split into three bf16
+// pieces so that six tensor-core passes reproduce the fp32 product (see evox_lora_gradient_tc).
+__global__ void __launch_bounds__(256)
+    lora_grad_pack_kernel(const float* __restrict__ fitness, const long long* __restrict__ seeds, unsigned long long a_counter,
+                          unsigned long long b_counter, long long pop, long long d, long long k, __nv_bfloat16* __restrict__ bf3,
+                          __nv_bfloat16* __restrict__ at3) {
+  const long long Kt = pop * RANK;
+  const long long n_b = pop * d;          // one task per (i, j): 8 values of B_i[j][:]
+  const long long n_a = pop * (k / 4);    // one task per (i, l / 4): 8 x 4 values of A_i[:][l..l+3]
+  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < n_b + n_a; t += (long long)gridDim.x * blockDim.x) {
+    if (t < n_b) {
+      const long long i = t / d, j = t - i * d;
+      const unsigned long long seed = (unsigned long long)seeds[i];
+      const float f = fitness[i];
+      const float4 z0 = normal4(seed, b_counter, (uint32_t)(2 * j)), z1 = normal4(seed, b_counter, (uint32_t)(2 * j + 1));
+      const float v[8] = {z0.x * f, z0.y * f, z0.z * f, z0.w * f, z1.x * f, z1.y * f, z1.z * f, z1.w * f};
+      __align__(16) __nv_bfloat16 p[3][8];
+#pragma unroll
+      for (int q = 0; q < 8; ++q) split3(v[q], p[0][q], p[1][q], p[2][q]);
+#pragma unroll
+      for (int c = 0; c < 3; ++c)
+        *reinterpret_cast<uint4*>(bf3 + j * (3 * Kt) + c * Kt + i * RANK) = *reinterpret_cast<const uint4*>(p[c]);
+    } else {
+      const long long u = t - n_b;
+      const long long i = u / (k / 4), l4 = u - i * (k / 4);
+      const unsigned long long seed = (unsigned long long)seeds[i];
+      __align__(16) __nv_bfloat16 p[4][3][8];  // [row l..l+3][piece][q]
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        const float4 z = normal4(seed, a_counter, (uint32_t)(((long long)q * k) / 4 + l4));
+        split3(z.x, p[0][0][q], p[0][1][q], p[0][2][q]);
+        split3(z.y, p[1][0][q], p[1][1][q], p[1][2][q]);
+        split3(z.z, p[2][0][q], p[2][1][q], p[2][2][q]);
+        split3(z.w, p[3][0][q], p[3][1][q], p[3][2][q]);
+      }
+#pragma unroll
+      for (int r = 0; r < 4; ++r)
+#pragma unroll
+        for (int c = 0; c < 3; ++c)
+          *reinterpret_cast<uint4*>(at3 + (l4 * 4 + r) * (3 * Kt) + c * Kt + i * RANK) = *reinterpret_cast<const uint4*>(p[r][c]);
+    }
+  }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -536,6 +622,11 @@ extern "C" int evox_lora_gemm_bf16(const void* h, const void* w, const float* bi
   a.target = target;
   a.row_partial = row_partial;
   a.error_flag = error_flag;
+  a.n_combo = 1;
+  for (int c = 0; c < 6; ++c) a.a_piece[c] = a.b_piece[c] = 0;
+  a.out_scale = 1.0f;
+  a.ld_out = d;
+  a.chunk_kblocks = 0;
   CUtensorMap map_h, map_w;
   if (int rc = make_map(&map_h, h, a.M, k, BM)) return rc;
   if (int rc = make_map(&map_w, w, d, k, BN)) return rc;
@@ -554,6 +645,74 @@ extern "C" int evox_neg_mse_from_partials(const float* row_partial, int64_t pop,
   EVOX_REQUIRE(pop > 0 && batch > 0 && d > 0 && d % BN == 0, EVOX_ERR_INVALID, "neg_mse_from_partials: bad sizes");
   neg_mse_kernel<<<(unsigned)((pop + 127) / 128), 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(row_partial, batch, d / BN, d, pop,
                                                                                                  fitness);
+  EVOX_LAUNCH_CHECK();
+  return EVOX_OK;
+}
+
+extern "C" size_t evox_lora_gradient_tc_workspace_bytes(int64_t pop, int64_t d, int64_t k) {
+  if (pop <= 0 || d <= 0 || k <= 0) return 0;
+  return (size_t)(d + k) * 3 * (size_t)pop * RANK * sizeof(__nv_bfloat16) + 512;
+}
+
+extern "C" int evox_lora_gradient_tc_supported(int64_t pop, int64_t d, int64_t k, int32_t r) {
+  return (r == RANK && pop > 0 && (pop * RANK) % BK == 0 && d % BM == 0 && k % BN == 0 && 3 * pop * RANK < (1ll << 31)) ? 1 : 0;
+}
+
+extern "C" int evox_lora_gradient_tc(const float* fitness, const int64_t* seeds, uint64_t counter, int64_t pop, float sigma,
+                                     int64_t d, int64_t k, int32_t r, float* grad, void* workspace, size_t workspace_bytes,
+                                     int32_t* error_flag, void* stream) {
+  EVOX_REQUIRE(fitness && seeds && grad && workspace && error_flag, EVOX_ERR_INVALID, "lora_gradient_tc: NULL pointer");
+  EVOX_REQUIRE(evox_lora_gradient_tc_supported(pop, d, k, r), EVOX_ERR_INVALID,
+               "lora_gradient_tc: shape (pop %lld, d %lld, k %lld, r %d) is not supported", (long long)pop, (long long)d, (long long)k, r);
+  EVOX_REQUIRE(workspace_bytes >= evox_lora_gradient_tc_workspace_bytes(pop, d, k), EVOX_ERR_WORKSPACE, "lora_gradient_tc: workspace too small");
+  EVOX_REQUIRE(((uintptr_t)workspace & 255u) == 0, EVOX_ERR_INVALID, "lora_gradient_tc: workspace must be 256-byte aligned");
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const long long Kt = pop * RANK;
+  __nv_bfloat16* bf3 = reinterpret_cast<__nv_bfloat16*>(workspace);
+  __nv_bfloat16* at3 = bf3 + (size_t)d * 3 * Kt;  // d * 3 * Kt * 2 bytes is a multiple of 256
+  const unsigned long long b_counter = counter + (unsigned long long)((RANK * k + 3) / 4 * 4);
+  const long long tasks = pop * d + pop * (k / 4);
+  long long blocks = (tasks + 255) / 256;
+  const long long cap = (long long)sm_count() * 16;
+  lora_grad_pack_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, s>>>(fitness, (const long long*)seeds, counter, b_counter,
+                                                                               pop, d, k, bf3, at3);
+  EVOX_LAUNCH_CHECK();
+  GemmArgs a;
+  a.M = d;
+  a.N = k;
+  a.K = Kt;
+  a.batch = BM;
+  a.bias = nullptr;
+  a.t = nullptr;
+  a.seeds = (const long long*)seeds;
+  a.b_counter = 0;
+  a.noise_counter = 0;
+  a.has_bias_noise = 0;
+  a.sigma = 0.f;
+  a.relu = 0;
+  a.out_bf16 = nullptr;
+  a.out_f32 = grad;
+  a.target = nullptr;
+  a.row_partial = nullptr;
+  a.error_flag = error_flag;
+  // x = hi + mid + lo for both operands; keep every product down to 2^-24 of the largest one
+  static const int pa[6] = {0, 0, 1, 0, 2, 1}, pb[6] = {0, 1, 0, 2, 0, 1};
+  a.n_combo = 6;
+  for (int c = 0; c < 6; ++c) {
+    a.a_piece[c] = pa[c];
+    a.b_piece[c] = pb[c];
+  }
+  a.out_scale = 1.0f / ((float)pop * sigma);
+  a.ld_out = k;
+  a.chunk_kblocks = 32;  // 128 truncating accumulations per accumulator at most
+  CUtensorMap map_a, map_b;
+  if (int rc = make_map(&map_a, bf3, d, 3 * Kt, BM)) return rc;
+  if (int rc = make_map(&map_b, at3, k, 3 * Kt, BN)) return rc;
+  EVOX_CUDA(cudaFuncSetAttribute(lora_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+  const long long n_tiles = (a.M / BM) * (a.N / BN);
+  long long grid = sm_count();
+  if (grid > n_tiles) grid = n_tiles;
+  lora_gemm_kernel<<<(unsigned)grid, kGemmThreads, kSmemBytes, s>>>(map_a, map_b, a);
   EVOX_LAUNCH_CHECK();
   return EVOX_OK;
 }

@@ -14,8 +14,10 @@ from . import _cabi
 
 __all__ = [
     "philox_uniform", "philox_normal", "compute_counter_offsets", "generate_lora_factors",
-    "lora_delta_output", "lora_gradient",
+    "lora_delta_output", "lora_gradient", "lora_gradient_from_seeds", "lora_layer_bf16",
 ]
+
+_grad_ws: dict[torch.device, torch.Tensor] = {}
 
 
 def _seeds(seeds: torch.Tensor) -> torch.Tensor:
@@ -157,3 +159,39 @@ def lora_layer_bf16(h: torch.Tensor, w: torch.Tensor, seeds: torch.Tensor, count
         _cabi.check(lib.evox_neg_mse_from_partials(_cabi.ptr(partial), pop, batch, d, _cabi.ptr(fitness), s))
         return fitness
     return out_bf16 if out_bf16 is not None else out_f32
+
+
+def lora_gradient_from_seeds(fitness: torch.Tensor, seeds: torch.Tensor, weight_shape: tuple, rank: int, counter: int,
+                             pop_size: int, sigma: float, out: torch.Tensor | None = None) -> torch.Tensor:
+    """`lora_gradient(fitness, *generate_lora_factors(seeds, weight_shape, rank, counter), ...)` without
+    the factors ever existing in fp32: on supported shapes the tensor-core kernel regenerates them;
+    otherwise this falls back to generating them and calling `lora_gradient`. `out`: optional flat
+    fp32 destination of prod(weight_shape) elements."""
+    fitness = fitness.float().contiguous()
+    seeds = _seeds(seeds)
+    dev = fitness.device
+    n = int(math.prod(weight_shape))
+    if out is None:
+        out = torch.empty(n, dtype=torch.float32, device=dev)
+    if len(weight_shape) >= 2:
+        d, k = _as_2d(weight_shape)
+        if _cabi.lib.evox_lora_gradient_tc_supported(pop_size, d, k, rank) and out.data_ptr() % 16 == 0:
+            nbytes = _cabi.lib.evox_lora_gradient_tc_workspace_bytes(pop_size, d, k)
+            ws = _grad_ws.get(dev)
+            if ws is None or ws.numel() < nbytes:
+                ws = _grad_ws[dev] = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+            err = torch.zeros(1, dtype=torch.int32, device=dev)
+            _cabi.check(
+                _cabi.lib.evox_lora_gradient_tc(
+                    _cabi.ptr(fitness), _cabi.ptr(seeds), counter, pop_size, float(sigma), d, k, rank, _cabi.ptr(out),
+                    _cabi.ptr(ws), ws.numel(), _cabi.ptr(err), _cabi.stream_ptr(dev),
+                )
+            )
+            lora_gradient_from_seeds.last_error_flag = err
+            return out.view(weight_shape)
+        a, b = generate_lora_factors(seeds, weight_shape, rank, counter)
+        out.copy_(lora_gradient(fitness, a, b, pop_size, sigma, weight_shape).reshape(-1))
+        return out.view(weight_shape)
+    noise = generate_lora_factors(seeds, weight_shape, rank, counter)
+    out.copy_(lora_gradient(fitness, noise, None, pop_size, sigma, weight_shape).reshape(-1))
+    return out.view(weight_shape)

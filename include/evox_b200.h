@@ -252,6 +252,19 @@ int evox_lora_gemm_bf16(const void* h, const void* w, const float* bias, const f
                         int64_t d, int32_t r, int32_t relu, void* out_bf16, float* out_f32,
                         const float* target, float* row_partial, int32_t* error_flag, void* stream);
 
+/* Population gradient of a 2-D block on the tensor cores without materialising fp32 factors:
+ *   grad (d x k, fp32) = sum_i fitness_i B_i A_i / (pop * sigma)       (lora_noise.py:157-196)
+ * with A_i, B_i regenerated from seeds / counter as generate_lora_factors does. The kernel
+ * writes f_i B_i and A_i as three bf16 pieces each (x = hi + mid + lo) into the workspace and sums
+ * six tcgen05 passes (hi hi, hi mid, mid hi, hi lo, lo hi, mid mid) in fp32, which keeps the
+ * result within fp32 rounding of the reference's einsum. Needs rank 8, d a multiple of 128, k a
+ * multiple of 256, pop a multiple of 8 (evox_lora_gradient_tc_supported). error_flag as above. */
+size_t evox_lora_gradient_tc_workspace_bytes(int64_t pop, int64_t d, int64_t k);
+int evox_lora_gradient_tc_supported(int64_t pop, int64_t d, int64_t k, int32_t r);
+int evox_lora_gradient_tc(const float* fitness, const int64_t* seeds, uint64_t counter, int64_t pop,
+                          float sigma, int64_t d, int64_t k, int32_t r, float* grad, void* workspace,
+                          size_t workspace_bytes, int32_t* error_flag, void* stream);
+
 /* fitness (pop) = -(sum of an individual's row_partial entries) / (batch * d): negative mean
  * squared error of the last layer, summed in a fixed order. */
 int evox_neg_mse_from_partials(const float* row_partial, int64_t pop, int64_t batch, int64_t d,

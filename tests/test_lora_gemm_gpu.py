@@ -80,3 +80,19 @@ def test_unsupported_shape_is_rejected(cuda):
     w = torch.zeros(256, 256, dtype=torch.bfloat16, device=cuda)
     with pytest.raises(_cabi.EvoxKernelError):
         lora_layer_bf16(h, w, torch.zeros(2, dtype=torch.int64, device=cuda), 0, 0.1)
+
+
+@pytest.mark.parametrize("pop,d,k", [(8, 128, 256), (64, 256, 512), (256, 512, 256), (1024, 256, 512)])
+def test_tensor_core_gradient_vs_fp32(cuda, pop, d, k):
+    """Split-precision tensor-core gradient against the fp32 einsum: 1e-5 of the largest entry."""
+    from evox_b200.lora_kernels import lora_gradient_from_seeds
+
+    g = torch.Generator().manual_seed(d + k)
+    seeds = torch.randint(0, 2**31, (pop,), generator=g, dtype=torch.int64)
+    fit = torch.rand(pop, generator=g) - 0.5
+    a, b = lora.generate_lora_factors(seeds, (d, k), 8, 24)
+    want = torch.einsum("i,ijk,ikl->jl", fit.double(), b.double(), a.double()) / (pop * 0.02)
+    got = lora_gradient_from_seeds(fit.to(cuda), seeds.to(cuda), (d, k), 8, 24, pop, 0.02)
+    torch.cuda.synchronize()
+    assert int(lora_gradient_from_seeds.last_error_flag) == 0
+    assert rel_err(got, want) <= 1e-5
