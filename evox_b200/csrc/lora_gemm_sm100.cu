@@ -419,49 +419,85 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 }
 
 // t[p][b][q] = sum_k H[p][b][k] * A_p[q][k] with A_p regenerated from the seed (never stored).
-// One block per individual; 256 threads; K is walked in chunks of 256 columns staged in shared memory.
+// One block of 256 threads per individual. K is walked in chunks of 128 columns: the chunk of A_p
+// (8 x 128 normals) and of H_p (batch x 128, widened to fp32) are staged in shared memory; thread
+// (row group g, column slice c) accumulates 4 rows x 8 factors over 8 interleaved columns, so every pair of
+// shared-memory loads feeds 32 / 12 multiply-adds; the 16 column slices are folded with shuffles at the end.
 __global__ void __launch_bounds__(256)
     lora_down_bf16_kernel(const __nv_bfloat16* __restrict__ h, const long long* __restrict__ seeds, unsigned long long a_counter,
                           long long batch, long long K, float* __restrict__ t) {
-  constexpr int KC = 256;
+  constexpr int KC = 128;
   __shared__ float sA[RANK][KC + 4];
   extern __shared__ float sH[];  // [batch][KC + 1]
   const long long p = blockIdx.x;
   const unsigned long long seed = (unsigned long long)seeds[p];
   const int tid = threadIdx.x;
-  const int n_out = (int)batch * RANK;
-  float acc[4] = {0.f, 0.f, 0.f, 0.f};  // outputs tid, tid + 256, ... (batch * RANK <= 1024)
-  for (long long k0 = 0; k0 < K; k0 += KC) {
-    // A_p[q][k]: element q * K + k -> call (q * K + k) / 4 (K is a multiple of 4)
-    for (int idx = tid; idx < RANK * (KC / 4); idx += 256) {
-      const int q = idx / (KC / 4), c4 = idx - q * (KC / 4);
-      const float4 z = normal4(seed, a_counter, (uint32_t)(((long long)q * K + k0) / 4 + c4));
-      sA[q][c4 * 4 + 0] = z.x;
-      sA[q][c4 * 4 + 1] = z.y;
-      sA[q][c4 * 4 + 2] = z.z;
-      sA[q][c4 * 4 + 3] = z.w;
-    }
-    for (int idx = tid; idx < (int)batch * KC; idx += 256) {
-      const int b = idx / KC, c = idx - b * KC;
-      sH[b * (KC + 1) + c] = __bfloat162float(h[(p * batch + b) * K + k0 + c]);
-    }
-    __syncthreads();
+  const int slice = tid & 15, group = tid >> 4;     // 16 column slices x 16 row groups
+  const int n_pass = (int)((batch + 63) / 64);      // 64 rows (16 groups x 4) per pass
+  for (int pass = 0; pass < n_pass; ++pass) {
+    const int row0 = pass * 64 + group * 4;
+    float acc[4][RANK];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int o = tid + u * 256;
-      if (o < n_out) {
-        const int b = o / RANK, q = o - b * RANK;
-        float s = acc[u];
-        for (int c = 0; c < KC; ++c) s = fmaf(sH[b * (KC + 1) + c], sA[q][c], s);
-        acc[u] = s;
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+      for (int q = 0; q < RANK; ++q) acc[r][q] = 0.f;
+    for (long long k0 = 0; k0 < K; k0 += KC) {
+      // A_p[q][k]: element q * K + k of the stream -> Philox call (q * K + k) / 4 (K is a multiple of 4)
+      {
+        const int q = tid >> 5, c4 = tid & 31;  // 8 x 32 calls cover the 8 x 128 chunk
+        const float4 z = normal4(seed, a_counter, (uint32_t)(((long long)q * K + k0) / 4 + c4));
+        sA[q][c4 * 4 + 0] = z.x;
+        sA[q][c4 * 4 + 1] = z.y;
+        sA[q][c4 * 4 + 2] = z.z;
+        sA[q][c4 * 4 + 3] = z.w;
+      }
+      for (int idx = tid; idx < 64 * (KC / 2); idx += 256) {
+        const int b = idx / (KC / 2), c2 = idx - b * (KC / 2);
+        const long long row = (long long)pass * 64 + b;
+        float2 v = make_float2(0.f, 0.f);
+        if (row < batch) v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(h + (p * batch + row) * K + k0 + 2 * c2));
+        sH[b * (KC + 1) + 2 * c2] = v.x;
+        sH[b * (KC + 1) + 2 * c2 + 1] = v.y;
+      }
+      __syncthreads();
+#pragma unroll
+      for (int cc = 0; cc < 8; ++cc) {
+        const int c = cc * 16 + slice;  // lanes of a slice group read consecutive banks
+        float av[RANK], hv[4];
+#pragma unroll
+        for (int q = 0; q < RANK; ++q) av[q] = sA[q][c];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) hv[r] = sH[(group * 4 + r) * (KC + 1) + c];
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+#pragma unroll
+          for (int q = 0; q < RANK; ++q) acc[r][q] = fmaf(hv[r], av[q], acc[r][q]);
+      }
+      __syncthreads();
+    }
+    // fold the 16 column slices (lanes that differ in the low 4 bits)
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+      for (int q = 0; q < RANK; ++q) {
+        float v = acc[r][q];
+        v += __shfl_xor_sync(0xffffffffu, v, 1);
+        v += __shfl_xor_sync(0xffffffffu, v, 2);
+        v += __shfl_xor_sync(0xffffffffu, v, 4);
+        v += __shfl_xor_sync(0xffffffffu, v, 8);
+        acc[r][q] = v;
+      }
+    if (slice == 0) {
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const long long row = row0 + r;
+        if (row < batch) {
+          float* o = t + (p * batch + row) * RANK;
+          *reinterpret_cast<float4*>(o) = make_float4(acc[r][0], acc[r][1], acc[r][2], acc[r][3]);
+          *reinterpret_cast<float4*>(o + 4) = make_float4(acc[r][4], acc[r][5], acc[r][6], acc[r][7]);
+        }
       }
     }
-    __syncthreads();
-  }
-#pragma unroll
-  for (int u = 0; u < 4; ++u) {
-    const int o = tid + u * 256;
-    if (o < n_out) t[p * n_out + o] = acc[u];
   }
 }
 
@@ -582,10 +618,9 @@ extern "C" int evox_lora_gemm_supported(int64_t pop, int64_t batch, int64_t k, i
 extern "C" int evox_lora_down_bf16(const void* h, const int64_t* seeds, uint64_t a_counter, int64_t pop, int64_t batch,
                                    int64_t k, int32_t r, float* t, void* stream) {
   EVOX_REQUIRE(h && seeds && t, EVOX_ERR_INVALID, "lora_down_bf16: NULL pointer");
-  EVOX_REQUIRE(r == RANK && k % 256 == 0 && batch > 0 && batch * RANK <= 1024 && pop > 0, EVOX_ERR_INVALID,
-               "lora_down_bf16: needs rank 8, k a multiple of 256 and batch <= 128");
-  const size_t smem = sizeof(float) * (size_t)batch * 257;
-  EVOX_CUDA(cudaFuncSetAttribute(lora_down_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  EVOX_REQUIRE(r == RANK && k % 128 == 0 && batch > 0 && pop > 0, EVOX_ERR_INVALID,
+               "lora_down_bf16: needs rank 8 and k a multiple of 128");
+  const size_t smem = sizeof(float) * 64 * 129;
   lora_down_bf16_kernel<<<(unsigned)pop, 256, smem, reinterpret_cast<cudaStream_t>(stream)>>>(
       (const __nv_bfloat16*)h, (const long long*)seeds, a_counter, batch, k, t);
   EVOX_LAUNCH_CHECK();

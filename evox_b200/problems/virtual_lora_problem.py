@@ -64,7 +64,11 @@ class VirtualLoRAProblem(Problem):
         n = int(torch.tensor(self.param_shapes[i]).prod())
         return center[self._starts[i] : self._starts[i] + n].view(self.param_shapes[i]), i
 
-    def _virtual_forward(self, inputs: torch.Tensor, center: torch.Tensor, seeds: torch.Tensor, sigma: float, pop_size: int) -> torch.Tensor:
+    def _virtual_forward(self, inputs: torch.Tensor, center: torch.Tensor, seeds: torch.Tensor, sigma: float, pop_size: int,
+                         mse_target: torch.Tensor | None = None):
+        """Activations of the last layer, (pop, batch, out) fp32. With `mse_target` (batch, out) and a
+        last Linear layer on the tensor-core path, the squared error is reduced inside that layer's
+        epilogue and a `("mse", per-individual mean squared error)` tuple is returned instead."""
         dev = center.device
         shared = inputs.ndim == 2
         h = inputs.to(device=dev).contiguous()
@@ -89,6 +93,10 @@ class VirtualLoRAProblem(Problem):
                         bias, bi = self._param(center, f"{name}.bias")
                         bias_counter = self.counter_offsets[bi]
                     last = pos + (2 if relu else 1) >= len(children)
+                    if last and not relu and mse_target is not None:
+                        neg = lora_layer_bf16(h.to(torch.bfloat16), weight.to(torch.bfloat16), seeds, self.counter_offsets[wi], sigma,
+                                              bias=bias, bias_counter=bias_counter, target=mse_target)
+                        return "mse", -neg
                     h = lora_layer_bf16(
                         h.to(torch.bfloat16), weight.to(torch.bfloat16), seeds, self.counter_offsets[wi], sigma, bias=bias,
                         bias_counter=bias_counter, relu=relu, out_dtype=torch.float32 if last else torch.bfloat16,
@@ -138,7 +146,12 @@ class VirtualLoRAProblem(Problem):
         for inputs, labels in batches:
             inputs = inputs.to(device=self.device, non_blocking=True)
             labels = labels.to(device=self.device, non_blocking=True)
-            logits = self._virtual_forward(inputs, center, seeds, sigma, pop_size)
+            fuse = (isinstance(self.criterion, nn.MSELoss) and self.criterion.reduction == "none" and labels.ndim == 2
+                    and self.reduction == "mean")
+            logits = self._virtual_forward(inputs, center, seeds, sigma, pop_size, mse_target=labels if fuse else None)
+            if isinstance(logits, tuple):  # the last layer already reduced (y - target)^2 per individual
+                per_individual.append(logits[1])
+                continue
             batch = logits.shape[1]
             flat_logits = logits.reshape(pop_size * batch, -1)
             if labels.ndim == 1:  # class labels shared by the population (virtual_lora_problem.py:247)

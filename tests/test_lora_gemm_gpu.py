@@ -96,3 +96,33 @@ def test_tensor_core_gradient_vs_fp32(cuda, pop, d, k):
     torch.cuda.synchronize()
     assert int(lora_gradient_from_seeds.last_error_flag) == 0
     assert rel_err(got, want) <= 1e-5
+
+
+def test_problem_bf16_path_with_fused_mse(cuda):
+    """VirtualLoRAProblem(compute_dtype=bf16): three tensor-core layers, the last one reducing the
+    squared error in its epilogue, against the fp32 oracle forward on the bf16-rounded operands."""
+    from torch import nn
+
+    from evox_b200.problems import VirtualLoRAProblem
+
+    g = torch.Generator().manual_seed(9)
+    pop, batch, width, rank, sigma = 4, 64, 256, 8, 0.05
+    layers = []
+    for i in range(3):
+        lin = nn.Linear(width, width, bias=False)
+        with torch.no_grad():
+            lin.weight.copy_((torch.randn(width, width, generator=g) / width**0.5).bfloat16().float())
+        layers += [lin] + ([nn.ReLU()] if i < 2 else [])
+    model = nn.Sequential(*layers)
+    x = torch.randn(pop, batch, width, generator=g).bfloat16()
+    target = torch.randn(batch, width, generator=g)
+    prob = VirtualLoRAProblem(model, [(x, target)], nn.MSELoss(reduction="none"), rank, device=cuda, compute_dtype=torch.bfloat16)
+    center = torch.cat([p.detach().reshape(-1) for p in model.parameters()])
+    seeds = torch.randint(0, 2**31, (pop,), generator=g, dtype=torch.int64)
+    got = prob.evaluate((center.to(cuda), seeds.to(cuda), sigma))
+    weights = [m.weight.detach() for m in model if isinstance(m, nn.Linear)]
+    # the oracle keeps activations in fp32; the kernel rounds them to bf16 between layers
+    out = lora.virtual_forward(x.float(), weights, [None] * 3, seeds, prob.counter_offsets, prob.param_shapes, rank, sigma)
+    want = ((out - target) ** 2).mean(dim=(1, 2))
+    assert got.shape == (pop,)
+    assert rel_err(got, want) <= 2e-2
