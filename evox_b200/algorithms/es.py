@@ -7,21 +7,31 @@ from typing import Literal
 
 import torch
 
+import torch.distributed as dist
+
 from .. import _cabi
 from ..core import Algorithm, Mutable, Parameter
 from ..lora_kernels import compute_counter_offsets, lora_gradient_from_seeds
+from ..sharding import group_info, shard_bounds
 
 
-def _update_center(algo, grad: torch.Tensor) -> None:
+def _update_center(algo, grad: torch.Tensor, start: int = 0, count: int | None = None) -> None:
+    """center[start : start + count] -= lr * grad (or the Adam step) — `grad` holds `count` values."""
     dev = algo.center.device
     adam = algo.optimizer == "adam"
+    count = algo.center.numel() - start if count is None else count
+    assert grad.numel() == count and grad.is_contiguous()
+
+    def at(t):
+        return None if t is None else _cabi.ptr(t, torch.float32) + 4 * start
+
     _cabi.check(
         _cabi.lib.evox_es_update(
-            _cabi.ptr(algo.center, torch.float32, "center"), _cabi.ptr(grad, torch.float32, "grad"),
+            at(algo.center), _cabi.ptr(grad, torch.float32, "grad"),
             _cabi.ptr(algo.learning_rate, torch.float32, "learning_rate"),
-            _cabi.ptr(algo.exp_avg) if adam else None, _cabi.ptr(algo.exp_avg_sq) if adam else None,
+            at(algo.exp_avg) if adam else None, at(algo.exp_avg_sq) if adam else None,
             _cabi.ptr(algo.beta1) if adam else None, _cabi.ptr(algo.beta2) if adam else None,
-            1e-8, algo.center.numel(), _cabi.stream_ptr(dev),
+            1e-8, count, _cabi.stream_ptr(dev),
         )
     )
 
@@ -109,9 +119,16 @@ class VirtualLoRAES(_ESBase):
         noise_stdev: float,
         optimizer: Literal["adam"] | None = None,
         device: torch.device | None = None,
+        shard: bool = False,
+        group=None,
     ):
+        """`shard=True` (under an initialised torch.distributed group): every rank keeps the whole
+        centre, but the gradient and update of each 2-D block are computed for this rank's rows only
+        and the updated rows are allgathered; seeds are broadcast from rank 0 each generation."""
         super().__init__()
         device = torch.get_default_device() if device is None else torch.device(device)
+        self.group = group
+        self.rank, self.world_size = group_info(group) if shard else (0, 1)
         assert lora_rank > 0, "lora_rank must be greater than 0."
         self._common_init(pop_size, center_init, learning_rate, noise_stdev, optimizer, device)
         self.param_shapes = [tuple(s) for s in param_shapes]
@@ -128,12 +145,36 @@ class VirtualLoRAES(_ESBase):
         instead of fresh torch.randint draws."""
         dev = self.center.device
         self.seeds = torch.randint(0, 2**31, (self.pop_size,), device=dev, dtype=torch.int64) if seeds is None else seeds.to(dev)
+        if self.world_size > 1:
+            dist.broadcast(self.seeds, src=dist.get_global_rank(self.group, 0) if self.group is not None else 0, group=self.group)
         sigma = self.sigma()
         fitness = self.evaluate((self.center, self.seeds, sigma)).to(torch.float32).contiguous()
-        grad = torch.empty(self.dim, dtype=torch.float32, device=dev)
         start = 0
         for shape, offset in zip(self.param_shapes, self.counter_offsets):
             n = int(torch.tensor(shape).prod())
-            lora_gradient_from_seeds(fitness, self.seeds, shape, self.lora_rank, offset, self.pop_size, sigma, out=grad[start : start + n])
+            rows = self._row_shard(shape)
+            if rows is None:  # whole block on every rank (identical arithmetic everywhere)
+                grad = torch.empty(n, dtype=torch.float32, device=dev)
+                lora_gradient_from_seeds(fitness, self.seeds, shape, self.lora_rank, offset, self.pop_size, sigma, out=grad)
+                _update_center(self, grad, start, n)
+            else:
+                r0, r1 = rows
+                k = int(shape[-1])
+                grad = torch.empty((r1 - r0) * k, dtype=torch.float32, device=dev)
+                lora_gradient_from_seeds(fitness, self.seeds, shape, self.lora_rank, offset, self.pop_size, sigma, out=grad, rows=rows)
+                _update_center(self, grad, start + r0 * k, (r1 - r0) * k)
+                block = self.center[start : start + n]
+                dist.all_gather_into_tensor(block, block[r0 * k : r1 * k].clone(), group=self.group)
             start += n
-        _update_center(self, grad)
+
+    def _row_shard(self, shape) -> tuple[int, int] | None:
+        """This rank's rows of a 2-D block, or None when the block is not sharded (1-D blocks, a
+        single rank, or row counts the tensor-core gradient cannot split evenly)."""
+        if self.world_size == 1 or len(shape) < 2:
+            return None
+        d = int(torch.tensor(shape[:-1]).prod())
+        if d % (128 * self.world_size) != 0:
+            return None
+        if not _cabi.lib.evox_lora_gradient_tc_supported(self.pop_size, d // self.world_size, int(shape[-1]), self.lora_rank):
+            return None
+        return shard_bounds(d, self.world_size, self.rank)

@@ -32,7 +32,9 @@ namespace evox {
 namespace {
 
 constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4, RANK = 8;
-constexpr int kGemmThreads = 192;
+constexpr int kEpilogueWarps = 8;  // two warps per TMEM lane quarter, 128 columns each
+constexpr int kEpilogueThreads = kEpilogueWarps * 32;
+constexpr int kGemmThreads = 64 + kEpilogueThreads;
 constexpr uint32_t kBytesA = BM * BK * 2, kBytesB = BN * BK * 2, kStageBytes = kBytesA + kBytesB;
 constexpr uint32_t kMaxInd = 2;  // individuals per 128-row tile (batch is a multiple of 64)
 constexpr uint32_t kOffBfac = STAGES * kStageBytes;                  // float [kMaxInd][BN][RANK]
@@ -165,12 +167,17 @@ __device__ __forceinline__ float4 normal4(unsigned long long seed, unsigned long
   const uint4 r = philox4x32_10((uint32_t)counter + call, (uint32_t)(counter >> 32), 0u, 0u, (uint32_t)seed,
                                 (uint32_t)(seed >> 32));
   const float u0 = u24_to_unit(r.x), u1 = u24_to_unit(r.y), u2 = u24_to_unit(r.z), u3 = u24_to_unit(r.w);
-  const float r0 = sqrtf(__fmul_rn(-2.0f, logf(fmaxf(u0, 1e-10f))));
-  const float r1 = sqrtf(__fmul_rn(-2.0f, logf(fmaxf(u2, 1e-10f))));
+  // hardware log / sin / cos: the angle is first brought into [-pi, pi), where their absolute
+  // error is about 2^-21; the normals agree with philox_normal's to ~1e-6
+  const float r0 = sqrtf(-2.0f * __logf(fmaxf(u0, 1e-10f)));
+  const float r1 = sqrtf(-2.0f * __logf(fmaxf(u2, 1e-10f)));
+  float a0 = 6.283185307179586f * u1, a1 = 6.283185307179586f * u3;
+  if (a0 >= 3.14159265358979f) a0 -= 6.283185307179586f;
+  if (a1 >= 3.14159265358979f) a1 -= 6.283185307179586f;
   float s0, c0, s1, c1;
-  sincosf(__fmul_rn(6.283185307179586f, u1), &s0, &c0);
-  sincosf(__fmul_rn(6.283185307179586f, u3), &s1, &c1);
-  return make_float4(__fmul_rn(r0, c0), __fmul_rn(r0, s0), __fmul_rn(r1, c1), __fmul_rn(r1, s1));
+  __sincosf(a0, &s0, &c0);
+  __sincosf(a1, &s1, &c1);
+  return make_float4(r0 * c0, r0 * s0, r1 * c1, r1 * s1);
 }
 
 __global__ void __launch_bounds__(kGemmThreads, 1)
@@ -202,7 +209,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(tfull_bar(b), 1);
-      mbar_init(tempty_bar(b), 128);
+      mbar_init(tempty_bar(b), kEpilogueThreads);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -293,10 +300,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       }
     }
   } else {
-    // ------------------------------- epilogue (128 threads) --------------------------------
+    // ------------------------------- epilogue (256 threads) --------------------------------
     const int quarter = warp & 3;           // TMEM lanes this warp may read
+    const int col_half = (warp - 2) >> 2;   // which 128 of the tile's 256 columns this warp handles
     const int row_in_tile = quarter * 32 + lane;
-    const int et = threadIdx.x - 64;        // 0..127 within the epilogue group
+    const int et = threadIdx.x - 64;        // 0..255 within the epilogue group
     const int inds_per_tile = (a.batch >= BM) ? 1 : (int)(BM / a.batch);
     long long it = 0;
     bool ok = true;
@@ -306,10 +314,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       const long long n0 = (long long)n_blk * BN;
       const long long p_first = m0 / a.batch;
       // all epilogue threads are done with the previous tile's factors
-      asm volatile("bar.sync 1, 128;" ::: "memory");
+      asm volatile("bar.sync 1, 256;" ::: "memory");
       if (a.t != nullptr) {
         // B_p[n][q], q = 0..7: elements n * 8 + q of the stream -> Philox calls 2n and 2n + 1
-        for (int idx = et; idx < inds_per_tile * BN * 2; idx += 128) {
+        for (int idx = et; idx < inds_per_tile * BN * 2; idx += kEpilogueThreads) {
           const int ind = idx / (BN * 2), rest = idx - ind * (BN * 2);
           const int col = rest >> 1, half = rest & 1;
           const unsigned long long seed = (unsigned long long)a.seeds[p_first + ind];
@@ -318,7 +326,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         }
       }
       if (a.has_bias_noise) {
-        for (int idx = et; idx < inds_per_tile * (BN / 4); idx += 128) {
+        for (int idx = et; idx < inds_per_tile * (BN / 4); idx += kEpilogueThreads) {
           const int ind = idx / (BN / 4), c4 = idx - ind * (BN / 4);
           const unsigned long long seed = (unsigned long long)a.seeds[p_first + ind];
           const float4 z = normal4(seed, a.noise_counter, (uint32_t)((n0 >> 2) + c4));
@@ -336,7 +344,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         tr[0] = t0.x; tr[1] = t0.y; tr[2] = t0.z; tr[3] = t0.w;
         tr[4] = t1.x; tr[5] = t1.y; tr[6] = t1.z; tr[7] = t1.w;
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
+      asm volatile("bar.sync 1, 256;" ::: "memory");
       for (int chunk = 0; chunk < n_chunks; ++chunk, ++it) {
       const int buf = (int)(it & 1);
       const uint32_t acc_ph = (uint32_t)((it >> 1) & 1);
@@ -347,7 +355,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       const float* bn = bnoise + (size_t)my_ind * BN;
       const float* target_row = a.target ? a.target + (row % a.batch) * a.N + n0 : nullptr;
       float sq_sum = 0.f;
-      for (int c = 0; c < BN; c += 32) {
+      for (int c = col_half * (BN / 2); c < (col_half + 1) * (BN / 2); c += 32) {
         uint32_t v[32];
         tmem_ld32(tmem_base + (uint32_t)(buf * BN + c) + ((uint32_t)(quarter * 32) << 16), v);
         tmem_ld_wait();
@@ -404,7 +412,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           }
         }
       }
-      if (target_row) a.row_partial[row * n_tiles_n + n_blk] = sq_sum;
+      if (target_row) a.row_partial[(row * n_tiles_n + n_blk) * 2 + col_half] = sq_sum;
       fence_before_sync();
       mbar_arrive(tempty_bar(buf));  // this thread no longer reads the accumulator
       }
@@ -507,8 +515,8 @@ __global__ void neg_mse_kernel(const float* __restrict__ row_partial, long long 
   const long long p = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (p >= pop) return;
   float s = 0.f;
-  const float* rp = row_partial + p * batch * tiles_n;
-  for (long long i = 0; i < batch * tiles_n; ++i) s += rp[i];
+  const float* rp = row_partial + p * batch * tiles_n * 2;  // two column halves per tile
+  for (long long i = 0; i < batch * tiles_n * 2; ++i) s += rp[i];
   fitness[p] = -s / (float)(batch * N);
 }
 
@@ -527,8 +535,9 @@ __device__ __forceinline__ void split3(float x, __nv_bfloat16& hi, __nv_bfloat16
 // pieces so that six tensor-core passes reproduce the fp32 product (see evox_lora_gradient_tc).
 __global__ void __launch_bounds__(256)
     lora_grad_pack_kernel(const float* __restrict__ fitness, const long long* __restrict__ seeds, unsigned long long a_counter,
-                          unsigned long long b_counter, long long pop, long long d, long long k, __nv_bfloat16* __restrict__ bf3,
-                          __nv_bfloat16* __restrict__ at3) {
+                          unsigned long long b_counter, long long pop, long long row_begin, long long d, long long k,
+                          __nv_bfloat16* __restrict__ bf3, __nv_bfloat16* __restrict__ at3) {
+  // d = number of rows of the block computed here, starting at row `row_begin` of the weight
   const long long Kt = pop * RANK;
   const long long n_b = pop * d;          // one task per (i, j): 8 values of B_i[j][:]
   const long long n_a = pop * (k / 4);    // one task per (i, l / 4): 8 x 4 values of A_i[:][l..l+3]
@@ -537,7 +546,8 @@ __global__ void __launch_bounds__(256)
       const long long i = t / d, j = t - i * d;
       const unsigned long long seed = (unsigned long long)seeds[i];
       const float f = fitness[i];
-      const float4 z0 = normal4(seed, b_counter, (uint32_t)(2 * j)), z1 = normal4(seed, b_counter, (uint32_t)(2 * j + 1));
+      const long long jg = row_begin + j;  // row of the whole weight block
+      const float4 z0 = normal4(seed, b_counter, (uint32_t)(2 * jg)), z1 = normal4(seed, b_counter, (uint32_t)(2 * jg + 1));
       const float v[8] = {z0.x * f, z0.y * f, z0.z * f, z0.w * f, z1.x * f, z1.y * f, z1.z * f, z1.w * f};
       __align__(16) __nv_bfloat16 p[3][8];
 #pragma unroll
@@ -694,8 +704,9 @@ extern "C" int evox_lora_gradient_tc_supported(int64_t pop, int64_t d, int64_t k
 }
 
 extern "C" int evox_lora_gradient_tc(const float* fitness, const int64_t* seeds, uint64_t counter, int64_t pop, float sigma,
-                                     int64_t d, int64_t k, int32_t r, float* grad, void* workspace, size_t workspace_bytes,
-                                     int32_t* error_flag, void* stream) {
+                                     int64_t row_begin, int64_t d, int64_t k, int32_t r, float* grad, void* workspace,
+                                     size_t workspace_bytes, int32_t* error_flag, void* stream) {
+  EVOX_REQUIRE(row_begin >= 0, EVOX_ERR_INVALID, "lora_gradient_tc: row_begin must be non-negative");
   EVOX_REQUIRE(fitness && seeds && grad && workspace && error_flag, EVOX_ERR_INVALID, "lora_gradient_tc: NULL pointer");
   EVOX_REQUIRE(evox_lora_gradient_tc_supported(pop, d, k, r), EVOX_ERR_INVALID,
                "lora_gradient_tc: shape (pop %lld, d %lld, k %lld, r %d) is not supported", (long long)pop, (long long)d, (long long)k, r);
@@ -710,7 +721,7 @@ extern "C" int evox_lora_gradient_tc(const float* fitness, const int64_t* seeds,
   long long blocks = (tasks + 255) / 256;
   const long long cap = (long long)sm_count() * 16;
   lora_grad_pack_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, s>>>(fitness, (const long long*)seeds, counter, b_counter,
-                                                                               pop, d, k, bf3, at3);
+                                                                               pop, row_begin, d, k, bf3, at3);
   EVOX_LAUNCH_CHECK();
   GemmArgs a;
   a.M = d;

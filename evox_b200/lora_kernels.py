@@ -140,7 +140,7 @@ def lora_layer_bf16(h: torch.Tensor, w: torch.Tensor, seeds: torch.Tensor, count
     out_bf16 = out_f32 = partial = None
     if target is not None:
         target = target.to(device=dev, dtype=torch.float32).contiguous()
-        partial = torch.empty(pop * batch, d // 256, dtype=torch.float32, device=dev)
+        partial = torch.empty(pop * batch, d // 128, dtype=torch.float32, device=dev)
     elif out_dtype == torch.bfloat16:
         out_bf16 = torch.empty(pop, batch, d, dtype=torch.bfloat16, device=dev)
     else:
@@ -162,20 +162,29 @@ def lora_layer_bf16(h: torch.Tensor, w: torch.Tensor, seeds: torch.Tensor, count
 
 
 def lora_gradient_from_seeds(fitness: torch.Tensor, seeds: torch.Tensor, weight_shape: tuple, rank: int, counter: int,
-                             pop_size: int, sigma: float, out: torch.Tensor | None = None) -> torch.Tensor:
+                             pop_size: int, sigma: float, out: torch.Tensor | None = None,
+                             rows: tuple[int, int] | None = None) -> torch.Tensor:
     """`lora_gradient(fitness, *generate_lora_factors(seeds, weight_shape, rank, counter), ...)` without
     the factors ever existing in fp32: on supported shapes the tensor-core kernel regenerates them;
     otherwise this falls back to generating them and calling `lora_gradient`. `out`: optional flat
-    fp32 destination of prod(weight_shape) elements."""
+    fp32 destination of prod(weight_shape) elements. `rows = (begin, end)` computes only those rows
+    of a 2-D block (tensor-core path only) and returns that slice; `out` then has (end - begin) * k
+    elements."""
     fitness = fitness.float().contiguous()
     seeds = _seeds(seeds)
     dev = fitness.device
     n = int(math.prod(weight_shape))
+    if rows is not None:
+        n = (rows[1] - rows[0]) * int(weight_shape[-1])
     if out is None:
         out = torch.empty(n, dtype=torch.float32, device=dev)
     if len(weight_shape) >= 2:
         d, k = _as_2d(weight_shape)
-        if _cabi.lib.evox_lora_gradient_tc_supported(pop_size, d, k, rank) and out.data_ptr() % 16 == 0:
+        r0, r1 = rows if rows is not None else (0, d)
+        if rows is not None and not _cabi.lib.evox_lora_gradient_tc_supported(pop_size, r1 - r0, k, rank):
+            raise _cabi.EvoxKernelError("a row range needs the tensor-core gradient path")
+        if _cabi.lib.evox_lora_gradient_tc_supported(pop_size, r1 - r0, k, rank) and out.data_ptr() % 16 == 0:
+            d = r1 - r0
             nbytes = _cabi.lib.evox_lora_gradient_tc_workspace_bytes(pop_size, d, k)
             ws = _grad_ws.get(dev)
             if ws is None or ws.numel() < nbytes:
@@ -183,12 +192,12 @@ def lora_gradient_from_seeds(fitness: torch.Tensor, seeds: torch.Tensor, weight_
             err = torch.zeros(1, dtype=torch.int32, device=dev)
             _cabi.check(
                 _cabi.lib.evox_lora_gradient_tc(
-                    _cabi.ptr(fitness), _cabi.ptr(seeds), counter, pop_size, float(sigma), d, k, rank, _cabi.ptr(out),
+                    _cabi.ptr(fitness), _cabi.ptr(seeds), counter, pop_size, float(sigma), r0, d, k, rank, _cabi.ptr(out),
                     _cabi.ptr(ws), ws.numel(), _cabi.ptr(err), _cabi.stream_ptr(dev),
                 )
             )
             lora_gradient_from_seeds.last_error_flag = err
-            return out.view(weight_shape)
+            return out.view(d, k) if rows is not None else out.view(weight_shape)
         a, b = generate_lora_factors(seeds, weight_shape, rank, counter)
         out.copy_(lora_gradient(fitness, a, b, pop_size, sigma, weight_shape).reshape(-1))
         return out.view(weight_shape)

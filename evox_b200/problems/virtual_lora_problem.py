@@ -18,6 +18,7 @@ from torch import nn
 from .. import _cabi
 from ..core import Problem
 from ..lora_kernels import compute_counter_offsets, generate_lora_factors, lora_layer_bf16
+from ..sharding import group_info, shard_bounds
 
 __all__ = ["VirtualLoRAProblem"]
 
@@ -26,12 +27,17 @@ _ACTIVATIONS = (nn.ReLU, nn.Tanh, nn.Sigmoid, nn.GELU, nn.LeakyReLU, nn.ELU, nn.
 
 class VirtualLoRAProblem(Problem):
     def __init__(self, model: nn.Sequential, data_loader, criterion, lora_rank: int, n_batch_per_eval: int = 1,
-                 device: torch.device | None = None, reduction: str = "mean", compute_dtype: torch.dtype = torch.float32):
+                 device: torch.device | None = None, reduction: str = "mean", compute_dtype: torch.dtype = torch.float32,
+                 shard: bool = False, group=None):
         """`compute_dtype=torch.bfloat16` runs every Linear layer whose shape the tensor-core kernel
         supports (rank 8, batch 64 or 128 per individual, feature sizes multiples of 256) with bf16
         operands and fp32 accumulation; other layers and the default use the fp32 kernels."""
         super().__init__()
         self.compute_dtype = compute_dtype
+        # shard=True: this rank evaluates only its tensor_split share of the individuals and the
+        # fitness values are allgathered (the reference's one collective, std_workflow.py:185-189)
+        self.group = group
+        self.rank, self.world_size = group_info(group) if shard else (0, 1)
         if not isinstance(model, nn.Sequential):
             raise TypeError(f"VirtualLoRAProblem requires an nn.Sequential model, got {type(model).__name__}.")
         self.device = torch.get_default_device() if device is None else torch.device(device)
@@ -130,6 +136,28 @@ class VirtualLoRAProblem(Problem):
 
     def evaluate(self, payload) -> torch.Tensor:
         center_flat, seeds, sigma = payload
+        if self.world_size > 1:
+            return self._evaluate_sharded(center_flat, seeds, sigma)
+        return self._evaluate_local(center_flat, seeds, sigma, None)
+
+    def _evaluate_sharded(self, center_flat, seeds, sigma) -> torch.Tensor:
+        import torch.distributed as dist
+
+        pop = seeds.shape[0]
+        a, b = shard_bounds(pop, self.world_size, self.rank)
+        local = self._evaluate_local(center_flat, seeds[a:b].contiguous(), sigma, (a, b, pop)).contiguous()
+        if pop % self.world_size == 0:
+            out = torch.empty(pop, dtype=local.dtype, device=local.device)
+            dist.all_gather_into_tensor(out, local, group=self.group)
+            return out
+        pieces = [torch.empty(shard_bounds(pop, self.world_size, r)[1] - shard_bounds(pop, self.world_size, r)[0],
+                              dtype=local.dtype, device=local.device) for r in range(self.world_size)]
+        dist.all_gather(pieces, local, group=self.group)
+        return torch.cat(pieces)
+
+    def _evaluate_local(self, center_flat, seeds, sigma, span) -> torch.Tensor:
+        """Fitness of the individuals in `seeds`; `span = (a, b, pop)` says they are rows a..b of a
+        population of `pop`, so per-individual inputs are sliced the same way."""
         pop_size = seeds.shape[0]
         center = center_flat.to(torch.float32).contiguous()
         if self.n_batch_per_eval == -1:
@@ -146,6 +174,8 @@ class VirtualLoRAProblem(Problem):
         for inputs, labels in batches:
             inputs = inputs.to(device=self.device, non_blocking=True)
             labels = labels.to(device=self.device, non_blocking=True)
+            if span is not None and inputs.ndim == 3 and inputs.shape[0] == span[2]:
+                inputs = inputs[span[0] : span[1]]
             fuse = (isinstance(self.criterion, nn.MSELoss) and self.criterion.reduction == "none" and labels.ndim == 2
                     and self.reduction == "mean")
             logits = self._virtual_forward(inputs, center, seeds, sigma, pop_size, mse_target=labels if fuse else None)

@@ -243,7 +243,7 @@ int evox_lora_down_bf16(const void* h, const int64_t* seeds, uint64_t a_counter,
  * with B_p (d x 8) and the bias noise regenerated in the epilogue from the Philox streams
  * (b_counter = block counter + ceil4(8 k); noise_counter = the bias block's counter).
  * t = NULL skips the correction. Exactly one sink: out_bf16 (pop*batch x d), out_f32, or
- * target (batch x d, fp32, shared by all individuals) + row_partial (pop*batch x d/256) which
+ * target (batch x d, fp32, shared by all individuals) + row_partial (pop*batch x d/128) which
  * receives per-row sums of (y - target)^2 instead of y. error_flag: device int32, zero on
  * entry; non-zero afterwards means a bounded wait expired (1 producer, 2/3 issuer, 4 epilogue). */
 int evox_lora_gemm_bf16(const void* h, const void* w, const float* bias, const float* t,
@@ -258,12 +258,14 @@ int evox_lora_gemm_bf16(const void* h, const void* w, const float* bias, const f
  * writes f_i B_i and A_i as three bf16 pieces each (x = hi + mid + lo) into the workspace and sums
  * six tcgen05 passes (hi hi, hi mid, mid hi, hi lo, lo hi, mid mid) in fp32, which keeps the
  * result within fp32 rounding of the reference's einsum. Needs rank 8, d a multiple of 128, k a
- * multiple of 256, pop a multiple of 8 (evox_lora_gradient_tc_supported). error_flag as above. */
+ * multiple of 256, pop a multiple of 8 (evox_lora_gradient_tc_supported). error_flag as above.
+ * Only the d rows starting at row `row_begin` of the weight are computed (grad points at the
+ * first of them): ranks that shard a block by rows each pass their own range. */
 size_t evox_lora_gradient_tc_workspace_bytes(int64_t pop, int64_t d, int64_t k);
 int evox_lora_gradient_tc_supported(int64_t pop, int64_t d, int64_t k, int32_t r);
 int evox_lora_gradient_tc(const float* fitness, const int64_t* seeds, uint64_t counter, int64_t pop,
-                          float sigma, int64_t d, int64_t k, int32_t r, float* grad, void* workspace,
-                          size_t workspace_bytes, int32_t* error_flag, void* stream);
+                          float sigma, int64_t row_begin, int64_t d, int64_t k, int32_t r, float* grad,
+                          void* workspace, size_t workspace_bytes, int32_t* error_flag, void* stream);
 
 /* fitness (pop) = -(sum of an individual's row_partial entries) / (batch * d): negative mean
  * squared error of the last layer, summed in a fixed order. */
