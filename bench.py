@@ -386,6 +386,45 @@ def run_nds(args):
     print(json.dumps(line), flush=True)
 
 
+def run_rvea(args):
+    """Secondary workload: RVEA selection at BASELINE configs[2] (50,000 x 10 objectives, 275 vectors)
+    and at 5,000,000 rows, where the pass is long enough for its HBM rate to show."""
+    from evox_b200.operators.selection import ref_vec_guided
+    from oracle import rvea as orvea
+
+    dev = torch.device("cuda", 0)
+    n = {"rvea_config2": 50_000, "rvea_5e6": 5_000_000}[args.workload]
+    x, f, v, theta = orvea.config2_inputs(n=n)
+    xd, fd, vd, td = x.to(dev), f.to(dev), v.to(dev), theta.to(dev)
+    for _ in range(3):
+        ref_vec_guided(xd, fd, vd, td)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        ref_vec_guided(xd, fd, vd, td)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    m, nv, dx = f.shape[1], v.shape[0], x.shape[1]
+    alg_bytes = n * m * 4 * 2 + nv * (dx + m) * 4  # objectives are read twice: ideal point, then association
+    peak, kind = measured_peaks()
+    line = {
+        "metric": "rvea_selection_ms", "value": ms, "unit": "ms", "n_gpus": 1, "steps": args.steps, "warmup": 3,
+        "ms_per_step": ms, "higher_is_better": False, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "n": n, "m": m, "nv": nv},
+        "roofline": {"bound": "hbm", "kernel": "rvea_assign_kernel + rvea_ideal_kernel", "achieved": alg_bytes / (ms * 1e-3) / 1e9,
+                     "peak": peak, "unit": "GB/s", "frac": alg_bytes / (ms * 1e-3) / 1e9 / peak, "peak_kind": kind, "traffic": None},
+        "pairs_per_s": n * nv / (ms * 1e-3),
+    }
+    if not args.no_cpu_baseline and n <= 50_000:
+        t0 = time.perf_counter()
+        orvea.ref_vec_guided(x, f, v, theta)
+        line["cpu_baseline"] = {"value": (time.perf_counter() - t0) * 1e3, "unit": "ms", "cores": torch.get_num_threads(),
+                                "kind": "port", "sample": "whole workload, one run"}
+    print(json.dumps(line), flush=True)
+
+
 def run_lora_es(args):
     """Secondary workload: BASELINE configs[3] — VirtualLoRAES over a 3 x (4096 -> 4096) bf16 MLP,
     1,024 individuals with their own 64 x 4096 batch, rank-8 factors, sigma 0.02, lr 0.01, centred
@@ -459,7 +498,7 @@ def main():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="pso_ackley_1e6x1000", choices=sorted(WORKLOADS) + ["nds_rank_2e4", "nds_rank_1e5", "lora_es_config3"])
+    ap.add_argument("--workload", default="pso_ackley_1e6x1000", choices=sorted(WORKLOADS) + ["nds_rank_2e4", "nds_rank_1e5", "lora_es_config3", "rvea_config2", "rvea_5e6"])
     ap.add_argument("--lora-pop", type=int, default=1024)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
@@ -467,6 +506,8 @@ def main():
         run_nds(args)
     elif args.workload == "lora_es_config3":
         run_lora_es(args)
+    elif args.workload.startswith("rvea_"):
+        run_rvea(args)
     elif args.impl == "reference":
         run_reference(args)
     else:
