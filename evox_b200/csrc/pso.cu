@@ -108,6 +108,7 @@ struct RoundKeys {
   uint32_t k[20];  // (k0, k1) of each of the 10 rounds, computed once on the host
 };
 
+template <bool SCALED = true>
 __device__ __forceinline__ float4 pso_uniform4(uint64_t q, uint64_t generation, uint32_t which,
                                                const RoundKeys& rk) {
   uint32_t c0 = (uint32_t)q, c1 = (uint32_t)(q >> 32), c2 = (uint32_t)generation;
@@ -122,7 +123,10 @@ __device__ __forceinline__ float4 pso_uniform4(uint64_t q, uint64_t generation, 
     c2 = (uint32_t)(p0 >> 32) ^ c3 ^ rk.k[2 * r + 1];
     c3 = (uint32_t)p0;
   }
-  return make_float4(u24_to_unit(c0), u24_to_unit(c1), u24_to_unit(c2), u24_to_unit(c3));
+  if (SCALED) return make_float4(u24_to_unit(c0), u24_to_unit(c1), u24_to_unit(c2), u24_to_unit(c3));
+  // the 24-bit integers as floats; the caller folds the factor 2^-24 into phi (an exact power-of-two
+  // scaling: phi * (m * 2^-24) and (phi * 2^-24) * m round to the same float)
+  return make_float4(__uint2float_rn(c0 >> 8), __uint2float_rn(c1 >> 8), __uint2float_rn(c2 >> 8), __uint2float_rn(c3 >> 8));
 }
 
 static RoundKeys make_round_keys(uint64_t seed) {
@@ -181,6 +185,9 @@ __global__ void __launch_bounds__(kThreads, MOVE_BLOCKS_PER_SM) pso_move_eval_ke
   const long long warp0 = (long long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
   const long long n_warps = (long long)gridDim.x * kWarpsPerBlock;
   const float w = *a.w, phi_p = *a.phi_p, phi_g = *a.phi_g;
+  // vector path in Philox mode: the draws arrive as 24-bit integers, 2^-24 rides on phi (exact)
+  const float phi_p_v = (PHILOX && VEC == 4) ? phi_p * 5.9604644775390625e-08f : phi_p;
+  const float phi_g_v = (PHILOX && VEC == 4) ? phi_g * 5.9604644775390625e-08f : phi_g;
   const int d = a.d;
   const int n_call = (d + 3) >> 2;  // Philox calls per row and draw
 
@@ -219,8 +226,8 @@ __global__ void __launch_bounds__(kThreads, MOVE_BLOCKS_PER_SM) pso_move_eval_ke
         }
         float4 rg, rp;
         if constexpr (PHILOX) {
-          rg = pso_uniform4(q0 + c, a.generation, 0u, a.rk);
-          rp = pso_uniform4(q0 + c, a.generation, 1u, a.rk);
+          rg = pso_uniform4<false>(q0 + c, a.generation, 0u, a.rk);
+          rp = pso_uniform4<false>(q0 + c, a.generation, 1u, a.rk);
         } else {
           rg = __ldcs(rg4 + c);
           rp = __ldcs(rp4 + c);
@@ -229,10 +236,10 @@ __global__ void __launch_bounds__(kThreads, MOVE_BLOCKS_PER_SM) pso_move_eval_ke
         const float4 lb = __ldg(lb4 + c);
         const float4 ub = __ldg(ub4 + c);
         float4 xo;
-        xo.x = move_one(x.x, v.x, pb.x, gb.x, lb.x, ub.x, rg.x, rp.x, w, phi_p, phi_g);
-        xo.y = move_one(x.y, v.y, pb.y, gb.y, lb.y, ub.y, rg.y, rp.y, w, phi_p, phi_g);
-        xo.z = move_one(x.z, v.z, pb.z, gb.z, lb.z, ub.z, rg.z, rp.z, w, phi_p, phi_g);
-        xo.w = move_one(x.w, v.w, pb.w, gb.w, lb.w, ub.w, rg.w, rp.w, w, phi_p, phi_g);
+        xo.x = move_one(x.x, v.x, pb.x, gb.x, lb.x, ub.x, rg.x, rp.x, w, phi_p_v, phi_g_v);
+        xo.y = move_one(x.y, v.y, pb.y, gb.y, lb.y, ub.y, rg.y, rp.y, w, phi_p_v, phi_g_v);
+        xo.z = move_one(x.z, v.z, pb.z, gb.z, lb.z, ub.z, rg.z, rp.z, w, phi_p_v, phi_g_v);
+        xo.w = move_one(x.w, v.w, pb.w, gb.w, lb.w, ub.w, rg.w, rp.w, w, phi_p_v, phi_g_v);
         if (better) __stcs(pb4 + c, x);  // pso.py:90 — own position becomes the personal best
         __stcs(pop4 + c, xo);
         __stcs(vel4 + c, v);
@@ -272,135 +279,6 @@ __global__ void __launch_bounds__(kThreads, MOVE_BLOCKS_PER_SM) pso_move_eval_ke
       if (better) a.pbest_fit[row] = f_old;  // pso.py:91
     }
   }
-}
-
-// ---------------------------------------------------------------------------------------------
-// Same step with the swarm's three big streams (pop, velocity, personal best) fetched by
-// asynchronous 16-byte copies (cp.async) into a per-warp shared-memory ring, three chunk-iterations
-// ahead of the arithmetic. A lane only ever reads back what it copied itself, so no barrier is
-// needed, just cp.async.wait_group; the copies keep HBM busy while the ~94 instructions per
-// particle-dimension (two Philox calls per four dimensions, the separately rounded update, two
-// relu-form clamps, the fitness terms) issue. The ring runs across row boundaries.
-// ---------------------------------------------------------------------------------------------
-constexpr int kRingStages = 4;  // 3 in flight + the one being consumed
-constexpr int kRingBytes = kWarpsPerBlock * kRingStages * 3 * 32 * 16;
-
-__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
-
-template <bool PHILOX, int FIT>
-__global__ void __launch_bounds__(kThreads, MOVE_BLOCKS_PER_SM) pso_move_eval_async_kernel(const MoveArgs a) {
-  extern __shared__ float4 ring[];
-  const int lane = threadIdx.x & 31;
-  const int wib = threadIdx.x >> 5;
-  float4* slot = ring + (size_t)wib * kRingStages * 96 + lane;  // slot[(stage * 3 + array) * 32]
-  const long long warp0 = (long long)blockIdx.x * kWarpsPerBlock + wib;
-  const long long n_warps = (long long)gridDim.x * kWarpsPerBlock;
-  if (warp0 >= a.P) return;
-  const float w = *a.w, phi_p = *a.phi_p, phi_g = *a.phi_g;
-  const int d = a.d;
-  const int n_call = d >> 2;               // 16-byte chunks per row (d is a multiple of 4 here)
-  const int n_it = (n_call + 31) >> 5;     // chunk-iterations per row
-  const long long n_rows = (a.P - warp0 + n_warps - 1) / n_warps;
-  const long long total = n_rows * n_it;
-  const float4* gb4 = reinterpret_cast<const float4*>(a.gbest_loc);
-  const float4* lb4 = reinterpret_cast<const float4*>(a.lb);
-  const float4* ub4 = reinterpret_cast<const float4*>(a.ub);
-
-  // ---- issue side -------------------------------------------------------------------------
-  long long i_row = warp0;   // row of the next item to issue
-  int i_it = 0;
-  bool i_better = false;
-  long long issued = 0;
-  auto issue_one = [&]() {
-    if (issued < total) {
-      if (i_it == 0) i_better = a.pbest_fit[i_row] > a.fit[i_row];  // pso.py:89
-      const int c = i_it * 32 + lane;
-      if (c < n_call) {
-        const size_t off = (size_t)i_row * (size_t)d + 4 * (size_t)c;
-        float4* s = slot + (int)(issued % kRingStages) * 96;
-        cp_async16(s, a.pop + off);
-        cp_async16(s + 32, a.vel + off);
-        if (!i_better) cp_async16(s + 64, a.pbest_loc + off);
-      }
-      if (++i_it == n_it) {
-        i_it = 0;
-        i_row += n_warps;
-      }
-    }
-    ++issued;
-    cp_async_commit();  // one group per item, also when nothing was copied: keeps the count uniform
-  };
-#pragma unroll
-  for (int s = 0; s < kRingStages - 1; ++s) issue_one();
-
-  // ---- consume side -----------------------------------------------------------------------
-  long long row = warp0;
-  int it = 0;
-  bool better = false;
-  float f_old = 0.f;
-  Fitness<FIT> acc;
-  for (long long i = 0; i < total; ++i) {
-    cp_async_wait<kRingStages - 2>();  // item i has landed
-    if (it == 0) {
-      f_old = a.fit[row];
-      better = a.pbest_fit[row] > f_old;
-      acc = Fitness<FIT>();
-    }
-    const int c = it * 32 + lane;
-    const bool live = c < n_call;
-    float4 x, v, pb;
-    if (live) {
-      const float4* s = slot + (int)(i % kRingStages) * 96;
-      x = s[0];
-      v = s[32];
-      pb = better ? x : s[64];
-    }
-    issue_one();  // refills the stage consumed one iteration ago
-    if (live) {
-      const size_t off = (size_t)row * (size_t)d + 4 * (size_t)c;
-      float4 rg, rp;
-      if constexpr (PHILOX) {
-        const uint64_t q = (uint64_t)(a.row_offset + row) * (uint64_t)n_call + (uint64_t)c;
-        rg = pso_uniform4(q, a.generation, 0u, a.rk);
-        rp = pso_uniform4(q, a.generation, 1u, a.rk);
-      } else {
-        rg = __ldcs(reinterpret_cast<const float4*>(a.rg + off));
-        rp = __ldcs(reinterpret_cast<const float4*>(a.rp + off));
-      }
-      const float4 gb = __ldg(gb4 + c);
-      const float4 lb = __ldg(lb4 + c);
-      const float4 ub = __ldg(ub4 + c);
-      float4 xo;
-      xo.x = move_one(x.x, v.x, pb.x, gb.x, lb.x, ub.x, rg.x, rp.x, w, phi_p, phi_g);
-      xo.y = move_one(x.y, v.y, pb.y, gb.y, lb.y, ub.y, rg.y, rp.y, w, phi_p, phi_g);
-      xo.z = move_one(x.z, v.z, pb.z, gb.z, lb.z, ub.z, rg.z, rp.z, w, phi_p, phi_g);
-      xo.w = move_one(x.w, v.w, pb.w, gb.w, lb.w, ub.w, rg.w, rp.w, w, phi_p, phi_g);
-      if (better) __stcs(reinterpret_cast<float4*>(a.pbest_loc + off), x);  // pso.py:90
-      __stcs(reinterpret_cast<float4*>(a.pop + off), xo);
-      __stcs(reinterpret_cast<float4*>(a.vel + off), v);
-      acc.add(xo.x, a.fp);
-      acc.add(xo.y, a.fp);
-      acc.add(xo.z, a.fp);
-      acc.add(xo.w, a.fp);
-    }
-    if (++it == n_it) {
-      acc.reduce();
-      if (lane == 0) {
-        a.fit[row] = acc.finish(d, a.fp);     // pso.py:106
-        if (better) a.pbest_fit[row] = f_old;  // pso.py:91
-      }
-      it = 0;
-      row += n_warps;
-    }
-  }
-  cp_async_wait<0>();
 }
 
 template <int VEC, int FIT>
@@ -602,21 +480,6 @@ int check_fit(int fitness_id, const float* params, FitParams* fp) {
   return EVOX_OK;
 }
 
-template <bool PHILOX>
-void launch_move_async(int fitness_id, int grid, cudaStream_t s, const MoveArgs& a) {
-  switch (fitness_id) {
-    case EVOX_FIT_ACKLEY:
-      pso_move_eval_async_kernel<PHILOX, EVOX_FIT_ACKLEY><<<grid, kThreads, kRingBytes, s>>>(a);
-      break;
-    case EVOX_FIT_RASTRIGIN:
-      pso_move_eval_async_kernel<PHILOX, EVOX_FIT_RASTRIGIN><<<grid, kThreads, kRingBytes, s>>>(a);
-      break;
-    default:
-      pso_move_eval_async_kernel<PHILOX, EVOX_FIT_SPHERE><<<grid, kThreads, kRingBytes, s>>>(a);
-      break;
-  }
-}
-
 template <int VEC, bool PHILOX>
 void launch_move(int fitness_id, int grid, cudaStream_t s, const MoveArgs& a) {
   switch (fitness_id) {
@@ -756,8 +619,8 @@ extern "C" int evox_pso_move_eval(float* pop, float* velocity, float* local_best
              aligned16(global_best_location) && aligned16(lb) && aligned16(ub);
   if (!philox) vec = vec && aligned16(rg) && aligned16(rp);
   if (vec) {
-    if (philox) launch_move_async<true>(fitness_id, grid, s, a);
-    else launch_move_async<false>(fitness_id, grid, s, a);
+    if (philox) launch_move<4, true>(fitness_id, grid, s, a);
+    else launch_move<4, false>(fitness_id, grid, s, a);
   } else {
     if (philox) launch_move<1, true>(fitness_id, grid, s, a);
     else launch_move<1, false>(fitness_id, grid, s, a);
