@@ -39,8 +39,9 @@ constexpr uint32_t kBytesA = BM * BK * 2, kBytesB = BN * BK * 2, kStageBytes = k
 constexpr uint32_t kMaxInd = 2;  // individuals per 128-row tile (batch is a multiple of 64)
 constexpr uint32_t kOffBfac = STAGES * kStageBytes;                  // float [kMaxInd][BN][RANK]
 constexpr uint32_t kOffBnoise = kOffBfac + kMaxInd * BN * RANK * 4;  // float [kMaxInd][BN]
-constexpr uint32_t kOffBars = kOffBnoise + kMaxInd * BN * 4;         // mbarriers + tmem base
-constexpr uint32_t kSmemBytes = kOffBars + 256 + 1024;               // + alignment slack
+constexpr uint32_t kOffAfac = kOffBnoise + kMaxInd * BN * 4;         // float [kMaxInd][BN][RANK]: next layer's A_p slice
+constexpr uint32_t kOffBars = kOffAfac + kMaxInd * BN * RANK * 4;    // mbarriers + tmem base
+constexpr uint32_t kSmemBytes = kOffBars + 256;                      // 231,680 B of the 232,448 B a CTA may use
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;           // 2 s per wait
 
 struct GemmArgs {
@@ -67,6 +68,11 @@ struct GemmArgs {
   int b_piece[6];
   float out_scale;
   long long ld_out;         // row stride of out_f32 (elements)
+  // Fused down-projection of the NEXT layer: its input is this layer's bf16 output, so each
+  // epilogue thread also accumulates y[row][n] * A'_p[q][n] over its 128 columns (A' = the next
+  // weight block's factor, counter next_a_counter, row length N) into t_partial[row][2 * n_blk + half][q].
+  float* t_partial;
+  unsigned long long next_a_counter;
   // The tensor core adds each K = 16 product into the fp32 accumulator with truncation, a bias that
   // grows with the number of accumulations. With chunk_kblocks > 0 an accumulator only collects that
   // many k-blocks; the epilogue then adds the chunks into out_f32 in round-to-nearest fp32.
@@ -182,9 +188,14 @@ __device__ __forceinline__ float4 normal4(unsigned long long seed, unsigned long
 
 __global__ void __launch_bounds__(kGemmThreads, 1)
     lora_gemm_kernel(const __grid_constant__ CUtensorMap map_h, const __grid_constant__ CUtensorMap map_w, const GemmArgs a) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~(uintptr_t)1023u);
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
   const uint32_t smem_base = smem_u32(smem);
+  if ((smem_base & 1023u) != 0) {  // the swizzled tiles need a 1024-byte aligned window: refuse to run otherwise
+    if (threadIdx.x == 0) atomicCAS(a.error_flag, 0, 5);
+    return;
+  }
+  float* afac = reinterpret_cast<float*>(smem + kOffAfac);
   float* bfac = reinterpret_cast<float*>(smem + kOffBfac);
   float* bnoise = reinterpret_cast<float*>(smem + kOffBnoise);
   const uint32_t bars = smem_base + kOffBars;
@@ -333,6 +344,20 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           *reinterpret_cast<float4*>(bnoise + (size_t)ind * BN + c4 * 4) = z;
         }
       }
+      if (a.t_partial != nullptr) {
+        // A'_p[q][n]: element q * N + n of the next block's stream; one call covers 4 columns of one q
+        for (int idx = et; idx < inds_per_tile * RANK * (BN / 4); idx += kEpilogueThreads) {
+          const int ind = idx / (RANK * (BN / 4)), rest = idx - ind * (RANK * (BN / 4));
+          const int q = rest / (BN / 4), c4 = rest - q * (BN / 4);
+          const unsigned long long seed = (unsigned long long)a.seeds[p_first + ind];
+          const float4 z = normal4(seed, a.next_a_counter, (uint32_t)(((long long)q * a.N + n0) / 4 + c4));
+          float* dst = afac + ((size_t)(ind * BN + c4 * 4) * RANK + q);
+          dst[0] = z.x;
+          dst[RANK] = z.y;
+          dst[2 * RANK] = z.z;
+          dst[3 * RANK] = z.w;
+        }
+      }
       const long long row = m0 + row_in_tile;
       const int my_ind = (int)(row / a.batch - p_first);
       float tr[RANK];
@@ -353,6 +378,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       fence_after_sync();
       const float* bf = bfac + (size_t)my_ind * BN * RANK;
       const float* bn = bnoise + (size_t)my_ind * BN;
+      const float* af = afac + (size_t)my_ind * BN * RANK;
+      float tp[RANK];
+#pragma unroll
+      for (int q = 0; q < RANK; ++q) tp[q] = 0.f;
       const float* target_row = a.target ? a.target + (row % a.batch) * a.N + n0 : nullptr;
       float sq_sum = 0.f;
       for (int c = col_half * (BN / 2); c < (col_half + 1) * (BN / 2); c += 32) {
@@ -387,6 +416,22 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             sq_sum = fmaf(dlt, dlt, sq_sum);
           }
         } else if (a.out_bf16) {
+          if (a.t_partial != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const float yb = __bfloat162float(__float2bfloat16_rn(y[j]));  // what the next layer will read
+              const float4 a0 = *reinterpret_cast<const float4*>(af + (size_t)(c + j) * RANK);
+              const float4 a1 = *reinterpret_cast<const float4*>(af + (size_t)(c + j) * RANK + 4);
+              tp[0] = fmaf(yb, a0.x, tp[0]);
+              tp[1] = fmaf(yb, a0.y, tp[1]);
+              tp[2] = fmaf(yb, a0.z, tp[2]);
+              tp[3] = fmaf(yb, a0.w, tp[3]);
+              tp[4] = fmaf(yb, a1.x, tp[4]);
+              tp[5] = fmaf(yb, a1.y, tp[5]);
+              tp[6] = fmaf(yb, a1.z, tp[6]);
+              tp[7] = fmaf(yb, a1.w, tp[7]);
+            }
+          }
           __nv_bfloat16* o = a.out_bf16 + row * a.N + n0 + c;
 #pragma unroll
           for (int j = 0; j < 32; j += 8) {
@@ -413,6 +458,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         }
       }
       if (target_row) a.row_partial[(row * n_tiles_n + n_blk) * 2 + col_half] = sq_sum;
+      if (a.t_partial != nullptr && a.out_bf16 != nullptr) {
+        float* o = a.t_partial + ((size_t)row * (size_t)(n_tiles_n * 2) + (size_t)(n_blk * 2 + col_half)) * RANK;
+        *reinterpret_cast<float4*>(o) = make_float4(tp[0], tp[1], tp[2], tp[3]);
+        *reinterpret_cast<float4*>(o + 4) = make_float4(tp[4], tp[5], tp[6], tp[7]);
+      }
       fence_before_sync();
       mbar_arrive(tempty_bar(buf));  // this thread no longer reads the accumulator
       }
@@ -507,6 +557,17 @@ __global__ void __launch_bounds__(256)
       }
     }
   }
+}
+
+// t[row][q] = sum over the 2 * N / 256 column slices of t_partial[row][slice][q], in slice order.
+__global__ void t_partial_reduce_kernel(const float* __restrict__ t_partial, long long rows, int slices, float* __restrict__ t) {
+  const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= rows * RANK) return;
+  const long long row = e / RANK;
+  const int q = (int)(e - row * RANK);
+  float s = 0.f;
+  for (int j = 0; j < slices; ++j) s += t_partial[(row * slices + j) * RANK + q];
+  t[e] = s;
 }
 
 // fitness[p] = -(sum of row partials of individual p) / (batch * N): negative mean squared error.
@@ -641,7 +702,7 @@ extern "C" int evox_lora_gemm_bf16(const void* h, const void* w, const float* bi
                                    uint64_t b_counter, int32_t has_bias_noise, uint64_t noise_counter, float sigma,
                                    int64_t pop, int64_t batch, int64_t k, int64_t d, int32_t r, int32_t relu,
                                    void* out_bf16, float* out_f32, const float* target, float* row_partial,
-                                   int32_t* error_flag, void* stream) {
+                                   float* t_next_partial, uint64_t next_a_counter, int32_t* error_flag, void* stream) {
   EVOX_REQUIRE(h && w && seeds && error_flag, EVOX_ERR_INVALID, "lora_gemm_bf16: NULL pointer");
   EVOX_REQUIRE(evox_lora_gemm_supported(pop, batch, k, d, r), EVOX_ERR_INVALID,
                "lora_gemm_bf16: shape (pop %lld, batch %lld, k %lld, d %lld, r %d) is not supported by the tensor-core path",
@@ -672,6 +733,10 @@ extern "C" int evox_lora_gemm_bf16(const void* h, const void* w, const float* bi
   a.out_scale = 1.0f;
   a.ld_out = d;
   a.chunk_kblocks = 0;
+  a.t_partial = t_next_partial;
+  a.next_a_counter = next_a_counter;
+  EVOX_REQUIRE(t_next_partial == nullptr || out_bf16 != nullptr, EVOX_ERR_INVALID,
+               "lora_gemm_bf16: the fused next-layer projection needs the bf16 output sink");
   CUtensorMap map_h, map_w;
   if (int rc = make_map(&map_h, h, a.M, k, BM)) return rc;
   if (int rc = make_map(&map_w, w, d, k, BN)) return rc;
@@ -748,6 +813,8 @@ extern "C" int evox_lora_gradient_tc(const float* fitness, const int64_t* seeds,
     a.a_piece[c] = pa[c];
     a.b_piece[c] = pb[c];
   }
+  a.t_partial = nullptr;
+  a.next_a_counter = 0;
   a.out_scale = 1.0f / ((float)pop * sigma);
   a.ld_out = k;
   a.chunk_kblocks = 32;  // 128 truncating accumulations per accumulator at most
@@ -759,6 +826,16 @@ extern "C" int evox_lora_gradient_tc(const float* fitness, const int64_t* seeds,
   long long grid = sm_count();
   if (grid > n_tiles) grid = n_tiles;
   lora_gemm_kernel<<<(unsigned)grid, kGemmThreads, kSmemBytes, s>>>(map_a, map_b, a);
+  EVOX_LAUNCH_CHECK();
+  return EVOX_OK;
+}
+
+extern "C" int evox_lora_t_from_partials(const float* t_partial, int64_t rows, int64_t d, float* t, void* stream) {
+  EVOX_REQUIRE(t_partial && t, EVOX_ERR_INVALID, "lora_t_from_partials: NULL pointer");
+  EVOX_REQUIRE(rows > 0 && d > 0 && d % BN == 0, EVOX_ERR_INVALID, "lora_t_from_partials: bad sizes");
+  const long long n = rows * RANK;
+  t_partial_reduce_kernel<<<(unsigned)((n + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(t_partial, rows,
+                                                                                                         (int)(d / BN * 2), t);
   EVOX_LAUNCH_CHECK();
   return EVOX_OK;
 }

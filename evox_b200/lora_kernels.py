@@ -116,12 +116,16 @@ def lora_gradient(fitness: torch.Tensor, A: torch.Tensor, B: torch.Tensor | None
 
 def lora_layer_bf16(h: torch.Tensor, w: torch.Tensor, seeds: torch.Tensor, counter: int, sigma: float, *,
                     bias: torch.Tensor | None = None, bias_counter: int | None = None, relu: bool = False,
-                    out_dtype: torch.dtype = torch.bfloat16, target: torch.Tensor | None = None, lora: bool = True):
+                    out_dtype: torch.dtype = torch.bfloat16, target: torch.Tensor | None = None, lora: bool = True,
+                    t: torch.Tensor | None = None, next_counter: int | None = None):
     """One virtual-LoRA Linear layer on the tensor cores: h (pop, batch, k) bf16, w (d, k) bf16.
 
     Returns y (pop, batch, d) in `out_dtype`, or, with `target` (batch, d) given, the per-individual
     fitness -mean((y - target)^2) without ever writing y. `counter` is the weight block's Philox
-    counter (A at `counter`, B at `counter + ceil4(8 k)`), `bias_counter` the bias block's."""
+    counter (A at `counter`, B at `counter + ceil4(8 k)`), `bias_counter` the bias block's.
+    `t` (pop, batch, 8): this layer's h A_p^T if already known (skips the projection kernel).
+    `next_counter`: counter of the NEXT layer's weight block (whose row length is d); the kernel then
+    also accumulates that layer's projection from its own bf16 output and `(y, t_next)` is returned."""
     rank = 8
     pop, batch, k = h.shape
     d = w.shape[0]
@@ -132,8 +136,11 @@ def lora_layer_bf16(h: torch.Tensor, w: torch.Tensor, seeds: torch.Tensor, count
         raise _cabi.EvoxKernelError(f"layer shape (pop {pop}, batch {batch}, k {k}, d {d}) is not supported by the tensor-core path")
     h, w, seeds = h.contiguous(), w.contiguous(), _seeds(seeds)
     lib, s = _cabi.lib, _cabi.stream_ptr(dev)
-    t = None
-    if lora:
+    if not lora:
+        t = None
+    elif t is not None:
+        t = t.contiguous()
+    elif lora:
         t = torch.empty(pop, batch, rank, dtype=torch.float32, device=dev)
         _cabi.check(lib.evox_lora_down_bf16(_cabi.ptr(h), _cabi.ptr(seeds), counter, pop, batch, k, rank, _cabi.ptr(t), s))
     err = torch.zeros(1, dtype=torch.int32, device=dev)
@@ -146,11 +153,15 @@ def lora_layer_bf16(h: torch.Tensor, w: torch.Tensor, seeds: torch.Tensor, count
     else:
         out_f32 = torch.empty(pop, batch, d, dtype=torch.float32, device=dev)
     bias_f = None if bias is None else bias.to(device=dev, dtype=torch.float32).contiguous()
+    t_partial = None
+    if next_counter is not None and out_bf16 is not None and lora:
+        t_partial = torch.empty(pop * batch, 2 * (d // 256), rank, dtype=torch.float32, device=dev)
     _cabi.check(
         lib.evox_lora_gemm_bf16(
             _cabi.ptr(h), _cabi.ptr(w), _cabi.ptr(bias_f), _cabi.ptr(t), _cabi.ptr(seeds), counter + _ceil4(rank * k),
             int(bias is not None and bias_counter is not None and lora), bias_counter or 0, float(sigma), pop, batch, k, d, rank,
-            int(relu), _cabi.ptr(out_bf16), _cabi.ptr(out_f32), _cabi.ptr(target), _cabi.ptr(partial), _cabi.ptr(err), s,
+            int(relu), _cabi.ptr(out_bf16), _cabi.ptr(out_f32), _cabi.ptr(target), _cabi.ptr(partial), _cabi.ptr(t_partial),
+            next_counter or 0, _cabi.ptr(err), s,
         )
     )
     lora_layer_bf16.last_error_flag = err
@@ -158,6 +169,10 @@ def lora_layer_bf16(h: torch.Tensor, w: torch.Tensor, seeds: torch.Tensor, count
         fitness = torch.empty(pop, dtype=torch.float32, device=dev)
         _cabi.check(lib.evox_neg_mse_from_partials(_cabi.ptr(partial), pop, batch, d, _cabi.ptr(fitness), s))
         return fitness
+    if t_partial is not None:
+        t_next = torch.empty(pop, batch, rank, dtype=torch.float32, device=dev)
+        _cabi.check(lib.evox_lora_t_from_partials(_cabi.ptr(t_partial), pop * batch, d, _cabi.ptr(t_next), s))
+        return out_bf16, t_next
     return out_bf16 if out_bf16 is not None else out_f32
 
 

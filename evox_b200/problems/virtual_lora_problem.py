@@ -84,6 +84,7 @@ class VirtualLoRAProblem(Problem):
         children = list(self.model.named_children())
         lib, s = _cabi.lib, _cabi.stream_ptr(dev)
         skip = False
+        pending_t = None  # next layer's h A^T, accumulated by the previous tensor-core layer's epilogue
         for pos, (name, module) in enumerate(children):
             if skip:
                 skip = False
@@ -98,17 +99,28 @@ class VirtualLoRAProblem(Problem):
                     if module.bias is not None:
                         bias, bi = self._param(center, f"{name}.bias")
                         bias_counter = self.counter_offsets[bi]
-                    last = pos + (2 if relu else 1) >= len(children)
+                    nxt = pos + (2 if relu else 1)
+                    last = nxt >= len(children)
+                    t_now, pending_t = pending_t, None
                     if last and not relu and mse_target is not None:
                         neg = lora_layer_bf16(h.to(torch.bfloat16), weight.to(torch.bfloat16), seeds, self.counter_offsets[wi], sigma,
-                                              bias=bias, bias_counter=bias_counter, target=mse_target)
+                                              bias=bias, bias_counter=bias_counter, target=mse_target, t=t_now)
                         return "mse", -neg
-                    h = lora_layer_bf16(
+                    # if the next layer is a tensor-core Linear too, let this layer's epilogue project for it
+                    next_counter = None
+                    if not last and isinstance(children[nxt][1], nn.Linear):
+                        nd, nk = children[nxt][1].weight.shape
+                        if nk == d and lib.evox_lora_gemm_supported(pop_size, batch, nk, nd, self.lora_rank):
+                            next_counter = self.counter_offsets[self.param_names.index(f"{children[nxt][0]}.weight")]
+                    res = lora_layer_bf16(
                         h.to(torch.bfloat16), weight.to(torch.bfloat16), seeds, self.counter_offsets[wi], sigma, bias=bias,
-                        bias_counter=bias_counter, relu=relu, out_dtype=torch.float32 if last else torch.bfloat16,
+                        bias_counter=bias_counter, relu=relu, out_dtype=torch.float32 if last else torch.bfloat16, t=t_now,
+                        next_counter=next_counter,
                     )
+                    h, pending_t = res if isinstance(res, tuple) else (res, None)
                     skip = relu
                     continue
+                pending_t = None
                 a, b = generate_lora_factors(seeds, (d, k), self.lora_rank, self.counter_offsets[wi])
                 bias = bias_noise = None
                 if module.bias is not None:

@@ -244,13 +244,22 @@ int evox_lora_down_bf16(const void* h, const int64_t* seeds, uint64_t a_counter,
  * (b_counter = block counter + ceil4(8 k); noise_counter = the bias block's counter).
  * t = NULL skips the correction. Exactly one sink: out_bf16 (pop*batch x d), out_f32, or
  * target (batch x d, fp32, shared by all individuals) + row_partial (pop*batch x d/128) which
- * receives per-row sums of (y - target)^2 instead of y. error_flag: device int32, zero on
- * entry; non-zero afterwards means a bounded wait expired (1 producer, 2/3 issuer, 4 epilogue). */
+ * receives per-row sums of (y - target)^2 instead of y. With the bf16 sink, t_next_partial
+ * (pop*batch x 2*d/256 x 8, optional) receives the partial down-projection of the NEXT layer,
+ * y_bf16 A'_p^T over each 128-column slice, A'_p being the factor at next_a_counter with row
+ * length d; evox_lora_t_from_partials sums the slices. error_flag: device int32, zero on entry;
+ * non-zero afterwards means a bounded wait expired (1 producer, 2/3 issuer, 4 epilogue) or the
+ * shared-memory window was not 1024-byte aligned (5). */
 int evox_lora_gemm_bf16(const void* h, const void* w, const float* bias, const float* t,
                         const int64_t* seeds, uint64_t b_counter, int32_t has_bias_noise,
                         uint64_t noise_counter, float sigma, int64_t pop, int64_t batch, int64_t k,
                         int64_t d, int32_t r, int32_t relu, void* out_bf16, float* out_f32,
-                        const float* target, float* row_partial, int32_t* error_flag, void* stream);
+                        const float* target, float* row_partial, float* t_next_partial,
+                        uint64_t next_a_counter, int32_t* error_flag, void* stream);
+
+/* t (rows x 8) = sum of the 2 * d / 256 column slices of t_next_partial, in slice order: the
+ * next layer's h A_p^T, accumulated by evox_lora_gemm_bf16 while it still held its output. */
+int evox_lora_t_from_partials(const float* t_partial, int64_t rows, int64_t d, float* t, void* stream);
 
 /* Population gradient of a 2-D block on the tensor cores without materialising fp32 factors:
  *   grad (d x k, fp32) = sum_i fitness_i B_i A_i / (pop * sigma)       (lora_noise.py:157-196)

@@ -126,3 +126,28 @@ def test_problem_bf16_path_with_fused_mse(cuda):
     want = ((out - target) ** 2).mean(dim=(1, 2))
     assert got.shape == (pop,)
     assert rel_err(got, want) <= 2e-2
+
+
+def test_fused_next_layer_projection(cuda):
+    """The epilogue's projection for the next layer equals the standalone projection kernel run on
+    the bf16 output (same factors, fp32 accumulation; only the summation order differs)."""
+    from evox_b200 import _cabi
+    from evox_b200.lora_kernels import lora_layer_bf16
+
+    g = torch.Generator().manual_seed(17)
+    pop, batch, k, d = 6, 64, 256, 512
+    h = torch.randn(pop, batch, k, generator=g).bfloat16().to(cuda)
+    w = (torch.randn(d, k, generator=g) / k**0.5).bfloat16().to(cuda)
+    seeds = torch.randint(0, 2**31, (pop,), generator=g, dtype=torch.int64).to(cuda)
+    next_counter = 123456
+    y, t_next = lora_layer_bf16(h, w, seeds, 40, 0.05, relu=True, next_counter=next_counter)
+    torch.cuda.synchronize()
+    assert int(lora_layer_bf16.last_error_flag) == 0
+    want = torch.empty(pop, batch, 8, dtype=torch.float32, device=cuda)
+    _cabi.check(_cabi.lib.evox_lora_down_bf16(_cabi.ptr(y), _cabi.ptr(seeds), next_counter, pop, batch, d, 8, _cabi.ptr(want),
+                                              _cabi.stream_ptr(cuda)))
+    assert rel_err(t_next, want.cpu()) <= 1e-4
+    # and against the oracle's factors
+    a, _ = lora.generate_lora_factors(seeds.cpu(), (d, d), 8, next_counter)
+    ref = torch.bmm(y.float().cpu(), a.transpose(1, 2))
+    assert rel_err(t_next, ref) <= 1e-4
