@@ -5,7 +5,7 @@ no CPU implementation behind these classes.
 """
 
 from . import _cabi  # noqa: F401  (fails loudly when the kernels are not built)
-from . import algorithms, core, operators, problems, workflows
+from . import algorithms, core, operators, ops, problems, workflows
 from .core import ModuleBase, Mutable, Parameter
 
 __all__ = ["algorithms", "core", "operators", "problems", "workflows", "ModuleBase", "Mutable", "Parameter"]

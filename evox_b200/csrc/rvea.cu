@@ -40,6 +40,15 @@ __device__ __forceinline__ float relu_clamp01(float a) {
   return __fsub_rn(__fadd_rn(a, lo), hi);
 }
 
+__global__ void rvea_decode_ideal_kernel(const uint32_t* zmin_key, int m, float* zmin) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t < m) zmin[t] = order_key_inv(zmin_key[t]);
+}
+__global__ void rvea_encode_ideal_kernel(const float* zmin, int m, uint32_t* zmin_key) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t < m) zmin_key[t] = order_key(zmin[t]);
+}
+
 __global__ void rvea_init_kernel(uint32_t* zmin_key, int m, unsigned long long* best, int nv) {
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
   if (t < m) zmin_key[t] = order_key(INFINITY);
@@ -90,7 +99,8 @@ template <int MP>
 __global__ void __launch_bounds__(kThreads)
     rvea_assign_kernel(const float* __restrict__ f, long long n, int m, const uint32_t* __restrict__ zmin_key,
                        const float* __restrict__ vn, const float* __restrict__ gamma, int nv,
-                       const float* __restrict__ theta_p, unsigned long long* best, int* __restrict__ associate) {
+                       const float* __restrict__ theta_p, unsigned long long* best, int* __restrict__ associate,
+                       long long row_offset) {
   extern __shared__ float s_vn[];  // nv x MP, zero padded
   for (int t = threadIdx.x; t < nv * MP; t += blockDim.x) {
     const int j = t / MP, k = t - j * MP;
@@ -153,9 +163,9 @@ __global__ void __launch_bounds__(kThreads)
         const float left = __fdiv_rn(__fadd_rn(1.0f, __fmul_rn(m_theta, best_angle)), gamma[best_j]);
         const float apd = __fmul_rn(left, norm);
         // NaN sorts first (torch.argmin); +inf keeps its bit pattern and is resolved at gather time
+        const unsigned long long grow = (unsigned long long)(row + row_offset);  // row number in the whole population
         const unsigned long long key =
-            (apd != apd) ? (unsigned long long)row
-                         : (((unsigned long long)__float_as_uint(apd) << 32) | (unsigned long long)(uint32_t)row);
+            (apd != apd) ? grow : (((unsigned long long)__float_as_uint(apd) << 32) | (grow & 0xffffffffull));
         atomicMin(best + best_j, key);
       }
     }
@@ -164,7 +174,8 @@ __global__ void __launch_bounds__(kThreads)
 
 __global__ void rvea_gather_kernel(const unsigned long long* __restrict__ best, int nv, const float* __restrict__ x,
                                    long long dx, const float* __restrict__ f, int m, float* __restrict__ next_x,
-                                   float* __restrict__ next_f, long long* __restrict__ next_index) {
+                                   float* __restrict__ next_f, long long* __restrict__ next_index, long long row_begin,
+                                   long long row_count, int sharded) {
   const long long per = dx + m;
   const long long total = (long long)nv * per;
   for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
@@ -176,8 +187,12 @@ __global__ void rvea_gather_kernel(const unsigned long long* __restrict__ best, 
     const bool all_inf = !empty && (uint32_t)(key >> 32) == 0x7f800000u;
     const long long src = all_inf ? 0 : (long long)(uint32_t)key;
     const float nanv = __int_as_float(0x7fc00000);
-    if (c < dx) next_x[(long long)j * dx + c] = empty ? nanv : x[src * dx + c];
-    else next_f[(long long)j * m + (c - dx)] = empty ? nanv : f[src * m + (c - dx)];
+    // sharded: x and f hold rows [row_begin, row_begin + row_count); rows of other shards and empty
+    // vectors contribute 0 so that a sum over the shards reproduces the gathered row
+    const long long loc = src - row_begin;
+    const bool mine = !empty && loc >= 0 && loc < row_count;
+    if (c < dx) next_x[(long long)j * dx + c] = sharded ? (mine ? x[loc * dx + c] : 0.0f) : (empty ? nanv : x[src * dx + c]);
+    else next_f[(long long)j * m + (c - dx)] = sharded ? (mine ? f[loc * m + (c - dx)] : 0.0f) : (empty ? nanv : f[src * m + (c - dx)]);
     if (c == 0 && next_index) next_index[j] = empty ? -1 : src;
   }
 }
@@ -205,7 +220,7 @@ Layout make_layout(long long n, int m, int nv) {
 
 template <int MP>
 int launch_assign(const float* f, long long n, int m, const uint32_t* zmin, const float* vn, const float* gamma, int nv,
-                  const float* theta, unsigned long long* best, int* associate, cudaStream_t s) {
+                  const float* theta, unsigned long long* best, int* associate, long long row_offset, cudaStream_t s) {
   const size_t smem = sizeof(float) * (size_t)nv * MP;
   EVOX_REQUIRE(smem <= 200 * 1024, EVOX_ERR_INVALID, "ref_vec_guided: %d reference vectors x %d objectives do not fit in shared memory", nv, m);
   if (smem > 48 * 1024) {
@@ -215,7 +230,7 @@ int launch_assign(const float* f, long long n, int m, const uint32_t* zmin, cons
   long long blocks = (n + rows_per_block - 1) / rows_per_block;
   const long long cap = (long long)sm_count() * 8;
   if (blocks > cap) blocks = cap;
-  rvea_assign_kernel<MP><<<(unsigned)blocks, kThreads, smem, s>>>(f, n, m, zmin, vn, gamma, nv, theta, best, associate);
+  rvea_assign_kernel<MP><<<(unsigned)blocks, kThreads, smem, s>>>(f, n, m, zmin, vn, gamma, nv, theta, best, associate, row_offset);
   EVOX_LAUNCH_CHECK();
   return EVOX_OK;
 }
@@ -262,19 +277,74 @@ extern "C" int evox_ref_vec_guided(const float* x, int64_t dx, const float* f, i
   rvea_vectors_kernel<<<1, kThreads, 0, s>>>(v, nv, m, vn, gamma);
   EVOX_LAUNCH_CHECK();
   int rc;
-  if (m <= 4) rc = launch_assign<4>(f, n, m, zmin, vn, gamma, nv, theta, best, associate, s);
-  else if (m <= 8) rc = launch_assign<8>(f, n, m, zmin, vn, gamma, nv, theta, best, associate, s);
-  else if (m <= 12) rc = launch_assign<12>(f, n, m, zmin, vn, gamma, nv, theta, best, associate, s);
-  else if (m <= 16) rc = launch_assign<16>(f, n, m, zmin, vn, gamma, nv, theta, best, associate, s);
-  else rc = launch_assign<32>(f, n, m, zmin, vn, gamma, nv, theta, best, associate, s);
+  if (m <= 4) rc = launch_assign<4>(f, n, m, zmin, vn, gamma, nv, theta, best, associate, 0, s);
+  else if (m <= 8) rc = launch_assign<8>(f, n, m, zmin, vn, gamma, nv, theta, best, associate, 0, s);
+  else if (m <= 12) rc = launch_assign<12>(f, n, m, zmin, vn, gamma, nv, theta, best, associate, 0, s);
+  else if (m <= 16) rc = launch_assign<16>(f, n, m, zmin, vn, gamma, nv, theta, best, associate, 0, s);
+  else rc = launch_assign<32>(f, n, m, zmin, vn, gamma, nv, theta, best, associate, 0, s);
   if (rc) return rc;
   {
     const long long total = (long long)nv * (dx + m);
     const long long cap = (long long)sm_count() * 8;
     long long want = (total + kThreads - 1) / kThreads;
     rvea_gather_kernel<<<(unsigned)(want < cap ? want : cap), kThreads, 0, s>>>(best, nv, x, dx, f, m, next_x, next_f,
-                                                                                 (long long*)next_index);
+                                                                                 (long long*)next_index, 0, n, 0);
     EVOX_LAUNCH_CHECK();
   }
+  return EVOX_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Row-sharded selection: the same kernels in three phases with one small exchange after each of
+// the first two (ideal point: minimum over shards; per-vector winners: minimum over shards of the
+// packed (APD, global row) keys) and a sum of the gathered rows at the end.
+// ---------------------------------------------------------------------------------------------
+extern "C" int evox_ref_vec_guided_phase(int32_t phase, const float* x, int64_t dx, const float* f, int64_t n, int32_t m,
+                                         const float* v, int32_t nv, const float* theta, int64_t row_offset,
+                                         float* ideal, int64_t* best_keys, float* next_x, float* next_f,
+                                         int64_t* next_index, void* workspace, size_t workspace_bytes, void* stream) {
+  EVOX_REQUIRE(phase >= 1 && phase <= 3, EVOX_ERR_INVALID, "ref_vec_guided_phase: phase must be 1, 2 or 3");
+  EVOX_REQUIRE(f && ideal && best_keys, EVOX_ERR_INVALID, "ref_vec_guided_phase: NULL pointer");
+  EVOX_REQUIRE(n > 0 && row_offset >= 0 && row_offset + n < (1ll << 32), EVOX_ERR_INVALID, "ref_vec_guided_phase: rows out of range");
+  EVOX_REQUIRE(m > 0 && m <= 32 && nv > 0, EVOX_ERR_INVALID, "ref_vec_guided_phase: bad m or nv");
+  const Layout L = make_layout(n, m, nv);
+  EVOX_REQUIRE(workspace != nullptr && workspace_bytes >= L.total && ((uintptr_t)workspace & 255u) == 0, EVOX_ERR_WORKSPACE,
+               "ref_vec_guided_phase: workspace missing, misaligned or smaller than %zu bytes", L.total);
+  char* ws = reinterpret_cast<char*>(workspace);
+  uint32_t* zmin = reinterpret_cast<uint32_t*>(ws + L.zmin);
+  unsigned long long* best = reinterpret_cast<unsigned long long*>(best_keys);
+  float* vn = reinterpret_cast<float*>(ws + L.vn);
+  float* gamma = reinterpret_cast<float*>(ws + L.gamma);
+  int* associate = reinterpret_cast<int*>(ws + L.associate);
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (phase == 1) {  // this shard's column minima -> ideal (m floats)
+    const int init_n = m > nv ? m : nv;
+    rvea_init_kernel<<<(init_n + kThreads - 1) / kThreads, kThreads, 0, s>>>(zmin, m, best, nv);
+    long long want = (n * m + kThreads * 8 - 1) / (kThreads * 8);
+    const long long cap = (long long)sm_count() * 4;
+    rvea_ideal_kernel<<<(int)(want < 1 ? 1 : (want < cap ? want : cap)), kThreads, 0, s>>>(f, n, m, zmin);
+    rvea_decode_ideal_kernel<<<1, 32, 0, s>>>(zmin, m, ideal);
+    EVOX_LAUNCH_CHECK();
+    return EVOX_OK;
+  }
+  if (phase == 2) {  // ideal = minimum over all shards -> packed winners of this shard (nv keys)
+    EVOX_REQUIRE(v && theta, EVOX_ERR_INVALID, "ref_vec_guided_phase: NULL pointer");
+    rvea_encode_ideal_kernel<<<1, 32, 0, s>>>(ideal, m, zmin);
+    rvea_vectors_kernel<<<1, kThreads, 0, s>>>(v, nv, m, vn, gamma);
+    EVOX_LAUNCH_CHECK();
+    if (m <= 4) return launch_assign<4>(f, n, m, zmin, vn, gamma, nv, theta, best, associate, row_offset, s);
+    if (m <= 8) return launch_assign<8>(f, n, m, zmin, vn, gamma, nv, theta, best, associate, row_offset, s);
+    if (m <= 12) return launch_assign<12>(f, n, m, zmin, vn, gamma, nv, theta, best, associate, row_offset, s);
+    if (m <= 16) return launch_assign<16>(f, n, m, zmin, vn, gamma, nv, theta, best, associate, row_offset, s);
+    return launch_assign<32>(f, n, m, zmin, vn, gamma, nv, theta, best, associate, row_offset, s);
+  }
+  // phase 3: best_keys = minimum over all shards -> this shard's rows of the winners (others 0)
+  EVOX_REQUIRE(x && next_x && next_f && dx > 0, EVOX_ERR_INVALID, "ref_vec_guided_phase: NULL pointer");
+  const long long total = (long long)nv * (dx + m);
+  const long long cap = (long long)sm_count() * 8;
+  long long want = (total + kThreads - 1) / kThreads;
+  rvea_gather_kernel<<<(unsigned)(want < cap ? want : cap), kThreads, 0, s>>>(best, nv, x, dx, f, m, next_x, next_f,
+                                                                               (long long*)next_index, row_offset, n, 1);
+  EVOX_LAUNCH_CHECK();
   return EVOX_OK;
 }

@@ -10,7 +10,7 @@ import torch
 
 from .. import _cabi
 
-__all__ = ["non_dominate_rank", "crowding_distance", "nd_environmental_selection", "ref_vec_guided"]
+__all__ = ["non_dominate_rank", "crowding_distance", "nd_environmental_selection", "ref_vec_guided", "ref_vec_guided_sharded"]
 
 _workspaces: dict[tuple[str, torch.device], torch.Tensor] = {}
 
@@ -141,6 +141,59 @@ def ref_vec_guided(x: torch.Tensor, f: torch.Tensor, v: torch.Tensor, theta: tor
             _cabi.ptr(next_index), _cabi.ptr(ws), ws.numel(), _cabi.stream_ptr(dev),
         )
     )
+    if return_index:
+        return next_x, next_f, next_index
+    return next_x, next_f
+
+
+def ref_vec_guided_sharded(x: torch.Tensor, f: torch.Tensor, v: torch.Tensor, theta: torch.Tensor | float, row_offset: int,
+                           group=None, return_index: bool = False):
+    """`ref_vec_guided` when every rank of `group` holds a contiguous block of rows (x, f local;
+    `row_offset` = global number of the first local row). Three small NCCL exchanges: minimum of the
+    ideal point (m floats), minimum of the packed per-vector winners (nv int64), sum of the gathered
+    rows. Every rank returns the full (nv, d) / (nv, m) result, identical to the single-GPU call."""
+    import torch.distributed as dist
+
+    fo = _check_objectives(f, "f")
+    n, m = fo.shape
+    dev = fo.device
+    xo = x.to(torch.float32).contiguous()
+    vo = v.to(device=dev, dtype=torch.float32).contiguous()
+    nv, dx = vo.shape[0], xo.shape[1]
+    th = torch.as_tensor(theta, dtype=torch.float32, device=dev).reshape(())
+    ideal = torch.empty(m, dtype=torch.float32, device=dev)
+    keys = torch.empty(nv, dtype=torch.int64, device=dev)
+    next_x = torch.empty(nv, dx, dtype=torch.float32, device=dev)
+    next_f = torch.empty(nv, m, dtype=torch.float32, device=dev)
+    next_index = torch.empty(nv, dtype=torch.int64, device=dev)
+    ws = _workspace("rvea", dev, _cabi.lib.evox_rvea_workspace_bytes(n, m, nv))
+
+    def phase(k):
+        _cabi.check(
+            _cabi.lib.evox_ref_vec_guided_phase(
+                k, _cabi.ptr(xo), dx, _cabi.ptr(fo), n, m, _cabi.ptr(vo), nv, _cabi.ptr(th), row_offset, _cabi.ptr(ideal),
+                _cabi.ptr(keys), _cabi.ptr(next_x), _cabi.ptr(next_f), _cabi.ptr(next_index), _cabi.ptr(ws), ws.numel(),
+                _cabi.stream_ptr(dev),
+            )
+        )
+
+    sharded = dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1
+    phase(1)
+    if sharded:
+        dist.all_reduce(ideal, op=dist.ReduceOp.MIN, group=group)
+    phase(2)
+    if sharded:
+        # keys are unsigned; as int64 the "nobody" key (all ones) is -1, so compare in a shifted domain
+        shifted = keys ^ torch.iinfo(torch.int64).min
+        dist.all_reduce(shifted, op=dist.ReduceOp.MIN, group=group)
+        keys.copy_(shifted ^ torch.iinfo(torch.int64).min)
+    phase(3)
+    if sharded:
+        dist.all_reduce(next_x, op=dist.ReduceOp.SUM, group=group)
+        dist.all_reduce(next_f, op=dist.ReduceOp.SUM, group=group)
+    empty = (next_index < 0)[:, None]
+    next_x = torch.where(empty, torch.nan, next_x)
+    next_f = torch.where(empty, torch.nan, next_f)
     if return_index:
         return next_x, next_f, next_index
     return next_x, next_f

@@ -166,6 +166,19 @@ int evox_ref_vec_guided(const float* x, int64_t dx, const float* f, int64_t n, i
                         float* next_f, int64_t* next_index, void* workspace,
                         size_t workspace_bytes, void* stream);
 
+/* evox_ref_vec_guided for a population whose rows are spread over several GPUs. Each shard holds
+ * rows [row_offset, row_offset + n) of x and f. phase 1: `ideal` (m floats) = this shard's column
+ * minima (the caller takes the minimum over shards). phase 2: with the global `ideal`,
+ * `best_keys` (nv int64) = this shard's winners packed as (APD bits << 32 | global row) (the caller
+ * takes the minimum over shards; all-ones = nobody). phase 3: with the global `best_keys`, next_x /
+ * next_f = the winners' rows this shard owns and zeros elsewhere (the caller sums over shards and
+ * writes NaN where next_index is -1); next_index = global row numbers. Same arithmetic as the
+ * single-GPU call, so the result does not depend on the sharding. */
+int evox_ref_vec_guided_phase(int32_t phase, const float* x, int64_t dx, const float* f, int64_t n, int32_t m,
+                              const float* v, int32_t nv, const float* theta, int64_t row_offset,
+                              float* ideal, int64_t* best_keys, float* next_x, float* next_f,
+                              int64_t* next_index, void* workspace, size_t workspace_bytes, void* stream);
+
 /* ------------------------------------------------------------------------------------------
  * P4. Evolution strategies: Philox streams, virtual LoRA population, OpenES.
  * ------------------------------------------------------------------------------------------ */

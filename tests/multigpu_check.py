@@ -5,7 +5,8 @@
 
 Every rank runs the sharded algorithm on its GPU and, next to it, the single-GPU algorithm on the same
 GPU; after a few generations the gathered sharded state must equal the single-GPU state bit for bit
-(PSO) and the centre of the sharded virtual-LoRA ES must equal the single-GPU centre. Prints
+(PSO), the centre of the sharded virtual-LoRA ES must equal the single-GPU centre, and the
+row-sharded RVEA selection must pick and gather the same rows as the single call. Prints
 "multigpu ok" from rank 0 and exits non-zero on any mismatch.
 """
 import os
@@ -75,6 +76,22 @@ def check_lora_es(dev, rank, world):
     assert torch.equal(results[0], results[1]), f"rank {rank}: sharded centre differs by {(results[0] - results[1]).abs().max().item():.3e}"
 
 
+def check_rvea(dev, rank, world):
+    from evox_b200.operators.selection import ref_vec_guided, ref_vec_guided_sharded
+    from evox_b200.sharding import shard_bounds
+    from oracle import rvea
+
+    x, f, v, theta = rvea.config2_inputs(n=30_001)
+    xd, fd, vd, td = x.to(dev), f.to(dev), v.to(dev), theta.to(dev)
+    want = ref_vec_guided(xd, fd, vd, td, return_index=True)
+    a, b = shard_bounds(x.shape[0], world, rank)
+    got = ref_vec_guided_sharded(xd[a:b], fd[a:b], vd, td, a, return_index=True)
+    torch.cuda.synchronize()
+    assert torch.equal(got[2], want[2]), f"rank {rank}: selected rows differ"
+    for g, w in zip(got[:2], want[:2]):
+        assert torch.equal(torch.nan_to_num(g, nan=-1.0), torch.nan_to_num(w, nan=-1.0)), f"rank {rank}: gathered rows differ"
+
+
 def main():
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
@@ -83,6 +100,7 @@ def main():
     try:
         check_pso(dev, rank, world)
         check_lora_es(dev, rank, world)
+        check_rvea(dev, rank, world)
         dist.barrier()
         if rank == 0:
             print("multigpu ok", flush=True)

@@ -97,3 +97,51 @@ def test_float_theta_and_shapes(cuda):
     assert nx.shape == (275, 19) and nf.shape == (275, 10)
     with pytest.raises(_cabi.EvoxKernelError):
         ref_vec_guided(x.to(cuda), f.to(cuda), v[:, :5].to(cuda), 0.25)
+
+
+def test_sharded_phases_equal_single_call(cuda):
+    """Two row shards emulated on one GPU: ideal point and packed winners merged by minimum, gathered
+    rows by sum — exactly what the NCCL reductions do — reproduce the single call bit for bit."""
+    from evox_b200 import _cabi as c
+    from evox_b200.operators.selection import ref_vec_guided, ref_vec_guided_sharded
+
+    x, f, v, theta = rvea.config2_inputs(n=7001)
+    f[5] = float("nan")
+    xd, fd, vd, td = x.to(cuda), f.to(cuda), v.to(cuda), theta.to(cuda)
+    want_x, want_f, want_i = ref_vec_guided(xd, fd, vd, td, return_index=True)
+    # world size 1 through the sharded entry point
+    got = ref_vec_guided_sharded(xd, fd, vd, td, 0, return_index=True)
+    assert torch.equal(got[2], want_i)
+    assert torch.equal(torch.nan_to_num(got[0], nan=-1.0), torch.nan_to_num(want_x, nan=-1.0))
+    # two shards by hand
+    n, m, nv, dx = 7001, f.shape[1], v.shape[0], x.shape[1]
+    bounds = [(0, 3000), (3000, n)]
+    parts = []
+    for a, b in bounds:
+        xs, fs = xd[a:b].contiguous(), fd[a:b].contiguous()
+        ws = torch.empty(c.lib.evox_rvea_workspace_bytes(b - a, m, nv), dtype=torch.uint8, device=cuda)
+        parts.append(dict(x=xs, f=fs, ws=ws, a=a, n=b - a, ideal=torch.empty(m, device=cuda), keys=torch.empty(nv, dtype=torch.int64, device=cuda),
+                          nx=torch.empty(nv, dx, device=cuda), nf=torch.empty(nv, m, device=cuda), ni=torch.empty(nv, dtype=torch.int64, device=cuda)))
+
+    def phase(k, p):
+        c.check(c.lib.evox_ref_vec_guided_phase(k, c.ptr(p["x"]), dx, c.ptr(p["f"]), p["n"], m, c.ptr(vd), nv, c.ptr(td), p["a"],
+                                                c.ptr(p["ideal"]), c.ptr(p["keys"]), c.ptr(p["nx"]), c.ptr(p["nf"]), c.ptr(p["ni"]),
+                                                c.ptr(p["ws"]), p["ws"].numel(), c.stream_ptr(cuda)))
+
+    for p in parts:
+        phase(1, p)
+    ideal = torch.minimum(parts[0]["ideal"], parts[1]["ideal"])
+    for p in parts:
+        p["ideal"].copy_(ideal)
+        phase(2, p)
+    flip = torch.iinfo(torch.int64).min
+    keys = torch.minimum(parts[0]["keys"] ^ flip, parts[1]["keys"] ^ flip) ^ flip
+    for p in parts:
+        p["keys"].copy_(keys)
+        phase(3, p)
+    torch.cuda.synchronize()
+    idx = parts[0]["ni"]
+    assert torch.equal(idx, parts[1]["ni"]) and torch.equal(idx, want_i)
+    sx, sf = parts[0]["nx"] + parts[1]["nx"], parts[0]["nf"] + parts[1]["nf"]
+    live = idx >= 0
+    assert torch.equal(sx[live], want_x[live]) and torch.equal(sf[live], want_f[live])
