@@ -38,9 +38,10 @@ sys.path.insert(0, str(ROOT))
 PSO_BYTES_PER_ELEM = 20.0
 
 # DRAM traffic per particle-dimension of pso_move_eval_kernel from the ncu capture summarised in
-# profiles/ (dram__bytes_read.sum + dram__bytes_write.sum over the elements of the captured
-# launch); None until a capture exists for the current kernel.
-PSO_NCU_TRAFFIC_BYTES_PER_ELEM = None
+# profiles/pso_move_eval_kernel_ackley_65536x1000.md: (589.6 MB read + 665.7 MB written) over the
+# 65,536,000 particle-dimensions of the captured launch. Traffic grows in proportion to the number of
+# particle-dimensions (every element is read and written once), so it is scaled to the launch size.
+PSO_NCU_TRAFFIC_BYTES_PER_ELEM = 19.15
 
 WORKLOADS = {
     # name: (fitness, pop, dim, lb, ub, w, phi_p, phi_g)
@@ -453,7 +454,7 @@ def run_lora_es(args):
     target = torch.randn(batch, width, generator=gen).to(dev)
     prob = VirtualLoRAProblem(model, [(x, target)], nn.MSELoss(reduction="none"), rank, device=dev, compute_dtype=torch.bfloat16)
     center = torch.cat([p.detach().reshape(-1) for p in model.parameters()])
-    algo = VirtualLoRAES(prob.param_shapes, rank, pop, center, 0.01, 0.02, device=dev)
+    algo = VirtualLoRAES(prob.param_shapes, rank, pop, center, 0.01, 0.02, device=dev, gradient_passes=args.gradient_passes)
     wf = StdWorkflow(algo, prob, device=dev, fitness_transform=CenteredRank())
 
     def timed(fn, reps):
@@ -481,7 +482,8 @@ def run_lora_es(args):
     line = {
         "metric": "lora_es_generations_per_s", "value": 1e3 / step_ms, "unit": "gens/s", "n_gpus": 1, "steps": args.steps,
         "warmup": 2, "ms_per_step": step_ms, "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "lora_es_config3", "pop": pop, "batch": batch, "width": width, "layers": layers, "rank": rank},
+        "config": {"workload": "lora_es_config3", "pop": pop, "batch": batch, "width": width, "layers": layers, "rank": rank,
+                   "gradient_passes": args.gradient_passes},
         "forward_ms": fwd_ms,
         "roofline": {"bound": "tensor", "kernel": "lora_gemm_kernel (forward, 3 layers)", "achieved": flop_fwd / (fwd_ms * 1e-3) / 1e12,
                      "peak": peak, "unit": "TFLOP/s", "frac": flop_fwd / (fwd_ms * 1e-3) / 1e12 / peak,
@@ -500,6 +502,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="pso_ackley_1e6x1000", choices=sorted(WORKLOADS) + ["nds_rank_2e4", "nds_rank_1e5", "lora_es_config3", "rvea_config2", "rvea_5e6"])
     ap.add_argument("--lora-pop", type=int, default=1024)
+    ap.add_argument("--gradient-passes", type=int, default=6, choices=[1, 3, 6])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     if args.workload.startswith("nds_"):

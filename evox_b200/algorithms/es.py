@@ -121,13 +121,17 @@ class VirtualLoRAES(_ESBase):
         device: torch.device | None = None,
         shard: bool = False,
         group=None,
+        gradient_passes: int = 6,
     ):
-        """`shard=True` (under an initialised torch.distributed group): every rank keeps the whole
+        """`gradient_passes`: tensor-core passes of the population gradient (6 = fp32-accurate, the
+        default; 3 or 1 trade accuracy for speed, see `lora_gradient_from_seeds`).
+        `shard=True` (under an initialised torch.distributed group): every rank keeps the whole
         centre, but the gradient and update of each 2-D block are computed for this rank's rows only
         and the updated rows are allgathered; seeds are broadcast from rank 0 each generation."""
         super().__init__()
         device = torch.get_default_device() if device is None else torch.device(device)
         self.group = group
+        self.gradient_passes = gradient_passes
         self.rank, self.world_size = group_info(group) if shard else (0, 1)
         assert lora_rank > 0, "lora_rank must be greater than 0."
         self._common_init(pop_size, center_init, learning_rate, noise_stdev, optimizer, device)
@@ -155,13 +159,13 @@ class VirtualLoRAES(_ESBase):
             rows = self._row_shard(shape)
             if rows is None:  # whole block on every rank (identical arithmetic everywhere)
                 grad = torch.empty(n, dtype=torch.float32, device=dev)
-                lora_gradient_from_seeds(fitness, self.seeds, shape, self.lora_rank, offset, self.pop_size, sigma, out=grad)
+                lora_gradient_from_seeds(fitness, self.seeds, shape, self.lora_rank, offset, self.pop_size, sigma, out=grad, passes=self.gradient_passes)
                 _update_center(self, grad, start, n)
             else:
                 r0, r1 = rows
                 k = int(shape[-1])
                 grad = torch.empty((r1 - r0) * k, dtype=torch.float32, device=dev)
-                lora_gradient_from_seeds(fitness, self.seeds, shape, self.lora_rank, offset, self.pop_size, sigma, out=grad, rows=rows)
+                lora_gradient_from_seeds(fitness, self.seeds, shape, self.lora_rank, offset, self.pop_size, sigma, out=grad, rows=rows, passes=self.gradient_passes)
                 _update_center(self, grad, start + r0 * k, (r1 - r0) * k)
                 block = self.center[start : start + n]
                 dist.all_gather_into_tensor(block, block[r0 * k : r1 * k].clone(), group=self.group)

@@ -769,8 +769,9 @@ extern "C" int evox_lora_gradient_tc_supported(int64_t pop, int64_t d, int64_t k
 }
 
 extern "C" int evox_lora_gradient_tc(const float* fitness, const int64_t* seeds, uint64_t counter, int64_t pop, float sigma,
-                                     int64_t row_begin, int64_t d, int64_t k, int32_t r, float* grad, void* workspace,
-                                     size_t workspace_bytes, int32_t* error_flag, void* stream) {
+                                     int64_t row_begin, int64_t d, int64_t k, int32_t r, int32_t passes, float* grad,
+                                     void* workspace, size_t workspace_bytes, int32_t* error_flag, void* stream) {
+  EVOX_REQUIRE(passes == 1 || passes == 3 || passes == 6, EVOX_ERR_INVALID, "lora_gradient_tc: passes must be 1, 3 or 6");
   EVOX_REQUIRE(row_begin >= 0, EVOX_ERR_INVALID, "lora_gradient_tc: row_begin must be non-negative");
   EVOX_REQUIRE(fitness && seeds && grad && workspace && error_flag, EVOX_ERR_INVALID, "lora_gradient_tc: NULL pointer");
   EVOX_REQUIRE(evox_lora_gradient_tc_supported(pop, d, k, r), EVOX_ERR_INVALID,
@@ -808,7 +809,7 @@ extern "C" int evox_lora_gradient_tc(const float* fitness, const int64_t* seeds,
   a.error_flag = error_flag;
   // x = hi + mid + lo for both operands; keep every product down to 2^-24 of the largest one
   static const int pa[6] = {0, 0, 1, 0, 2, 1}, pb[6] = {0, 1, 0, 2, 0, 1};
-  a.n_combo = 6;
+  a.n_combo = passes;  // 1: bf16 operands (~4e-3); 3: + hi mid, mid hi (~2e-5); 6: fp32-accurate
   for (int c = 0; c < 6; ++c) {
     a.a_piece[c] = pa[c];
     a.b_piece[c] = pb[c];

@@ -282,12 +282,15 @@ int evox_lora_t_from_partials(const float* t_partial, int64_t rows, int64_t d, f
  * result within fp32 rounding of the reference's einsum. Needs rank 8, d a multiple of 128, k a
  * multiple of 256, pop a multiple of 8 (evox_lora_gradient_tc_supported). error_flag as above.
  * Only the d rows starting at row `row_begin` of the weight are computed (grad points at the
- * first of them): ranks that shard a block by rows each pass their own range. */
+ * first of them): ranks that shard a block by rows each pass their own range.
+ * passes = 6 is the fp32-accurate sum described above; 3 keeps hi hi + hi mid + mid hi (relative
+ * error about 2e-5); 1 is a plain bf16 product (about 4e-3), for callers that prefer speed. */
 size_t evox_lora_gradient_tc_workspace_bytes(int64_t pop, int64_t d, int64_t k);
 int evox_lora_gradient_tc_supported(int64_t pop, int64_t d, int64_t k, int32_t r);
 int evox_lora_gradient_tc(const float* fitness, const int64_t* seeds, uint64_t counter, int64_t pop,
-                          float sigma, int64_t row_begin, int64_t d, int64_t k, int32_t r, float* grad,
-                          void* workspace, size_t workspace_bytes, int32_t* error_flag, void* stream);
+                          float sigma, int64_t row_begin, int64_t d, int64_t k, int32_t r, int32_t passes,
+                          float* grad, void* workspace, size_t workspace_bytes, int32_t* error_flag,
+                          void* stream);
 
 /* fitness (pop) = -(sum of an individual's row_partial entries) / (batch * d): negative mean
  * squared error of the last layer, summed in a fixed order. */
