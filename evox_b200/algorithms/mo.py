@@ -1,0 +1,161 @@
+"""NSGA-II and RVEA with every step of a generation on the device.
+
+Constructor arguments and state names follow the reference (evox/algorithms/mo/nsga2.py:27-102,
+rvea.py:28-154). With the default operators a generation is: mating selection kernel -> one fused
+crossover + mutation + clamp kernel -> `evaluate` -> the environmental-selection kernels. Custom
+`selection_op` / `mutation_op` / `crossover_op` callables are honoured as in the reference."""
+
+from __future__ import annotations
+
+from typing import Callable, Optional
+
+import torch
+
+from ..core import Algorithm, Mutable, Parameter
+from ..operators.selection import nd_environmental_selection, ref_vec_guided
+from ..operators.variation import make_offspring, tournament_selection_multifit
+from ..problems.numerical import _relu_clamp_rows
+
+__all__ = ["NSGA2", "RVEA", "uniform_sampling"]
+
+
+def uniform_sampling(n: int, m: int) -> tuple[torch.Tensor, int]:
+    """Das-Dennis two-layer simplex-lattice reference vectors (host arithmetic, done once): the
+    largest design with at most `n` points, as evox/operators/sampling/uniform.py:8-51 builds it."""
+    from itertools import combinations
+    from math import comb
+
+    h1 = 1
+    while comb(h1 + m, m - 1) <= n:
+        h1 += 1
+
+    def lattice(h):
+        rows = []
+        for c in combinations(range(1, h + m), m - 1):
+            prev, parts = 0, []
+            for x in c:
+                parts.append(x - prev - 1)
+                prev = x
+            parts.append(h + m - 1 - prev)
+            rows.append(parts)
+        return torch.tensor(rows, dtype=torch.float32) / h
+
+    w = lattice(h1)
+    if h1 < m:
+        h2 = 0
+        while comb(h1 + m - 1, m - 1) + comb(h2 + m, m - 1) <= n:
+            h2 += 1
+        if h2 > 0:
+            w = torch.cat([w, lattice(h2) / 2 + 1 / (2 * m)], dim=0)
+    w = torch.maximum(w, torch.tensor(1e-6))
+    return w, w.shape[0]
+
+
+class _MOBase(Algorithm):
+    def _setup(self, pop_size, n_objs, lb, ub, selection_op, mutation_op, crossover_op, device):
+        assert lb.shape == ub.shape and lb.ndim == 1 and ub.ndim == 1
+        assert lb.dtype == ub.dtype and lb.device == ub.device
+        self.n_objs = n_objs
+        self.dim = lb.shape[0]
+        self.lb = lb.to(device=device, dtype=torch.float32)
+        self.ub = ub.to(device=device, dtype=torch.float32)
+        self.selection, self.mutation, self.crossover = selection_op, mutation_op, crossover_op
+        self.seed = int(torch.randint(0, 2**62, (), device="cpu"))
+        self.generation = 0
+
+    def _variation(self, pop: torch.Tensor, mating_pool: torch.Tensor | None, draws: dict | None) -> torch.Tensor:
+        """crossover -> mutation -> clamp (nsga2.py:95-97). Fused kernel unless custom operators are set."""
+        if self.crossover is None and self.mutation is None:
+            return make_offspring(pop, self.lb, self.ub, mating_pool, draws, seed=self.seed, generation=self.generation)
+        from ..operators.variation import polynomial_mutation, simulated_binary
+
+        parents = pop if mating_pool is None else pop[mating_pool]
+        crossed = (self.crossover or simulated_binary)(parents)
+        mutated = (self.mutation or polynomial_mutation)(crossed, self.lb, self.ub)
+        return _relu_clamp_rows(mutated, self.lb, self.ub)
+
+
+class NSGA2(_MOBase):
+    def __init__(self, pop_size: int, n_objs: int, lb: torch.Tensor, ub: torch.Tensor, selection_op: Optional[Callable] = None,
+                 mutation_op: Optional[Callable] = None, crossover_op: Optional[Callable] = None, device: torch.device | None = None):
+        super().__init__()
+        device = torch.get_default_device() if device is None else torch.device(device)
+        self.pop_size = pop_size
+        self._setup(pop_size, n_objs, lb, ub, selection_op, mutation_op, crossover_op, device)
+        pop = (self.ub - self.lb) * torch.rand(pop_size, self.dim, device=device) + self.lb
+        self.pop = Mutable(pop)
+        self.fit = Mutable(torch.full((pop_size, n_objs), torch.inf, device=device))
+        self.rank = Mutable(torch.full((pop_size,), torch.inf, device=device))
+        self.dis = Mutable(torch.full((pop_size,), -torch.inf, device=device))
+
+    def init_step(self):
+        self.fit = self.evaluate(self.pop)
+        _, _, self.rank, self.dis = nd_environmental_selection(self.pop, self.fit, self.pop_size)
+
+    def step(self, parents: torch.Tensor | None = None, draws: dict | None = None):
+        """One generation (nsga2.py:92-102). `parents` (pop_size, 2) and `draws` replace the random
+        draws of the tournament and of crossover / mutation."""
+        select = self.selection or tournament_selection_multifit
+        kwargs = {"parents": parents} if (self.selection is None and parents is not None) else {}
+        mating_pool = select(self.pop_size, [-self.dis, self.rank.to(torch.float32)], **kwargs)
+        offspring = self._variation(self.pop, mating_pool, draws)
+        off_fit = self.evaluate(offspring)
+        merge_pop = torch.cat([self.pop, offspring], dim=0)
+        merge_fit = torch.cat([self.fit, off_fit], dim=0)
+        self.pop, self.fit, self.rank, self.dis = nd_environmental_selection(merge_pop, merge_fit, self.pop_size)
+        self.generation += 1
+
+
+class RVEA(_MOBase):
+    def __init__(self, pop_size: int, n_objs: int, lb: torch.Tensor, ub: torch.Tensor, alpha: float = 2.0, fr: float = 0.1,
+                 max_gen: int = 100, selection_op: Optional[Callable] = None, mutation_op: Optional[Callable] = None,
+                 crossover_op: Optional[Callable] = None, device: torch.device | None = None):
+        super().__init__()
+        device = torch.get_default_device() if device is None else torch.device(device)
+        self._setup(pop_size, n_objs, lb, ub, selection_op, mutation_op, crossover_op, device)
+        self.alpha = Parameter(alpha, dtype=torch.float32, device=device)
+        self.fr = Parameter(fr, dtype=torch.float32, device=device)
+        self.max_gen = Parameter(max_gen, dtype=torch.float32, device=device)
+        self._adapt_every = max(int(round(1.0 / fr)), 1)
+        v, n = uniform_sampling(pop_size, n_objs)
+        v = v.to(device)
+        self.pop_size = n
+        self.pop = Mutable((self.ub - self.lb) * torch.rand(n, self.dim, device=device) + self.lb)
+        self.fit = Mutable(torch.full((n, n_objs), torch.inf, device=device))
+        self.reference_vector = Mutable(v.clone())
+        self.init_v = v
+        self.gen = Mutable(torch.tensor(0, dtype=torch.int64, device=device))
+
+    def init_step(self):
+        self.fit = self.evaluate(self.pop)
+
+    def _mating_rows(self, picks: torch.Tensor | None) -> torch.Tensor:
+        """Row numbers of the mating pool: uniform picks among the rows that are not all-NaN
+        (rvea.py:118-125)."""
+        n = self.pop_size
+        valid = ~torch.isnan(self.pop).all(dim=1)
+        order = torch.argsort(torch.where(valid, torch.arange(n, device=self.pop.device), torch.iinfo(torch.int32).max), stable=True)
+        if picks is None:
+            picks = (torch.rand(n, device=self.pop.device) * valid.sum()).long().clamp_(max=n - 1)
+        return order[picks]
+
+    def step(self, picks: torch.Tensor | None = None, draws: dict | None = None):
+        """One generation (rvea.py:135-154). `picks` (pop_size,) in [0, #valid rows) and `draws` replace
+        the random draws of the mating pool and of crossover / mutation."""
+        self.gen = self.gen + 1
+        self._gen_host = getattr(self, "_gen_host", 0) + 1
+        mating = self._mating_rows(picks)
+        # NaN rows never enter the pool, so the fused kernel can gather straight from pop
+        offspring = self._variation(self.pop, mating, draws)
+        off_fit = self.evaluate(offspring)
+        merge_pop = torch.cat([self.pop, offspring], dim=0)
+        merge_fit = torch.cat([self.fit, off_fit], dim=0)
+        theta = (self.gen / self.max_gen) ** self.alpha
+        select = self.selection or ref_vec_guided
+        self.pop, self.fit = select(merge_pop, merge_fit, self.reference_vector, theta)
+        if self._gen_host % self._adapt_every == 0:  # rvea.py:110-113, 127-133
+            f = self.fit
+            mx = torch.where(torch.isnan(f), -torch.inf, f).max(dim=0)[0]
+            mn = torch.where(torch.isnan(f), torch.inf, f).min(dim=0)[0]
+            self.reference_vector = self.init_v * (mx - mn)
+        self.generation += 1

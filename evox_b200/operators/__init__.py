@@ -1,3 +1,3 @@
-from . import selection
+from . import selection, variation
 
-__all__ = ["selection"]
+__all__ = ["selection", "variation"]

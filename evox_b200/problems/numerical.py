@@ -17,7 +17,13 @@ from ..core import Problem
 
 FIT_ACKLEY, FIT_RASTRIGIN, FIT_SPHERE = 0, 1, 2
 
-__all__ = ["ShiftAffineNumericalProblem", "Ackley", "Rastrigin", "Sphere", "ackley_func", "rastrigin_func", "sphere_func"]
+__all__ = ["ShiftAffineNumericalProblem", "Ackley", "Rastrigin", "Sphere", "DTLZ2", "ackley_func", "rastrigin_func", "sphere_func"]
+
+
+def _relu_clamp_rows(a: torch.Tensor, lb: torch.Tensor, ub: torch.Tensor) -> torch.Tensor:
+    """The reference's relu-form clamp (utils/jit_fix_operator.py:42-44) for the rare path where user
+    operators produce the offspring; the fused kernels apply it themselves."""
+    return a + torch.relu(lb - a) - torch.relu(a - ub)
 
 
 def _eval_rows(fitness_id: int, params: tuple[float, float, float], x: torch.Tensor) -> torch.Tensor:
@@ -116,3 +122,22 @@ class Sphere(ShiftAffineNumericalProblem):
 
     def _descriptor(self):
         return FIT_SPHERE, (0.0, 0.0, 0.0)
+
+
+class DTLZ2(Problem):
+    """DTLZ2 test problem (problems/numerical/dtlz.py:93-127): objectives on the unit sphere scaled by
+    1 + g, g = sum over the last d - m + 1 variables of (x - 0.5)^2. Used to build benchmark inputs and
+    to exercise NSGA-II / RVEA end to end; a handful of elementwise torch ops, not a kernel."""
+
+    def __init__(self, d: int = 12, m: int = 3):
+        super().__init__()
+        self.d, self.m = d, m
+
+    def evaluate(self, X: torch.Tensor) -> torch.Tensor:
+        m = self.m
+        n = X.shape[0]
+        g = torch.sum((X[:, m - 1 :] - 0.5) ** 2, dim=1, keepdim=True)
+        ones = torch.ones(n, 1, device=X.device)
+        cosines = torch.cat([ones, torch.clamp_min(torch.cos(X[:, : m - 1] * torch.pi / 2), 0.0)], dim=1)
+        sines = torch.cat([ones, torch.sin(torch.flip(X[:, : m - 1], dims=[1]) * torch.pi / 2)], dim=1)
+        return (1 + g) * torch.flip(torch.cumprod(cosines, dim=1), dims=[1]) * sines

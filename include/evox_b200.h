@@ -180,6 +180,31 @@ int evox_ref_vec_guided_phase(int32_t phase, const float* x, int64_t dx, const f
                               int64_t* next_index, void* workspace, size_t workspace_bytes, void* stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Mating and variation around P2 / P3 (NSGA2.step, RVEA.step).
+ * ------------------------------------------------------------------------------------------ */
+
+/* selected[r] = the candidate of parents[r][0..tournament_size) that sorts first by the LAST column
+ * of fitness (n_candidates x n_keys), ties by the earlier columns, ties by tournament slot.
+ * Replaces tournament_selection_multifit (operators/selection/tournament_selection.py:8-29) given
+ * its randint draw `parents`. */
+int evox_tournament_multifit(const int64_t* parents, int64_t n_round, int32_t tournament_size,
+                             const float* fitness, int64_t n_candidates, int32_t n_keys,
+                             int64_t* selected, void* stream);
+
+/* offspring (2 * (n / 2) x dim) from parents pop[mating_pool] (or rows 0..n-1 when mating_pool is
+ * NULL): simulated binary crossover (operators/crossover/sbx.py:4-39; flags bit 0), polynomial
+ * mutation (operators/mutation/pm_mutation.py:6-68; bit 1) and the relu-form clamp that NSGA2.step
+ * and RVEA.step apply next (algorithms/mo/nsga2.py:95-97; bit 2) in one pass. The six draw tensors
+ * are the reference's torch.rand / randint results in its order (sbx: mu, sign in {0,1} int64,
+ * half, pc — each (n/2 x dim); mutation: site, mu — each (2*(n/2) x dim)); all NULL = Philox
+ * streams keyed by (seed, generation). */
+int evox_offspring(const float* pop, const int64_t* mating_pool, int64_t n, int32_t dim, const float* lb,
+                   const float* ub, const float* sbx_mu, const int64_t* sbx_sign, const float* sbx_half,
+                   const float* sbx_pc, const float* pm_site, const float* pm_mu, float pro_c, float dis_c,
+                   float pro_m, float dis_m, int32_t flags, uint64_t seed, uint64_t generation,
+                   float* offspring, void* stream);
+
+/* ------------------------------------------------------------------------------------------
  * P4. Evolution strategies: Philox streams, virtual LoRA population, OpenES.
  * ------------------------------------------------------------------------------------------ */
 

@@ -218,7 +218,53 @@ def golden_es(out: dict):
         out[f"{tag}_center0"], out[f"{tag}_noise"], out[f"{tag}_center1"] = _np(center), _np(noise), _np(algo.center)
 
 
-GENERATORS = {"pso": golden_pso, "nds": golden_nds, "rvea": golden_rvea, "es": golden_es}
+def golden_variation(out: dict):
+    """tournament_selection_multifit, simulated_binary and polynomial_mutation with their random
+    draws replaced by recorded tensors (queued in the order the reference draws them)."""
+    import evox.operators.crossover.sbx as sbx_mod
+    import evox.operators.mutation.pm_mutation as pm_mod
+    import evox.operators.selection  # noqa: F401  (the package re-exports a function under the module's name)
+
+    ts_mod = sys.modules["evox.operators.selection.tournament_selection"]
+
+    g = torch.Generator().manual_seed(77)
+
+    def with_queue(mod, rands, ints, fn):
+        rq, iq = list(rands), list(ints)
+        real_rand, real_randint = mod.torch.rand, mod.torch.randint
+        mod.torch.rand = lambda *a, **k: rq.pop(0)
+        mod.torch.randint = lambda *a, **k: iq.pop(0)
+        try:
+            res = fn()
+        finally:
+            mod.torch.rand, mod.torch.randint = real_rand, real_randint
+        assert not rq and not iq
+        return res
+
+    n, d = 40, 7
+    lb, ub = torch.full((d,), -1.0), torch.linspace(1.0, 3.0, d)
+    x = lb + (ub - lb) * torch.rand(n, d, generator=g)
+    x[3, 2] = 5.0  # outside the box: exercises the clamps inside the mutation
+    h = n // 2
+    mu, sign = torch.rand(h, d, generator=g), torch.randint(0, 2, (h, d), generator=g)
+    r_half, r_pc = torch.rand(h, d, generator=g), torch.rand(h, d, generator=g)
+    crossed = with_queue(sbx_mod, [mu, r_half, r_pc], [sign], lambda: sbx_mod.simulated_binary(x))
+    site = torch.rand(n, d, generator=g) * 0.5  # pro_m / d = 1/7: make mutation sites common
+    pmu = torch.rand(n, d, generator=g)
+    mutated = with_queue(pm_mod, [site, pmu], [], lambda: pm_mod.polynomial_mutation(crossed, lb, ub))
+    for k, v in dict(x=x, lb=lb, ub=ub, sbx_mu=mu, sbx_sign=sign, sbx_half=r_half, sbx_pc=r_pc, crossed=crossed,
+                     pm_site=site, pm_mu=pmu, mutated=mutated).items():
+        out[f"var_{k}"] = _np(v)
+
+    rank = torch.randint(0, 4, (n,), generator=g).float()
+    dis = torch.rand(n, generator=g)
+    dis[::5] = float("inf")
+    parents = torch.randint(0, n, (n, 2), generator=g)
+    picked = with_queue(ts_mod, [], [parents], lambda: ts_mod.tournament_selection_multifit(n, [-dis, rank]))
+    out["ts_rank"], out["ts_dis"], out["ts_parents"], out["ts_selected"] = _np(rank), _np(dis), _np(parents), _np(picked)
+
+
+GENERATORS = {"pso": golden_pso, "nds": golden_nds, "rvea": golden_rvea, "es": golden_es, "variation": golden_variation}
 
 
 def main():
