@@ -14,10 +14,26 @@ from . import _cabi
 
 __all__ = [
     "philox_uniform", "philox_normal", "compute_counter_offsets", "generate_lora_factors",
-    "lora_delta_output", "lora_gradient", "lora_gradient_from_seeds", "lora_layer_bf16",
+    "lora_delta_output", "lora_gradient", "lora_gradient_from_seeds", "lora_layer_bf16", "raise_on_kernel_errors",
 ]
 
 _grad_ws: dict[torch.device, torch.Tensor] = {}
+
+# Error flags of tensor-core launches that have not been looked at yet. The kernels bound every wait
+# and report an expired one through a device word; reading it needs a host synchronisation, so the
+# flags are collected here and examined by `raise_on_kernel_errors()` (the problem / algorithm
+# classes call it once per generation, on the flags of the previous one).
+_pending_flags: list[tuple[str, torch.Tensor]] = []
+
+
+def raise_on_kernel_errors() -> None:
+    """Synchronise on and check every tensor-core launch since the last call; raise if a bounded
+    device-side wait expired (1 producer, 2 / 3 issuer, 4 epilogue) or shared memory was misaligned (5)."""
+    pending, _pending_flags[:] = list(_pending_flags), []
+    for what, flag in pending:
+        code = int(flag)
+        if code != 0:
+            raise _cabi.EvoxKernelError(f"{what}: the tensor-core kernel gave up with status {code} (a bounded wait expired)")
 
 
 def _seeds(seeds: torch.Tensor) -> torch.Tensor:
@@ -165,6 +181,7 @@ def lora_layer_bf16(h: torch.Tensor, w: torch.Tensor, seeds: torch.Tensor, count
         )
     )
     lora_layer_bf16.last_error_flag = err
+    _pending_flags.append(("lora_layer_bf16", err))
     if target is not None:
         fitness = torch.empty(pop, dtype=torch.float32, device=dev)
         _cabi.check(lib.evox_neg_mse_from_partials(_cabi.ptr(partial), pop, batch, d, _cabi.ptr(fitness), s))
@@ -213,6 +230,7 @@ def lora_gradient_from_seeds(fitness: torch.Tensor, seeds: torch.Tensor, weight_
                 )
             )
             lora_gradient_from_seeds.last_error_flag = err
+            _pending_flags.append(("lora_gradient_from_seeds", err))
             return out.view(d, k) if rows is not None else out.view(weight_shape)
         a, b = generate_lora_factors(seeds, weight_shape, rank, counter)
         out.copy_(lora_gradient(fitness, a, b, pop_size, sigma, weight_shape).reshape(-1))

@@ -17,7 +17,7 @@ from torch import nn
 
 from .. import _cabi
 from ..core import Problem
-from ..lora_kernels import compute_counter_offsets, generate_lora_factors, lora_layer_bf16
+from ..lora_kernels import compute_counter_offsets, generate_lora_factors, lora_layer_bf16, raise_on_kernel_errors
 from ..sharding import group_info, shard_bounds
 
 __all__ = ["VirtualLoRAProblem"]
@@ -148,6 +148,7 @@ class VirtualLoRAProblem(Problem):
 
     def evaluate(self, payload) -> torch.Tensor:
         center_flat, seeds, sigma = payload
+        raise_on_kernel_errors()  # status words of the previous generation's tensor-core launches
         if self.world_size > 1:
             return self._evaluate_sharded(center_flat, seeds, sigma)
         return self._evaluate_local(center_flat, seeds, sigma, None)
