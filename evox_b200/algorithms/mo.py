@@ -12,7 +12,7 @@ from typing import Callable, Optional
 import torch
 
 from ..core import Algorithm, Mutable, Parameter
-from ..operators.selection import nd_environmental_selection, ref_vec_guided
+from ..operators.selection import nd_environmental_selection, raise_on_kernel_errors, ref_vec_guided
 from ..operators.variation import make_offspring, tournament_selection_multifit
 from ..problems.numerical import _relu_clamp_rows
 
@@ -95,6 +95,7 @@ class NSGA2(_MOBase):
     def step(self, parents: torch.Tensor | None = None, draws: dict | None = None):
         """One generation (nsga2.py:92-102). `parents` (pop_size, 2) and `draws` replace the random
         draws of the tournament and of crossover / mutation."""
+        raise_on_kernel_errors()  # status of the previous generation's non-dominated sort
         select = self.selection or tournament_selection_multifit
         kwargs = {"parents": parents} if (self.selection is None and parents is not None) else {}
         mating_pool = select(self.pop_size, [-self.dis, self.rank.to(torch.float32)], **kwargs)

@@ -182,6 +182,7 @@ def lora_layer_bf16(h: torch.Tensor, w: torch.Tensor, seeds: torch.Tensor, count
     )
     lora_layer_bf16.last_error_flag = err
     _pending_flags.append(("lora_layer_bf16", err))
+    del _pending_flags[:-256]
     if target is not None:
         fitness = torch.empty(pop, dtype=torch.float32, device=dev)
         _cabi.check(lib.evox_neg_mse_from_partials(_cabi.ptr(partial), pop, batch, d, _cabi.ptr(fitness), s))

@@ -10,9 +10,27 @@ import torch
 
 from .. import _cabi
 
-__all__ = ["non_dominate_rank", "crowding_distance", "nd_environmental_selection", "ref_vec_guided", "ref_vec_guided_sharded"]
+__all__ = ["non_dominate_rank", "crowding_distance", "nd_environmental_selection", "ref_vec_guided", "ref_vec_guided_sharded",
+           "raise_on_kernel_errors"]
 
 _workspaces: dict[tuple[str, torch.device], torch.Tensor] = {}
+
+# Status words of rank computations that were launched without `check=True`; `raise_on_kernel_errors()`
+# reads them later (one host synchronisation), e.g. once per NSGA-II generation.
+_pending_status: list[torch.Tensor] = []
+
+
+def _remember(status: torch.Tensor) -> None:
+    _pending_status.append(status)
+    if len(_pending_status) > 64:  # nobody is checking: keep only the most recent ones
+        del _pending_status[:-64]
+
+
+def raise_on_kernel_errors() -> None:
+    """Check the status word of every non-dominated sort launched since the last call."""
+    pending, _pending_status[:] = list(_pending_status), []
+    for status in pending:
+        _raise_on_status(status)
 
 
 def _workspace(kind: str, device: torch.device, nbytes: int) -> torch.Tensor:
@@ -59,6 +77,8 @@ def non_dominate_rank(x: torch.Tensor, check: bool = False) -> torch.Tensor:
     )
     if check:
         _raise_on_status(status)
+    else:
+        _remember(status)
     return rank
 
 
@@ -110,6 +130,8 @@ def nd_environmental_selection(x: torch.Tensor, f: torch.Tensor, topk: int, retu
     )
     if check:
         _raise_on_status(status)
+    else:
+        _remember(status)
     if return_index:
         return out_x, out_f, out_rank, out_crowd, out_index
     return out_x, out_f, out_rank, out_crowd
