@@ -12,7 +12,9 @@
 //                              dominates j. A warp holds 32 dominators per word in registers,
 //                              walks the columns of a shared-memory tile and turns 32 comparisons
 //                              into one word with a ballot; tiles leave through shared memory as
-//                              128-byte rows. n^2 / 8 bytes are written once.
+//                              128-byte rows. Tiles above the diagonal band get both directions of a
+//                              pair from the same 2 m comparisons and also write the mirrored bits,
+//                              so tiles below the band are skipped. n^2 / 8 bytes are written once.
 //   3. nds_peel_kernel         persistent cooperative kernel. Front k = the unranked columns whose
 //                              row of Dt has no bit left in the unranked mask. Every column keeps a
 //                              witness position: the scan of its row resumes where it last found an
@@ -120,15 +122,38 @@ __device__ __forceinline__ bool dominates(const float (&a)[M], const float (&b)[
   return le && lt;
 }
 
+// Both directions of one pair from 2 m comparisons: with A = all(a <= b) and B = all(b <= a),
+// "a dominates b" = A and not B, "b dominates a" = B and not A. (A and B both true means a == b; a
+// NaN in either vector makes both false, so neither dominates, as in the reference.)
+template <int M>
+__device__ __forceinline__ void dominates_both(const float (&a)[M], const float (&b)[M], bool& a_dom_b, bool& b_dom_a) {
+  bool ab = true, ba = true;
+#pragma unroll
+  for (int k = 0; k < M; ++k) {
+    ab = ab && (a[k] <= b[k]);
+    ba = ba && (b[k] <= a[k]);
+  }
+  a_dom_b = ab && !ba;
+  b_dom_a = ba && !ab;
+}
+
+// One block = (32 * 8 * R dominators i) x (128 columns j). Blocks whose columns all lie AFTER their
+// dominators compute both directions of every pair at once and also emit the transposed bits
+// (row i, bits j); blocks whose columns all lie BEFORE their dominators have nothing left to do;
+// the blocks on the diagonal band compute the forward direction only, as every block used to.
 template <int M, int R>
 __global__ void __launch_bounds__(kThreads)
     nds_dominance_kernel(const float* __restrict__ fs, long long npad, long long n, uint32_t* __restrict__ Dt, int wp) {
-  constexpr int kWords = 8 * R;  // words of dominators per block (8 warps x R)
+  constexpr int kWords = 8 * R;         // words of dominators per block (8 warps x R)
+  constexpr int kRows = 32 * kWords;    // dominators per block
   __shared__ float sfj[M][kTileJ];
   __shared__ uint32_t sout[kTileJ][kWords];
+  __shared__ uint32_t sback[kTileJ / 32][kRows + 1];  // transposed direction: [word of j][dominator i]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const long long i0 = (long long)blockIdx.y * (32 * kWords);
+  const long long i0 = (long long)blockIdx.y * kRows;
   const long long j0 = (long long)blockIdx.x * kTileJ;
+  if (j0 + kTileJ <= i0) return;              // covered by the transposed output of the mirrored block
+  const bool both = j0 >= i0 + kRows;         // every column index exceeds every dominator index
 
   float fi[R][M];
 #pragma unroll
@@ -143,15 +168,42 @@ __global__ void __launch_bounds__(kThreads)
     sfj[k][jj] = (j < n) ? fs[(long long)k * npad + j] : __int_as_float(0x7fc00000);
   }
   __syncthreads();
+  if (!both) {
 #pragma unroll 4
-  for (int jj = 0; jj < kTileJ; ++jj) {
-    float fj[M];
+    for (int jj = 0; jj < kTileJ; ++jj) {
+      float fj[M];
 #pragma unroll
-    for (int k = 0; k < M; ++k) fj[k] = sfj[k][jj];
+      for (int k = 0; k < M; ++k) fj[k] = sfj[k][jj];
 #pragma unroll
-    for (int r = 0; r < R; ++r) {
-      const uint32_t word = __ballot_sync(0xffffffffu, dominates<M>(fi[r], fj));
-      if (lane == 0) sout[jj][warp * R + r] = word;
+      for (int r = 0; r < R; ++r) {
+        const uint32_t word = __ballot_sync(0xffffffffu, dominates<M>(fi[r], fj));
+        if (lane == 0) sout[jj][warp * R + r] = word;
+      }
+    }
+  } else {
+    uint32_t back[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) back[r] = 0u;
+#pragma unroll 4
+    for (int jj = 0; jj < kTileJ; ++jj) {
+      float fj[M];
+#pragma unroll
+      for (int k = 0; k < M; ++k) fj[k] = sfj[k][jj];
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        bool fwd, bwd;
+        dominates_both<M>(fi[r], fj, fwd, bwd);
+        const uint32_t word = __ballot_sync(0xffffffffu, fwd);
+        if (lane == 0) sout[jj][warp * R + r] = word;
+        back[r] |= (uint32_t)bwd << (jj & 31);
+      }
+      if ((jj & 31) == 31) {
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          sback[jj >> 5][(warp * R + r) * 32 + lane] = back[r];
+          back[r] = 0u;
+        }
+      }
     }
   }
   __syncthreads();
@@ -160,6 +212,16 @@ __global__ void __launch_bounds__(kThreads)
     const int jj = t / kWords, w = t - jj * kWords;
     const long long j = j0 + jj;
     if (j < n && w0 + w < wp) Dt[j * wp + w0 + w] = sout[jj][w];
+  }
+  if (both) {
+    // row i of Dt, the four words that hold columns j0 .. j0 + 127 (16-byte aligned: j0 is a multiple of 128)
+    const int wj = (int)(j0 >> 5);
+    for (int il = threadIdx.x; il < kRows; il += kThreads) {
+      const long long i = i0 + il;
+      if (i < n && wj + 3 < wp) {
+        *reinterpret_cast<uint4*>(Dt + i * wp + wj) = make_uint4(sback[0][il], sback[1][il], sback[2][il], sback[3][il]);
+      }
+    }
   }
 }
 
