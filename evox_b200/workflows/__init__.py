@@ -1,3 +1,4 @@
+from .eval_monitor import EvalMonitor
 from .std_workflow import StdWorkflow
 
-__all__ = ["StdWorkflow"]
+__all__ = ["StdWorkflow", "EvalMonitor"]

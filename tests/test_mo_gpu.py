@@ -146,3 +146,36 @@ def test_rvea_generation_vs_oracle(cuda):
     got = wf.algorithm.pop.cpu()
     assert torch.equal(torch.isnan(got), torch.isnan(want["next_x"]))
     close(torch.nan_to_num(got), torch.nan_to_num(want["next_x"]), 1.0, rel=1e-4)
+
+
+def test_eval_monitor_single_and_multi_objective(cuda):
+    """EvalMonitor with the fused PSO step (best-so-far must never get worse and must equal the
+    swarm's own global best) and with NSGA-II (the extracted front is non-dominated)."""
+    from evox_b200.algorithms import NSGA2, PSO
+    from evox_b200.problems.numerical import DTLZ2, Ackley
+    from evox_b200.workflows import EvalMonitor, StdWorkflow
+
+    d = 30
+    mon = EvalMonitor(topk=3, full_sol_history=False, device=cuda)
+    wf = StdWorkflow(PSO(256, torch.full((d,), -32.768), torch.full((d,), 32.768), device=cuda, seed=3), Ackley(), monitor=mon, device=cuda)
+    wf.init_step()
+    best = [float(mon.get_best_fitness())]
+    for _ in range(15):
+        wf.step()
+        best.append(float(mon.get_best_fitness()))
+    assert all(b <= a + 1e-12 for a, b in zip(best, best[1:]))
+    assert mon.get_topk_fitness().shape == (3,) and mon.get_topk_solutions().shape == (3, d)
+    assert len(mon.fitness_history) == 16
+    # the swarm's global best lags the monitor by one evaluation (it is folded in at the next step)
+    assert float(wf.algorithm.global_best_fit) >= best[-1] - 1e-6
+
+    mon = EvalMonitor(full_sol_history=True, device=cuda)
+    wf = StdWorkflow(NSGA2(64, 3, torch.zeros(12), torch.ones(12), device=cuda), DTLZ2(12, 3), monitor=mon, device=cuda)
+    wf.init_step()
+    for _ in range(5):
+        wf.step()
+    sol, fit = mon.get_pf()
+    assert sol.shape[0] == fit.shape[0] > 0
+    assert int(onds.non_dominate_rank(fit.cpu()).max()) == 0
+    with pytest.raises(ValueError):
+        mon.get_best_fitness()
