@@ -467,11 +467,12 @@ def run_lora_es(args):
         torch.cuda.synchronize()
         return e0.elapsed_time(e1) / reps
 
-    for _ in range(2):
+    for _ in range(3):
         wf.step()
-    step_ms = timed(wf.step, args.steps)
-    seeds = wf.algorithm.seeds
-    fwd_ms = timed(lambda: prob.evaluate((wf.algorithm.center, seeds, 0.02)), args.steps)
+    with ClockSampler(0) as clocks:
+        step_ms = timed(wf.step, args.steps)
+        seeds = wf.algorithm.seeds
+        fwd_ms = timed(lambda: prob.evaluate((wf.algorithm.center, seeds, 0.02)), args.steps)
     m = pop * batch
     flop_fwd = layers * (2.0 * m * width * width + 2.0 * m * rank * 2 * width)
     flop_grad = layers * 2.0 * width * (pop * rank) * width
@@ -481,7 +482,7 @@ def run_lora_es(args):
     peak = float(peaks.get("bf16_tflops_sustained", 1400.0))
     line = {
         "metric": "lora_es_generations_per_s", "value": 1e3 / step_ms, "unit": "gens/s", "n_gpus": 1, "steps": args.steps,
-        "warmup": 2, "ms_per_step": step_ms, "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
+        "warmup": 3, "ms_per_step": step_ms, "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": "lora_es_config3", "pop": pop, "batch": batch, "width": width, "layers": layers, "rank": rank,
                    "gradient_passes": args.gradient_passes},
         "forward_ms": fwd_ms,
@@ -490,6 +491,7 @@ def run_lora_es(args):
                      "peak_kind": "measured sustained" if peaks else "fallback", "traffic": None},
         "generation_tflops": (flop_fwd + flop_grad) / (step_ms * 1e-3) / 1e12,
         "gemm_error_flag": int(lora_layer_bf16.last_error_flag),
+        "clocks": clocks.summary(),
     }
     print(json.dumps(line), flush=True)
 

@@ -18,6 +18,13 @@
 //             the rank-r correction sigma * t B_p^T (t = H A_p^T from lora_down_bf16_kernel), ReLU,
 //             and store bf16 / fp32 — or, for the last layer, reduce (y - target)^2 per row.
 //             The second accumulator lets the next tile's products run underneath.
+// PAIR variant (rows a multiple of 256): two CTAs of a cluster share one 256 x 256 tile through
+// tcgen05.mma.cta_group::2. Each CTA loads its own 128 rows of H and HALF of the W tile (128 rows), so
+// a k-block costs 32 KB of shared-memory fill per SM instead of 48 KB and six stages fit; the leader
+// CTA (cluster rank 0) issues the products for both, each CTA keeps the accumulator of its own 128
+// rows in its own TMEM and runs the same epilogue on it. Both CTAs' copies report to the leader's
+// "full" barrier; tcgen05.commit releases the stage in both CTAs and hands the accumulator to both
+// epilogues; the epilogues return accumulators to the leader's "empty" barrier by a remote arrive.
 // Every mbarrier wait is bounded by a wall-clock limit; on expiry the kernel raises an error flag,
 // all roles leave their loops, outstanding copies are drained with the same bound and TMEM is freed.
 #include <cuda.h>
@@ -31,15 +38,24 @@
 namespace evox {
 namespace {
 
-constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4, RANK = 8;
+constexpr int BM = 128, BN = 256, BK = 64, RANK = 8;
+constexpr int kRingBytes = 196608;  // shared-memory ring: 4 stages of 48 KB, or 6 stages of 32 KB for a CTA pair
 constexpr int kEpilogueWarps = 8;  // two warps per TMEM lane quarter, 128 columns each
 constexpr int kEpilogueThreads = kEpilogueWarps * 32;
 constexpr int kGemmThreads = 64 + kEpilogueThreads;
-constexpr uint32_t kBytesA = BM * BK * 2, kBytesB = BN * BK * 2, kStageBytes = kBytesA + kBytesB;
+constexpr uint32_t kBytesA = BM * BK * 2;
+template <bool PAIR>
+struct Ring {
+  static constexpr uint32_t kBytesB = (PAIR ? BN / 2 : BN) * BK * 2;  // a CTA of a pair holds half of the W tile
+  static constexpr uint32_t kStageBytes = kBytesA + kBytesB;
+  static constexpr int STAGES = kRingBytes / kStageBytes;
+  static constexpr uint32_t kTxBytes = PAIR ? 2 * kStageBytes : kStageBytes;  // both CTAs report to the leader's barrier
+};
+constexpr int kMaxStages = 6;
 constexpr uint32_t kMaxInd = 2;  // individuals per 128-row tile (batch is a multiple of 64)
-constexpr uint32_t kOffBfac = STAGES * kStageBytes;                  // float [kMaxInd][BN][RANK]
+constexpr uint32_t kOffBfac = kRingBytes;                             // float [kMaxInd][BN][RANK]
 constexpr uint32_t kOffBnoise = kOffBfac + kMaxInd * BN * RANK * 4;  // float [kMaxInd][BN]
-constexpr uint32_t kOffAfac = kOffBnoise + kMaxInd * BN * 4;         // float [kMaxInd][BN][RANK]: next layer's A_p slice
+constexpr uint32_t kOffAfac = kOffBnoise + kMaxInd * BN * 4;         // float4 [kMaxInd][2][4][BN / 4]: next layer's A_p slice
 constexpr uint32_t kOffBars = kOffAfac + kMaxInd * BN * RANK * 4;    // mbarriers + tmem base
 constexpr uint32_t kSmemBytes = kOffBars + 256;                      // 231,680 B of the 232,448 B a CTA may use
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;           // 2 s per wait
@@ -128,6 +144,33 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       : "memory");
 }
 
+// ---- CTA-pair primitives -----------------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// Address of this CTA's shared-memory location `addr` as seen in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release;\nbarrier.cluster.wait.acquire;" ::: "memory");
+}
+// Tile copy issued by either CTA of a pair into its OWN shared memory; the bytes are reported to the
+// mbarrier at cluster address `bar` (the leader's).
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"((unsigned long long)map), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+
 // Shared-memory operand descriptor: K-major tile, rows of 128 bytes, 128-byte swizzle, 8-row groups
 // 1024 bytes apart (descriptor version 1 of sm_100).
 __device__ __forceinline__ unsigned long long umma_desc(uint32_t smem_addr) {
@@ -139,8 +182,10 @@ __device__ __forceinline__ unsigned long long umma_desc(uint32_t smem_addr) {
   return d;
 }
 
-// kind::f16 instruction descriptor: D = fp32, A = B = bf16, both K-major, N = 256, M = 128.
+// kind::f16 instruction descriptor: D = fp32, A = B = bf16, both K-major, N = 256, M = 128
+// (M = 256 for a CTA pair: 128 rows in each CTA).
 constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+constexpr uint32_t kIdescPair = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
 
 __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, unsigned long long a, unsigned long long b, uint32_t accumulate) {
   asm volatile(
@@ -150,6 +195,21 @@ __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, unsigned long long a,
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// Issued by one thread of the leader CTA: both CTAs' tensor cores multiply their own 128 rows of A by the
+// 256-row B tile whose halves sit in the two CTAs' shared memory (same offsets in both).
+__device__ __forceinline__ void umma_bf16_pair(uint32_t d_tmem, unsigned long long a, unsigned long long b, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n}"
+      ::"r"(d_tmem), "l"(a), "l"(b), "r"(kIdescPair), "r"(accumulate), "r"(0u)
+      : "memory");
+}
+// Arrives, once the products issued so far are complete, on the barrier at offset `bar` in BOTH CTAs.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(bar), "h"((unsigned short)3)
+               : "memory");
 }
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
   asm volatile(
@@ -186,8 +246,13 @@ __device__ __forceinline__ float4 normal4(unsigned long long seed, unsigned long
   return make_float4(r0 * c0, r0 * s0, r1 * c1, r1 * s1);
 }
 
+template <bool PAIR>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     lora_gemm_kernel(const __grid_constant__ CUtensorMap map_h, const __grid_constant__ CUtensorMap map_w, const GemmArgs a) {
+  constexpr int STAGES = Ring<PAIR>::STAGES;
+  constexpr uint32_t kStageBytes = Ring<PAIR>::kStageBytes;
+  constexpr int TM = PAIR ? 2 * BM : BM;  // rows of one scheduled tile
+  static_assert(STAGES <= kMaxStages, "barrier block too small");
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw;
   const uint32_t smem_base = smem_u32(smem);
@@ -207,7 +272,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long n_tiles_n = a.N / BN;
-  const long long n_tiles = (a.M / BM) * n_tiles_n;
+  const long long n_tiles = (a.M / TM) * n_tiles_n;
+  // a CTA pair walks the tile list together; each CTA owns 128 of the tile's 256 rows
+  const uint32_t cta_rank = PAIR ? cluster_rank() : 0u;
+  const long long tile_first = PAIR ? (long long)(blockIdx.x >> 1) : (long long)blockIdx.x;
+  const long long tile_step = PAIR ? (long long)(gridDim.x >> 1) : (long long)gridDim.x;
   const int k_blocks = (int)(a.K / BK);
   const int total_kb = k_blocks * a.n_combo;
   const int chunk_kb = a.chunk_kblocks > 0 ? a.chunk_kblocks : total_kb;
@@ -220,16 +289,22 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(tfull_bar(b), 1);
-      mbar_init(tempty_bar(b), kEpilogueThreads);
+      mbar_init(tempty_bar(b), PAIR ? 2 * kEpilogueThreads : kEpilogueThreads);  // the leader's collects both epilogues
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(tmem_slot)) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if constexpr (PAIR) {  // warp 1 of both CTAs takes part in the pair's allocation
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(tmem_slot)) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(tmem_slot)) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   fence_before_sync();
   __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();  // the peer's barriers exist before anything is sent to them
   fence_after_sync();
   const uint32_t tmem_base = *((volatile uint32_t*)tmem_slot);
 
@@ -240,18 +315,38 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       uint32_t ph = 0;
       uint32_t issued = 0;  // bit s: a copy into stage s may still be in flight
       bool ok = true;
-      for (long long tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-        const int m0 = (int)((tile / n_tiles_n) * BM), n0 = (int)((tile % n_tiles_n) * BN);
+      const uint32_t leader_full0 = PAIR ? map_to_cta(full_bar(0), 0u) : full_bar(0);
+      for (long long tile = tile_first; tile < n_tiles && ok; tile += tile_step) {
+        const int m0 = (int)((tile / n_tiles_n) * TM) + (int)cta_rank * BM;
+        const int n0 = (int)((tile % n_tiles_n) * BN) + (PAIR ? (int)cta_rank * (BN / 2) : 0);
         for (int kb = 0; kb < k_blocks * a.n_combo; ++kb) {
           if (!mbar_wait(empty_bar(s), ph ^ 1u, a.error_flag, 1)) {
             ok = false;
             break;
           }
           const int combo = kb / k_blocks, kk = kb - combo * k_blocks;
-          mbar_expect_tx(full_bar(s), kStageBytes);
-          tma_load_2d(smem_base + s * kStageBytes, &map_h, full_bar(s), (int)(a.a_piece[combo] * a.K) + kk * BK, m0);
-          tma_load_2d(smem_base + s * kStageBytes + kBytesA, &map_w, full_bar(s), (int)(a.b_piece[combo] * a.K) + kk * BK, n0);
+          if constexpr (PAIR) {
+            if (cta_rank == 0) mbar_expect_tx(full_bar(s), Ring<PAIR>::kTxBytes);
+            const uint32_t fb = leader_full0 + 8u * s;
+            tma_load_2d_pair(smem_base + s * kStageBytes, &map_h, fb, (int)(a.a_piece[combo] * a.K) + kk * BK, m0);
+            tma_load_2d_pair(smem_base + s * kStageBytes + kBytesA, &map_w, fb, (int)(a.b_piece[combo] * a.K) + kk * BK, n0);
+          } else {
+            mbar_expect_tx(full_bar(s), kStageBytes);
+            tma_load_2d(smem_base + s * kStageBytes, &map_h, full_bar(s), (int)(a.a_piece[combo] * a.K) + kk * BK, m0);
+            tma_load_2d(smem_base + s * kStageBytes + kBytesA, &map_w, full_bar(s), (int)(a.b_piece[combo] * a.K) + kk * BK, n0);
+          }
           issued |= 1u << s;
+          if (++s == STAGES) {
+            s = 0;
+            ph ^= 1u;
+          }
+        }
+      }
+      if constexpr (PAIR) {
+        // the leader's releases of this CTA's stages arrive asynchronously: see the last one of every stage
+        // land before this CTA may leave
+        for (int q = 0; q < STAGES && ok; ++q) {
+          if (!mbar_wait(empty_bar(s), ph ^ 1u, a.error_flag, 1)) ok = false;
           if (++s == STAGES) {
             s = 0;
             ph ^= 1u;
@@ -262,6 +357,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         // drain: the last copy issued into each stage must land before shared memory is released
         for (int q = 0; q < STAGES; ++q) {
           if (!(issued & (1u << q))) continue;
+          if (PAIR && cta_rank != 0) continue;  // the follower's copies report to the leader: timed wait below
           // stage q was last filled in phase (ph if q < s else ph ^ 1)
           const uint32_t last = (q < s) ? ph : (ph ^ 1u);
           const unsigned long long t0 = global_timer_ns();
@@ -269,16 +365,23 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             if (global_timer_ns() - t0 > kWaitLimitNs) break;
           }
         }
+        if constexpr (PAIR) {
+          // nothing in this CTA can observe the follower's copies (or the products the leader still has in
+          // flight on this CTA's shared memory): give them a millisecond, far beyond their latency
+          const unsigned long long t0 = global_timer_ns();
+          while (global_timer_ns() - t0 < 1000000ull) {
+          }
+        }
       }
     }
   } else if (warp == 1) {
     // ------------------------------- MMA issuer --------------------------------------------
-    if (lane == 0) {
+    if (lane == 0 && cta_rank == 0) {  // of a pair only the leader issues
       int s = 0;
       uint32_t ph = 0;
       long long it = 0;
       bool ok = true;
-      for (long long tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+      for (long long tile = tile_first; tile < n_tiles && ok; tile += tile_step) {
         for (int chunk = 0; chunk < n_chunks && ok; ++chunk, ++it) {
           const int buf = (int)(it & 1);
           const uint32_t acc_ph = (uint32_t)((it >> 1) & 1);
@@ -298,15 +401,21 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             const uint32_t sa = smem_base + s * kStageBytes, sb = sa + kBytesA;
 #pragma unroll
             for (int k = 0; k < BK / 16; ++k) {
-              umma_bf16(d_tmem, umma_desc(sa + k * 32), umma_desc(sb + k * 32), (kb > kb0 || k > 0) ? 1u : 0u);
+              if constexpr (PAIR)
+                umma_bf16_pair(d_tmem, umma_desc(sa + k * 32), umma_desc(sb + k * 32), (kb > kb0 || k > 0) ? 1u : 0u);
+              else
+                umma_bf16(d_tmem, umma_desc(sa + k * 32), umma_desc(sb + k * 32), (kb > kb0 || k > 0) ? 1u : 0u);
             }
-            umma_commit(empty_bar(s));  // stage reusable once these products have read it
+            // stage reusable (in both CTAs of a pair) once these products have read it
+            if constexpr (PAIR) umma_commit_pair(empty_bar(s)); else umma_commit(empty_bar(s));
             if (++s == STAGES) {
               s = 0;
               ph ^= 1u;
             }
           }
-          if (ok) umma_commit(tfull_bar(buf));  // accumulator complete
+          if (ok) {  // accumulator complete
+            if constexpr (PAIR) umma_commit_pair(tfull_bar(buf)); else umma_commit(tfull_bar(buf));
+          }
         }
       }
     }
@@ -319,8 +428,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     const int inds_per_tile = (a.batch >= BM) ? 1 : (int)(BM / a.batch);
     long long it = 0;
     bool ok = true;
-    for (long long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-      const long long m0 = (tile / n_tiles_n) * BM;
+    const uint32_t leader_tempty0 = PAIR ? map_to_cta(tempty_bar(0), 0u) : tempty_bar(0);
+    for (long long tile = tile_first; tile < n_tiles; tile += tile_step) {
+      const long long m0 = (tile / n_tiles_n) * TM + (long long)cta_rank * BM;
       const int n_blk = (int)(tile % n_tiles_n);
       const long long n0 = (long long)n_blk * BN;
       const long long p_first = m0 / a.batch;
@@ -345,17 +455,23 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         }
       }
       if (a.t_partial != nullptr) {
-        // A'_p[q][n]: element q * N + n of the next block's stream; one call covers 4 columns of one q
-        for (int idx = et; idx < inds_per_tile * RANK * (BN / 4); idx += kEpilogueThreads) {
-          const int ind = idx / (RANK * (BN / 4)), rest = idx - ind * (RANK * (BN / 4));
-          const int q = rest / (BN / 4), c4 = rest - q * (BN / 4);
+        // A'_p[q][n]: element q * N + n of the next block's stream; one call covers 4 columns of one q.
+        // A task makes 4 calls (q = 4 half .. 4 half + 3) for columns 4 c4 .. 4 c4 + 3 and stores, per column,
+        // the four q values as one float4 at [ind][half][column & 3][column >> 2]: neighbouring threads write
+        // neighbouring float4s (the readers all read one address at a time, any layout serves them).
+        for (int idx = et; idx < inds_per_tile * 2 * (BN / 4); idx += kEpilogueThreads) {
+          const int ind = idx / (2 * (BN / 4)), rest = idx - ind * (2 * (BN / 4));
+          const int half = rest / (BN / 4), c4 = rest - half * (BN / 4);
           const unsigned long long seed = (unsigned long long)a.seeds[p_first + ind];
-          const float4 z = normal4(seed, a.next_a_counter, (uint32_t)(((long long)q * a.N + n0) / 4 + c4));
-          float* dst = afac + ((size_t)(ind * BN + c4 * 4) * RANK + q);
-          dst[0] = z.x;
-          dst[RANK] = z.y;
-          dst[2 * RANK] = z.z;
-          dst[3 * RANK] = z.w;
+          float4 z[4];
+#pragma unroll
+          for (int qq = 0; qq < 4; ++qq)
+            z[qq] = normal4(seed, a.next_a_counter, (uint32_t)(((long long)(half * 4 + qq) * a.N + n0) / 4 + c4));
+          float4* dst = reinterpret_cast<float4*>(afac) + (size_t)ind * (BN * 2) + (size_t)(half * 4) * (BN / 4) + c4;
+          dst[0] = make_float4(z[0].x, z[1].x, z[2].x, z[3].x);
+          dst[BN / 4] = make_float4(z[0].y, z[1].y, z[2].y, z[3].y);
+          dst[2 * (BN / 4)] = make_float4(z[0].z, z[1].z, z[2].z, z[3].z);
+          dst[3 * (BN / 4)] = make_float4(z[0].w, z[1].w, z[2].w, z[3].w);
         }
       }
       const long long row = m0 + row_in_tile;
@@ -411,17 +527,22 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         }
         if (target_row) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const float dlt = y[j] - __ldg(target_row + c + j);
-            sq_sum = fmaf(dlt, dlt, sq_sum);
+          for (int j = 0; j < 32; j += 4) {
+            const float4 tg = __ldg(reinterpret_cast<const float4*>(target_row + c + j));
+            const float d0 = y[j] - tg.x, d1 = y[j + 1] - tg.y, d2 = y[j + 2] - tg.z, d3 = y[j + 3] - tg.w;
+            sq_sum = fmaf(d0, d0, sq_sum);
+            sq_sum = fmaf(d1, d1, sq_sum);
+            sq_sum = fmaf(d2, d2, sq_sum);
+            sq_sum = fmaf(d3, d3, sq_sum);
           }
         } else if (a.out_bf16) {
           if (a.t_partial != nullptr) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
               const float yb = __bfloat162float(__float2bfloat16_rn(y[j]));  // what the next layer will read
-              const float4 a0 = *reinterpret_cast<const float4*>(af + (size_t)(c + j) * RANK);
-              const float4 a1 = *reinterpret_cast<const float4*>(af + (size_t)(c + j) * RANK + 4);
+              const float4* af4 = reinterpret_cast<const float4*>(af) + (size_t)(j & 3) * (BN / 4) + ((c + j) >> 2);
+              const float4 a0 = af4[0];             // q = 0..3 of column c + j
+              const float4 a1 = af4[BN];            // q = 4..7: half 1 starts 4 * (BN / 4) float4s further
               tp[0] = fmaf(yb, a0.x, tp[0]);
               tp[1] = fmaf(yb, a0.y, tp[1]);
               tp[2] = fmaf(yb, a0.z, tp[2]);
@@ -464,15 +585,22 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         *reinterpret_cast<float4*>(o + 4) = make_float4(tp[4], tp[5], tp[6], tp[7]);
       }
       fence_before_sync();
-      mbar_arrive(tempty_bar(buf));  // this thread no longer reads the accumulator
+      // this thread no longer reads the accumulator
+      if constexpr (PAIR) mbar_arrive_cluster(leader_tempty0 + 8u * buf); else mbar_arrive(tempty_bar(buf));
       }
     }
   }
   fence_before_sync();
   __syncthreads();
+  // a pair leaves together: until here the peer may still arrive on this CTA's barriers, and the leader's
+  // products read this CTA's shared memory
+  if constexpr (PAIR) cluster_sync_all();
   if (warp == 1) {
     fence_after_sync();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
+    if constexpr (PAIR)
+      asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
+    else
+      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
   }
 }
 
@@ -571,14 +699,20 @@ __global__ void t_partial_reduce_kernel(const float* __restrict__ t_partial, lon
 }
 
 // fitness[p] = -(sum of row partials of individual p) / (batch * N): negative mean squared error.
-__global__ void neg_mse_kernel(const float* __restrict__ row_partial, long long batch, long long tiles_n, long long N,
-                               long long pop, float* __restrict__ fitness) {
-  const long long p = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (p >= pop) return;
+// One block of 128 threads per individual (fixed summation order: strided per thread, then a tree).
+__global__ void __launch_bounds__(128)
+    neg_mse_kernel(const float* __restrict__ row_partial, long long batch, long long tiles_n, long long N, long long pop,
+                   float* __restrict__ fitness) {
+  __shared__ float part[4];
+  const long long p = blockIdx.x;
+  const long long n = batch * tiles_n * 2;  // two column halves per tile
+  const float* rp = row_partial + p * n;
   float s = 0.f;
-  const float* rp = row_partial + p * batch * tiles_n * 2;  // two column halves per tile
-  for (long long i = 0; i < batch * tiles_n * 2; ++i) s += rp[i];
-  fitness[p] = -s / (float)(batch * N);
+  for (long long i = threadIdx.x; i < n; i += 128) s += rp[i];
+  s = warp_sum(s);
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x == 0) fitness[p] = -((part[0] + part[1]) + (part[2] + part[3])) / (float)(batch * N);
 }
 
 // fp32 -> three bf16 pieces with x = hi + mid + lo (each piece rounds what the previous ones left).
@@ -604,7 +738,8 @@ __global__ void __launch_bounds__(256)
   const long long n_a = pop * (k / 4);    // one task per (i, l / 4): 8 x 4 values of A_i[:][l..l+3]
   for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < n_b + n_a; t += (long long)gridDim.x * blockDim.x) {
     if (t < n_b) {
-      const long long i = t / d, j = t - i * d;
+      // neighbouring threads take neighbouring individuals: their 16-byte pieces are adjacent in a row
+      const long long j = t / pop, i = t - j * pop;
       const unsigned long long seed = (unsigned long long)seeds[i];
       const float f = fitness[i];
       const long long jg = row_begin + j;  // row of the whole weight block
@@ -618,7 +753,7 @@ __global__ void __launch_bounds__(256)
         *reinterpret_cast<uint4*>(bf3 + j * (3 * Kt) + c * Kt + i * RANK) = *reinterpret_cast<const uint4*>(p[c]);
     } else {
       const long long u = t - n_b;
-      const long long i = u / (k / 4), l4 = u - i * (k / 4);
+      const long long l4 = u / pop, i = u - l4 * pop;
       const unsigned long long seed = (unsigned long long)seeds[i];
       __align__(16) __nv_bfloat16 p[4][3][8];  // [row l..l+3][piece][q]
 #pragma unroll
@@ -671,6 +806,43 @@ int make_map(CUtensorMap* map, const void* base, long long rows, long long K, in
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   EVOX_REQUIRE(r == CUDA_SUCCESS, EVOX_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+  return EVOX_OK;
+}
+
+// A CTA pair per 256 x 256 tile when the rows allow it, one CTA per 128 x 256 tile otherwise.
+int launch_gemm(const void* a_base, long long a_rows, const void* b_base, long long b_rows, long long k_cols, const GemmArgs& a,
+                cudaStream_t stream) {
+  const bool pair = (a.M % (2 * BM) == 0) && sm_count() >= 2;
+  CUtensorMap map_a, map_b;
+  if (int rc = make_map(&map_a, a_base, a_rows, k_cols, BM)) return rc;
+  if (int rc = make_map(&map_b, b_base, b_rows, k_cols, pair ? BN / 2 : BN)) return rc;
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  if (pair) {
+    EVOX_CUDA(cudaFuncSetAttribute(lora_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+    const long long n_tiles = (a.M / (2 * BM)) * (a.N / BN);
+    long long pairs = sm_count() / 2;
+    if (pairs > n_tiles) pairs = n_tiles;
+    cfg.gridDim = dim3((unsigned)(2 * pairs));
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    EVOX_CUDA(cudaLaunchKernelEx(&cfg, lora_gemm_kernel<true>, map_a, map_b, a));
+  } else {
+    EVOX_CUDA(cudaFuncSetAttribute(lora_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+    const long long n_tiles = (a.M / BM) * (a.N / BN);
+    long long grid = sm_count();
+    if (grid > n_tiles) grid = n_tiles;
+    cfg.gridDim = dim3((unsigned)grid);
+    EVOX_CUDA(cudaLaunchKernelEx(&cfg, lora_gemm_kernel<false>, map_a, map_b, a));
+  }
+  EVOX_LAUNCH_CHECK();
   return EVOX_OK;
 }
 
@@ -737,24 +909,14 @@ extern "C" int evox_lora_gemm_bf16(const void* h, const void* w, const float* bi
   a.next_a_counter = next_a_counter;
   EVOX_REQUIRE(t_next_partial == nullptr || out_bf16 != nullptr, EVOX_ERR_INVALID,
                "lora_gemm_bf16: the fused next-layer projection needs the bf16 output sink");
-  CUtensorMap map_h, map_w;
-  if (int rc = make_map(&map_h, h, a.M, k, BM)) return rc;
-  if (int rc = make_map(&map_w, w, d, k, BN)) return rc;
-  EVOX_CUDA(cudaFuncSetAttribute(lora_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
-  const long long n_tiles = (a.M / BM) * (a.N / BN);
-  long long grid = sm_count();
-  if (grid > n_tiles) grid = n_tiles;
-  lora_gemm_kernel<<<(unsigned)grid, kGemmThreads, kSmemBytes, reinterpret_cast<cudaStream_t>(stream)>>>(map_h, map_w, a);
-  EVOX_LAUNCH_CHECK();
-  return EVOX_OK;
+  return launch_gemm(h, a.M, w, d, k, a, reinterpret_cast<cudaStream_t>(stream));
 }
 
 extern "C" int evox_neg_mse_from_partials(const float* row_partial, int64_t pop, int64_t batch, int64_t d, float* fitness,
                                           void* stream) {
   EVOX_REQUIRE(row_partial && fitness, EVOX_ERR_INVALID, "neg_mse_from_partials: NULL pointer");
   EVOX_REQUIRE(pop > 0 && batch > 0 && d > 0 && d % BN == 0, EVOX_ERR_INVALID, "neg_mse_from_partials: bad sizes");
-  neg_mse_kernel<<<(unsigned)((pop + 127) / 128), 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(row_partial, batch, d / BN, d, pop,
-                                                                                                 fitness);
+  neg_mse_kernel<<<(unsigned)pop, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(row_partial, batch, d / BN, d, pop, fitness);
   EVOX_LAUNCH_CHECK();
   return EVOX_OK;
 }
@@ -819,16 +981,7 @@ extern "C" int evox_lora_gradient_tc(const float* fitness, const int64_t* seeds,
   a.out_scale = 1.0f / ((float)pop * sigma);
   a.ld_out = k;
   a.chunk_kblocks = 32;  // 128 truncating accumulations per accumulator at most
-  CUtensorMap map_a, map_b;
-  if (int rc = make_map(&map_a, bf3, d, 3 * Kt, BM)) return rc;
-  if (int rc = make_map(&map_b, at3, k, 3 * Kt, BN)) return rc;
-  EVOX_CUDA(cudaFuncSetAttribute(lora_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
-  const long long n_tiles = (a.M / BM) * (a.N / BN);
-  long long grid = sm_count();
-  if (grid > n_tiles) grid = n_tiles;
-  lora_gemm_kernel<<<(unsigned)grid, kGemmThreads, kSmemBytes, s>>>(map_a, map_b, a);
-  EVOX_LAUNCH_CHECK();
-  return EVOX_OK;
+  return launch_gemm(bf3, d, at3, k, 3 * Kt, a, s);
 }
 
 extern "C" int evox_lora_t_from_partials(const float* t_partial, int64_t rows, int64_t d, float* t, void* stream) {

@@ -31,7 +31,9 @@ def rel_err(got, want):
     (2, 64, 256, 256, False, False),
     (4, 64, 512, 512, True, True),
     (3, 128, 256, 768, False, True),
-    (128, 64, 256, 2048, False, True),   # 512 tiles: every CTA walks several tiles and both accumulators
+    (128, 64, 256, 2048, False, True),   # 256 pair tiles: every CTA pair walks several tiles and both accumulators
+    (130, 64, 1024, 1024, True, True),   # 8,320 rows = 65 x 128: single-CTA tiles, 16 k-blocks through the 4-stage ring
+    (64, 128, 1024, 512, True, False),   # pairs, 16 k-blocks through the 6-stage ring
 ])
 def test_layer_vs_fp32(cuda, pop, batch, k, d, bias, relu):
     from evox_b200.lora_kernels import lora_layer_bf16
@@ -56,11 +58,12 @@ def test_layer_vs_fp32(cuda, pop, batch, k, d, bias, relu):
     assert rel_err(plain, h.float() @ w.float().t()) <= 1e-3
 
 
-def test_fused_negative_mse(cuda):
+@pytest.mark.parametrize("pop", [6, 8])  # 384 rows: one CTA per tile; 512 rows: CTA pairs
+def test_fused_negative_mse(cuda, pop):
     from evox_b200.lora_kernels import lora_layer_bf16
 
     g = torch.Generator().manual_seed(5)
-    pop, batch, k, d = 6, 64, 256, 512
+    batch, k, d = 64, 256, 512
     h = torch.randn(pop, batch, k, generator=g).bfloat16()
     w = (torch.randn(d, k, generator=g) / k**0.5).bfloat16()
     seeds = torch.randint(0, 2**31, (pop,), generator=g, dtype=torch.int64)
@@ -132,14 +135,15 @@ def test_problem_bf16_path_with_fused_mse(cuda):
     assert rel_err(got, want) <= 2e-2
 
 
-def test_fused_next_layer_projection(cuda):
+@pytest.mark.parametrize("pop", [6, 8])
+def test_fused_next_layer_projection(cuda, pop):
     """The epilogue's projection for the next layer equals the standalone projection kernel run on
     the bf16 output (same factors, fp32 accumulation; only the summation order differs)."""
     from evox_b200 import _cabi
     from evox_b200.lora_kernels import lora_layer_bf16
 
     g = torch.Generator().manual_seed(17)
-    pop, batch, k, d = 6, 64, 256, 512
+    batch, k, d = 64, 256, 512
     h = torch.randn(pop, batch, k, generator=g).bfloat16().to(cuda)
     w = (torch.randn(d, k, generator=g) / k**0.5).bfloat16().to(cuda)
     seeds = torch.randint(0, 2**31, (pop,), generator=g, dtype=torch.int64).to(cuda)
