@@ -91,8 +91,13 @@ struct GemmArgs {
   unsigned long long next_a_counter;
   // The tensor core adds each K = 16 product into the fp32 accumulator with truncation, a bias that
   // grows with the number of accumulations. With chunk_kblocks > 0 an accumulator only collects that
-  // many k-blocks; the epilogue then adds the chunks into out_f32 in round-to-nearest fp32.
+  // many k-blocks; the epilogue (ACCUM variant of the kernel) adds the chunks in round-to-nearest fp32
+  // registers and writes out_f32 once.
   int chunk_kblocks;
+  // ACCUM variant only: the chunks of a tile are divided among k_split (1 or 2) work items that run on
+  // different CTAs; with 2 each adds its sum into the zero-filled out_f32 with an atomic add (two addends:
+  // the result does not depend on their order).
+  int k_split;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -246,7 +251,7 @@ __device__ __forceinline__ float4 normal4(unsigned long long seed, unsigned long
   return make_float4(r0 * c0, r0 * s0, r1 * c1, r1 * s1);
 }
 
-template <bool PAIR>
+template <bool PAIR, bool ACCUM>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     lora_gemm_kernel(const __grid_constant__ CUtensorMap map_h, const __grid_constant__ CUtensorMap map_w, const GemmArgs a) {
   constexpr int STAGES = Ring<PAIR>::STAGES;
@@ -281,6 +286,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   const int total_kb = k_blocks * a.n_combo;
   const int chunk_kb = a.chunk_kblocks > 0 ? a.chunk_kblocks : total_kb;
   const int n_chunks = (total_kb + chunk_kb - 1) / chunk_kb;
+  // work item w = part * n_tiles + tile: chunks [part * n_chunks / k_split, (part + 1) * n_chunks / k_split) of a tile
+  const int k_split = ACCUM ? a.k_split : 1;
+  const long long n_work = n_tiles * k_split;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -316,10 +324,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       uint32_t issued = 0;  // bit s: a copy into stage s may still be in flight
       bool ok = true;
       const uint32_t leader_full0 = PAIR ? map_to_cta(full_bar(0), 0u) : full_bar(0);
-      for (long long tile = tile_first; tile < n_tiles && ok; tile += tile_step) {
+      for (long long work = tile_first; work < n_work && ok; work += tile_step) {
+        const long long tile = work % n_tiles;
+        const int part = (int)(work / n_tiles);
+        const int kb_begin = (part * n_chunks / k_split) * chunk_kb;
+        const int kb_end = min(((part + 1) * n_chunks / k_split) * chunk_kb, total_kb);
         const int m0 = (int)((tile / n_tiles_n) * TM) + (int)cta_rank * BM;
         const int n0 = (int)((tile % n_tiles_n) * BN) + (PAIR ? (int)cta_rank * (BN / 2) : 0);
-        for (int kb = 0; kb < k_blocks * a.n_combo; ++kb) {
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
           if (!mbar_wait(empty_bar(s), ph ^ 1u, a.error_flag, 1)) {
             ok = false;
             break;
@@ -381,8 +393,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       uint32_t ph = 0;
       long long it = 0;
       bool ok = true;
-      for (long long tile = tile_first; tile < n_tiles && ok; tile += tile_step) {
-        for (int chunk = 0; chunk < n_chunks && ok; ++chunk, ++it) {
+      for (long long work = tile_first; work < n_work && ok; work += tile_step) {
+        const int part = (int)(work / n_tiles);
+        const int ch0 = part * n_chunks / k_split, ch1 = (part + 1) * n_chunks / k_split;
+        for (int chunk = ch0; chunk < ch1 && ok; ++chunk, ++it) {
           const int buf = (int)(it & 1);
           const uint32_t acc_ph = (uint32_t)((it >> 1) & 1);
           if (!mbar_wait(tempty_bar(buf), acc_ph ^ 1u, a.error_flag, 2)) {
@@ -429,10 +443,53 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     long long it = 0;
     bool ok = true;
     const uint32_t leader_tempty0 = PAIR ? map_to_cta(tempty_bar(0), 0u) : tempty_bar(0);
-    for (long long tile = tile_first; tile < n_tiles; tile += tile_step) {
+    for (long long work = tile_first; work < n_work; work += tile_step) {
+      const long long tile = work % n_tiles;
+      const int part = (int)(work / n_tiles);
+      const int ch0 = part * n_chunks / k_split, ch1 = (part + 1) * n_chunks / k_split;
       const long long m0 = (tile / n_tiles_n) * TM + (long long)cta_rank * BM;
       const int n_blk = (int)(tile % n_tiles_n);
       const long long n0 = (long long)n_blk * BN;
+      if constexpr (ACCUM) {
+        // plain product summed over the work item's chunks in registers (one row, 128 columns per thread)
+        float sum[4][32];
+#pragma unroll
+        for (int ci = 0; ci < 4; ++ci)
+#pragma unroll
+          for (int j = 0; j < 32; ++j) sum[ci][j] = 0.f;
+        for (int chunk = ch0; chunk < ch1; ++chunk, ++it) {
+          const int buf = (int)(it & 1);
+          const uint32_t acc_ph = (uint32_t)((it >> 1) & 1);
+          if (ok && !mbar_wait(tfull_bar(buf), acc_ph, a.error_flag, 4)) ok = false;
+          if (!ok) continue;
+          fence_after_sync();
+#pragma unroll
+          for (int ci = 0; ci < 4; ++ci) {
+            uint32_t v[32];
+            tmem_ld32(tmem_base + (uint32_t)(buf * BN + col_half * (BN / 2) + ci * 32) + ((uint32_t)(quarter * 32) << 16), v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) sum[ci][j] += __uint_as_float(v[j]);
+          }
+          fence_before_sync();
+          if constexpr (PAIR) mbar_arrive_cluster(leader_tempty0 + 8u * buf); else mbar_arrive(tempty_bar(buf));
+        }
+        if (ok) {
+          float* o = a.out_f32 + (m0 + row_in_tile) * a.ld_out + n0 + col_half * (BN / 2);
+#pragma unroll
+          for (int ci = 0; ci < 4; ++ci)
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              const float4 r = make_float4(sum[ci][j] * a.out_scale, sum[ci][j + 1] * a.out_scale, sum[ci][j + 2] * a.out_scale,
+                                           sum[ci][j + 3] * a.out_scale);
+              if (k_split > 1)
+                atomicAdd(reinterpret_cast<float4*>(o + ci * 32 + j), r);
+              else
+                *reinterpret_cast<float4*>(o + ci * 32 + j) = r;
+            }
+        }
+        continue;
+      }
       const long long p_first = m0 / a.batch;
       // all epilogue threads are done with the previous tile's factors
       asm volatile("bar.sync 1, 256;" ::: "memory");
@@ -486,7 +543,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         tr[4] = t1.x; tr[5] = t1.y; tr[6] = t1.z; tr[7] = t1.w;
       }
       asm volatile("bar.sync 1, 256;" ::: "memory");
-      for (int chunk = 0; chunk < n_chunks; ++chunk, ++it) {
+      for (int chunk = ch0; chunk < ch1; ++chunk, ++it) {
       const int buf = (int)(it & 1);
       const uint32_t acc_ph = (uint32_t)((it >> 1) & 1);
       if (ok && !mbar_wait(tfull_bar(buf), acc_ph, a.error_flag, 4)) ok = false;
@@ -569,12 +626,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           float* o = a.out_f32 + row * a.ld_out + n0 + c;
 #pragma unroll
           for (int j = 0; j < 32; j += 4) {
-            float4 r = make_float4(y[j], y[j + 1], y[j + 2], y[j + 3]);
-            if (chunk > 0) {  // later chunks of the same tile: fp32 round-to-nearest accumulation
-              const float4 prev = *reinterpret_cast<const float4*>(o + j);
-              r = make_float4(prev.x + r.x, prev.y + r.y, prev.z + r.z, prev.w + r.w);
-            }
-            *reinterpret_cast<float4*>(o + j) = r;
+            *reinterpret_cast<float4*>(o + j) = make_float4(y[j], y[j + 1], y[j + 2], y[j + 3]);
           }
         }
       }
@@ -606,15 +658,18 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 
 // t[p][b][q] = sum_k H[p][b][k] * A_p[q][k] with A_p regenerated from the seed (never stored).
 // One block of 256 threads per individual. K is walked in chunks of 128 columns: the chunk of A_p
-// (8 x 128 normals) and of H_p (batch x 128, widened to fp32) are staged in shared memory; thread
-// (row group g, column slice c) accumulates 4 rows x 8 factors over 8 interleaved columns, so every pair of
-// shared-memory loads feeds 32 / 12 multiply-adds; the 16 column slices are folded with shuffles at the end.
+// (8 x 128 normals, fp32) and of H_p (64 rows x 128, kept in bf16) are staged in shared memory; thread
+// (row group g, column slice s) accumulates 4 rows x 8 factors over columns 4s..4s+3 and 64+4s..64+4s+3,
+// reading H as 8-byte and A_p as 16-byte words (24 shared-memory loads per 256 multiply-adds, all
+// conflict-free); the next chunk of H is already on its way from global memory while one is processed; the
+// 16 column slices are folded with shuffles at the end.
 __global__ void __launch_bounds__(256)
     lora_down_bf16_kernel(const __nv_bfloat16* __restrict__ h, const long long* __restrict__ seeds, unsigned long long a_counter,
                           long long batch, long long K, float* __restrict__ t) {
   constexpr int KC = 128;
-  __shared__ float sA[RANK][KC + 4];
-  extern __shared__ float sH[];  // [batch][KC + 1]
+  constexpr int kRowBytes = KC * 2 + 16;  // padded row of the bf16 chunk
+  __shared__ __align__(16) float sA[RANK][KC];
+  __shared__ __align__(16) uint8_t sH[64 * kRowBytes];
   const long long p = blockIdx.x;
   const unsigned long long seed = (unsigned long long)seeds[p];
   const int tid = threadIdx.x;
@@ -627,37 +682,52 @@ __global__ void __launch_bounds__(256)
     for (int r = 0; r < 4; ++r)
 #pragma unroll
       for (int q = 0; q < RANK; ++q) acc[r][q] = 0.f;
+    // this thread's four 16-byte pieces of a chunk: piece i is row (tid + 256 i) / 16, segment (tid + 256 i) % 16
+    uint4 stage[4];
+    auto fetch = [&](long long k0) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int idx = tid + 256 * i, b = idx >> 4, seg = idx & 15;
+        const long long row = (long long)pass * 64 + b;
+        stage[i] = make_uint4(0u, 0u, 0u, 0u);
+        if (row < batch) stage[i] = __ldcs(reinterpret_cast<const uint4*>(h + (p * batch + row) * K + k0 + seg * 8));
+      }
+    };
+    fetch(0);
     for (long long k0 = 0; k0 < K; k0 += KC) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int idx = tid + 256 * i, b = idx >> 4, seg = idx & 15;
+        *reinterpret_cast<uint4*>(sH + b * kRowBytes + seg * 16) = stage[i];
+      }
       // A_p[q][k]: element q * K + k of the stream -> Philox call (q * K + k) / 4 (K is a multiple of 4)
       {
         const int q = tid >> 5, c4 = tid & 31;  // 8 x 32 calls cover the 8 x 128 chunk
-        const float4 z = normal4(seed, a_counter, (uint32_t)(((long long)q * K + k0) / 4 + c4));
-        sA[q][c4 * 4 + 0] = z.x;
-        sA[q][c4 * 4 + 1] = z.y;
-        sA[q][c4 * 4 + 2] = z.z;
-        sA[q][c4 * 4 + 3] = z.w;
-      }
-      for (int idx = tid; idx < 64 * (KC / 2); idx += 256) {
-        const int b = idx / (KC / 2), c2 = idx - b * (KC / 2);
-        const long long row = (long long)pass * 64 + b;
-        float2 v = make_float2(0.f, 0.f);
-        if (row < batch) v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(h + (p * batch + row) * K + k0 + 2 * c2));
-        sH[b * (KC + 1) + 2 * c2] = v.x;
-        sH[b * (KC + 1) + 2 * c2 + 1] = v.y;
+        *reinterpret_cast<float4*>(&sA[q][c4 * 4]) = normal4(seed, a_counter, (uint32_t)(((long long)q * K + k0) / 4 + c4));
       }
       __syncthreads();
+      if (k0 + KC < K) fetch(k0 + KC);
 #pragma unroll
-      for (int cc = 0; cc < 8; ++cc) {
-        const int c = cc * 16 + slice;  // lanes of a slice group read consecutive banks
-        float av[RANK], hv[4];
+      for (int set = 0; set < 2; ++set) {
+        const int c = set * 64 + slice * 4;
+        float4 av[RANK];
 #pragma unroll
-        for (int q = 0; q < RANK; ++q) av[q] = sA[q][c];
+        for (int q = 0; q < RANK; ++q) av[q] = *reinterpret_cast<const float4*>(&sA[q][c]);
 #pragma unroll
-        for (int r = 0; r < 4; ++r) hv[r] = sH[(group * 4 + r) * (KC + 1) + c];
+        for (int r = 0; r < 4; ++r) {
+          const uint2 hw = *reinterpret_cast<const uint2*>(sH + (group * 4 + r) * kRowBytes + c * 2);
+          const float h0 = __uint_as_float(hw.x << 16), h1 = __uint_as_float(hw.x & 0xffff0000u);
+          const float h2 = __uint_as_float(hw.y << 16), h3 = __uint_as_float(hw.y & 0xffff0000u);
 #pragma unroll
-        for (int r = 0; r < 4; ++r)
-#pragma unroll
-          for (int q = 0; q < RANK; ++q) acc[r][q] = fmaf(hv[r], av[q], acc[r][q]);
+          for (int q = 0; q < RANK; ++q) {
+            float v = acc[r][q];
+            v = fmaf(h0, av[q].x, v);
+            v = fmaf(h1, av[q].y, v);
+            v = fmaf(h2, av[q].z, v);
+            v = fmaf(h3, av[q].w, v);
+            acc[r][q] = v;
+          }
+        }
       }
       __syncthreads();
     }
@@ -810,8 +880,23 @@ int make_map(CUtensorMap* map, const void* base, long long rows, long long K, in
 }
 
 // A CTA pair per 256 x 256 tile when the rows allow it, one CTA per 128 x 256 tile otherwise.
-int launch_gemm(const void* a_base, long long a_rows, const void* b_base, long long b_rows, long long k_cols, const GemmArgs& a,
-                cudaStream_t stream) {
+template <bool PAIR, bool ACCUM>
+int launch_variant(cudaLaunchConfig_t& cfg, const CUtensorMap& map_a, const CUtensorMap& map_b, const GemmArgs& a) {
+  EVOX_CUDA(cudaFuncSetAttribute(lora_gemm_kernel<PAIR, ACCUM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+  EVOX_CUDA(cudaLaunchKernelEx(&cfg, lora_gemm_kernel<PAIR, ACCUM>, map_a, map_b, a));
+  return EVOX_OK;
+}
+
+// Share of the CTA slots that do work when `items` equal work items are dealt round-robin to `slots`.
+double wave_efficiency(long long items, long long slots) {
+  const long long waves = (items + slots - 1) / slots;
+  return (double)items / (double)(waves * slots);
+}
+
+// accumulate = true: plain product summed chunk by chunk in registers into out_f32 (the gradient);
+// otherwise the layer epilogue.
+int launch_gemm(const void* a_base, long long a_rows, const void* b_base, long long b_rows, long long k_cols, GemmArgs a,
+                bool accumulate, cudaStream_t stream) {
   const bool pair = (a.M % (2 * BM) == 0) && sm_count() >= 2;
   CUtensorMap map_a, map_b;
   if (int rc = make_map(&map_a, a_base, a_rows, k_cols, BM)) return rc;
@@ -821,27 +906,33 @@ int launch_gemm(const void* a_base, long long a_rows, const void* b_base, long l
   cfg.dynamicSmemBytes = kSmemBytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
+  const long long n_tiles = (a.M / (pair ? 2 * BM : BM)) * (a.N / BN);
+  const long long slots = pair ? sm_count() / 2 : sm_count();
+  a.k_split = 1;
+  if (accumulate) {
+    // few tiles and a long K: halve each tile's chunk list when that fills the last wave better
+    const long long total_kb = (a.K / BK) * a.n_combo;
+    const long long n_chunks = a.chunk_kblocks > 0 ? (total_kb + a.chunk_kblocks - 1) / a.chunk_kblocks : 1;
+    if (n_chunks >= 2 && wave_efficiency(2 * n_tiles, slots) > 1.03 * wave_efficiency(n_tiles, slots)) a.k_split = 2;
+    if (a.k_split == 2) EVOX_CUDA(cudaMemsetAsync(a.out_f32, 0, sizeof(float) * (size_t)a.M * (size_t)a.ld_out, stream));
+  }
+  const long long n_work = n_tiles * a.k_split;
+  const long long used = slots < n_work ? slots : n_work;
+  cfg.gridDim = dim3((unsigned)(pair ? 2 * used : used));
   if (pair) {
-    EVOX_CUDA(cudaFuncSetAttribute(lora_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
-    const long long n_tiles = (a.M / (2 * BM)) * (a.N / BN);
-    long long pairs = sm_count() / 2;
-    if (pairs > n_tiles) pairs = n_tiles;
-    cfg.gridDim = dim3((unsigned)(2 * pairs));
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    EVOX_CUDA(cudaLaunchKernelEx(&cfg, lora_gemm_kernel<true>, map_a, map_b, a));
-  } else {
-    EVOX_CUDA(cudaFuncSetAttribute(lora_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
-    const long long n_tiles = (a.M / BM) * (a.N / BN);
-    long long grid = sm_count();
-    if (grid > n_tiles) grid = n_tiles;
-    cfg.gridDim = dim3((unsigned)grid);
-    EVOX_CUDA(cudaLaunchKernelEx(&cfg, lora_gemm_kernel<false>, map_a, map_b, a));
   }
+  int rc;
+  if (pair)
+    rc = accumulate ? launch_variant<true, true>(cfg, map_a, map_b, a) : launch_variant<true, false>(cfg, map_a, map_b, a);
+  else
+    rc = accumulate ? launch_variant<false, true>(cfg, map_a, map_b, a) : launch_variant<false, false>(cfg, map_a, map_b, a);
+  if (rc) return rc;
   EVOX_LAUNCH_CHECK();
   return EVOX_OK;
 }
@@ -863,8 +954,8 @@ extern "C" int evox_lora_down_bf16(const void* h, const int64_t* seeds, uint64_t
   EVOX_REQUIRE(h && seeds && t, EVOX_ERR_INVALID, "lora_down_bf16: NULL pointer");
   EVOX_REQUIRE(r == RANK && k % 128 == 0 && batch > 0 && pop > 0, EVOX_ERR_INVALID,
                "lora_down_bf16: needs rank 8 and k a multiple of 128");
-  const size_t smem = sizeof(float) * 64 * 129;
-  lora_down_bf16_kernel<<<(unsigned)pop, 256, smem, reinterpret_cast<cudaStream_t>(stream)>>>(
+  EVOX_REQUIRE(((uintptr_t)h & 15u) == 0, EVOX_ERR_INVALID, "lora_down_bf16: h must be 16-byte aligned");
+  lora_down_bf16_kernel<<<(unsigned)pop, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       (const __nv_bfloat16*)h, (const long long*)seeds, a_counter, batch, k, t);
   EVOX_LAUNCH_CHECK();
   return EVOX_OK;
@@ -905,11 +996,12 @@ extern "C" int evox_lora_gemm_bf16(const void* h, const void* w, const float* bi
   a.out_scale = 1.0f;
   a.ld_out = d;
   a.chunk_kblocks = 0;
+  a.k_split = 1;
   a.t_partial = t_next_partial;
   a.next_a_counter = next_a_counter;
   EVOX_REQUIRE(t_next_partial == nullptr || out_bf16 != nullptr, EVOX_ERR_INVALID,
                "lora_gemm_bf16: the fused next-layer projection needs the bf16 output sink");
-  return launch_gemm(h, a.M, w, d, k, a, reinterpret_cast<cudaStream_t>(stream));
+  return launch_gemm(h, a.M, w, d, k, a, false, reinterpret_cast<cudaStream_t>(stream));
 }
 
 extern "C" int evox_neg_mse_from_partials(const float* row_partial, int64_t pop, int64_t batch, int64_t d, float* fitness,
@@ -981,7 +1073,7 @@ extern "C" int evox_lora_gradient_tc(const float* fitness, const int64_t* seeds,
   a.out_scale = 1.0f / ((float)pop * sigma);
   a.ld_out = k;
   a.chunk_kblocks = 32;  // 128 truncating accumulations per accumulator at most
-  return launch_gemm(bf3, d, at3, k, 3 * Kt, a, s);
+  return launch_gemm(bf3, d, at3, k, 3 * Kt, a, true, s);
 }
 
 extern "C" int evox_lora_t_from_partials(const float* t_partial, int64_t rows, int64_t d, float* t, void* stream) {
