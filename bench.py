@@ -504,7 +504,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="pso_ackley_1e6x1000", choices=sorted(WORKLOADS) + ["nds_rank_2e4", "nds_rank_1e5", "lora_es_config3", "rvea_config2", "rvea_5e6"])
     ap.add_argument("--lora-pop", type=int, default=1024)
-    ap.add_argument("--gradient-passes", type=int, default=6, choices=[1, 3, 6])
+    ap.add_argument("--gradient-passes", type=int, default=3, choices=[1, 3, 6])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     if args.workload.startswith("nds_"):

@@ -121,10 +121,10 @@ class VirtualLoRAES(_ESBase):
         device: torch.device | None = None,
         shard: bool = False,
         group=None,
-        gradient_passes: int = 6,
+        gradient_passes: int = 3,
     ):
-        """`gradient_passes`: tensor-core passes of the population gradient (6 = fp32-accurate, the
-        default; 3 or 1 trade accuracy for speed, see `lora_gradient_from_seeds`).
+        """`gradient_passes`: tensor-core passes of the population gradient (3 = fp32-accurate, the
+        default; 1 = bf16 operands; see `lora_gradient_from_seeds`).
         `shard=True` (under an initialised torch.distributed group): every rank keeps the whole
         centre, but the gradient and update of each 2-D block are computed for this rank's rows only
         and the updated rows are allgathered; seeds are broadcast from rank 0 each generation."""

@@ -29,6 +29,7 @@
 // all roles leave their loops, outstanding copies are drained with the same bound and TMEM is freed.
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <math.h>
 
 #include <mutex>
@@ -82,6 +83,9 @@ struct GemmArgs {
   int n_combo;
   int a_piece[6];
   int b_piece[6];
+  float combo_scale[6];        // ACCUM variant: weight of pass c in the sum (pieces may carry a power-of-two scale)
+  uint32_t operand_format;     // instruction-descriptor format bits of both operands: bf16 or fp16
+  const float* out_scale_dev;  // ACCUM variant: optional device scalar multiplied into out_scale
   float out_scale;
   long long ld_out;         // row stride of out_f32 (elements)
   // Fused down-projection of the NEXT layer: its input is this layer's bf16 output, so each
@@ -189,13 +193,16 @@ __device__ __forceinline__ unsigned long long umma_desc(uint32_t smem_addr) {
 
 // kind::f16 instruction descriptor: D = fp32, A = B = bf16, both K-major, N = 256, M = 128
 // (M = 256 for a CTA pair: 128 rows in each CTA).
-constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-constexpr uint32_t kIdescPair = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
+// The operand format bits (A at bit 7, B at bit 10: 0 = fp16, 1 = bf16) are added at run time.
+constexpr uint32_t kIdesc = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+constexpr uint32_t kIdescPair = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
+constexpr uint32_t kFormatBf16 = (1u << 7) | (1u << 10), kFormatFp16 = 0u;
 
-__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, unsigned long long a, unsigned long long b, uint32_t accumulate) {
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, unsigned long long a, unsigned long long b, uint32_t accumulate,
+                                          uint32_t format) {
   asm volatile(
       "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
-      ::"r"(d_tmem), "l"(a), "l"(b), "r"(kIdesc), "r"(accumulate)
+      ::"r"(d_tmem), "l"(a), "l"(b), "r"(kIdesc | format), "r"(accumulate)
       : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
@@ -203,11 +210,12 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
 }
 // Issued by one thread of the leader CTA: both CTAs' tensor cores multiply their own 128 rows of A by the
 // 256-row B tile whose halves sit in the two CTAs' shared memory (same offsets in both).
-__device__ __forceinline__ void umma_bf16_pair(uint32_t d_tmem, unsigned long long a, unsigned long long b, uint32_t accumulate) {
+__device__ __forceinline__ void umma_bf16_pair(uint32_t d_tmem, unsigned long long a, unsigned long long b, uint32_t accumulate,
+                                               uint32_t format) {
   asm volatile(
       "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
       "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n}"
-      ::"r"(d_tmem), "l"(a), "l"(b), "r"(kIdescPair), "r"(accumulate), "r"(0u)
+      ::"r"(d_tmem), "l"(a), "l"(b), "r"(kIdescPair | format), "r"(accumulate), "r"(0u)
       : "memory");
 }
 // Arrives, once the products issued so far are complete, on the barrier at offset `bar` in BOTH CTAs.
@@ -416,9 +424,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 #pragma unroll
             for (int k = 0; k < BK / 16; ++k) {
               if constexpr (PAIR)
-                umma_bf16_pair(d_tmem, umma_desc(sa + k * 32), umma_desc(sb + k * 32), (kb > kb0 || k > 0) ? 1u : 0u);
+                umma_bf16_pair(d_tmem, umma_desc(sa + k * 32), umma_desc(sb + k * 32), (kb > kb0 || k > 0) ? 1u : 0u, a.operand_format);
               else
-                umma_bf16(d_tmem, umma_desc(sa + k * 32), umma_desc(sb + k * 32), (kb > kb0 || k > 0) ? 1u : 0u);
+                umma_bf16(d_tmem, umma_desc(sa + k * 32), umma_desc(sb + k * 32), (kb > kb0 || k > 0) ? 1u : 0u, a.operand_format);
             }
             // stage reusable (in both CTAs of a pair) once these products have read it
             if constexpr (PAIR) umma_commit_pair(empty_bar(s)); else umma_commit(empty_bar(s));
@@ -463,25 +471,26 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           if (ok && !mbar_wait(tfull_bar(buf), acc_ph, a.error_flag, 4)) ok = false;
           if (!ok) continue;
           fence_after_sync();
+          const float cs = a.combo_scale[(chunk * chunk_kb) / k_blocks];  // a chunk never straddles two passes
 #pragma unroll
           for (int ci = 0; ci < 4; ++ci) {
             uint32_t v[32];
             tmem_ld32(tmem_base + (uint32_t)(buf * BN + col_half * (BN / 2) + ci * 32) + ((uint32_t)(quarter * 32) << 16), v);
             tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 32; ++j) sum[ci][j] += __uint_as_float(v[j]);
+            for (int j = 0; j < 32; ++j) sum[ci][j] = fmaf(__uint_as_float(v[j]), cs, sum[ci][j]);
           }
           fence_before_sync();
           if constexpr (PAIR) mbar_arrive_cluster(leader_tempty0 + 8u * buf); else mbar_arrive(tempty_bar(buf));
         }
         if (ok) {
           float* o = a.out_f32 + (m0 + row_in_tile) * a.ld_out + n0 + col_half * (BN / 2);
+          const float os = a.out_scale_dev ? a.out_scale * __ldg(a.out_scale_dev) : a.out_scale;
 #pragma unroll
           for (int ci = 0; ci < 4; ++ci)
 #pragma unroll
             for (int j = 0; j < 32; j += 4) {
-              const float4 r = make_float4(sum[ci][j] * a.out_scale, sum[ci][j + 1] * a.out_scale, sum[ci][j + 2] * a.out_scale,
-                                           sum[ci][j + 3] * a.out_scale);
+              const float4 r = make_float4(sum[ci][j] * os, sum[ci][j + 1] * os, sum[ci][j + 2] * os, sum[ci][j + 3] * os);
               if (k_split > 1)
                 atomicAdd(reinterpret_cast<float4*>(o + ci * 32 + j), r);
               else
@@ -785,60 +794,115 @@ __global__ void __launch_bounds__(128)
   if (threadIdx.x == 0) fitness[p] = -((part[0] + part[1]) + (part[2] + part[3])) / (float)(batch * N);
 }
 
-// fp32 -> three bf16 pieces with x = hi + mid + lo (each piece rounds what the previous ones left).
-__device__ __forceinline__ void split3(float x, __nv_bfloat16& hi, __nv_bfloat16& mid, __nv_bfloat16& lo) {
-  hi = __float2bfloat16_rn(x);
-  const float r1 = x - __bfloat162float(hi);
-  mid = __float2bfloat16_rn(r1);
-  lo = __float2bfloat16_rn(r1 - __bfloat162float(mid));
+// Splitting schemes of the gradient's operands (x = sum of the pieces, piece c scaled by kPieceScale^c):
+//   kSplitFp16x2  two fp16 pieces, the second one scaled by 2^11: 22 significand bits; the products
+//                 hi*hi + (hi*lo + lo*hi) * 2^-11 are exact in the fp32 accumulator and miss x only by 2^-22
+//   kSplitBf16x3  three bf16 pieces (24 bits), six products
+//   kSplitBf16x1  plain bf16 rounding, one product
+enum { kSplitFp16x2 = 0, kSplitBf16x3 = 1, kSplitBf16x1 = 2 };
+
+template <int SCHEME>
+struct Pieces {
+  static constexpr int N = SCHEME == kSplitFp16x2 ? 2 : (SCHEME == kSplitBf16x3 ? 3 : 1);
+  // 16-bit patterns of the pieces of x
+  __device__ static __forceinline__ void split(float x, unsigned short (&out)[N]) {
+    if constexpr (SCHEME == kSplitFp16x2) {
+      const __half hi = __float2half_rn(x);
+      const __half lo = __float2half_rn((x - __half2float(hi)) * 2048.0f);
+      out[0] = __half_as_ushort(hi);
+      out[1] = __half_as_ushort(lo);
+    } else {
+      float r = x;
+#pragma unroll
+      for (int c = 0; c < N; ++c) {
+        const __nv_bfloat16 pc = __float2bfloat16_rn(r);
+        out[c] = __bfloat16_as_ushort(pc);
+        r -= __bfloat162float(pc);
+      }
+    }
+  }
+};
+
+// scale[0] = 2^-e with 2^(e-1) <= max |fitness| < 2^e (1 if the maximum is zero or not finite), scale[1] = 2^e:
+// the fp16 pieces of f_i * B_i then stay in range whatever the magnitude of the fitness.
+__global__ void __launch_bounds__(256) fitness_pow2_scale_kernel(const float* __restrict__ fitness, long long pop, float* __restrict__ scale) {
+  __shared__ float part[8];
+  float m = 0.f;
+  for (long long i = threadIdx.x; i < pop; i += 256) {
+    const float v = fabsf(fitness[i]);
+    if (v == v && v <= 3.0e38f) m = fmaxf(m, v);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 8; ++w) m = fmaxf(m, part[w]);
+    int e = 0;
+    if (m > 0.f) (void)frexpf(m, &e);  // m = f * 2^e, f in [0.5, 1)
+    e = max(-100, min(100, e));
+    scale[0] = ldexpf(1.0f, -e);
+    scale[1] = ldexpf(1.0f, e);
+  }
 }
 
 // Operands of the population gradient sum_i f_i B_i A_i as two K-major matrices over K = pop * 8:
-//   bf3[j][piece * K + i * 8 + q] = piece of (f_i * B_i[j][q]),   j < d
-//   at3[l][piece * K + i * 8 + q] = piece of A_i[q][l],            l < k
-// with the factors regenerated from the seeds (lora_noise.py:118-125) and split into three bf16
-// pieces so that six tensor-core passes reproduce the fp32 product (see evox_lora_gradient_tc).
+//   bf[j][piece * K + i * 8 + q] = piece of (f_i * B_i[j][q]),   j < d
+//   at[l][piece * K + i * 8 + q] = piece of A_i[q][l],            l < k
+// with the factors regenerated from the seeds (lora_noise.py:118-125) and split as SCHEME says.
+template <int SCHEME>
 __global__ void __launch_bounds__(256)
-    lora_grad_pack_kernel(const float* __restrict__ fitness, const long long* __restrict__ seeds, unsigned long long a_counter,
-                          unsigned long long b_counter, long long pop, long long row_begin, long long d, long long k,
-                          __nv_bfloat16* __restrict__ bf3, __nv_bfloat16* __restrict__ at3) {
+    lora_grad_pack_kernel(const float* __restrict__ fitness, const float* __restrict__ fit_scale, const long long* __restrict__ seeds,
+                          unsigned long long a_counter, unsigned long long b_counter, long long pop, long long row_begin,
+                          long long d, long long k, unsigned short* __restrict__ bf, unsigned short* __restrict__ at) {
   // d = number of rows of the block computed here, starting at row `row_begin` of the weight
+  constexpr int NP = Pieces<SCHEME>::N;
   const long long Kt = pop * RANK;
   const long long n_b = pop * d;          // one task per (i, j): 8 values of B_i[j][:]
   const long long n_a = pop * (k / 4);    // one task per (i, l / 4): 8 x 4 values of A_i[:][l..l+3]
+  const float fs = fit_scale ? fit_scale[0] : 1.0f;
   for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < n_b + n_a; t += (long long)gridDim.x * blockDim.x) {
     if (t < n_b) {
       // neighbouring threads take neighbouring individuals: their 16-byte pieces are adjacent in a row
       const long long j = t / pop, i = t - j * pop;
       const unsigned long long seed = (unsigned long long)seeds[i];
-      const float f = fitness[i];
+      const float f = fitness[i] * fs;
       const long long jg = row_begin + j;  // row of the whole weight block
       const float4 z0 = normal4(seed, b_counter, (uint32_t)(2 * jg)), z1 = normal4(seed, b_counter, (uint32_t)(2 * jg + 1));
       const float v[8] = {z0.x * f, z0.y * f, z0.z * f, z0.w * f, z1.x * f, z1.y * f, z1.z * f, z1.w * f};
-      __align__(16) __nv_bfloat16 p[3][8];
+      __align__(16) unsigned short pc[NP][8];
 #pragma unroll
-      for (int q = 0; q < 8; ++q) split3(v[q], p[0][q], p[1][q], p[2][q]);
+      for (int q = 0; q < 8; ++q) {
+        unsigned short one[NP];
+        Pieces<SCHEME>::split(v[q], one);
 #pragma unroll
-      for (int c = 0; c < 3; ++c)
-        *reinterpret_cast<uint4*>(bf3 + j * (3 * Kt) + c * Kt + i * RANK) = *reinterpret_cast<const uint4*>(p[c]);
+        for (int c = 0; c < NP; ++c) pc[c][q] = one[c];
+      }
+#pragma unroll
+      for (int c = 0; c < NP; ++c)
+        *reinterpret_cast<uint4*>(bf + j * (NP * Kt) + c * Kt + i * RANK) = *reinterpret_cast<const uint4*>(pc[c]);
     } else {
       const long long u = t - n_b;
       const long long l4 = u / pop, i = u - l4 * pop;
       const unsigned long long seed = (unsigned long long)seeds[i];
-      __align__(16) __nv_bfloat16 p[4][3][8];  // [row l..l+3][piece][q]
+      __align__(16) unsigned short pc[4][NP][8];  // [row l..l+3][piece][q]
 #pragma unroll
       for (int q = 0; q < 8; ++q) {
         const float4 z = normal4(seed, a_counter, (uint32_t)(((long long)q * k) / 4 + l4));
-        split3(z.x, p[0][0][q], p[0][1][q], p[0][2][q]);
-        split3(z.y, p[1][0][q], p[1][1][q], p[1][2][q]);
-        split3(z.z, p[2][0][q], p[2][1][q], p[2][2][q]);
-        split3(z.w, p[3][0][q], p[3][1][q], p[3][2][q]);
+        const float zz[4] = {z.x, z.y, z.z, z.w};
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          unsigned short one[NP];
+          Pieces<SCHEME>::split(zz[r], one);
+#pragma unroll
+          for (int c = 0; c < NP; ++c) pc[r][c][q] = one[c];
+        }
       }
 #pragma unroll
       for (int r = 0; r < 4; ++r)
 #pragma unroll
-        for (int c = 0; c < 3; ++c)
-          *reinterpret_cast<uint4*>(at3 + (l4 * 4 + r) * (3 * Kt) + c * Kt + i * RANK) = *reinterpret_cast<const uint4*>(p[r][c]);
+        for (int c = 0; c < NP; ++c)
+          *reinterpret_cast<uint4*>(at + (l4 * 4 + r) * (NP * Kt) + c * Kt + i * RANK) = *reinterpret_cast<const uint4*>(pc[r][c]);
     }
   }
 }
@@ -865,14 +929,14 @@ int encode_fn(EncodeTiledFn* out) {
   return EVOX_OK;
 }
 
-int make_map(CUtensorMap* map, const void* base, long long rows, long long K, int box_rows) {
+int make_map(CUtensorMap* map, const void* base, long long rows, long long K, int box_rows, bool fp16 = false) {
   EncodeTiledFn fn;
   if (int rc = encode_fn(&fn)) return rc;
   const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
   const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
   const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
   const cuuint32_t estr[2] = {1, 1};
-  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+  const CUresult r = fn(map, fp16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   EVOX_REQUIRE(r == CUDA_SUCCESS, EVOX_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
@@ -899,8 +963,9 @@ int launch_gemm(const void* a_base, long long a_rows, const void* b_base, long l
                 bool accumulate, cudaStream_t stream) {
   const bool pair = (a.M % (2 * BM) == 0) && sm_count() >= 2;
   CUtensorMap map_a, map_b;
-  if (int rc = make_map(&map_a, a_base, a_rows, k_cols, BM)) return rc;
-  if (int rc = make_map(&map_b, b_base, b_rows, k_cols, pair ? BN / 2 : BN)) return rc;
+  const bool fp16 = a.operand_format == kFormatFp16;
+  if (int rc = make_map(&map_a, a_base, a_rows, k_cols, BM, fp16)) return rc;
+  if (int rc = make_map(&map_b, b_base, b_rows, k_cols, pair ? BN / 2 : BN, fp16)) return rc;
   cudaLaunchConfig_t cfg = {};
   cfg.blockDim = dim3(kGemmThreads);
   cfg.dynamicSmemBytes = kSmemBytes;
@@ -997,6 +1062,9 @@ extern "C" int evox_lora_gemm_bf16(const void* h, const void* w, const float* bi
   a.ld_out = d;
   a.chunk_kblocks = 0;
   a.k_split = 1;
+  a.operand_format = kFormatBf16;
+  a.out_scale_dev = nullptr;
+  for (int c = 0; c < 6; ++c) a.combo_scale[c] = 1.0f;
   a.t_partial = t_next_partial;
   a.next_a_counter = next_a_counter;
   EVOX_REQUIRE(t_next_partial == nullptr || out_bf16 != nullptr, EVOX_ERR_INVALID,
@@ -1015,7 +1083,8 @@ extern "C" int evox_neg_mse_from_partials(const float* row_partial, int64_t pop,
 
 extern "C" size_t evox_lora_gradient_tc_workspace_bytes(int64_t pop, int64_t d, int64_t k) {
   if (pop <= 0 || d <= 0 || k <= 0) return 0;
-  return (size_t)(d + k) * 3 * (size_t)pop * RANK * sizeof(__nv_bfloat16) + 512;
+  // 256 bytes of scalars, then both operand matrices with up to three 16-bit pieces per value
+  return 256 + (size_t)(d + k) * 3 * (size_t)pop * RANK * sizeof(__nv_bfloat16) + 512;
 }
 
 extern "C" int evox_lora_gradient_tc_supported(int64_t pop, int64_t d, int64_t k, int32_t r) {
@@ -1034,14 +1103,33 @@ extern "C" int evox_lora_gradient_tc(const float* fitness, const int64_t* seeds,
   EVOX_REQUIRE(((uintptr_t)workspace & 255u) == 0, EVOX_ERR_INVALID, "lora_gradient_tc: workspace must be 256-byte aligned");
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   const long long Kt = pop * RANK;
-  __nv_bfloat16* bf3 = reinterpret_cast<__nv_bfloat16*>(workspace);
-  __nv_bfloat16* at3 = bf3 + (size_t)d * 3 * Kt;  // d * 3 * Kt * 2 bytes is a multiple of 256
+  // passes: 3 = two fp16 pieces per operand, products hi hi, hi lo, lo hi (fp32-accurate, ~1e-6);
+  //         6 = three bf16 pieces, six products (~2e-6, twice the work: kept for comparison);
+  //         1 = operands rounded to bf16 (~4e-3)
+  const int scheme = passes == 3 ? kSplitFp16x2 : (passes == 6 ? kSplitBf16x3 : kSplitBf16x1);
+  const int n_pieces = passes == 3 ? 2 : (passes == 6 ? 3 : 1);
+  float* scalars = reinterpret_cast<float*>(workspace);
+  unsigned short* bf = reinterpret_cast<unsigned short*>(reinterpret_cast<uint8_t*>(workspace) + 256);
+  unsigned short* at = bf + (size_t)d * n_pieces * Kt;  // d * n_pieces * Kt * 2 bytes is a multiple of 256
   const unsigned long long b_counter = counter + (unsigned long long)((RANK * k + 3) / 4 * 4);
   const long long tasks = pop * d + pop * (k / 4);
   long long blocks = (tasks + 255) / 256;
   const long long cap = (long long)sm_count() * 16;
-  lora_grad_pack_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, s>>>(fitness, (const long long*)seeds, counter, b_counter,
-                                                                               pop, row_begin, d, k, bf3, at3);
+  const unsigned grid = (unsigned)(blocks < cap ? blocks : cap);
+  const float* fit_scale = nullptr;
+  if (scheme == kSplitFp16x2) {
+    fitness_pow2_scale_kernel<<<1, 256, 0, s>>>(fitness, pop, scalars);
+    EVOX_LAUNCH_CHECK();
+    fit_scale = scalars;
+    lora_grad_pack_kernel<kSplitFp16x2><<<grid, 256, 0, s>>>(fitness, fit_scale, (const long long*)seeds, counter, b_counter, pop,
+                                                             row_begin, d, k, bf, at);
+  } else if (scheme == kSplitBf16x3) {
+    lora_grad_pack_kernel<kSplitBf16x3><<<grid, 256, 0, s>>>(fitness, nullptr, (const long long*)seeds, counter, b_counter, pop,
+                                                             row_begin, d, k, bf, at);
+  } else {
+    lora_grad_pack_kernel<kSplitBf16x1><<<grid, 256, 0, s>>>(fitness, nullptr, (const long long*)seeds, counter, b_counter, pop,
+                                                             row_begin, d, k, bf, at);
+  }
   EVOX_LAUNCH_CHECK();
   GemmArgs a;
   a.M = d;
@@ -1061,19 +1149,38 @@ extern "C" int evox_lora_gradient_tc(const float* fitness, const int64_t* seeds,
   a.target = nullptr;
   a.row_partial = nullptr;
   a.error_flag = error_flag;
-  // x = hi + mid + lo for both operands; keep every product down to 2^-24 of the largest one
-  static const int pa[6] = {0, 0, 1, 0, 2, 1}, pb[6] = {0, 1, 0, 2, 0, 1};
-  a.n_combo = passes;  // 1: bf16 operands (~4e-3); 3: + hi mid, mid hi (~2e-5); 6: fp32-accurate
-  for (int c = 0; c < 6; ++c) {
-    a.a_piece[c] = pa[c];
-    a.b_piece[c] = pb[c];
+  a.n_combo = passes;
+  if (scheme == kSplitFp16x2) {
+    static const int pa[3] = {0, 0, 1}, pb[3] = {0, 1, 0};
+    static const float sc[3] = {1.0f, 1.0f / 2048.0f, 1.0f / 2048.0f};
+    for (int c = 0; c < 6; ++c) {
+      a.a_piece[c] = pa[c % 3];
+      a.b_piece[c] = pb[c % 3];
+      a.combo_scale[c] = sc[c % 3];
+    }
+    a.operand_format = kFormatFp16;
+    a.out_scale_dev = scalars + 1;  // undoes the power-of-two scaling of the fitness
+  } else {
+    // x = hi + mid + lo for both operands; keep every product down to 2^-24 of the largest one
+    static const int pa[6] = {0, 0, 1, 0, 2, 1}, pb[6] = {0, 1, 0, 2, 0, 1};
+    for (int c = 0; c < 6; ++c) {
+      a.a_piece[c] = pa[c];
+      a.b_piece[c] = pb[c];
+      a.combo_scale[c] = 1.0f;
+    }
+    a.operand_format = kFormatBf16;
+    a.out_scale_dev = nullptr;
   }
   a.t_partial = nullptr;
   a.next_a_counter = 0;
   a.out_scale = 1.0f / ((float)pop * sigma);
   a.ld_out = k;
-  a.chunk_kblocks = 32;  // 128 truncating accumulations per accumulator at most
-  return launch_gemm(bf3, d, at3, k, 3 * Kt, a, true, s);
+  // at most 128 truncating accumulations (32 k-blocks) per accumulator, and no chunk across two passes
+  const int k_blocks = (int)(Kt / BK);
+  int chunk = k_blocks < 32 ? k_blocks : 32;
+  while (k_blocks % chunk != 0) --chunk;
+  a.chunk_kblocks = chunk;
+  return launch_gemm(bf, d, at, k, (long long)n_pieces * Kt, a, true, s);
 }
 
 extern "C" int evox_lora_t_from_partials(const float* t_partial, int64_t rows, int64_t d, float* t, void* stream) {

@@ -196,14 +196,15 @@ def lora_layer_bf16(h: torch.Tensor, w: torch.Tensor, seeds: torch.Tensor, count
 
 def lora_gradient_from_seeds(fitness: torch.Tensor, seeds: torch.Tensor, weight_shape: tuple, rank: int, counter: int,
                              pop_size: int, sigma: float, out: torch.Tensor | None = None,
-                             rows: tuple[int, int] | None = None, passes: int = 6) -> torch.Tensor:
+                             rows: tuple[int, int] | None = None, passes: int = 3) -> torch.Tensor:
     """`lora_gradient(fitness, *generate_lora_factors(seeds, weight_shape, rank, counter), ...)` without
     the factors ever existing in fp32: on supported shapes the tensor-core kernel regenerates them;
     otherwise this falls back to generating them and calling `lora_gradient`. `out`: optional flat
     fp32 destination of prod(weight_shape) elements. `rows = (begin, end)` computes only those rows
     of a 2-D block (tensor-core path only) and returns that slice; `out` then has (end - begin) * k
-    elements. `passes`: 6 = fp32-accurate split-precision product (default), 3 or 1 = fewer tensor-core
-    passes at about 2e-5 / 4e-3 relative error."""
+    elements. `passes`: 3 (default) = operands split into two fp16 pieces, three tensor-core products,
+    about 1e-6 relative error; 6 = three bf16 pieces, six products, same accuracy at twice the work;
+    1 = bf16 operands, about 4e-3."""
     fitness = fitness.float().contiguous()
     seeds = _seeds(seeds)
     dev = fitness.device

@@ -301,15 +301,19 @@ int evox_lora_t_from_partials(const float* t_partial, int64_t rows, int64_t d, f
 
 /* Population gradient of a 2-D block on the tensor cores without materialising fp32 factors:
  *   grad (d x k, fp32) = sum_i fitness_i B_i A_i / (pop * sigma)       (lora_noise.py:157-196)
- * with A_i, B_i regenerated from seeds / counter as generate_lora_factors does. The kernel
- * writes f_i B_i and A_i as three bf16 pieces each (x = hi + mid + lo) into the workspace and sums
- * six tcgen05 passes (hi hi, hi mid, mid hi, hi lo, lo hi, mid mid) in fp32, which keeps the
- * result within fp32 rounding of the reference's einsum. Needs rank 8, d a multiple of 128, k a
- * multiple of 256, pop a multiple of 8 (evox_lora_gradient_tc_supported). error_flag as above.
+ * with A_i, B_i regenerated from seeds / counter as generate_lora_factors does. With passes = 3
+ * the kernel writes f_i B_i (fitness first normalised by a power of two) and A_i as two fp16
+ * pieces each, x = hi + lo / 2048, into the workspace and sums the three tcgen05 products hi hi,
+ * hi lo, lo hi; every product is exact in the fp32 accumulator, accumulators are drained every 32
+ * k-blocks and added in round-to-nearest fp32 registers, so the result stays within about 1e-6 of
+ * the reference's fp32 einsum. passes = 6 does the same with three bf16 pieces and six products
+ * (twice the work, same accuracy); passes = 1 is a plain bf16 product (about 4e-3), for callers
+ * that prefer speed. Needs rank 8, d a multiple of 128, k a multiple of 256, pop a multiple of 8
+ * (evox_lora_gradient_tc_supported). error_flag as above.
  * Only the d rows starting at row `row_begin` of the weight are computed (grad points at the
- * first of them): ranks that shard a block by rows each pass their own range.
- * passes = 6 is the fp32-accurate sum described above; 3 keeps hi hi + hi mid + mid hi (relative
- * error about 2e-5); 1 is a plain bf16 product (about 4e-3), for callers that prefer speed. */
+ * first of them): ranks that shard a block by rows each pass their own range. When the tile count
+ * is small against the SM count, a tile's K range is halved between two CTA groups that add into
+ * the zero-filled grad (two addends, order-independent). */
 size_t evox_lora_gradient_tc_workspace_bytes(int64_t pop, int64_t d, int64_t k);
 int evox_lora_gradient_tc_supported(int64_t pop, int64_t d, int64_t k, int32_t r);
 int evox_lora_gradient_tc(const float* fitness, const int64_t* seeds, uint64_t counter, int64_t pop,

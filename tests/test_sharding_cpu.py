@@ -90,7 +90,7 @@ def _oracle_kernels(monkeypatch_target):
     """Replace the two kernel-calling helpers of evox_b200.algorithms.es by oracle arithmetic."""
     from oracle import lora
 
-    def grad_from_seeds(fitness, seeds, shape, rank, counter, pop_size, sigma, out=None, rows=None, passes=6):
+    def grad_from_seeds(fitness, seeds, shape, rank, counter, pop_size, sigma, out=None, rows=None, passes=3):
         f = lora.generate_lora_factors(seeds, shape, rank, counter)
         if isinstance(f, tuple):
             g = lora.lora_gradient(fitness, f[0], f[1], pop_size, sigma, shape)
