@@ -16,6 +16,7 @@
 #include <math.h>
 
 #include "common.cuh"
+#include "fitness.cuh"
 
 namespace evox {
 
@@ -27,77 +28,6 @@ constexpr int kMaxPartials = 2048;
 #ifndef MOVE_BLOCKS_PER_SM
 #define MOVE_BLOCKS_PER_SM 4
 #endif
-
-struct FitParams {
-  float a, b, c;
-};
-
-// --------------------------------------------------------------------------------------------
-// Fitness functors: per-element accumulation + per-row finalisation. The sums use fused
-// multiply-adds and a lane-strided order, so fitness values agree with the reference to
-// rounding (relative 1e-5 is the tested bound), not bit for bit.
-// --------------------------------------------------------------------------------------------
-// cos(t) for the fitness sums: Cody-Waite reduction to [-pi, pi] with 2*pi split in two floats,
-// then the hardware cosine (absolute error 2^-21.4 on that interval). Per term the error is below
-// 1e-6, i.e. below 1e-6 on mean(cos) for Ackley and below 1e-5 * d on Rastrigin's sum of 10*cos,
-// an order of magnitude inside the 1e-5 relative tolerance of the fitness values.
-__device__ __forceinline__ float fast_cos(float t) {
-  if (fabsf(t) > 32768.0f) return cosf(t);  // far outside any benchmark's bounds: exact path
-  const float magic = 12582912.0f;          // 1.5 * 2^23: adding and subtracting rounds to nearest integer
-  const float k = __fadd_rn(__fmaf_rn(t, 0.15915494309189535f, magic), -magic);
-  float r = __fmaf_rn(-k, 6.2831854820251465f, t);
-  r = __fmaf_rn(-k, -1.7484555e-07f, r);
-  return __cosf(r);
-}
-
-template <int FIT>
-struct Fitness;
-
-template <>
-struct Fitness<EVOX_FIT_ACKLEY> {
-  float s_sq = 0.f, s_cos = 0.f;
-  __device__ __forceinline__ void add(float x, const FitParams& p) {
-    s_sq = __fmaf_rn(x, x, s_sq);
-    s_cos += fast_cos(__fmul_rn(p.c, x));
-  }
-  __device__ __forceinline__ void reduce() {
-    s_sq = warp_sum(s_sq);
-    s_cos = warp_sum(s_cos);
-  }
-  __device__ __forceinline__ float finish(int d, const FitParams& p) const {
-    const float fd = (float)d;
-    const float m_sq = __fdiv_rn(s_sq, fd);
-    const float m_cos = __fdiv_rn(s_cos, fd);
-    const float t1 = __fmul_rn(-p.a, expf(__fmul_rn(-p.b, sqrtf(m_sq))));
-    const float t2 = expf(m_cos);
-    return __fadd_rn(__fadd_rn(__fsub_rn(t1, t2), p.a), 2.718281828459045f);
-  }
-};
-
-template <>
-struct Fitness<EVOX_FIT_RASTRIGIN> {
-  float s = 0.f, s_cos = 0.f;
-  __device__ __forceinline__ void add(float x, const FitParams&) {
-    const float t = __fmul_rn(6.283185307179586f, x);
-    s = __fmaf_rn(x, x, s);
-    s_cos += fast_cos(t);
-  }
-  __device__ __forceinline__ void reduce() {
-    s = warp_sum(s);
-    s_cos = warp_sum(s_cos);
-  }
-  __device__ __forceinline__ float finish(int d, const FitParams&) const {
-    return __fadd_rn((float)(10 * (long long)d), __fmaf_rn(-10.0f, s_cos, s));
-  }
-};
-
-template <>
-struct Fitness<EVOX_FIT_SPHERE> {
-  float s = 0.f;
-  __device__ __forceinline__ void add(float x, const FitParams&) { s = __fmaf_rn(x, x, s); }
-  __device__ __forceinline__ void reduce() { s = warp_sum(s); }
-  __device__ __forceinline__ float finish(int, const FitParams&) const { return s; }
-};
 
 // --------------------------------------------------------------------------------------------
 // Uniform stream of the in-kernel generator. One Philox call covers 4 consecutive columns of

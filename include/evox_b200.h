@@ -113,6 +113,35 @@ int evox_pso_fill_uniform(float* out, int64_t pop_size, int32_t dim, uint64_t se
                           uint64_t generation, int32_t which, int64_t row_offset, void* stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Competitive swarm optimiser (a PSO variant with the same memory-bound update shape).
+ * ------------------------------------------------------------------------------------------ */
+
+/* Bytes of scratch evox_cso_step needs: the swarm's mean position and per-block column sums. */
+size_t evox_cso_workspace_bytes(int64_t pop_size, int32_t dim);
+
+/* CSO.step (algorithms/so/pso_variants/cso.py:71-105) fused with the evaluation of the students.
+ * perm (pop_size, int64) is the random permutation of cso.py:81: pair i is (perm[i],
+ * perm[i + pop_size / 2]); the one with the smaller fitness teaches (ties and NaN: the second one),
+ * the other learns:  v' = l1 * velocity + l2 * (teacher - student) + phi * l3 * (center - student),
+ * relu-form clamp to +-(ub - lb), position = clamp(student + v', lb, ub), fit = f(position).
+ * pop and fit are updated in place for the students' rows; with store_velocity = 0 velocity is only
+ * read (the reference does not store v' either, cso.py:98-105), with 1 the students' rows receive v'
+ * (the rule of the original algorithm). phi is a DEVICE scalar. lambdas is the (3, pop_size / 2, dim) uniform
+ * draw of cso.py:90, or NULL: then Philox4x32-10 with key = seed and counter = (pair, column / 4,
+ * generation, which) supplies it. fitness_id = -1 skips the evaluation (fit is left alone): pass
+ * candidates (pop_size / 2, dim) and students (pop_size / 2, int64) to get the new positions and
+ * their rows for an evaluation outside.
+ * The mean position (cso.py:87) is taken from the workspace when center_ready != 0, otherwise it is
+ * computed first. For rows of up to 1,024 floats the update kernel accumulates the NEXT generation's
+ * mean while it has every row in hand and *next_center_ready is set to 1: pass that value back as
+ * center_ready of the next call if nothing else wrote to pop in between. */
+int evox_cso_step(float* pop, float* velocity, int32_t store_velocity, float* fit, const int64_t* perm, const float* lb,
+                  const float* ub, const float* phi, const float* lambdas, int64_t pop_size,
+                  int32_t dim, int32_t fitness_id, const float* params, uint64_t seed,
+                  uint64_t generation, int32_t center_ready, float* candidates, int64_t* students,
+                  void* workspace, size_t workspace_bytes, int32_t* next_center_ready, void* stream);
+
+/* ------------------------------------------------------------------------------------------
  * P2. NSGA-II environmental selection.
  * ------------------------------------------------------------------------------------------ */
 

@@ -22,7 +22,8 @@ HERE = Path(__file__).resolve().parent
 
 
 def _np(t):
-    return t.detach().cpu().numpy() if isinstance(t, torch.Tensor) else np.asarray(t)
+    # a copy: some reference algorithms update their state tensors in place afterwards
+    return t.detach().cpu().numpy().copy() if isinstance(t, torch.Tensor) else np.asarray(t)
 
 
 def golden_pso(out: dict):
@@ -264,7 +265,49 @@ def golden_variation(out: dict):
     out["ts_rank"], out["ts_dis"], out["ts_parents"], out["ts_selected"] = _np(rank), _np(dis), _np(parents), _np(picked)
 
 
-GENERATORS = {"pso": golden_pso, "nds": golden_nds, "rvea": golden_rvea, "es": golden_es, "variation": golden_variation}
+def golden_cso(out: dict):
+    """CSO.init_step + 3 teacher-forced steps (randperm and the three lambda draws recorded) on Ackley
+    and Sphere, dims 12 and 10, 38 particles, phi 0.1; pop / fit / velocity after every step."""
+    from evox.algorithms import CSO
+    from evox.problems.numerical import Ackley, Sphere
+    from evox.workflows import StdWorkflow
+
+    import evox.algorithms.so.pso_variants.cso as cso_mod
+
+    names = ["pop", "fit", "velocity"]
+    for prob_name, prob_cls, lo, hi in (("ackley", Ackley, -32.768, 32.768), ("sphere", Sphere, -5.0, 7.0)):
+        for dim in (12, 10):
+            pop_size, phi = 38, 0.1
+            torch.manual_seed(4321 + dim)
+            algo = CSO(pop_size, torch.full((dim,), lo), torch.full((dim,), hi), phi=phi)
+            wf = StdWorkflow(algo, prob_cls())
+            tag = f"cso_{prob_name}_d{dim}"
+            out[f"{tag}_phi"] = np.asarray(phi, dtype=np.float32)
+            out[f"{tag}_bounds"] = np.asarray([lo, hi], dtype=np.float32)
+            for n in names:
+                out[f"{tag}_s0_{n}"] = _np(wf.algorithm.state_dict()[n])
+            wf.init_step()
+            for n in names:
+                out[f"{tag}_s1_{n}"] = _np(wf.algorithm.state_dict()[n])
+            gen = torch.Generator().manual_seed(77 + dim)
+            for g in range(3):
+                perm = torch.randperm(pop_size, generator=gen)
+                lambdas = torch.rand(3, pop_size // 2, dim, generator=gen)
+                real_rand, real_perm = torch.rand, torch.randperm
+                cso_mod.torch.rand = lambda *a, **k: lambdas
+                cso_mod.torch.randperm = lambda *a, **k: perm
+                try:
+                    wf.step()
+                finally:
+                    cso_mod.torch.rand, cso_mod.torch.randperm = real_rand, real_perm
+                out[f"{tag}_g{g}_perm"] = _np(perm)
+                out[f"{tag}_g{g}_lambdas"] = _np(lambdas)
+                for n in names:
+                    out[f"{tag}_s{g + 2}_{n}"] = _np(wf.algorithm.state_dict()[n])
+
+
+GENERATORS = {"pso": golden_pso, "nds": golden_nds, "rvea": golden_rvea, "es": golden_es, "variation": golden_variation,
+              "cso": golden_cso}
 
 
 def main():
