@@ -73,6 +73,37 @@ __device__ __forceinline__ uint4 philox4x32_10(uint32_t c0, uint32_t c1, uint32_
   return make_uint4(c0, c1, c2, c3);
 }
 
+// The same generator with the key schedule taken out of the kernel: the ten (k0, k1) pairs depend only
+// on the seed, so the host computes them once per launch and they travel as kernel arguments.
+struct PhiloxKeys {
+  uint32_t k[20];
+};
+
+static inline PhiloxKeys philox_round_keys(uint64_t seed) {
+  PhiloxKeys rk;
+  uint32_t k0 = (uint32_t)seed, k1 = (uint32_t)(seed >> 32);
+  for (int r = 0; r < 10; ++r) {
+    rk.k[2 * r] = k0;
+    rk.k[2 * r + 1] = k1;
+    k0 += EVOX_PHILOX_W0;
+    k1 += EVOX_PHILOX_W1;
+  }
+  return rk;
+}
+
+__device__ __forceinline__ uint4 philox4x32_10_keyed(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3, const PhiloxKeys& rk) {
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    const unsigned long long p0 = (unsigned long long)EVOX_PHILOX_M0 * (unsigned long long)c0;
+    const unsigned long long p1 = (unsigned long long)EVOX_PHILOX_M1 * (unsigned long long)c2;
+    c0 = (uint32_t)(p1 >> 32) ^ c1 ^ rk.k[2 * r];
+    c1 = (uint32_t)p1;
+    c2 = (uint32_t)(p0 >> 32) ^ c3 ^ rk.k[2 * r + 1];
+    c3 = (uint32_t)p0;
+  }
+  return make_uint4(c0, c1, c2, c3);
+}
+
 // 24-bit uniform in [0,1): (u >> 8) * 2^-24, as philox.py:108-110.
 __device__ __forceinline__ float u24_to_unit(uint32_t u) {
   return __uint2float_rn(u >> 8) * 5.9604644775390625e-08f;

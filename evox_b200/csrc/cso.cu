@@ -24,8 +24,9 @@ namespace {
 
 constexpr int kWarpsPerBlock = 8;
 constexpr int kThreads = kWarpsPerBlock * 32;
-constexpr int kMaxChunks = 8;           // float4 chunks per lane whose column sums stay in registers
+constexpr int kMaxChunks = 8;           // float4 chunks per lane whose column sums a warp keeps in shared memory
 constexpr int kMaxFusedDim = kMaxChunks * 32 * 4;
+constexpr int kBlocksPerSM = 3;
 
 struct CsoArgs {
   float* pop;
@@ -41,7 +42,8 @@ struct CsoArgs {
   long long P;
   int d;
   FitParams fp;
-  unsigned long long seed, generation;
+  PhiloxKeys keys;
+  unsigned long long generation;
   int write_fit;
   float* candidates;     // optional (P / 2, d): the students' new positions, pair order
   long long* students;   // optional (P / 2): row of each pair's student
@@ -52,8 +54,8 @@ struct CsoArgs {
 // (q lo, q hi, generation lo, which + 4 * generation hi), q = pair * ceil(d / 4) + column / 4, which = 0..2
 // for lambda1..lambda3 (cso.py:90 draws them as one (3, P / 2, d) block).
 __device__ __forceinline__ float4 cso_uniform4(const CsoArgs& a, unsigned long long q, uint32_t which) {
-  const uint4 r = philox4x32_10((uint32_t)q, (uint32_t)(q >> 32), (uint32_t)a.generation, which + 4u * (uint32_t)(a.generation >> 32),
-                                (uint32_t)a.seed, (uint32_t)(a.seed >> 32));
+  const uint4 r = philox4x32_10_keyed((uint32_t)q, (uint32_t)(q >> 32), (uint32_t)a.generation,
+                                      which + 4u * (uint32_t)(a.generation >> 32), a.keys);
   return make_float4(u24_to_unit(r.x), u24_to_unit(r.y), u24_to_unit(r.z), u24_to_unit(r.w));
 }
 
@@ -70,7 +72,7 @@ __device__ __forceinline__ float learn_one(float& v, float pt, float ps, float c
 }
 
 template <int VEC, bool PHILOX, int FIT, bool SUMS>
-__global__ void __launch_bounds__(kThreads) cso_update_kernel(const CsoArgs a) {
+__global__ void __launch_bounds__(kThreads, kBlocksPerSM) cso_update_kernel(const CsoArgs a) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const long long warp0 = (long long)blockIdx.x * kWarpsPerBlock + warp;
   const long long n_warps = (long long)gridDim.x * kWarpsPerBlock;
@@ -78,14 +80,24 @@ __global__ void __launch_bounds__(kThreads) cso_update_kernel(const CsoArgs a) {
   const int d = a.d;
   const int n_call = (d + 3) >> 2;
   const float phi = *a.phi;
-  float4 sum[SUMS ? kMaxChunks : 1];
+  // running column sums of the rows this warp has seen: slot [warp][chunk], each owned by one lane
+  __shared__ float4 ssum[SUMS ? kWarpsPerBlock : 1][SUMS ? kMaxChunks * 32 : 1];
   if constexpr (SUMS) {
-#pragma unroll
-    for (int k = 0; k < kMaxChunks; ++k) sum[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int c = lane; c < kMaxChunks * 32; c += 32) ssum[warp][c] = make_float4(0.f, 0.f, 0.f, 0.f);
   }
 
+  // the pair after this one is looked up while this one is processed (perm -> fit is a dependent chain)
+  long long left_n = 0, right_n = 0;
+  if (warp0 < half) {
+    left_n = a.perm[warp0];
+    right_n = a.perm[warp0 + half];
+  }
   for (long long pair = warp0; pair < half; pair += n_warps) {
-    const long long left = a.perm[pair], right = a.perm[pair + half];
+    const long long left = left_n, right = right_n;
+    if (pair + n_warps < half) {
+      left_n = __ldg(a.perm + pair + n_warps);
+      right_n = __ldg(a.perm + pair + n_warps + half);
+    }
     if ((unsigned long long)left >= (unsigned long long)a.P || (unsigned long long)right >= (unsigned long long)a.P) continue;
     const bool mask = a.fit[left] < a.fit[right];  // cso.py:82: ties and NaN make the LEFT one the student
     const long long teacher = mask ? left : right, student = mask ? right : left;
@@ -99,9 +111,7 @@ __global__ void __launch_bounds__(kThreads) cso_update_kernel(const CsoArgs a) {
       const float4* ce4 = reinterpret_cast<const float4*>(a.center);
       const float4* lb4 = reinterpret_cast<const float4*>(a.lb);
       const float4* ub4 = reinterpret_cast<const float4*>(a.ub);
-      auto chunk = [&](int c, float4& s) {
-        float4 v = __ldcs(v4 + c);
-        const float4 pt = __ldcs(pt4 + c), ps = __ldcs(ps4 + c);
+      auto chunk = [&](int c, float4 v, const float4 pt, const float4 ps) {
         const float4 ce = __ldg(ce4 + c), lb = __ldg(lb4 + c), ub = __ldg(ub4 + c);
         float4 l1, l2, l3;
         if constexpr (PHILOX) {
@@ -127,20 +137,35 @@ __global__ void __launch_bounds__(kThreads) cso_update_kernel(const CsoArgs a) {
         acc.add(xo.z, a.fp);
         acc.add(xo.w, a.fp);
         if constexpr (SUMS) {  // both rows of the pair as they stand after this generation
+          float4 s = ssum[warp][c];
           s.x += pt.x + xo.x;
           s.y += pt.y + xo.y;
           s.z += pt.z + xo.z;
           s.w += pt.w + xo.w;
+          ssum[warp][c] = s;
         }
       };
-      if constexpr (SUMS) {
-#pragma unroll
-        for (int k = 0; k < kMaxChunks; ++k) {
-          const int c = lane + 32 * k;
-          if (c < n_call) chunk(c, sum[k]);
+      // register double buffering: the rows' next chunk is in flight while this one is computed
+      int c = lane;
+      float4 v, pt, ps;
+      if (c < n_call) {
+        v = __ldcs(v4 + c);
+        pt = __ldcs(pt4 + c);
+        ps = __ldcs(ps4 + c);
+      }
+      while (c < n_call) {
+        const int cn = c + 32;
+        float4 vn, ptn, psn;
+        if (cn < n_call) {
+          vn = __ldcs(v4 + cn);
+          ptn = __ldcs(pt4 + cn);
+          psn = __ldcs(ps4 + cn);
         }
-      } else {
-        for (int c = lane; c < n_call; c += 32) chunk(c, sum[0]);
+        chunk(c, v, pt, ps);
+        v = vn;
+        pt = ptn;
+        ps = psn;
+        c = cn;
       }
     } else {
       for (int e = lane; e < d; e += 32) {
@@ -174,27 +199,17 @@ __global__ void __launch_bounds__(kThreads) cso_update_kernel(const CsoArgs a) {
   }
 
   if constexpr (SUMS) {
-    // warps of the block fold their sums in warp order, then the block writes one partial row
-    __shared__ float4 ssum[kMaxChunks * 32];
-    for (int w = 0; w < kWarpsPerBlock; ++w) {
-      if (warp == w) {
-#pragma unroll
-        for (int k = 0; k < kMaxChunks; ++k) {
-          const int c = lane + 32 * k;
-          if (c < n_call) {
-            float4 s = sum[k];
-            if (w > 0) {
-              const float4 o = ssum[c];
-              s = make_float4(o.x + s.x, o.y + s.y, o.z + s.z, o.w + s.w);
-            }
-            ssum[c] = s;
-          }
-        }
-      }
-      __syncthreads();
-    }
+    // the warps' sums are folded in warp order and the block writes one partial row
+    __syncthreads();
     float4* out = reinterpret_cast<float4*>(a.partial + (size_t)blockIdx.x * (size_t)d);
-    for (int c = threadIdx.x; c < n_call; c += kThreads) out[c] = ssum[c];
+    for (int c = threadIdx.x; c < n_call; c += kThreads) {
+      float4 s = ssum[0][c];
+      for (int w = 1; w < kWarpsPerBlock; ++w) {
+        const float4 o = ssum[w][c];
+        s = make_float4(s.x + o.x, s.y + o.y, s.z + o.z, s.w + o.w);
+      }
+      out[c] = s;
+    }
   }
 }
 
@@ -254,7 +269,7 @@ __global__ void __launch_bounds__(1024) cso_center_finish_kernel(const float* __
 
 // workspace: center [d padded to 4] | partial [max_partials][d]
 long long padded_dim(int d) { return ((long long)d + 3) / 4 * 4; }
-int max_partials() { return sm_count() * 4; }
+int max_partials() { return sm_count() * kBlocksPerSM; }
 
 template <int VEC, bool PHILOX, bool SUMS>
 void launch_update(int fitness_id, int grid, cudaStream_t s, const CsoArgs& a) {
@@ -332,7 +347,7 @@ extern "C" int evox_cso_step(float* pop, float* velocity, int32_t store_velocity
   a.P = pop_size;
   a.d = dim;
   a.fp = fitness_id == -1 ? FitParams{0.f, 0.f, 0.f} : FitParams{fit_params[0], fit_params[1], fit_params[2]};
-  a.seed = seed;
+  a.keys = philox_round_keys(seed);
   a.generation = generation;
   a.write_fit = fitness_id != -1;
   a.candidates = candidates;
