@@ -49,6 +49,8 @@ WORKLOADS = {
     "pso_rastrigin_1e6x1000": ("rastrigin", 1_000_000, 1000, -5.12, 5.12, 0.7, 1.5, 1.5),
     "pso_ackley_1e4x500": ("ackley", 10_000, 500, -32.768, 32.768, 0.6, 2.5, 0.8),
     "pso_ackley_small": ("ackley", 65_536, 1000, -32.768, 32.768, 0.6, 2.5, 0.8),
+    "pso_ackley_4e6x128": ("ackley", 4_000_000, 128, -32.768, 32.768, 0.6, 2.5, 0.8),  # short rows: one chunk per lane
+    "pso_ackley_2e6x256": ("ackley", 2_000_000, 256, -32.768, 32.768, 0.6, 2.5, 0.8),
 }
 
 
@@ -276,25 +278,21 @@ def run_ours(args):
         e2e_step()
     e2e_ms = timed(e2e_step, args.steps) / args.steps
 
-    # -- roofline of the dominant kernel, timed alone on its launch stream -------------------
-    lib = _cabi.lib
+    # -- roofline of the dominant kernel: CUDA events around pso_move_eval_kernel inside K more real
+    #    generations (same stream, same neighbours; the algorithm then issues its launches one C call at a
+    #    time instead of through the single fused call) -------------------------------------------------
     n_local = a.local_size
-    params = _cabi.host_floats(problem.fused_fitness()[1])
-    fid = problem.fused_fitness()[0]
-
-    def move_only():
-        _cabi.check(
-            lib.evox_pso_move_eval(
-                a.pop.data_ptr(), a.velocity.data_ptr(), a.local_best_location.data_ptr(),
-                a.local_best_fit.data_ptr(), a.fit.data_ptr(), a.global_best_location.data_ptr(),
-                a.lb.data_ptr(), a.ub.data_ptr(), a.w.data_ptr(), a.phi_p.data_ptr(), a.phi_g.data_ptr(),
-                None, None, n_local, d, fid, params, a.seed, a.generation, a.row_start,
-                _cabi.stream_ptr(dev),
-            )
-        )
-        a.generation += 1
-
-    kernel_ms = timed(move_only, args.steps) / args.steps
+    a._kernel_events = []
+    barrier()
+    for _ in range(args.steps):
+        wf.step()
+    barrier()
+    kernel_ms = sum(e0.elapsed_time(e1) for e0, e1 in a._kernel_events) / len(a._kernel_events)
+    a._kernel_events = None
+    if world > 1:
+        t = torch.tensor([kernel_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        kernel_ms = t.item()
     clocks.__exit__(None, None, None)
     clock_summary = clocks.summary()
     peak, peak_kind = measured_peaks()

@@ -95,6 +95,9 @@ class PSO(Algorithm):
         self.global_best_location = Mutable(pop[0].clone())
         self.global_best_fit = Mutable(torch.tensor(torch.inf, device=device))
         self._scratch: dict[str, torch.Tensor] = {}
+        # measurement hook: when a list, step() issues its launches one C call at a time and appends a
+        # (start, end) CUDA-event pair around the update kernel of every generation
+        self._kernel_events: list | None = None
 
     # -- checkpointing of the random stream position ------------------------------------------
     def get_extra_state(self):
@@ -170,7 +173,7 @@ class PSO(Algorithm):
             _cabi.ptr(rg, torch.float32, "rg"), _cabi.ptr(rp, torch.float32, "rp"),
             self.local_size, self.dim, fitness_id, _cabi.host_floats(params), self.seed, self.generation,
         )
-        if self.world_size == 1:
+        if self.world_size == 1 and self._kernel_events is None:
             _cabi.check(
                 lib.evox_pso_step(
                     _cabi.ptr(self.pop), _cabi.ptr(self.velocity), _cabi.ptr(self.local_best_location),
@@ -180,6 +183,9 @@ class PSO(Algorithm):
             )
         else:
             self._update_global_best(dev, have_previous=True)
+            if self._kernel_events is not None:
+                pair = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+                pair[0].record()
             _cabi.check(
                 lib.evox_pso_move_eval(
                     _cabi.ptr(self.pop), _cabi.ptr(self.velocity), _cabi.ptr(self.local_best_location),
@@ -187,6 +193,9 @@ class PSO(Algorithm):
                     *args, self.row_start, s,
                 )
             )
+            if self._kernel_events is not None:
+                pair[1].record()
+                self._kernel_events.append(pair)
         self.generation += 1
         if plan is None:
             self.fit = self.evaluate(self.pop)

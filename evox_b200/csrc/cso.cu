@@ -132,10 +132,7 @@ __global__ void __launch_bounds__(kThreads, kBlocksPerSM) cso_update_kernel(cons
         __stcs(ps4 + c, xo);
         if (a.store_velocity) __stcs(v4 + c, v);
         if (a.candidates) __stcs(reinterpret_cast<float4*>(a.candidates + bp) + c, xo);
-        acc.add(xo.x, a.fp);
-        acc.add(xo.y, a.fp);
-        acc.add(xo.z, a.fp);
-        acc.add(xo.w, a.fp);
+        acc.add4(xo, a.fp);
         if constexpr (SUMS) {  // both rows of the pair as they stand after this generation
           float4 s = ssum[warp][c];
           s.x += pt.x + xo.x;

@@ -20,14 +20,22 @@ struct FitParams {
 // then the hardware cosine (absolute error 2^-21.4 on that interval). Per term the error is below
 // 1e-6, i.e. below 1e-6 on mean(cos) for Ackley and below 1e-5 * d on Rastrigin's sum of 10*cos,
 // an order of magnitude inside the 1e-5 relative tolerance of the fitness values.
-__device__ __forceinline__ float fast_cos(float t) {
-  if (fabsf(t) > 32768.0f) return cosf(t);  // far outside any benchmark's bounds: exact path
-  const float magic = 12582912.0f;          // 1.5 * 2^23: adding and subtracting rounds to nearest integer
+// Valid for |t| <= 32768 (callers check, once per element or once per group of four).
+__device__ __forceinline__ float fast_cos_core(float t) {
+  const float magic = 12582912.0f;  // 1.5 * 2^23: adding and subtracting rounds to nearest integer
   const float k = __fadd_rn(__fmaf_rn(t, 0.15915494309189535f, magic), -magic);
   float r = __fmaf_rn(-k, 6.2831854820251465f, t);
   r = __fmaf_rn(-k, -1.7484555e-07f, r);
   return __cosf(r);
 }
+// Exact path for arguments far outside any benchmark's bounds; kept out of line so that its registers
+// and code do not weigh on the loops that never take it.
+static __device__ __noinline__ float slow_cos(float t) { return cosf(t); }
+__device__ __forceinline__ float fast_cos(float t) {
+  if (fabsf(t) > 32768.0f) return slow_cos(t);
+  return fast_cos_core(t);
+}
+__device__ __forceinline__ float max_abs4(const float4& x) { return fmaxf(fmaxf(fabsf(x.x), fabsf(x.y)), fmaxf(fabsf(x.z), fabsf(x.w))); }
 
 template <int FIT>
 struct Fitness;
@@ -38,6 +46,23 @@ struct Fitness<EVOX_FIT_ACKLEY> {
   __device__ __forceinline__ void add(float x, const FitParams& p) {
     s_sq = __fmaf_rn(x, x, s_sq);
     s_cos += fast_cos(__fmul_rn(p.c, x));
+  }
+  __device__ __forceinline__ void add4(const float4& x, const FitParams& p) {
+    if (max_abs4(x) * fabsf(p.c) > 32768.0f) {  // also taken for NaN-free infinities; NaN falls through and propagates
+      add(x.x, p);
+      add(x.y, p);
+      add(x.z, p);
+      add(x.w, p);
+      return;
+    }
+    s_sq = __fmaf_rn(x.x, x.x, s_sq);
+    s_sq = __fmaf_rn(x.y, x.y, s_sq);
+    s_sq = __fmaf_rn(x.z, x.z, s_sq);
+    s_sq = __fmaf_rn(x.w, x.w, s_sq);
+    s_cos += fast_cos_core(__fmul_rn(p.c, x.x));
+    s_cos += fast_cos_core(__fmul_rn(p.c, x.y));
+    s_cos += fast_cos_core(__fmul_rn(p.c, x.z));
+    s_cos += fast_cos_core(__fmul_rn(p.c, x.w));
   }
   __device__ __forceinline__ void reduce() {
     s_sq = warp_sum(s_sq);
@@ -57,9 +82,25 @@ template <>
 struct Fitness<EVOX_FIT_RASTRIGIN> {
   float s = 0.f, s_cos = 0.f;
   __device__ __forceinline__ void add(float x, const FitParams&) {
-    const float t = __fmul_rn(6.283185307179586f, x);
     s = __fmaf_rn(x, x, s);
-    s_cos += fast_cos(t);
+    s_cos += fast_cos(__fmul_rn(6.283185307179586f, x));
+  }
+  __device__ __forceinline__ void add4(const float4& x, const FitParams& p) {
+    if (max_abs4(x) > 5000.0f) {  // 2 pi x beyond the fast cosine's range
+      add(x.x, p);
+      add(x.y, p);
+      add(x.z, p);
+      add(x.w, p);
+      return;
+    }
+    s = __fmaf_rn(x.x, x.x, s);
+    s = __fmaf_rn(x.y, x.y, s);
+    s = __fmaf_rn(x.z, x.z, s);
+    s = __fmaf_rn(x.w, x.w, s);
+    s_cos += fast_cos_core(__fmul_rn(6.283185307179586f, x.x));
+    s_cos += fast_cos_core(__fmul_rn(6.283185307179586f, x.y));
+    s_cos += fast_cos_core(__fmul_rn(6.283185307179586f, x.z));
+    s_cos += fast_cos_core(__fmul_rn(6.283185307179586f, x.w));
   }
   __device__ __forceinline__ void reduce() {
     s = warp_sum(s);
@@ -74,6 +115,12 @@ template <>
 struct Fitness<EVOX_FIT_SPHERE> {
   float s = 0.f;
   __device__ __forceinline__ void add(float x, const FitParams&) { s = __fmaf_rn(x, x, s); }
+  __device__ __forceinline__ void add4(const float4& x, const FitParams&) {
+    s = __fmaf_rn(x.x, x.x, s);
+    s = __fmaf_rn(x.y, x.y, s);
+    s = __fmaf_rn(x.z, x.z, s);
+    s = __fmaf_rn(x.w, x.w, s);
+  }
   __device__ __forceinline__ void reduce() { s = warp_sum(s); }
   __device__ __forceinline__ float finish(int, const FitParams&) const { return s; }
 };

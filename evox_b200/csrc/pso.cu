@@ -138,22 +138,13 @@ __global__ void __launch_bounds__(kThreads, MOVE_BLOCKS_PER_SM) pso_move_eval_ke
       const float4* rg4 = PHILOX ? nullptr : reinterpret_cast<const float4*>(a.rg + base);
       const float4* rp4 = PHILOX ? nullptr : reinterpret_cast<const float4*>(a.rp + base);
       const uint64_t q0 = (uint64_t)(a.row_offset + row) * (uint64_t)n_call;
-      // register double buffering: the loads of chunk c + 32 are in flight while chunk c computes
-      int c = lane;
-      float4 x, v, pb;
-      if (c < n_call) {
-        x = __ldcs(pop4 + c);
-        v = __ldcs(vel4 + c);
-        pb = better ? x : __ldcs(pb4 + c);
-      }
-      while (c < n_call) {
-        const int cn = c + 32;
-        float4 xn, vn, pbn;
-        if (cn < n_call) {
-          xn = __ldcs(pop4 + cn);
-          vn = __ldcs(vel4 + cn);
-          pbn = better ? xn : __ldcs(pb4 + cn);
-        }
+      // Plain loop: with four blocks of eight warps per SM the other warps cover a chunk's load latency; a
+      // register double buffer (next chunk's loads issued ahead) measured 4 % slower here, and three blocks
+      // per SM 15 % slower.
+      for (int c = lane; c < n_call; c += 32) {
+        const float4 x = __ldcs(pop4 + c);
+        float4 v = __ldcs(vel4 + c);
+        const float4 pb = better ? x : __ldcs(pb4 + c);
         float4 rg, rp;
         if constexpr (PHILOX) {
           rg = pso_uniform4<false>(q0 + c, a.generation, 0u, a.rk);
@@ -173,14 +164,7 @@ __global__ void __launch_bounds__(kThreads, MOVE_BLOCKS_PER_SM) pso_move_eval_ke
         if (better) __stcs(pb4 + c, x);  // pso.py:90 — own position becomes the personal best
         __stcs(pop4 + c, xo);
         __stcs(vel4 + c, v);
-        acc.add(xo.x, a.fp);
-        acc.add(xo.y, a.fp);
-        acc.add(xo.z, a.fp);
-        acc.add(xo.w, a.fp);
-        x = xn;
-        v = vn;
-        pb = pbn;
-        c = cn;
+        acc.add4(xo, a.fp);
       }
     } else {
       const uint64_t q0 = (uint64_t)(a.row_offset + row) * (uint64_t)n_call;
@@ -226,10 +210,7 @@ __global__ void __launch_bounds__(kThreads)
 #pragma unroll 4
       for (int c = lane; c < n4; c += 32) {
         const float4 x = __ldg(p4 + c);
-        acc.add(x.x, fp);
-        acc.add(x.y, fp);
-        acc.add(x.z, fp);
-        acc.add(x.w, fp);
+        acc.add4(x, fp);
       }
     } else {
       for (int e = lane; e < d; e += 32) acc.add(pop[base + e], fp);
@@ -474,13 +455,14 @@ extern "C" int evox_eval_fitness(const float* pop, int64_t pop_size, int32_t dim
   const int grid = row_grid(pop_size);
   const bool vec = (dim % 4 == 0) && aligned16(pop);
 #define EVOX_EVAL(V, F) eval_fitness_kernel<V, F><<<grid, kThreads, 0, s>>>(pop, pop_size, dim, fp, fit)
+  const int fid = fitness_id;
   if (vec) {
-    if (fitness_id == EVOX_FIT_ACKLEY) EVOX_EVAL(4, EVOX_FIT_ACKLEY);
-    else if (fitness_id == EVOX_FIT_RASTRIGIN) EVOX_EVAL(4, EVOX_FIT_RASTRIGIN);
+    if (fid == EVOX_FIT_ACKLEY) EVOX_EVAL(4, EVOX_FIT_ACKLEY);
+    else if (fid == EVOX_FIT_RASTRIGIN) EVOX_EVAL(4, EVOX_FIT_RASTRIGIN);
     else EVOX_EVAL(4, EVOX_FIT_SPHERE);
   } else {
-    if (fitness_id == EVOX_FIT_ACKLEY) EVOX_EVAL(1, EVOX_FIT_ACKLEY);
-    else if (fitness_id == EVOX_FIT_RASTRIGIN) EVOX_EVAL(1, EVOX_FIT_RASTRIGIN);
+    if (fid == EVOX_FIT_ACKLEY) EVOX_EVAL(1, EVOX_FIT_ACKLEY);
+    else if (fid == EVOX_FIT_RASTRIGIN) EVOX_EVAL(1, EVOX_FIT_RASTRIGIN);
     else EVOX_EVAL(1, EVOX_FIT_SPHERE);
   }
 #undef EVOX_EVAL
