@@ -26,7 +26,7 @@ constexpr int kWarpsPerBlock = 8;
 constexpr int kThreads = kWarpsPerBlock * 32;
 constexpr int kMaxChunks = 8;           // float4 chunks per lane whose column sums a warp keeps in shared memory
 constexpr int kMaxFusedDim = kMaxChunks * 32 * 4;
-constexpr int kBlocksPerSM = 3;
+constexpr int kBlocksPerSM = 4;
 
 struct CsoArgs {
   float* pop;
@@ -142,28 +142,7 @@ __global__ void __launch_bounds__(kThreads, kBlocksPerSM) cso_update_kernel(cons
           ssum[warp][c] = s;
         }
       };
-      // register double buffering: the rows' next chunk is in flight while this one is computed
-      int c = lane;
-      float4 v, pt, ps;
-      if (c < n_call) {
-        v = __ldcs(v4 + c);
-        pt = __ldcs(pt4 + c);
-        ps = __ldcs(ps4 + c);
-      }
-      while (c < n_call) {
-        const int cn = c + 32;
-        float4 vn, ptn, psn;
-        if (cn < n_call) {
-          vn = __ldcs(v4 + cn);
-          ptn = __ldcs(pt4 + cn);
-          psn = __ldcs(ps4 + cn);
-        }
-        chunk(c, v, pt, ps);
-        v = vn;
-        pt = ptn;
-        ps = psn;
-        c = cn;
-      }
+      for (int c = lane; c < n_call; c += 32) chunk(c, __ldcs(v4 + c), __ldcs(pt4 + c), __ldcs(ps4 + c));
     } else {
       for (int e = lane; e < d; e += 32) {
         float v = a.vel[bs + e];
