@@ -1,5 +1,5 @@
-"""OpenES and VirtualLoRAES with the reference's constructor arguments and state names
-(evox/algorithms/so/es_variants/open_es.py:10-86, virtual_lora_es.py:18-138)."""
+"""OpenES, ARS and VirtualLoRAES with the reference's constructor arguments and state names
+(evox/algorithms/so/es_variants/open_es.py:10-86, ars.py:8-101, virtual_lora_es.py:18-138)."""
 
 from __future__ import annotations
 
@@ -15,9 +15,10 @@ from ..lora_kernels import compute_counter_offsets, lora_gradient_from_seeds
 from ..sharding import group_info, shard_bounds
 
 
-def _update_center(algo, grad: torch.Tensor, start: int = 0, count: int | None = None) -> None:
+def _update_center(algo, grad: torch.Tensor, start: int = 0, count: int | None = None, lr: torch.Tensor | None = None) -> None:
     """center[start : start + count] -= lr * grad (or the Adam step) — `grad` holds `count` values."""
     dev = algo.center.device
+    lr = algo.learning_rate if lr is None else lr
     adam = algo.optimizer == "adam"
     count = algo.center.numel() - start if count is None else count
     assert grad.numel() == count and grad.is_contiguous()
@@ -28,7 +29,7 @@ def _update_center(algo, grad: torch.Tensor, start: int = 0, count: int | None =
     _cabi.check(
         _cabi.lib.evox_es_update(
             at(algo.center), _cabi.ptr(grad, torch.float32, "grad"),
-            _cabi.ptr(algo.learning_rate, torch.float32, "learning_rate"),
+            _cabi.ptr(lr, torch.float32, "learning_rate"),
             at(algo.exp_avg) if adam else None, at(algo.exp_avg_sq) if adam else None,
             _cabi.ptr(algo.beta1) if adam else None, _cabi.ptr(algo.beta2) if adam else None,
             1e-8, count, _cabi.stream_ptr(dev),
@@ -103,6 +104,67 @@ class OpenES(_ESBase):
         grad = torch.empty(self.dim, dtype=torch.float32, device=dev)
         _cabi.check(lib.evox_openes_gradient(_cabi.ptr(noise), _cabi.ptr(fitness), self.pop_size, self.dim, rows, self.sigma(), _cabi.ptr(grad), s))
         _update_center(self, grad)
+
+
+class ARS(Algorithm):
+    """Augmented random search (ars.py:8-101): mirrored sampling, the `elite_pop_size` best directions
+    (by the better of their two evaluations) weighted by their fitness difference, scaled by the elite's
+    fitness spread. The population and the weighted sum of directions run on the OpenES kernels; the
+    elite bookkeeping works on pop_size / 2 scalars with torch ops on the device."""
+
+    def __init__(
+        self,
+        pop_size: int,
+        center_init: torch.Tensor,
+        elite_ratio: float = 0.1,
+        lr: float = 0.05,
+        sigma: float = 0.03,
+        optimizer: Literal["adam"] | None = None,
+        device: torch.device | None = None,
+    ):
+        super().__init__()
+        device = torch.get_default_device() if device is None else torch.device(device)
+        assert pop_size > 1 and pop_size % 2 == 0, "ARS mirrors its samples: pop_size must be even"
+        assert 0 <= elite_ratio <= 1
+        assert optimizer in [None, "adam"]
+        self.lr = Parameter(lr, dtype=torch.float32, device=device)
+        self.sigma = Parameter(sigma, dtype=torch.float32, device=device)
+        self.dim = center_init.shape[0]
+        self.pop_size = pop_size
+        self.optimizer = optimizer
+        self.elite_pop_size = max(1, int(pop_size / 2 * elite_ratio))
+        self.center = Mutable(center_init.to(device=device, dtype=torch.float32).contiguous().clone())
+        if optimizer == "adam":
+            self.exp_avg = Mutable(torch.zeros_like(self.center))
+            self.exp_avg_sq = Mutable(torch.zeros_like(self.center))
+            self.beta1 = Parameter(0.9, dtype=torch.float32, device=device)
+            self.beta2 = Parameter(0.999, dtype=torch.float32, device=device)
+
+    def step(self, z_plus: torch.Tensor | None = None):
+        """One generation (ars.py:62-98). `z_plus`: optional (pop_size / 2, dim) standard-normal draws."""
+        dev = self.center.device
+        half, k = self.pop_size // 2, self.elite_pop_size
+        if z_plus is None:
+            z_plus = torch.randn(half, self.dim, device=dev)
+        z_plus = z_plus.to(device=dev, dtype=torch.float32).contiguous()
+        assert z_plus.shape == (half, self.dim)
+        lib, s = _cabi.lib, _cabi.stream_ptr(dev)
+        pop = torch.empty(self.pop_size, self.dim, dtype=torch.float32, device=dev)
+        _cabi.check(lib.evox_openes_ask(_cabi.ptr(self.center), _cabi.ptr(z_plus), _cabi.ptr(self.sigma), self.pop_size, self.dim, half, _cabi.ptr(pop), s))
+        fitness = self.evaluate(pop).to(torch.float32)
+        fit_1, fit_2 = fitness[:half], fitness[half:]
+        elite_idx = torch.minimum(fit_1, fit_2).argsort()[:k]
+        sigma_fitness = torch.std(torch.cat([fit_1[elite_idx], fit_2[elite_idx]])) + 1e-05
+        # weights of all pop_size / 2 directions: the elite's fitness difference, zero elsewhere, pre-scaled so
+        # that the kernel's division by its row count leaves 1 / (k * sigma_fitness)
+        weights = torch.zeros(half, dtype=torch.float32, device=dev)
+        weights[elite_idx] = (fit_1[elite_idx] - fit_2[elite_idx]) * (half / (k * sigma_fitness))
+        grad = torch.empty(self.dim, dtype=torch.float32, device=dev)
+        _cabi.check(lib.evox_openes_gradient(_cabi.ptr(z_plus), _cabi.ptr(weights), half, self.dim, half, 1.0, _cabi.ptr(grad), s))
+        _update_center(self, grad, lr=self.lr)
+
+    def record_step(self):
+        return {"center": self.center}
 
 
 class VirtualLoRAES(_ESBase):

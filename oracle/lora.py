@@ -137,3 +137,22 @@ def open_es_step(center, noise_half, fitness_fn, lr, sigma, mirrored=True, adam_
     # the reference holds beta1 / beta2 as float32 tensors (open_es.py:57-58), so 1 - beta is rounded in fp32
     new_center, m, v = adam_single_tensor(center, grad, adam_state[0], adam_state[1], torch.tensor(0.9), torch.tensor(0.999), lr)
     return new_center, fitness, grad, (m, v)
+
+
+def ars_step(center, z_plus, fitness_fn, lr, sigma, elite_pop_size, adam_state=None):
+    """ARS.step (es_variants/ars.py:62-98) with the normal draws passed in."""
+    half = z_plus.shape[0]
+    noise = torch.cat([z_plus, -1.0 * z_plus])
+    population = center + sigma * noise
+    fitness = fitness_fn(population)
+    fit_1, fit_2 = fitness[:half], fitness[half:]
+    elite_idx = torch.minimum(fit_1, fit_2).argsort()[:elite_pop_size]
+    fitness_elite = torch.cat([fit_1[elite_idx], fit_2[elite_idx]])
+    sigma_fitness = torch.std(fitness_elite) + 1e-05
+    fit_diff = fit_1[elite_idx] - fit_2[elite_idx]
+    fit_diff_noise = noise[:half][elite_idx].T @ fit_diff
+    theta_grad = 1.0 / (elite_pop_size * sigma_fitness) * fit_diff_noise
+    if adam_state is None:
+        return center - lr * theta_grad, theta_grad
+    new_center, m, v = adam_single_tensor(center, theta_grad, adam_state[0], adam_state[1], torch.tensor(0.9), torch.tensor(0.999), lr)
+    return new_center, theta_grad, (m, v)

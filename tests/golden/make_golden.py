@@ -306,8 +306,36 @@ def golden_cso(out: dict):
                     out[f"{tag}_s{g + 2}_{n}"] = _np(wf.algorithm.state_dict()[n])
 
 
+def golden_ars(out: dict):
+    """ARS.step (es_variants/ars.py:62-98) with the normal draws fixed, a shifted-sphere fitness, SGD and Adam,
+    two consecutive steps each (the second exercises the optimiser state)."""
+    from evox.algorithms import ARS
+
+    import evox.algorithms.so.es_variants.ars as amod
+
+    g = torch.Generator().manual_seed(2468)
+    shift = torch.randn(24, generator=g)
+    for opt in (None, "adam"):
+        center = torch.randn(24, generator=g)
+        algo = ARS(16, center.clone(), elite_ratio=0.5, lr=0.05, sigma=0.1, optimizer=opt)
+        algo.evaluate = lambda pop: ((pop - shift) ** 2).sum(dim=1)
+        tag = f"ars_{opt}"
+        out[f"{tag}_center0"], out[f"{tag}_shift"] = _np(center), _np(shift)
+        for k in range(2):
+            z = torch.randn(8, 24, generator=g)
+            real = amod.torch.randn
+            amod.torch.randn = lambda *a, **kw: z
+            try:
+                algo.step()
+            finally:
+                amod.torch.randn = real
+            out[f"{tag}_z{k}"], out[f"{tag}_center{k + 1}"] = _np(z), _np(algo.center)
+        if opt:
+            out[f"{tag}_exp_avg"], out[f"{tag}_exp_avg_sq"] = _np(algo.exp_avg), _np(algo.exp_avg_sq)
+
+
 GENERATORS = {"pso": golden_pso, "nds": golden_nds, "rvea": golden_rvea, "es": golden_es, "variation": golden_variation,
-              "cso": golden_cso}
+              "cso": golden_cso, "ars": golden_ars}
 
 
 def main():

@@ -128,6 +128,36 @@ def test_open_es_step_golden(golden, cuda, opt):
     wf.step()  # default path draws its own noise
 
 
+@pytest.mark.parametrize("opt", [None, "adam"])
+def test_ars_steps_golden(golden, cuda, opt):
+    """ARS on the OpenES kernels: two teacher-forced generations against the reference's centres; then a
+    run with its own draws on a larger problem must reduce the fitness of the centre."""
+    from evox_b200.algorithms import ARS
+    from evox_b200.core import Problem
+    from evox_b200.workflows import StdWorkflow
+
+    g = golden("ars")
+    tag = f"ars_{opt}"
+    shift = t(g[f"{tag}_shift"]).to(cuda)
+
+    class ShiftedSphere(Problem):
+        def evaluate(self, pop):
+            return ((pop - shift) ** 2).sum(dim=1)
+
+    algo = ARS(16, t(g[f"{tag}_center0"]), elite_ratio=0.5, lr=0.05, sigma=0.1, optimizer=opt, device=cuda)
+    wf = StdWorkflow(algo, ShiftedSphere(), device=cuda)
+    for k in range(2):
+        wf.algorithm.step(z_plus=t(g[f"{tag}_z{k}"]))
+        close(wf.algorithm.center, t(g[f"{tag}_center{k + 1}"]))
+    if opt:
+        close(wf.algorithm.exp_avg, t(g[f"{tag}_exp_avg"]))
+        close(wf.algorithm.exp_avg_sq, t(g[f"{tag}_exp_avg_sq"]))
+    before = float(((wf.algorithm.center - shift) ** 2).sum())
+    for _ in range(200):
+        wf.step()
+    assert float(((wf.algorithm.center - shift) ** 2).sum()) < 0.5 * before
+
+
 def make_mlp(sizes, bias, gen):
     layers = []
     for i in range(len(sizes) - 1):
