@@ -344,7 +344,7 @@ def run_ours(args):
 
 def run_nds(args):
     """Secondary workload: non-dominated rank / full environmental selection on DTLZ2-shaped
-    objectives (BASELINE configs[1] at 2N = 20,000 and the metric's 2N = 100,000)."""
+    objectives (benchmark configuration 1 at 2N = 20,000 and the metric's 2N = 100,000)."""
     from evox_b200.operators.selection import nd_environmental_selection, non_dominate_rank
     from oracle import nds as onds
 
@@ -386,7 +386,7 @@ def run_nds(args):
 
 
 def run_rvea(args):
-    """Secondary workload: RVEA selection at BASELINE configs[2] (50,000 x 10 objectives, 275 vectors)
+    """Secondary workload: RVEA selection at benchmark configuration 2 (50,000 x 10 objectives, 275 vectors)
     and at 5,000,000 rows, where the pass is long enough for its HBM rate to show."""
     from evox_b200.operators.selection import ref_vec_guided
     from oracle import rvea as orvea
@@ -463,7 +463,7 @@ def run_cso(args):
 
 
 def run_lora_es(args):
-    """Secondary workload: BASELINE configs[3] — VirtualLoRAES over a 3 x (4096 -> 4096) bf16 MLP,
+    """Secondary workload: benchmark configuration 3 — VirtualLoRAES over a 3 x (4096 -> 4096) bf16 MLP,
     1,024 individuals with their own 64 x 4096 batch, rank-8 factors, sigma 0.02, lr 0.01, centred
     ranks, SGD. One step = seeds -> forward (tensor cores) -> fitness -> gradient -> centre update,
     through StdWorkflow.step()."""

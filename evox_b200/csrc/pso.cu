@@ -14,7 +14,6 @@
 // HBM traffic per particle-dimension: 12 B read (pop, velocity, personal best) + 8 B written
 // (pop, velocity), + 8 B read when rg / rp are supplied as tensors instead of Philox.
 #include <math.h>
-#include <stdlib.h>
 
 #include "common.cuh"
 #include "fitness.cuh"
@@ -110,7 +109,7 @@ __device__ __forceinline__ float move_one(float x, float& v, float pb, float gb,
   return relu_clamp(xn, lb, ub);
 }
 
-template <int VEC, bool PHILOX, int FIT, int TUNE = 0>
+template <int VEC, bool PHILOX, int FIT>
 __global__ void __launch_bounds__(kThreads, MOVE_BLOCKS_PER_SM) pso_move_eval_kernel(const MoveArgs a) {
   const int lane = threadIdx.x & 31;
   const long long warp0 = (long long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
@@ -142,7 +141,6 @@ __global__ void __launch_bounds__(kThreads, MOVE_BLOCKS_PER_SM) pso_move_eval_ke
       // Plain loop: with four blocks of eight warps per SM the other warps cover a chunk's load latency; a
       // register double buffer (next chunk's loads issued ahead) measured 4 % slower here, and three blocks
       // per SM 15 % slower.
-#pragma unroll TUNE == 1 ? 2 : 1
       for (int c = lane; c < n_call; c += 32) {
         const float4 x = __ldcs(pop4 + c);
         float4 v = __ldcs(vel4 + c);
@@ -397,8 +395,7 @@ template <int VEC, bool PHILOX>
 void launch_move(int fitness_id, int grid, cudaStream_t s, const MoveArgs& a) {
   switch (fitness_id) {
     case EVOX_FIT_ACKLEY:
-      if (getenv("EVOX_TUNE")) pso_move_eval_kernel<VEC, PHILOX, EVOX_FIT_ACKLEY, 1><<<grid, kThreads, 0, s>>>(a);
-      else pso_move_eval_kernel<VEC, PHILOX, EVOX_FIT_ACKLEY><<<grid, kThreads, 0, s>>>(a);
+      pso_move_eval_kernel<VEC, PHILOX, EVOX_FIT_ACKLEY><<<grid, kThreads, 0, s>>>(a);
       break;
     case EVOX_FIT_RASTRIGIN:
       pso_move_eval_kernel<VEC, PHILOX, EVOX_FIT_RASTRIGIN><<<grid, kThreads, 0, s>>>(a);

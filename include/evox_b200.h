@@ -142,6 +142,29 @@ int evox_cso_step(float* pop, float* velocity, int32_t store_velocity, float* fi
                   void* workspace, size_t workspace_bytes, int32_t* next_center_ready, void* stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Comprehensive-learning PSO (algorithms/so/pso_variants/clpso.py).
+ * ------------------------------------------------------------------------------------------ */
+
+/* Personal-best update of CLPSO.step (clpso.py:101-103): rows with personal_best_fit > fit copy
+ * pop -> personal_best_location and fit -> personal_best_fit, in place. Must complete before
+ * evox_clpso_move_eval, which reads OTHER particles' updated personal bests. */
+int evox_clpso_update_pbest(const float* pop, const float* fit, float* personal_best_location,
+                            float* personal_best_fit, int64_t pop_size, int32_t dim, void* stream);
+
+/* Move of CLPSO.step (clpso.py:110-123) fused with the evaluation: for particle i,
+ *   v' = w * v + c * r * (personal_best_location[source_rows[i]] - x),
+ * velocity = clamp(v', lb, ub), pop = clamp(x + v', lb, ub) (relu-form clamp), fit = f(pop).
+ * source_rows (pop_size, int64) is i itself or the exemplar chosen by clpso.py:95-99 and :110-115
+ * (host-side bookkeeping on pop_size scalars). w, c: DEVICE scalars. r: (pop_size x dim) uniform
+ * draws (clpso.py:92) or NULL for Philox4x32-10 with key = seed, counter = (row, column / 4,
+ * generation). fitness_id = -1 skips the evaluation. pop, velocity (and fit) are updated in place. */
+int evox_clpso_move_eval(float* pop, float* velocity, const float* personal_best_location, float* fit,
+                         const int64_t* source_rows, const float* lb, const float* ub, const float* w,
+                         const float* c, const float* r, int64_t pop_size, int32_t dim,
+                         int32_t fitness_id, const float* params, uint64_t seed, uint64_t generation,
+                         void* stream);
+
+/* ------------------------------------------------------------------------------------------
  * P2. NSGA-II environmental selection.
  * ------------------------------------------------------------------------------------------ */
 

@@ -71,7 +71,7 @@ def two_layer_vectors(h1: int, h2: int, m: int) -> torch.Tensor:
 
 
 def config2_inputs(n: int = 50_000, m: int = 10, dx: int = 19, seed: int = 0):
-    """BASELINE configs[2]: objectives uniform in [0,1] + 0.05 |N(0,1)|, 275 simplex-lattice vectors."""
+    """benchmark configuration 2: objectives uniform in [0,1] + 0.05 |N(0,1)|, 275 simplex-lattice vectors."""
     g = torch.Generator().manual_seed(seed)
     f = torch.rand(n, m, generator=g) + 0.05 * torch.randn(n, m, generator=g).abs()
     x = torch.rand(n, dx, generator=g)

@@ -1,7 +1,7 @@
 """Generate the golden vectors under tests/golden/ by running the REFERENCE implementation.
 
 Run in a container that has the reference checkout:
-    python tests/golden/make_golden.py --reference /root/reference/src [--only pso,...]
+    python tests/golden/make_golden.py --reference <checkout>/src [--only pso,...]
 The reference is imported from that path, run in eager mode on CPU (torch's own CPU kernels),
 and its inputs / outputs are saved as small .npz files. The tests never import the reference;
 they only read these files. Random draws the reference takes from torch's global generator
@@ -334,13 +334,57 @@ def golden_ars(out: dict):
             out[f"{tag}_exp_avg"], out[f"{tag}_exp_avg_sq"] = _np(algo.exp_avg), _np(algo.exp_avg_sq)
 
 
+def golden_clpso(out: dict):
+    """CLPSO.init_step + 3 teacher-forced steps (the four draws of clpso.py:92-95 recorded) on Ackley and
+    Sphere, dims 12 and 10, 37 particles, learning probability 0.3; all state after every step."""
+    from evox.algorithms import CLPSO
+    from evox.problems.numerical import Ackley, Sphere
+    from evox.workflows import StdWorkflow
+
+    import evox.algorithms.so.pso_variants.clpso as cmod
+
+    names = ["pop", "fit", "velocity", "personal_best_location", "personal_best_fit", "global_best_location", "global_best_fit"]
+    for prob_name, prob_cls, lo, hi in (("ackley", Ackley, -32.768, 32.768), ("sphere", Sphere, -5.0, 7.0)):
+        for dim in (12, 10):
+            pop_size = 37
+            torch.manual_seed(999 + dim)
+            algo = CLPSO(pop_size, torch.full((dim,), lo), torch.full((dim,), hi), 0.5, 1.5, 0.3)
+            algo.velocity = 0.2 * algo.velocity
+            wf = StdWorkflow(algo, prob_cls())
+            tag = f"clpso_{prob_name}_d{dim}"
+            out[f"{tag}_bounds"] = np.asarray([lo, hi], dtype=np.float32)
+            for n in names:
+                out[f"{tag}_s0_{n}"] = _np(wf.algorithm.state_dict()[n])
+            wf.init_step()
+            for n in names:
+                out[f"{tag}_s1_{n}"] = _np(wf.algorithm.state_dict()[n])
+            gen = torch.Generator().manual_seed(55 + dim)
+            for g in range(3):
+                coeff = torch.rand(pop_size, dim, generator=gen)
+                i1 = torch.randint(0, pop_size, (pop_size,), generator=gen)
+                i2 = torch.randint(0, pop_size, (pop_size,), generator=gen)
+                poss = torch.rand(pop_size, generator=gen)
+                rq, iq = [coeff, poss], [i1, i2]
+                real_rand, real_randint = torch.rand, torch.randint
+                cmod.torch.rand = lambda *a, **k: rq.pop(0)
+                cmod.torch.randint = lambda *a, **k: iq.pop(0)
+                try:
+                    wf.step()
+                finally:
+                    cmod.torch.rand, cmod.torch.randint = real_rand, real_randint
+                assert not rq and not iq
+                out[f"{tag}_g{g}_coeff"], out[f"{tag}_g{g}_i1"], out[f"{tag}_g{g}_i2"], out[f"{tag}_g{g}_poss"] = _np(coeff), _np(i1), _np(i2), _np(poss)
+                for n in names:
+                    out[f"{tag}_s{g + 2}_{n}"] = _np(wf.algorithm.state_dict()[n])
+
+
 GENERATORS = {"pso": golden_pso, "nds": golden_nds, "rvea": golden_rvea, "es": golden_es, "variation": golden_variation,
-              "cso": golden_cso, "ars": golden_ars}
+              "cso": golden_cso, "ars": golden_ars, "clpso": golden_clpso}
 
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference/src")
+    ap.add_argument("--reference", required=True, help="the src/ directory of an EMI-Group/evox checkout")
     ap.add_argument("--only", default="")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)

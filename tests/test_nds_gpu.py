@@ -105,7 +105,7 @@ def test_crowding_all_rows_and_large_front(cuda):
 
 
 def test_config1_full_size(cuda):
-    """BASELINE configs[1]: 2N = 20,000 DTLZ2-shaped rows (12 variables, 3 objectives) -> N = 10,000."""
+    """benchmark configuration 1: 2N = 20,000 DTLZ2-shaped rows (12 variables, 3 objectives) -> N = 10,000."""
     from evox_b200.operators.selection import nd_environmental_selection, non_dominate_rank
 
     n, topk = 20_000, 10_000

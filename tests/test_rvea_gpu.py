@@ -78,7 +78,7 @@ def test_vs_oracle(cuda, n, m, nv_h):
 
 
 def test_config2_full_size(cuda):
-    """BASELINE configs[2]: 50,000 x 10 objectives, 275 vectors, theta = 0.25."""
+    """benchmark configuration 2: 50,000 x 10 objectives, 275 vectors, theta = 0.25."""
     from evox_b200.operators.selection import ref_vec_guided
 
     x, f, v, theta = rvea.config2_inputs()
