@@ -167,6 +167,81 @@ class ARS(Algorithm):
         return {"center": self.center}
 
 
+class PersistentES(Algorithm):
+    """Persistent evolution strategies (persistent_es.py:9-115): mirrored perturbations are accumulated
+    over the inner steps of an unrolled problem and the gradient estimate uses the ACCUMULATED
+    perturbations. One kernel forms the population and adds the perturbations to `pert_accum`; the
+    weighted row sum and the centre update are the OpenES kernels. As in the reference, the stored
+    `inner_step_counter` is never reset (only a local copy is, persistent_es.py:100-105): once it has
+    reached T the accumulator is cleared after every step."""
+
+    def __init__(
+        self,
+        pop_size: int,
+        center_init: torch.Tensor,
+        optimizer: Literal["adam"] | None = None,
+        lr: float = 0.05,
+        sigma: float = 0.03,
+        T: int = 100,
+        K: int = 10,
+        sigma_decay: float = 1.0,
+        sigma_limit: float = 0.01,
+        device: torch.device | None = None,
+    ):
+        super().__init__()
+        device = torch.get_default_device() if device is None else torch.device(device)
+        assert pop_size > 1 and pop_size % 2 == 0
+        assert optimizer in [None, "adam"]
+        self.lr = Parameter(lr, dtype=torch.float32, device=device)
+        self.T = Parameter(T, device=device)
+        self.K = Parameter(K, device=device)
+        self.sigma_decay = Parameter(sigma_decay, dtype=torch.float32, device=device)
+        self.sigma_limit = Parameter(sigma_limit, dtype=torch.float32, device=device)
+        self.dim = center_init.shape[0]
+        self.pop_size = pop_size
+        self.optimizer = optimizer
+        self.sigma = Mutable(torch.tensor(sigma, dtype=torch.float32, device=device))
+        self.center = Mutable(center_init.to(device=device, dtype=torch.float32).contiguous().clone())
+        self.inner_step_counter = Mutable(torch.tensor(0.0, device=device))
+        self.pert_accum = Mutable(torch.zeros(pop_size, self.dim, device=device))
+        if optimizer == "adam":
+            self.exp_avg = Mutable(torch.zeros_like(self.center))
+            self.exp_avg_sq = Mutable(torch.zeros_like(self.center))
+            self.beta1 = Parameter(0.9, dtype=torch.float32, device=device)
+            self.beta2 = Parameter(0.999, dtype=torch.float32, device=device)
+
+    def step(self, z: torch.Tensor | None = None):
+        """One generation (persistent_es.py:74-112). `z`: optional (pop_size / 2, dim) standard-normal draws."""
+        dev = self.center.device
+        half = self.pop_size // 2
+        if z is None:
+            z = torch.randn(half, self.dim, device=dev)
+        z = z.to(device=dev, dtype=torch.float32).contiguous()
+        assert z.shape == (half, self.dim)
+        if not self.pert_accum.is_contiguous():
+            self.pert_accum = self.pert_accum.contiguous()
+        lib, s = _cabi.lib, _cabi.stream_ptr(dev)
+        pop = torch.empty(self.pop_size, self.dim, dtype=torch.float32, device=dev)
+        _cabi.check(lib.evox_pes_ask(_cabi.ptr(self.center), _cabi.ptr(z), _cabi.ptr(self.sigma, torch.float32, "sigma"), self.pop_size,
+                                     self.dim, _cabi.ptr(self.pert_accum, torch.float32, "pert_accum"), _cabi.ptr(pop), s))
+        fitness = self.evaluate(pop).to(torch.float32).contiguous()
+        # mean over the population of pert_accum * fitness / sigma^2: the division rides on the weights, which
+        # keeps sigma on the device (it decays every generation)
+        weights = fitness / (self.sigma**2)
+        grad = torch.empty(self.dim, dtype=torch.float32, device=dev)
+        _cabi.check(lib.evox_openes_gradient(_cabi.ptr(self.pert_accum), _cabi.ptr(weights), self.pop_size, self.dim, self.pop_size, 1.0,
+                                             _cabi.ptr(grad), s))
+        _update_center(self, grad, lr=self.lr)
+        self.inner_step_counter = self.inner_step_counter + self.K
+        # scalar bookkeeping on the device, no host synchronisation: clear the accumulator when the counter
+        # has reached T (an in-place masked fill with a 0-d mask)
+        self.pert_accum.masked_fill_(self.inner_step_counter >= self.T, 0.0)
+        self.sigma = torch.maximum(self.sigma_decay * self.sigma, self.sigma_limit)
+
+    def record_step(self):
+        return {"center": self.center, "sigma": self.sigma}
+
+
 class VirtualLoRAES(_ESBase):
     """ES over a virtual population: only the centre and one int64 seed per individual exist;
     perturbations are rank-r factors regenerated from the seeds."""

@@ -162,17 +162,20 @@ __global__ void __launch_bounds__(kThreads)
   }
 }
 
-// pop[i][l] = center[l] + sigma * (+-) noise[i mod rows][l]   (open_es.py:64-68)
+// pop[i][l] = center[l] + sigma * (+-) noise[i mod rows][l]   (open_es.py:64-68); with `accum` the same
+// perturbation is also added to accum[i][l] (PersistentES, persistent_es.py:76-80).
 __global__ void __launch_bounds__(kThreads)
     openes_ask_kernel(const float* __restrict__ center, const float* __restrict__ noise, const float* __restrict__ sigma_p,
-                      long long pop, long long n, long long noise_rows, float* __restrict__ out) {
+                      long long pop, long long n, long long noise_rows, float* __restrict__ out, float* __restrict__ accum) {
   const float sigma = *sigma_p;
   const long long total = pop * n;
   for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (long long)gridDim.x * blockDim.x) {
     const long long i = e / n, l = e - i * n;
     const bool mirrored = i >= noise_rows;
     const float z = noise[(mirrored ? i - noise_rows : i) * n + l];
-    out[e] = __fadd_rn(center[l], __fmul_rn(sigma, mirrored ? -z : z));
+    const float pert = __fmul_rn(sigma, mirrored ? -z : z);
+    out[e] = __fadd_rn(center[l], pert);
+    if (accum != nullptr) accum[e] = __fadd_rn(accum[e], pert);
   }
 }
 
@@ -360,7 +363,17 @@ extern "C" int evox_openes_ask(const float* center, const float* noise, const fl
   EVOX_REQUIRE(pop > 0 && dim > 0 && (noise_rows == pop || 2 * noise_rows == pop), EVOX_ERR_INVALID,
                "openes_ask: noise_rows must be pop or pop / 2");
   openes_ask_kernel<<<grid_for(pop * dim), kThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(center, noise, sigma, pop,
-                                                                                               dim, noise_rows, population);
+                                                                                               dim, noise_rows, population, nullptr);
+  EVOX_LAUNCH_CHECK();
+  return EVOX_OK;
+}
+
+extern "C" int evox_pes_ask(const float* center, const float* noise, const float* sigma, int64_t pop, int64_t dim,
+                            float* pert_accum, float* population, void* stream) {
+  EVOX_REQUIRE(center && noise && sigma && pert_accum && population, EVOX_ERR_INVALID, "pes_ask: NULL pointer");
+  EVOX_REQUIRE(pop > 0 && dim > 0 && pop % 2 == 0, EVOX_ERR_INVALID, "pes_ask: pop must be positive and even");
+  openes_ask_kernel<<<grid_for(pop * dim), kThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(center, noise, sigma, pop, dim,
+                                                                                               pop / 2, population, pert_accum);
   EVOX_LAUNCH_CHECK();
   return EVOX_OK;
 }

@@ -96,3 +96,34 @@ def lora_gradient(fitness: torch.Tensor, A: torch.Tensor, B: torch.Tensor, pop_s
 @lora_gradient.register_fake
 def _(fitness, A, B, pop_size, sigma):
     return A.new_empty(B.shape[1], A.shape[2], dtype=torch.float32)
+
+
+# ---------------------------------------------------------------------------------------------
+# vmap rules: the reference's programming model maps whole workflows over a batch dimension
+# (evox/utils/op_register.py:54-132 asks every custom op for a `vmap_fn`). A batched call runs the
+# kernel once per slice — the kernels take one problem instance — and stacks the results on dim 0.
+# ---------------------------------------------------------------------------------------------
+def _slices(batch: int, args, in_dims):
+    """Per-slice argument tuples; unbatched arguments (in_dim None) are passed to every slice as they are."""
+    moved = [a if d is None else a.movedim(d, 0) for a, d in zip(args, in_dims)]
+    return [tuple(m if d is None else m[i] for m, d in zip(moved, in_dims)) for i in range(batch)]
+
+
+def _register_loop_vmap(op, n_out: int):
+    def rule(info, in_dims, *args):
+        outs = [op(*one) for one in _slices(info.batch_size, args, in_dims)]
+        if n_out == 1:
+            return torch.stack(outs), 0
+        return tuple(torch.stack([o[k] for o in outs]) for k in range(n_out)), tuple(0 for _ in range(n_out))
+
+    torch.library.register_vmap(op, rule)
+
+
+_register_loop_vmap(nd_rank, 1)
+_register_loop_vmap(crowding_distance, 1)
+_register_loop_vmap(nd_environmental_selection, 4)
+_register_loop_vmap(ref_vec_guided, 2)
+_register_loop_vmap(philox_uniform, 1)
+_register_loop_vmap(philox_normal, 1)
+_register_loop_vmap(lora_delta_output, 1)
+_register_loop_vmap(lora_gradient, 1)

@@ -306,6 +306,12 @@ int evox_lora_linear_forward(const float* h, int32_t h_is_shared, const float* W
 int evox_openes_ask(const float* center, const float* noise, const float* sigma, int64_t pop,
                     int64_t dim, int64_t noise_rows, float* population, void* stream);
 
+/* PersistentES.step, first half (algorithms/so/es_variants/persistent_es.py:76-80): with
+ * perts = +-sigma * noise (noise: pop / 2 rows, mirrored), population = center + perts and
+ * pert_accum (pop x dim) += perts, in one pass. sigma: device scalar. */
+int evox_pes_ask(const float* center, const float* noise, const float* sigma, int64_t pop, int64_t dim,
+                 float* pert_accum, float* population, void* stream);
+
 /* grad (dim) = noise^T fitness / pop / sigma (open_es.py:70), same mirrored convention. */
 int evox_openes_gradient(const float* noise, const float* fitness, int64_t pop, int64_t dim,
                          int64_t noise_rows, float sigma, float* grad, void* stream);

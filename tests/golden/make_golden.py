@@ -378,8 +378,36 @@ def golden_clpso(out: dict):
                     out[f"{tag}_s{g + 2}_{n}"] = _np(wf.algorithm.state_dict()[n])
 
 
+def golden_pes(out: dict):
+    """PersistentES.step (es_variants/persistent_es.py:74-112) with the normal draws fixed: four steps with
+    T = 3 K (the accumulator resets after the third), sigma decay 0.9, SGD and Adam."""
+    from evox.algorithms import PersistentES
+
+    import evox.algorithms.so.es_variants.persistent_es as pmod
+
+    g = torch.Generator().manual_seed(1357)
+    shift = torch.randn(20, generator=g)
+    for opt in (None, "adam"):
+        center = torch.randn(20, generator=g)
+        algo = PersistentES(12, center.clone(), optimizer=opt, lr=0.05, sigma=0.1, T=30, K=10, sigma_decay=0.9, sigma_limit=0.075)
+        algo.evaluate = lambda pop: ((pop - shift) ** 2).sum(dim=1)
+        tag = f"pes_{opt}"
+        out[f"{tag}_center0"], out[f"{tag}_shift"] = _np(center), _np(shift)
+        for k in range(4):
+            z = torch.randn(6, 20, generator=g)
+            real = pmod.torch.randn
+            pmod.torch.randn = lambda *a, **kw: z
+            try:
+                algo.step()
+            finally:
+                pmod.torch.randn = real
+            out[f"{tag}_z{k}"], out[f"{tag}_center{k + 1}"] = _np(z), _np(algo.center)
+            out[f"{tag}_accum{k + 1}"], out[f"{tag}_sigma{k + 1}"] = _np(algo.pert_accum), _np(algo.sigma)
+            out[f"{tag}_counter{k + 1}"] = _np(algo.inner_step_counter)
+
+
 GENERATORS = {"pso": golden_pso, "nds": golden_nds, "rvea": golden_rvea, "es": golden_es, "variation": golden_variation,
-              "cso": golden_cso, "ars": golden_ars, "clpso": golden_clpso}
+              "cso": golden_cso, "ars": golden_ars, "clpso": golden_clpso, "pes": golden_pes}
 
 
 def main():

@@ -158,6 +158,34 @@ def test_ars_steps_golden(golden, cuda, opt):
     assert float(((wf.algorithm.center - shift) ** 2).sum()) < 0.5 * before
 
 
+@pytest.mark.parametrize("opt", [None, "adam"])
+def test_persistent_es_steps_golden(golden, cuda, opt):
+    """PersistentES: four teacher-forced generations (accumulator, reset at T, decaying sigma) against the
+    reference's recorded centres, accumulators and sigmas."""
+    from evox_b200.algorithms import PersistentES
+    from evox_b200.core import Problem
+    from evox_b200.workflows import StdWorkflow
+
+    g = golden("pes")
+    tag = f"pes_{opt}"
+    shift = t(g[f"{tag}_shift"]).to(cuda)
+
+    class ShiftedSphere(Problem):
+        def evaluate(self, pop):
+            return ((pop - shift) ** 2).sum(dim=1)
+
+    algo = PersistentES(12, t(g[f"{tag}_center0"]), optimizer=opt, lr=0.05, sigma=0.1, T=30, K=10, sigma_decay=0.9, sigma_limit=0.075,
+                        device=cuda)
+    wf = StdWorkflow(algo, ShiftedSphere(), device=cuda)
+    for k in range(4):
+        wf.algorithm.step(z=t(g[f"{tag}_z{k}"]))
+        close(wf.algorithm.center, t(g[f"{tag}_center{k + 1}"]))
+        assert torch.equal(wf.algorithm.pert_accum.cpu(), t(g[f"{tag}_accum{k + 1}"]))
+        assert torch.equal(wf.algorithm.sigma.cpu(), t(g[f"{tag}_sigma{k + 1}"]))
+        assert float(wf.algorithm.inner_step_counter) == float(g[f"{tag}_counter{k + 1}"])
+    wf.step()  # default path draws its own noise
+
+
 def make_mlp(sizes, bias, gen):
     layers = []
     for i in range(len(sizes) - 1):

@@ -41,3 +41,29 @@ def test_ops_match_wrappers(cuda):
     seeds = torch.arange(7, dtype=torch.int64, device=cuda)
     assert torch.equal(torch.ops.evox_b200.philox_uniform(seeds, 10, 3), philox_uniform(seeds, 10, 3))
     torch.library.opcheck(torch.ops.evox_b200.nd_rank.default, (f,), test_utils=("test_schema", "test_faketensor"))
+
+
+@pytest.mark.gpu
+def test_ops_under_vmap(cuda):
+    """torch.vmap over a batch of independent problems: one kernel call per slice, results stacked."""
+    import evox_b200.ops  # noqa: F401
+    from evox_b200.operators.selection import non_dominate_rank, ref_vec_guided
+
+    g = torch.Generator().manual_seed(0)
+    f = torch.rand(4, 300, 3, generator=g).to(cuda)
+    ranks = torch.vmap(torch.ops.evox_b200.nd_rank)(f)
+    assert ranks.shape == (4, 300)
+    for i in range(4):
+        assert torch.equal(ranks[i], non_dominate_rank(f[i]))
+    # a batched and an unbatched argument together; several outputs
+    x = torch.rand(4, 300, 6, generator=g).to(cuda)
+    v = torch.rand(10, 3, generator=g).to(cuda)
+    theta = torch.tensor(0.3, device=cuda)
+    nx, nf = torch.vmap(torch.ops.evox_b200.ref_vec_guided, in_dims=(0, 0, None, None))(x, f, v, theta)
+    assert nx.shape == (4, 10, 6) and nf.shape == (4, 10, 3)
+    for i in range(4):
+        wx, wf = ref_vec_guided(x[i], f[i], v, theta)
+        assert torch.equal(torch.nan_to_num(nx[i]), torch.nan_to_num(wx)) and torch.equal(torch.nan_to_num(nf[i]), torch.nan_to_num(wf))
+    seeds = torch.arange(12, dtype=torch.int64, device=cuda).view(3, 4)
+    u = torch.vmap(lambda s: torch.ops.evox_b200.philox_uniform(s, 8, 2))(seeds)
+    assert u.shape == (3, 4, 8)

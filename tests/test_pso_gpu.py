@@ -293,3 +293,53 @@ def test_reference_state_dict_loads(golden, cuda):
     wf.algorithm.step(rg=rg, rp=rp)
     got = {k: v for k, v in wf.algorithm.state_dict().items() if isinstance(v, torch.Tensor)}
     compare_states(got, load_state(g, tag, 3), "ackley")
+
+
+def test_headline_size_properties(cuda):
+    """1,000,000 x 1,000 (the headline workload, 12 GB of state), checked through properties that do not
+    need the CPU oracle at that size: (a) every row's update depends only on that row, the global best and
+    its position in the random stream — four row blocks re-run as small swarms with `row_offset` must
+    reproduce the big run bit for bit; (b) the stored fitness is the fitness of the stored positions;
+    (c) positions stay inside the bounds; (d) the global best is the smallest fitness seen so far and
+    never gets worse."""
+    from evox_b200 import _cabi as c
+    from evox_b200.algorithms import PSO
+    from evox_b200.problems.numerical import Ackley
+    from evox_b200.workflows import StdWorkflow
+
+    free, _ = torch.cuda.mem_get_info(cuda)
+    if free < 40e9:
+        pytest.skip("needs about 30 GB of free device memory")
+    P, d = 1_000_000, 1000
+    torch.manual_seed(0)
+    algo = PSO(P, torch.full((d,), -32.768), torch.full((d,), 32.768), 0.6, 2.5, 0.8, device=cuda, seed=77)
+    algo.velocity.mul_(0.2)
+    prob = Ackley()
+    wf = StdWorkflow(algo, prob, device=cuda)
+    wf.init_step()
+    wf.step()
+    best_before = float(algo.global_best_fit)
+    blocks = [(0, 513), (123_456, 124_000), (500_000, 500_257), (P - 300, P)]
+    names = ("pop", "velocity", "local_best_location", "local_best_fit", "fit")
+    saved = [{n: getattr(algo, n)[a:b].clone() for n in names} for a, b in blocks]
+    gen = algo.generation
+    min_fit_before = float(algo.fit.min())
+    wf.step()
+    # the step first folded the best of the previous swarm into the global best, then moved
+    assert float(algo.global_best_fit) == min(best_before, min_fit_before)
+    gbest = algo.global_best_location
+    fid, params = prob.fused_fitness()
+    for (a, b), part in zip(blocks, saved):
+        c.check(c.lib.evox_pso_move_eval(
+            c.ptr(part["pop"]), c.ptr(part["velocity"]), c.ptr(part["local_best_location"]), c.ptr(part["local_best_fit"]),
+            c.ptr(part["fit"]), c.ptr(gbest), c.ptr(algo.lb), c.ptr(algo.ub), c.ptr(algo.w), c.ptr(algo.phi_p), c.ptr(algo.phi_g),
+            None, None, b - a, d, fid, c.host_floats(params), algo.seed, gen, a, c.stream_ptr(cuda)))
+        for n in names:
+            assert torch.equal(part[n], getattr(algo, n)[a:b]), (a, n)
+    # (b) re-evaluation of the stored positions, in slabs to bound memory
+    for a in range(0, P, 250_000):
+        again = prob.evaluate(algo.pop[a:a + 250_000])
+        assert torch.equal(again, algo.fit[a:a + 250_000])
+    # (c) bounds
+    assert float(algo.pop.min()) >= float(algo.lb.min()) and float(algo.pop.max()) <= float(algo.ub.max())
+    assert torch.isfinite(algo.fit).all()
