@@ -3,5 +3,6 @@ from .mo import NSGA2, RVEA
 from .clpso import CLPSO
 from .cso import CSO
 from .pso import PSO
+from .slpso import SLPSOGS, SLPSOUS
 
-__all__ = ["PSO", "CSO", "CLPSO", "OpenES", "ARS", "PersistentES", "VirtualLoRAES", "NSGA2", "RVEA"]
+__all__ = ["PSO", "CSO", "CLPSO", "SLPSOGS", "SLPSOUS", "OpenES", "ARS", "PersistentES", "VirtualLoRAES", "NSGA2", "RVEA"]

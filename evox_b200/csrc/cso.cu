@@ -16,6 +16,7 @@
 // That is 8 B per particle-dimension per generation; the separate column-sum pass (cso_colsum_kernel,
 // 4 B more) only runs for the first generation, for longer rows, or when the swarm was changed from
 // outside between two steps.
+#include "colmean.cuh"
 #include "common.cuh"
 #include "fitness.cuh"
 
@@ -26,7 +27,7 @@ constexpr int kWarpsPerBlock = 8;
 constexpr int kThreads = kWarpsPerBlock * 32;
 constexpr int kMaxChunks = 8;           // float4 chunks per lane whose column sums a warp keeps in shared memory
 constexpr int kMaxFusedDim = kMaxChunks * 32 * 4;
-constexpr int kBlocksPerSM = 4;
+constexpr int kBlocksPerSM = 4;  // = kColmeanBlocksPerSM: the partial rows are indexed by block
 
 struct CsoArgs {
   float* pop;
@@ -189,64 +190,6 @@ __global__ void __launch_bounds__(kThreads, kBlocksPerSM) cso_update_kernel(cons
   }
 }
 
-// Column sums of a (P, d) matrix: block (x = column tile, y = row group) sums its rows, warps folded in
-// warp order, into partial[blockIdx.y][column].
-template <int VEC>
-__global__ void __launch_bounds__(kThreads) cso_colsum_kernel(const float* __restrict__ pop, long long P, int d, float* __restrict__ partial) {
-  __shared__ float sh[kWarpsPerBlock][32 * VEC];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int col = (blockIdx.x * 32 + lane) * VEC;
-  float s[VEC];
-#pragma unroll
-  for (int j = 0; j < VEC; ++j) s[j] = 0.f;
-  if (col < d) {
-    for (long long row = (long long)blockIdx.y * kWarpsPerBlock + warp; row < P; row += (long long)gridDim.y * kWarpsPerBlock) {
-      if constexpr (VEC == 4) {
-        const float4 x = __ldg(reinterpret_cast<const float4*>(pop + (size_t)row * d + col));
-        s[0] += x.x;
-        s[1] += x.y;
-        s[2] += x.z;
-        s[3] += x.w;
-      } else {
-        s[0] += pop[(size_t)row * d + col];
-      }
-    }
-  }
-#pragma unroll
-  for (int j = 0; j < VEC; ++j) sh[warp][lane * VEC + j] = s[j];
-  __syncthreads();
-  if (warp == 0 && col < d) {
-#pragma unroll
-    for (int j = 0; j < VEC; ++j) {
-      float t = sh[0][lane * VEC + j];
-      for (int w = 1; w < kWarpsPerBlock; ++w) t += sh[w][lane * VEC + j];
-      partial[(size_t)blockIdx.y * d + col + j] = t;
-    }
-  }
-}
-
-// center[col] = (sum over the n_partial rows of partial[.][col], 32 interleaved running sums folded by a
-// fixed tree) / P   (torch.mean(pop, axis=0), cso.py:87).
-__global__ void __launch_bounds__(1024) cso_center_finish_kernel(const float* __restrict__ partial, int n_partial, int d, long long P,
-                                                                  float* __restrict__ center) {
-  __shared__ float sh[32][33];
-  const int col = blockIdx.x * 32 + threadIdx.x;
-  float s = 0.f;
-  if (col < d)
-    for (int b = threadIdx.y; b < n_partial; b += 32) s += partial[(size_t)b * d + col];
-  sh[threadIdx.y][threadIdx.x] = s;
-  __syncthreads();
-  for (int off = 16; off > 0; off >>= 1) {
-    if ((int)threadIdx.y < off) sh[threadIdx.y][threadIdx.x] += sh[threadIdx.y + off][threadIdx.x];
-    __syncthreads();
-  }
-  if (threadIdx.y == 0 && col < d) center[col] = sh[0][threadIdx.x] / (float)P;
-}
-
-// workspace: center [d padded to 4] | partial [max_partials][d]
-long long padded_dim(int d) { return ((long long)d + 3) / 4 * 4; }
-int max_partials() { return sm_count() * kBlocksPerSM; }
-
 template <int VEC, bool PHILOX, bool SUMS>
 void launch_update(int fitness_id, int grid, cudaStream_t s, const CsoArgs& a) {
   switch (fitness_id) {
@@ -260,25 +203,6 @@ void launch_update(int fitness_id, int grid, cudaStream_t s, const CsoArgs& a) {
       cso_update_kernel<VEC, PHILOX, EVOX_FIT_SPHERE, SUMS><<<grid, kThreads, 0, s>>>(a);
       break;
   }
-}
-
-int run_colsum(const float* pop, long long P, int d, float* center, float* partial, cudaStream_t s) {
-  const bool vec = (d % 4 == 0) && aligned16(pop);
-  const int tile = vec ? 128 : 32;
-  const int gx = (d + tile - 1) / tile;
-  int gy = (max_partials() + gx - 1) / gx;
-  const long long row_groups = (P + kWarpsPerBlock - 1) / kWarpsPerBlock;
-  if (gy > row_groups) gy = (int)row_groups;
-  if (gy > max_partials()) gy = max_partials();
-  if (gy < 1) gy = 1;
-  if (vec)
-    cso_colsum_kernel<4><<<dim3(gx, gy), kThreads, 0, s>>>(pop, P, d, partial);
-  else
-    cso_colsum_kernel<1><<<dim3(gx, gy), kThreads, 0, s>>>(pop, P, d, partial);
-  EVOX_LAUNCH_CHECK();
-  cso_center_finish_kernel<<<(d + 31) / 32, dim3(32, 32), 0, s>>>(partial, gy, d, P, center);
-  EVOX_LAUNCH_CHECK();
-  return EVOX_OK;
 }
 
 }  // namespace
@@ -307,7 +231,7 @@ extern "C" int evox_cso_step(float* pop, float* velocity, int32_t store_velocity
   float* center = reinterpret_cast<float*>(workspace);
   float* partial = center + padded_dim(dim);
   if (!center_ready) {
-    if (int rc = run_colsum(pop, pop_size, dim, center, partial, s)) return rc;
+    if (int rc = run_colmean(pop, pop_size, dim, center, partial, s)) return rc;
   }
   CsoArgs a;
   a.pop = pop;
@@ -348,7 +272,7 @@ extern "C" int evox_cso_step(float* pop, float* velocity, int32_t store_velocity
   }
   EVOX_LAUNCH_CHECK();
   if (sums) {
-    cso_center_finish_kernel<<<(dim + 31) / 32, dim3(32, 32), 0, s>>>(partial, grid, dim, pop_size, center);
+    colmean_finish_kernel<<<(dim + 31) / 32, dim3(32, 32), 0, s>>>(partial, grid, dim, pop_size, center);
     EVOX_LAUNCH_CHECK();
   }
   if (next_center_ready) *next_center_ready = sums ? 1 : 0;

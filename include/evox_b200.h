@@ -165,6 +165,30 @@ int evox_clpso_move_eval(float* pop, float* velocity, const float* personal_best
                          void* stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Social-learning PSO (algorithms/so/pso_variants/sl_pso_gs.py, sl_pso_us.py).
+ * ------------------------------------------------------------------------------------------ */
+
+/* Bytes of scratch evox_slpso_step needs (the swarm's mean position and per-block column sums). */
+size_t evox_slpso_workspace_bytes(int64_t pop_size, int32_t dim);
+
+/* Update of SLPSOGS.step / SLPSOUS.step (sl_pso_gs.py:90-104, sl_pso_us.py:95-110) fused with the
+ * evaluation. For particle i with demonstrator row k = demonstrator_rows[i] (a row of the swarm
+ * BEFORE this generation, chosen by the caller as the reference does, sl_pso_gs.py:80-89):
+ *   v' = r1 * v + r2 * (pop[k] - pop[i]) + (r3 * social_influence_factor) * (mean(pop) - pop[i]),
+ *   pop_new[i] = clamp(pop[i] + v', lb, ub), velocity[i] = clamp(v', lb, ub), fit[i] = f(pop_new[i]).
+ * pop is only read; pop_new must be a different buffer (swap the two afterwards). r1, r2, r3 are
+ * the three (pop_size x dim) uniform draws or all NULL (Philox4x32-10, key = seed, counter = (row,
+ * column / 4, generation, which)). social_influence_factor: DEVICE scalar. fitness_id = -1 skips
+ * the evaluation. center_ready / next_center_ready as in evox_cso_step: when set on return, the
+ * workspace holds mean(pop_new). */
+int evox_slpso_step(const float* pop, float* pop_new, float* velocity, float* fit,
+                    const int64_t* demonstrator_rows, const float* lb, const float* ub,
+                    const float* social_influence_factor, const float* r1, const float* r2,
+                    const float* r3, int64_t pop_size, int32_t dim, int32_t fitness_id,
+                    const float* params, uint64_t seed, uint64_t generation, int32_t center_ready,
+                    void* workspace, size_t workspace_bytes, int32_t* next_center_ready, void* stream);
+
+/* ------------------------------------------------------------------------------------------
  * P2. NSGA-II environmental selection.
  * ------------------------------------------------------------------------------------------ */
 

@@ -406,8 +406,55 @@ def golden_pes(out: dict):
             out[f"{tag}_counter{k + 1}"] = _np(algo.inner_step_counter)
 
 
+def golden_slpso(out: dict):
+    """SLPSOGS / SLPSOUS: init_step + 3 teacher-forced steps (the demonstrator draw and r1, r2, r3 recorded)
+    on Ackley, dims 12 and 10, 33 particles; all state after every step."""
+    from evox.algorithms import SLPSOGS, SLPSOUS
+    from evox.problems.numerical import Ackley
+    from evox.workflows import StdWorkflow
+
+    import evox.algorithms.so.pso_variants.sl_pso_gs as gmod
+    import evox.algorithms.so.pso_variants.sl_pso_us as umod
+
+    names = ["pop", "fit", "velocity", "global_best_location", "global_best_fit"]
+    for kind, cls, mod in (("gs", SLPSOGS, gmod), ("us", SLPSOUS, umod)):
+        for dim in (12, 10):
+            pop_size, lo, hi = 33, -32.768, 32.768
+            torch.manual_seed(31 + dim)
+            algo = cls(pop_size, torch.full((dim,), lo), torch.full((dim,), hi), 0.2, 0.7)
+            algo.velocity = 0.2 * algo.velocity
+            wf = StdWorkflow(algo, Ackley())
+            tag = f"slpso_{kind}_d{dim}"
+            out[f"{tag}_bounds"] = np.asarray([lo, hi], dtype=np.float32)
+            for n in names:
+                out[f"{tag}_s0_{n}"] = _np(wf.algorithm.state_dict()[n])
+            wf.init_step()
+            for n in names:
+                out[f"{tag}_s1_{n}"] = _np(wf.algorithm.state_dict()[n])
+            gen = torch.Generator().manual_seed(17 + dim)
+            for g in range(3):
+                pick = torch.randn(pop_size, generator=gen) if kind == "gs" else torch.rand(pop_size, generator=gen)
+                rs = [torch.rand(pop_size, dim, generator=gen) for _ in range(3)]
+                # sl_pso_gs.py draws randn (demonstrator) then three rand; sl_pso_us.py draws rand (demonstrator) then three
+                nq = [pick] if kind == "gs" else []
+                uq = list(rs) if kind == "gs" else [pick] + list(rs)
+                real_rand, real_randn = torch.rand, torch.randn
+                mod.torch.rand = lambda *a, **k: uq.pop(0)
+                mod.torch.randn = lambda *a, **k: nq.pop(0)
+                try:
+                    wf.step()
+                finally:
+                    mod.torch.rand, mod.torch.randn = real_rand, real_randn
+                assert not nq and not uq
+                out[f"{tag}_g{g}_pick"] = _np(pick)
+                for j in range(3):
+                    out[f"{tag}_g{g}_r{j + 1}"] = _np(rs[j])
+                for n in names:
+                    out[f"{tag}_s{g + 2}_{n}"] = _np(wf.algorithm.state_dict()[n])
+
+
 GENERATORS = {"pso": golden_pso, "nds": golden_nds, "rvea": golden_rvea, "es": golden_es, "variation": golden_variation,
-              "cso": golden_cso, "ars": golden_ars, "clpso": golden_clpso, "pes": golden_pes}
+              "cso": golden_cso, "ars": golden_ars, "clpso": golden_clpso, "pes": golden_pes, "slpso": golden_slpso}
 
 
 def main():

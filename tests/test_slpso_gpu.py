@@ -1,0 +1,104 @@
+"""SL-PSO kernel against the reference's golden vectors and the oracle (teacher-forced draws)."""
+
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import pso as opso
+from oracle import slpso as oslpso
+
+pytestmark = pytest.mark.gpu
+GOLD = np.load(Path(__file__).parent / "golden" / "slpso.npz")
+NAMES = ["pop", "fit", "velocity", "global_best_location", "global_best_fit"]
+RTOL = 1e-5
+
+
+def close(a, b, scale=None):
+    a, b = a.detach().cpu().double(), torch.as_tensor(b).double()
+    s = b.abs().max() if scale is None else scale
+    return float((a - b).abs().max()) <= RTOL * float(max(s, 1e-30))
+
+
+@pytest.mark.parametrize("kind", ["gs", "us"])
+@pytest.mark.parametrize("dim", [12, 10])
+@pytest.mark.parametrize("fused", [True, False])
+def test_teacher_forced_generations_match_reference(cuda, kind, dim, fused):
+    from evox_b200.algorithms import SLPSOGS, SLPSOUS
+    from evox_b200.problems.numerical import Ackley
+    from evox_b200.workflows import StdWorkflow
+
+    tag = f"slpso_{kind}_d{dim}"
+    lo, hi = GOLD[f"{tag}_bounds"]
+    cls = SLPSOGS if kind == "gs" else SLPSOUS
+    algo = cls(33, torch.full((dim,), float(lo)), torch.full((dim,), float(hi)), 0.2, 0.7, device=cuda, seed=3)
+    for n in NAMES:
+        getattr(algo, n).copy_(torch.from_numpy(GOLD[f"{tag}_s0_{n}"]))
+    kw = {} if fused else {"fitness_transform": torch.nn.Identity()}
+    wf = StdWorkflow(algo, Ackley(), device=cuda, **kw)
+    wf.init_step()
+    for g in range(-1, 3):
+        if g >= 0:
+            # the demonstrator choice sorts the fitness: use the reference's values so that near-ties cannot reorder it
+            wf.algorithm.fit.copy_(torch.from_numpy(GOLD[f"{tag}_s{g + 1}_fit"]))
+            wf.algorithm.step(torch.from_numpy(GOLD[f"{tag}_g{g}_pick"]), *[torch.from_numpy(GOLD[f"{tag}_g{g}_r{j}"]) for j in (1, 2, 3)])
+        for n in NAMES:
+            want = GOLD[f"{tag}_s{g + 2}_{n}"]
+            scale = float(hi - lo) if n in ("pop", "velocity", "global_best_location") else None
+            assert close(getattr(wf.algorithm, n), want, scale=scale), (g, n)
+
+
+@pytest.mark.parametrize("n,d", [(1, 4), (300, 1000), (200, 1028), (64, 7), (2048, 64)])
+def test_random_swarms_against_oracle(cuda, n, d):
+    """Two generations (the second one uses the mean position the kernel accumulated, rows up to 1,024 floats)."""
+    from evox_b200.algorithms import SLPSOGS
+    from evox_b200.problems.numerical import Rastrigin
+    from evox_b200.workflows import StdWorkflow
+
+    g = torch.Generator().manual_seed(n + d)
+    lb, ub = torch.full((d,), -5.12), torch.full((d,), 5.12)
+    algo = SLPSOGS(n, lb, ub, 0.25, 0.6, device=cuda, seed=9)
+    algo.velocity.mul_(0.2)
+    wf = StdWorkflow(algo, Rastrigin(), device=cuda)
+    wf.init_step()
+    s = {k: getattr(algo, k).cpu().clone() for k in NAMES}
+    s.update(lb=lb[None], ub=ub[None], social_influence_factor=torch.tensor(0.25), demonstrator_choice_factor=torch.tensor(0.6))
+    for _ in range(2):
+        pick = torch.randn(n, generator=g)
+        rs = [torch.rand(n, d, generator=g) for _ in range(3)]
+        algo.fit.copy_(s["fit"])
+        rows = oslpso.demonstrator_rows_gs(s["fit"], s["demonstrator_choice_factor"], pick)
+        assert torch.equal(algo._demonstrator_rows(pick, cuda).cpu(), rows)
+        algo.step(pick, *rs)
+        s = oslpso.step(s, rows, *rs, opso.rastrigin)
+        assert close(algo.pop, s["pop"], scale=10.24)
+        assert close(algo.velocity, s["velocity"], scale=10.24)
+        assert close(algo.fit, s["fit"])
+        assert close(algo.global_best_fit, s["global_best_fit"])
+
+
+@pytest.mark.parametrize("kind", ["gs", "us"])
+def test_in_kernel_stream_improves_and_repeats(cuda, kind):
+    from evox_b200.algorithms import SLPSOGS, SLPSOUS
+    from evox_b200.problems.numerical import Sphere
+    from evox_b200.workflows import StdWorkflow
+
+    cls = SLPSOGS if kind == "gs" else SLPSOUS
+
+    def run(seed):
+        torch.manual_seed(5)
+        algo = cls(256, torch.full((30,), -10.0), torch.full((30,), 10.0), device=cuda, seed=seed)
+        algo.velocity.mul_(0.1)
+        wf = StdWorkflow(algo, Sphere(), device=cuda)
+        wf.init_step()
+        first = float(algo.global_best_fit)
+        for _ in range(100):
+            wf.step()
+        return algo.pop.clone(), first, float(algo.fit.min())
+
+    a, first, last = run(1)
+    b, _, _ = run(1)
+    assert torch.equal(a, b)
+    assert last < 0.1 * first
+    assert float(a.min()) >= -10.0 and float(a.max()) <= 10.0
