@@ -425,16 +425,29 @@ def run_rvea(args):
 
 
 def run_cso(args):
-    """Secondary workload: competitive swarm optimiser on Ackley, 1,000,000 x 1,000 (the headline
-    swarm size), phi 0.1, in-kernel Philox, fused evaluation; one step = StdWorkflow.step()."""
-    from evox_b200.algorithms import CSO
+    """Secondary workloads: the PSO variants on Ackley at 1,000,000 x 1,000 (the headline swarm size),
+    in-kernel Philox, fused evaluation; one step = StdWorkflow.step()."""
+    from evox_b200.algorithms import CLPSO, CSO, SLPSOGS
     from evox_b200.problems.numerical import Ackley
     from evox_b200.workflows import StdWorkflow
 
     dev = torch.device("cuda", 0)
-    n, d = {"cso_ackley_1e6x1000": (1_000_000, 1000), "cso_ackley_small": (65_536, 1000)}[args.workload]
+    kind, size = args.workload.split("_ackley_")
+    n, d = {"1e6x1000": (1_000_000, 1000), "small": (65_536, 1000)}[size]
+    lb, ub = torch.full((d,), -32.768), torch.full((d,), 32.768)
     torch.manual_seed(0)
-    algo = CSO(n, torch.full((d,), -32.768), torch.full((d,), 32.768), phi=0.1, device=dev, seed=1, store_velocity=True)
+    if kind == "cso":
+        algo = CSO(n, lb, ub, phi=0.1, device=dev, seed=1, store_velocity=True)
+        # per student-dimension: velocity, teacher and student rows read, student row and velocity written
+        alg_bytes, kernel = (n // 2) * d * 20.0, "cso_update_kernel (incl. randperm and the mean's finish)"
+    elif kind == "clpso":
+        algo = CLPSO(n, lb, ub, device=dev, seed=1)
+        # position, velocity, exemplar row read; position, velocity written (+ 8 B per improved particle-dimension)
+        alg_bytes, kernel = n * d * 20.0, "clpso_move_eval_kernel (incl. personal-best update and exemplar bookkeeping)"
+    else:
+        algo = SLPSOGS(n, lb, ub, device=dev, seed=1)
+        alg_bytes, kernel = n * d * 20.0, "slpso_update_kernel (incl. the fitness sort and the mean's finish)"
+    algo.velocity.mul_(0.2)
     wf = StdWorkflow(algo, Ackley(), device=dev)
     wf.init_step()
     for _ in range(max(args.warmup, 3)):
@@ -448,15 +461,13 @@ def run_cso(args):
         e1.record()
         torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / args.steps
-    # per student-dimension: velocity, teacher and student rows read, student row and velocity written
-    alg_bytes = (n // 2) * d * 20.0
-    peak, kind = measured_peaks()
+    peak, peak_kind = measured_peaks()
     line = {
-        "metric": "cso_generations_per_s", "value": 1e3 / ms, "unit": "gens/s", "n_gpus": 1, "steps": args.steps,
+        "metric": f"{kind}_generations_per_s", "value": 1e3 / ms, "unit": "gens/s", "n_gpus": 1, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": args.workload, "pop_size": n, "dim": d, "store_velocity": True, "l2": "state larger than L2"},
-        "roofline": {"bound": "hbm", "kernel": "cso_update_kernel (incl. randperm and the mean's finish)", "achieved": alg_bytes / (ms * 1e-3) / 1e9,
-                     "peak": peak, "unit": "GB/s", "frac": alg_bytes / (ms * 1e-3) / 1e9 / peak, "peak_kind": kind, "traffic": None},
+        "config": {"workload": args.workload, "pop_size": n, "dim": d, "l2": "state larger than L2"},
+        "roofline": {"bound": "hbm", "kernel": kernel, "achieved": alg_bytes / (ms * 1e-3) / 1e9,
+                     "peak": peak, "unit": "GB/s", "frac": alg_bytes / (ms * 1e-3) / 1e9 / peak, "peak_kind": peak_kind, "traffic": None},
         "clocks": clocks.summary(),
     }
     print(json.dumps(line), flush=True)
@@ -538,7 +549,7 @@ def main():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="pso_ackley_1e6x1000", choices=sorted(WORKLOADS) + ["nds_rank_2e4", "nds_rank_1e5", "lora_es_config3", "rvea_config2", "rvea_5e6", "cso_ackley_1e6x1000", "cso_ackley_small"])
+    ap.add_argument("--workload", default="pso_ackley_1e6x1000", choices=sorted(WORKLOADS) + ["nds_rank_2e4", "nds_rank_1e5", "lora_es_config3", "rvea_config2", "rvea_5e6", "cso_ackley_1e6x1000", "cso_ackley_small", "clpso_ackley_1e6x1000", "slpso_ackley_1e6x1000"])
     ap.add_argument("--lora-pop", type=int, default=1024)
     ap.add_argument("--gradient-passes", type=int, default=3, choices=[1, 3, 6])
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -547,7 +558,7 @@ def main():
         run_nds(args)
     elif args.workload == "lora_es_config3":
         run_lora_es(args)
-    elif args.workload.startswith("cso_"):
+    elif args.workload.split("_")[0] in ("cso", "clpso", "slpso"):
         run_cso(args)
     elif args.workload.startswith("rvea_"):
         run_rvea(args)
