@@ -1,8 +1,8 @@
 from .es import ARS, OpenES, PersistentES, VirtualLoRAES
-from .mo import NSGA2, RVEA
+from .mo import NSGA2, RVEA, RVEAa
 from .clpso import CLPSO
 from .cso import CSO
 from .pso import PSO
 from .slpso import SLPSOGS, SLPSOUS
 
-__all__ = ["PSO", "CSO", "CLPSO", "SLPSOGS", "SLPSOUS", "OpenES", "ARS", "PersistentES", "VirtualLoRAES", "NSGA2", "RVEA"]
+__all__ = ["PSO", "CSO", "CLPSO", "SLPSOGS", "SLPSOUS", "OpenES", "ARS", "PersistentES", "VirtualLoRAES", "NSGA2", "RVEA", "RVEAa"]

@@ -16,7 +16,7 @@ from ..operators.selection import nd_environmental_selection, raise_on_kernel_er
 from ..operators.variation import make_offspring, tournament_selection_multifit
 from ..problems.numerical import _relu_clamp_rows
 
-__all__ = ["NSGA2", "RVEA", "uniform_sampling"]
+__all__ = ["NSGA2", "RVEA", "RVEAa", "uniform_sampling"]
 
 
 def uniform_sampling(n: int, m: int) -> tuple[torch.Tensor, int]:
@@ -133,11 +133,11 @@ class RVEA(_MOBase):
     def _mating_rows(self, picks: torch.Tensor | None) -> torch.Tensor:
         """Row numbers of the mating pool: uniform picks among the rows that are not all-NaN
         (rvea.py:118-125)."""
-        n = self.pop_size
+        n, rows = self.pop_size, self.pop.shape[0]  # RVEAa keeps 2 * pop_size rows after its first generation
         valid = ~torch.isnan(self.pop).all(dim=1)
-        order = torch.argsort(torch.where(valid, torch.arange(n, device=self.pop.device), torch.iinfo(torch.int32).max), stable=True)
+        order = torch.argsort(torch.where(valid, torch.arange(rows, device=self.pop.device), torch.iinfo(torch.int32).max), stable=True)
         if picks is None:
-            picks = (torch.rand(n, device=self.pop.device) * valid.sum()).long().clamp_(max=n - 1)
+            picks = (torch.rand(n, device=self.pop.device) * valid.sum()).long().clamp_(max=rows - 1)
         return order[picks]
 
     def step(self, picks: torch.Tensor | None = None, draws: dict | None = None):
@@ -159,4 +159,75 @@ class RVEA(_MOBase):
             mx = torch.where(torch.isnan(f), -torch.inf, f).max(dim=0)[0]
             mn = torch.where(torch.isnan(f), torch.inf, f).min(dim=0)[0]
             self.reference_vector = self.init_v * (mx - mn)
+        self.generation += 1
+
+
+class RVEAa(RVEA):
+    """RVEA with reference-vector regeneration (evox/algorithms/mo/rveaa.py:17-212): a second set of
+    pop_size random reference vectors is selected against together with the lattice; vectors of that
+    set that no survivor is closest to are redrawn every generation; only non-dominated rows of the
+    merged population compete; the very last generation blanks half of the (2 * pop_size) rows.
+    Ranking and selection are the P2 / P3 kernels; the regeneration and truncation bookkeeping are
+    (pop_size x 2 pop_size) cosine tables in torch ops, as in the reference."""
+
+    def __init__(self, pop_size: int, n_objs: int, lb: torch.Tensor, ub: torch.Tensor, alpha: float = 2.0, fr: float = 0.1,
+                 max_gen: int = 100, selection_op: Optional[Callable] = None, mutation_op: Optional[Callable] = None,
+                 crossover_op: Optional[Callable] = None, device: torch.device | None = None):
+        super().__init__(pop_size, n_objs, lb, ub, alpha, fr, max_gen, selection_op, mutation_op, crossover_op, device)
+        extra = torch.rand(self.pop_size, n_objs, device=self.reference_vector.device)
+        self.reference_vector = Mutable(torch.cat([self.reference_vector, extra], dim=0))
+        self._max_gen_host = int(max_gen)
+
+    @staticmethod
+    def _rv_regeneration(pop_obj: torch.Tensor, v: torch.Tensor, draw: torch.Tensor | None = None) -> torch.Tensor:
+        """rveaa.py:129-142. `draw`: optional (len(v), n_objs) uniform draw."""
+        finite_min = torch.where(torch.isnan(pop_obj), torch.inf, pop_obj).min(dim=0).values
+        shifted = pop_obj - finite_min
+        cosine = torch.nn.functional.cosine_similarity(shifted.unsqueeze(1), v.unsqueeze(0), dim=-1)
+        cosine = torch.where(torch.isnan(cosine), -torch.inf, cosine)
+        nearest = cosine.max(dim=1).indices
+        nearest = torch.where(cosine[:, 0] == -torch.inf, -1, nearest)  # rows without objectives join nobody
+        joined = torch.zeros(v.size(0) + 1, dtype=torch.int64, device=v.device).index_add_(0, nearest + 1, torch.ones_like(nearest))[1:]
+        if draw is None:
+            draw = torch.rand(v.shape, device=v.device)
+        upper = torch.where(torch.isnan(shifted), -torch.inf, shifted).max(dim=0).values
+        return torch.where((joined == 0).unsqueeze(1), draw * upper, v)
+
+    @staticmethod
+    def _batch_truncation(pop: torch.Tensor, obj: torch.Tensor):
+        """rveaa.py:144-164: the reference ranks the rows by crowding and then masks by POSITION — the first
+        half of the rows becomes NaN whatever the ranking says; reproduced as is."""
+        keep = (torch.arange(pop.size(0), device=pop.device) >= pop.size(0) // 2).unsqueeze(1)
+        return torch.where(keep, pop, torch.nan), torch.where(keep, obj, torch.nan)
+
+    def step(self, picks: torch.Tensor | None = None, draws: dict | None = None, regeneration_draw: torch.Tensor | None = None):
+        """One generation (rveaa.py:189-212)."""
+        from ..operators.selection import non_dominate_rank
+
+        self.gen = self.gen + 1
+        self._gen_host = getattr(self, "_gen_host", 0) + 1
+        mating = self._mating_rows(picks)
+        offspring = self._variation(self.pop, mating, draws)
+        off_fit = self.evaluate(offspring)
+        merge_pop = torch.cat([self.pop, offspring], dim=0)
+        merge_fit = torch.cat([self.fit, off_fit], dim=0)
+        front = (non_dominate_rank(merge_fit) == 0).unsqueeze(1)
+        merge_fit = torch.where(front, merge_fit, torch.nan)
+        merge_pop = torch.where(front, merge_pop, torch.nan)
+        theta = (self.gen / self.max_gen) ** self.alpha
+        select = self.selection or ref_vec_guided
+        survivor, survivor_fit = select(merge_pop, merge_fit, self.reference_vector, theta)
+        n = self.pop_size
+        v_regen = self._rv_regeneration(survivor_fit, self.reference_vector[n:], regeneration_draw)
+        if self._gen_host % self._adapt_every == 0:
+            mx = torch.where(torch.isnan(survivor_fit), -torch.inf, survivor_fit).max(dim=0)[0]
+            mn = torch.where(torch.isnan(survivor_fit), torch.inf, survivor_fit).min(dim=0)[0]
+            v_adapt = self.init_v * (mx - mn)
+        else:
+            v_adapt = self.reference_vector[:n].clone()
+        if self._gen_host == self._max_gen_host:
+            self.pop, self.fit = self._batch_truncation(survivor, survivor_fit)
+        else:
+            self.pop, self.fit = survivor, survivor_fit
+        self.reference_vector = torch.cat([v_adapt, v_regen], dim=0)
         self.generation += 1

@@ -77,3 +77,41 @@ def config2_inputs(n: int = 50_000, m: int = 10, dx: int = 19, seed: int = 0):
     x = torch.rand(n, dx, generator=g)
     v = two_layer_vectors(3, 2, m)
     return x, f, v, torch.tensor(0.25)
+
+
+def _nanmin0(x: torch.Tensor) -> torch.Tensor:
+    return torch.where(torch.isnan(x), torch.inf, x).min(dim=0).values
+
+
+def _nanmax0(x: torch.Tensor) -> torch.Tensor:
+    return torch.where(torch.isnan(x), -torch.inf, x).max(dim=0).values
+
+
+def rv_regeneration(pop_obj: torch.Tensor, v: torch.Tensor, draw: torch.Tensor) -> torch.Tensor:
+    """RVEAa._rv_regeneration (algorithms/mo/rveaa.py:129-142): reference vectors of the second set that no
+    individual is closest to are redrawn inside the objectives' current range; `draw` is the uniform draw."""
+    import torch.nn.functional as F
+
+    pop_obj = pop_obj - _nanmin0(pop_obj)
+    cosine = F.cosine_similarity(pop_obj.unsqueeze(1), v.unsqueeze(0), dim=-1)
+    filled = torch.where(torch.isnan(cosine), -torch.inf, cosine)
+    associate = filled.max(dim=1).indices
+    associate = torch.where(filled[:, 0] == -torch.inf, -1, associate)
+    taken = torch.sum(associate.unsqueeze(1) == torch.arange(v.size(0)), dim=0)
+    return torch.where((taken == 0).unsqueeze(1), draw * _nanmax0(pop_obj), v)
+
+
+def batch_truncation(pop: torch.Tensor, obj: torch.Tensor):
+    """RVEAa._batch_truncation (rveaa.py:144-164): rank the rows by the cosine to their nearest other row
+    (most crowded first) and blank the first half with NaN."""
+    import torch.nn.functional as F
+
+    n = pop.size(0) // 2
+    cosine = F.cosine_similarity(obj.unsqueeze(1), obj.unsqueeze(0), dim=-1)
+    not_all_nan_rows = ~torch.isnan(cosine).all(dim=1)
+    cosine = torch.where(torch.eye(cosine.size(0), dtype=torch.bool) & not_all_nan_rows.unsqueeze(1), 0, cosine)
+    sorted_values, _ = torch.sort(-cosine, dim=1)
+    nearest = torch.where(torch.isnan(sorted_values[:, 0]), -torch.inf, sorted_values[:, 0])
+    rank = torch.argsort(nearest)  # computed by the reference and then not used: the mask below is by POSITION
+    keep = (torch.arange(rank.size(0)) >= n).unsqueeze(1)
+    return torch.where(keep, pop, torch.nan), torch.where(keep, obj, torch.nan)

@@ -453,8 +453,36 @@ def golden_slpso(out: dict):
                     out[f"{tag}_s{g + 2}_{n}"] = _np(wf.algorithm.state_dict()[n])
 
 
+def golden_rveaa(out: dict):
+    """RVEAa's own pieces (algorithms/mo/rveaa.py:129-164): `_rv_regeneration` (the uniform draw recorded) and
+    `_batch_truncation`, on objective sets with NaN rows as RVEA selection produces them."""
+    from evox.algorithms import RVEAa
+
+    import evox.algorithms.mo.rveaa as rmod
+
+    g = torch.Generator().manual_seed(4242)
+    algo = RVEAa(28, 3, torch.zeros(6), torch.ones(6))
+    n = algo.pop_size
+    obj = torch.rand(2 * n, 3, generator=g) + 0.1
+    obj[torch.tensor([1, 5, 17, 30])] = float("nan")
+    v = torch.rand(n, 3, generator=g)
+    v[3] = torch.tensor([1.0, 0.0, 0.0]) * 1e-3  # a direction nobody is closest to is likely; keep a few odd ones
+    draw = torch.rand(n, 3, generator=g)
+    real = rmod.torch.rand
+    rmod.torch.rand = lambda *a, **k: draw
+    try:
+        new_v = algo._rv_regeneration(obj, v)
+    finally:
+        rmod.torch.rand = real
+    out["regen_obj"], out["regen_v"], out["regen_draw"], out["regen_new_v"] = _np(obj), _np(v), _np(draw), _np(new_v)
+    pop = torch.rand(2 * n, 6, generator=g)
+    pop[torch.isnan(obj).all(dim=1)] = float("nan")
+    new_pop, new_obj = algo._batch_truncation(pop, obj)
+    out["trunc_pop"], out["trunc_new_pop"], out["trunc_new_obj"] = _np(pop), _np(new_pop), _np(new_obj)
+
+
 GENERATORS = {"pso": golden_pso, "nds": golden_nds, "rvea": golden_rvea, "es": golden_es, "variation": golden_variation,
-              "cso": golden_cso, "ars": golden_ars, "clpso": golden_clpso, "pes": golden_pes, "slpso": golden_slpso}
+              "cso": golden_cso, "ars": golden_ars, "clpso": golden_clpso, "pes": golden_pes, "slpso": golden_slpso, "rveaa": golden_rveaa}
 
 
 def main():

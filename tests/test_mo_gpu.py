@@ -179,3 +179,56 @@ def test_eval_monitor_single_and_multi_objective(cuda):
     assert int(onds.non_dominate_rank(fit.cpu()).max()) == 0
     with pytest.raises(ValueError):
         mon.get_best_fitness()
+
+
+def test_rveaa_pieces_and_generation(golden, cuda):
+    """RVEAa: regeneration and truncation against the reference's recorded outputs; one teacher-forced
+    generation against the oracle composition (rank kernel -> NaN masking -> selection kernel over the
+    doubled vector set -> regeneration); then a short run that must keep a non-dominated population."""
+    from evox_b200.algorithms import RVEAa
+    from evox_b200.problems.numerical import DTLZ2
+    from evox_b200.workflows import StdWorkflow
+
+    g = golden("rveaa")
+    new_v = RVEAa._rv_regeneration(t(g["regen_obj"]).to(cuda), t(g["regen_v"]).to(cuda), t(g["regen_draw"]).to(cuda))
+    close(new_v, t(g["regen_new_v"]), 1.0, rel=1e-6)
+    new_pop, new_obj = RVEAa._batch_truncation(t(g["trunc_pop"]).to(cuda), t(g["regen_obj"]).to(cuda))
+    assert torch.equal(torch.nan_to_num(new_pop.cpu(), nan=-7.0), torch.nan_to_num(t(g["trunc_new_pop"]), nan=-7.0))
+    assert torch.equal(torch.nan_to_num(new_obj.cpu(), nan=-7.0), torch.nan_to_num(t(g["trunc_new_obj"]), nan=-7.0))
+
+    d, m = 12, 3
+    lb, ub = torch.zeros(d), torch.ones(d)
+    torch.manual_seed(11)
+    algo = RVEAa(91, m, lb, ub, max_gen=50, device=cuda)
+    n = algo.pop_size
+    assert algo.reference_vector.shape == (2 * n, m)
+    wf = StdWorkflow(algo, DTLZ2(d, m), device=cuda)
+    gen = torch.Generator().manual_seed(8)
+    pop0 = torch.rand(n, d, generator=gen)
+    wf.algorithm.pop = pop0.to(cuda)
+    wf.init_step()
+    fit0 = wf.algorithm.fit.cpu()
+    v_all = wf.algorithm.reference_vector.cpu().clone()
+    picks = torch.randint(0, n, (n,), generator=gen)
+    draws = ov.make_draws(n, d, 3)
+    regen = torch.rand(n, m, generator=gen)
+    wf.algorithm.step(picks=picks.to(cuda), draws=draws, regeneration_draw=regen.to(cuda))
+    off = ov.offspring(ov.rvea_mating_pool(pop0, picks), lb, ub, draws)
+    off_fit = wf.problem.evaluate(off.to(cuda)).cpu()
+    merge_pop, merge_fit = torch.cat([pop0, off]), torch.cat([fit0, off_fit])
+    front = (onds.non_dominate_rank(merge_fit) == 0).unsqueeze(1)
+    merge_pop, merge_fit = torch.where(front, merge_pop, torch.nan), torch.where(front, merge_fit, torch.nan)
+    want = orvea.ref_vec_guided(merge_pop, merge_fit, v_all, (torch.tensor(1.0) / 50.0) ** 2.0)
+    got = wf.algorithm.pop.cpu()
+    assert got.shape == (2 * n, d)
+    assert torch.equal(torch.isnan(got), torch.isnan(want["next_x"]))
+    close(torch.nan_to_num(got), torch.nan_to_num(want["next_x"]), 1.0, rel=1e-4)
+    want_v = orvea.rv_regeneration(want["next_f"], v_all[n:], regen)
+    close(wf.algorithm.reference_vector[n:], want_v, 1.0, rel=1e-4)
+    assert torch.equal(wf.algorithm.reference_vector[:n].cpu(), v_all[:n])
+    for _ in range(12):
+        wf.step()
+    fit = wf.algorithm.fit
+    alive = ~torch.isnan(fit).any(dim=1)
+    assert int(alive.sum()) >= 10
+    assert int(onds.non_dominate_rank(fit[alive].cpu()).max()) == 0
