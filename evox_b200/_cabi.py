@@ -97,6 +97,12 @@ def ptr(t: torch.Tensor | None, dtype: torch.dtype | None = None, name: str = "t
         raise EvoxKernelError(f"{name} must have dtype {dtype}, got {t.dtype}")
     if not t.is_contiguous():
         raise EvoxKernelError(f"{name} must be contiguous")
+    if t.device.index != torch.cuda.current_device():
+        # the library launches on the calling thread's current device
+        raise EvoxKernelError(
+            f"{name} lives on {t.device} but the current CUDA device is cuda:{torch.cuda.current_device()}: "
+            f"make the call under `torch.cuda.device({t.device.index})` (or torch.cuda.set_device)"
+        )
     return t.data_ptr()
 
 
