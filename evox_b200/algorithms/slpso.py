@@ -107,9 +107,10 @@ class _SLPSO(Algorithm):
         raise NotImplementedError
 
     def step(self, pick: torch.Tensor | None = None, r1: torch.Tensor | None = None, r2: torch.Tensor | None = None,
-             r3: torch.Tensor | None = None):
+             r3: torch.Tensor | None = None, demonstrator_rows: torch.Tensor | None = None):
         """One generation. `pick`: the (pop_size,) draw of the demonstrator choice (standard normal for the
-        Gaussian variant, uniform for the uniform one); `r1`, `r2`, `r3`: the three (pop_size, dim) uniform draws."""
+        Gaussian variant, uniform for the uniform one); `r1`, `r2`, `r3`: the three (pop_size, dim) uniform draws;
+        `demonstrator_rows`: the chosen rows themselves (int64), bypassing the choice."""
         dev = self._ready()
         plan = self._fused_plan()
         n, sc = self.pop_size, self._scratch
@@ -119,7 +120,11 @@ class _SLPSO(Algorithm):
                                             _cabi.ptr(sc["best_ws"]), sc["best_ws"].numel(), s))
         _cabi.check(lib.evox_pso_merge_best(_cabi.ptr(sc["cand"]), 1, self.dim, 1, _cabi.ptr(self.global_best_location),
                                             _cabi.ptr(self.global_best_fit), s))
-        rows = self._demonstrator_rows(pick, dev).contiguous()
+        if demonstrator_rows is None:
+            rows = self._demonstrator_rows(pick, dev).contiguous()
+        else:
+            rows = demonstrator_rows.to(device=dev, dtype=torch.int64).contiguous()
+            assert rows.shape == (n,)
         draws = [None if r is None else r.to(device=dev, dtype=torch.float32).contiguous() for r in (r1, r2, r3)]
         assert all(r is None for r in draws) or all(r is not None and r.shape == self.pop.shape for r in draws)
         fitness_id, params = plan if plan is not None else (-1, (0.0, 0.0, 0.0))
