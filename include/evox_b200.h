@@ -1,7 +1,8 @@
 /*
  * evox_b200 — C-ABI of the B200 (sm_100a) kernels behind the population-batched
  * generation step of EvoX (PSO step, NSGA-II / RVEA environmental selection,
- * virtual-LoRA ES forward and update).
+ * virtual-LoRA ES forward and update) and of the algorithms that share its update shape
+ * (CSO, CLPSO, SL-PSO, mating / variation of the multi-objective algorithms, PersistentES).
  *
  * Conventions
  *  - Every pointer named in a signature is a DEVICE pointer unless its comment says
