@@ -96,6 +96,16 @@ class ClockSampler:
             except subprocess.TimeoutExpired:
                 self.proc.kill()
 
+    def sample_count(self) -> int:
+        """Samples of this GPU written so far."""
+        if self.path is None or not os.path.exists(self.path):
+            return 0
+        n = 0
+        for line in open(self.path):
+            parts = [p.strip() for p in line.split(",")]
+            n += len(parts) >= 9 and parts[0].isdigit() and int(parts[0]) == self.gpu_index
+        return n
+
     def summary(self) -> dict:
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
         if self.path is None or not os.path.exists(self.path):
@@ -293,6 +303,18 @@ def run_ours(args):
         t = torch.tensor([kernel_ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         kernel_ms = t.item()
+    # nvidia-smi needs a few hundred milliseconds before its first sample: short runs (many GPUs, few steps)
+    # keep stepping, untimed, until the clock record of the load has a few samples (every rank runs the same
+    # number of extra generations: the count is agreed on rank 0's record)
+    for _ in range(20):
+        enough = torch.tensor([1 if clocks.sample_count() >= 4 else 0], device=dev)
+        if world > 1:
+            dist.broadcast(enough, src=0)
+        if int(enough.item()):
+            break
+        for _ in range(max(args.steps // 2, 10)):
+            wf.step()
+        barrier()
     clocks.__exit__(None, None, None)
     clock_summary = clocks.summary()
     peak, peak_kind = measured_peaks()
