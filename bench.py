@@ -449,7 +449,7 @@ def run_rvea(args):
 def run_cso(args):
     """Secondary workloads: the PSO variants on Ackley at 1,000,000 x 1,000 (the headline swarm size),
     in-kernel Philox, fused evaluation; one step = StdWorkflow.step()."""
-    from evox_b200.algorithms import CLPSO, CSO, SLPSOGS
+    from evox_b200.algorithms import CLPSO, CSO, DE, SLPSOGS
     from evox_b200.problems.numerical import Ackley
     from evox_b200.workflows import StdWorkflow
 
@@ -466,10 +466,15 @@ def run_cso(args):
         algo = CLPSO(n, lb, ub, device=dev, seed=1)
         # position, velocity, exemplar row read; position, velocity written (+ 8 B per improved particle-dimension)
         alg_bytes, kernel = n * d * 20.0, "clpso_move_eval_kernel (incl. personal-best update and exemplar bookkeeping)"
+    elif kind == "de":
+        algo = DE(n, lb, ub, device=dev, seed=1)
+        # own row and three other rows read, trial written (+ 8 B per accepted individual-dimension)
+        alg_bytes, kernel = n * d * 20.0, "de_trial_kernel + de_select_kernel (incl. the index draws)"
     else:
         algo = SLPSOGS(n, lb, ub, device=dev, seed=1)
         alg_bytes, kernel = n * d * 20.0, "slpso_update_kernel (incl. the fitness sort and the mean's finish)"
-    algo.velocity.mul_(0.2)
+    if hasattr(algo, "velocity"):
+        algo.velocity.mul_(0.2)
     wf = StdWorkflow(algo, Ackley(), device=dev)
     wf.init_step()
     for _ in range(max(args.warmup, 3)):
@@ -571,7 +576,7 @@ def main():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="pso_ackley_1e6x1000", choices=sorted(WORKLOADS) + ["nds_rank_2e4", "nds_rank_1e5", "lora_es_config3", "rvea_config2", "rvea_5e6", "cso_ackley_1e6x1000", "cso_ackley_small", "clpso_ackley_1e6x1000", "slpso_ackley_1e6x1000"])
+    ap.add_argument("--workload", default="pso_ackley_1e6x1000", choices=sorted(WORKLOADS) + ["nds_rank_2e4", "nds_rank_1e5", "lora_es_config3", "rvea_config2", "rvea_5e6", "cso_ackley_1e6x1000", "cso_ackley_small", "clpso_ackley_1e6x1000", "slpso_ackley_1e6x1000", "de_ackley_1e6x1000"])
     ap.add_argument("--lora-pop", type=int, default=1024)
     ap.add_argument("--gradient-passes", type=int, default=3, choices=[1, 3, 6])
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -580,7 +585,7 @@ def main():
         run_nds(args)
     elif args.workload == "lora_es_config3":
         run_lora_es(args)
-    elif args.workload.split("_")[0] in ("cso", "clpso", "slpso"):
+    elif args.workload.split("_")[0] in ("cso", "clpso", "slpso", "de"):
         run_cso(args)
     elif args.workload.startswith("rvea_"):
         run_rvea(args)

@@ -190,6 +190,32 @@ int evox_slpso_step(const float* pop, float* pop_new, float* velocity, float* fi
                     void* workspace, size_t workspace_bytes, int32_t* next_center_ready, void* stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Differential evolution, one difference vector (algorithms/so/de_variants/de.py).
+ * ------------------------------------------------------------------------------------------ */
+
+/* Mutation, crossover and clamp of DE.step (de.py:105-146) fused with the evaluation of the trials:
+ *   mutant_i = base_i + F * (pop[rows_a[i]] - pop[rows_b[i]]),
+ *   trial_i  = clamp(where(cross_i < CR or column == forced_column[i], mutant_i, pop_i), lb, ub),
+ *   trial_fit_i = f(trial_i).
+ * base_i = pop[base_rows[i]] (base vector "rand") or pop[*best_row] for every i (base vector "best":
+ * best_row is a DEVICE int64 scalar, e.g. torch.argmin(fit)); exactly one of the two is non-NULL.
+ * The row and column indices are int64 device arrays of pop_size elements (de.py:112-113, :137).
+ * differential_weight (F) and cross_probability (CR) are DEVICE scalars. cross is the (pop_size x dim)
+ * uniform draw of de.py:136 or NULL (Philox4x32-10, key = seed, counter = (row, column / 4,
+ * generation)). pop is only read; trial must be a different buffer. fitness_id = -1 skips the
+ * evaluation (trial_fit may then be NULL). */
+int evox_de_trial(const float* pop, float* trial, float* trial_fit, const int64_t* base_rows,
+                  const int64_t* best_row, const int64_t* rows_a, const int64_t* rows_b,
+                  const int64_t* forced_column, const float* lb, const float* ub,
+                  const float* differential_weight, const float* cross_probability, const float* cross,
+                  int64_t pop_size, int32_t dim, int32_t fitness_id, const float* params, uint64_t seed,
+                  uint64_t generation, void* stream);
+
+/* Selection of DE.step (de.py:152-157): rows with trial_fit < fit take the trial and its fitness. */
+int evox_de_select(const float* trial, const float* trial_fit, float* pop, float* fit, int64_t pop_size,
+                   int32_t dim, void* stream);
+
+/* ------------------------------------------------------------------------------------------
  * P2. NSGA-II environmental selection.
  * ------------------------------------------------------------------------------------------ */
 

@@ -481,8 +481,50 @@ def golden_rveaa(out: dict):
     out["trunc_pop"], out["trunc_new_pop"], out["trunc_new_obj"] = _np(pop), _np(new_pop), _np(new_obj)
 
 
+def golden_de(out: dict):
+    """DE.init_step + 3 teacher-forced steps (index draws, crossover draws and forced dimensions recorded) with
+    base vector "rand" and "best", one difference vector, on Ackley, dims 12 and 10, 29 individuals."""
+    from evox.algorithms import DE
+    from evox.problems.numerical import Ackley
+    from evox.workflows import StdWorkflow
+
+    import evox.algorithms.so.de_variants.de as dmod
+
+    for base in ("rand", "best"):
+        for dim in (12, 10):
+            pop_size, lo, hi = 29, -32.768, 32.768
+            torch.manual_seed(77 + dim)
+            algo = DE(pop_size, torch.full((dim,), lo), torch.full((dim,), hi), base_vector=base, differential_weight=0.6,
+                      cross_probability=0.7)
+            wf = StdWorkflow(algo, Ackley())
+            tag = f"de_{base}_d{dim}"
+            out[f"{tag}_bounds"] = np.asarray([lo, hi], dtype=np.float32)
+            out[f"{tag}_s0_pop"] = _np(wf.algorithm.state_dict()["pop"])
+            wf.init_step()
+            out[f"{tag}_s1_pop"], out[f"{tag}_s1_fit"] = _np(wf.algorithm.state_dict()["pop"]), _np(wf.algorithm.state_dict()["fit"])
+            gen = torch.Generator().manual_seed(5 + dim)
+            n_idx = 3 if base == "rand" else 2
+            for g in range(3):
+                idx = [torch.randint(0, pop_size, (pop_size,), generator=gen) for _ in range(n_idx)]
+                cross = torch.rand(pop_size, dim, generator=gen)
+                forced = torch.randint(0, dim, (pop_size, 1), generator=gen)
+                iq, rq = list(idx) + [forced], [cross]
+                real_rand, real_randint = torch.rand, torch.randint
+                dmod.torch.rand = lambda *a, **k: rq.pop(0)
+                dmod.torch.randint = lambda *a, **k: iq.pop(0)
+                try:
+                    wf.step()
+                finally:
+                    dmod.torch.rand, dmod.torch.randint = real_rand, real_randint
+                assert not iq and not rq
+                for j, t_ in enumerate(idx):
+                    out[f"{tag}_g{g}_idx{j}"] = _np(t_)
+                out[f"{tag}_g{g}_cross"], out[f"{tag}_g{g}_forced"] = _np(cross), _np(forced)
+                out[f"{tag}_s{g + 2}_pop"], out[f"{tag}_s{g + 2}_fit"] = _np(wf.algorithm.state_dict()["pop"]), _np(wf.algorithm.state_dict()["fit"])
+
+
 GENERATORS = {"pso": golden_pso, "nds": golden_nds, "rvea": golden_rvea, "es": golden_es, "variation": golden_variation,
-              "cso": golden_cso, "ars": golden_ars, "clpso": golden_clpso, "pes": golden_pes, "slpso": golden_slpso, "rveaa": golden_rveaa}
+              "cso": golden_cso, "ars": golden_ars, "clpso": golden_clpso, "pes": golden_pes, "slpso": golden_slpso, "rveaa": golden_rveaa, "de": golden_de}
 
 
 def main():
