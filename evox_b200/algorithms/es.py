@@ -242,6 +242,97 @@ class PersistentES(Algorithm):
         return {"center": self.center, "sigma": self.sigma}
 
 
+def _rank_weighted_step(algo, noise, weights_by_rank, x_is_population: bool):
+    """Shared by SNES and DES: sample with per-coordinate step sizes, evaluate, give every row the weight of
+    its fitness rank and reduce the two weighted column sums in one pass. Returns (first, second)."""
+    dev = algo.center.device
+    pop_size, dim = algo.pop_size, algo.dim
+    if noise is None:
+        noise = torch.randn(pop_size, dim, device=dev)
+    noise = noise.to(device=dev, dtype=torch.float32).contiguous()
+    assert noise.shape == (pop_size, dim)
+    lib, s = _cabi.lib, _cabi.stream_ptr(dev)
+    pop = torch.empty(pop_size, dim, dtype=torch.float32, device=dev)
+    _cabi.check(lib.evox_es_ask_diag(_cabi.ptr(algo.center, torch.float32, "center"), _cabi.ptr(noise), _cabi.ptr(algo.sigma, torch.float32, "sigma"),
+                                     pop_size, dim, _cabi.ptr(pop), s))
+    fitness = algo.evaluate(pop)
+    row_weights = torch.empty(pop_size, dtype=torch.float32, device=dev)
+    row_weights[fitness.argsort()] = weights_by_rank
+    first = torch.empty(dim, dtype=torch.float32, device=dev)
+    second = torch.empty(dim, dtype=torch.float32, device=dev)
+    x, shift, offset = (pop, algo.center, 0.0) if x_is_population else (noise, None, -1.0)
+    _cabi.check(lib.evox_rank_weighted_moments(_cabi.ptr(x), _cabi.ptr(row_weights), _cabi.ptr(shift), offset, pop_size, dim,
+                                               _cabi.ptr(first), _cabi.ptr(second), s))
+    return first, second
+
+
+class SNES(Algorithm):
+    """Separable natural evolution strategy (snes.py:12-95): per-coordinate step sizes, rank-based weights."""
+
+    def __init__(self, pop_size: int, center_init: torch.Tensor, sigma: float = 1.0, lrate_mean: float = 1.0,
+                 temperature: float = 12.5, weight_type: Literal["recomb", "temp"] = "temp", device: torch.device | None = None):
+        import math
+
+        super().__init__()
+        device = torch.get_default_device() if device is None else torch.device(device)
+        assert pop_size > 1
+        dim = center_init.shape[0]
+        self.lrate_mean = Parameter(lrate_mean, dtype=torch.float32, device=device)
+        self.lrate_sigma = Parameter((3 + math.log(dim)) / (5 * math.sqrt(dim)), dtype=torch.float32, device=device)
+        self.temperature = Parameter(temperature, dtype=torch.float32, device=device)
+        self.dim = dim
+        self.pop_size = pop_size
+        if weight_type == "temp":
+            w = torch.arange(pop_size, device=device) / (pop_size - 1) - 0.5
+            w = torch.nn.functional.softmax(-20 * torch.sigmoid(temperature * w), dim=0)
+        else:
+            w = torch.clip(math.log(pop_size / 2 + 1) - torch.log(torch.arange(1, pop_size + 1, device=device)), 0)
+            w = w / torch.sum(w) - 1 / pop_size
+        # the reference keeps the weights tiled over the columns (pop_size, dim); one value per rank carries the same information
+        self.weights = Mutable(w.to(torch.float32).contiguous())
+        self.center = Mutable(center_init.to(device=device, dtype=torch.float32).contiguous().clone())
+        self.sigma = Mutable(sigma * torch.ones(dim, device=device))
+
+    def step(self, noise: torch.Tensor | None = None):
+        """One generation (snes.py:70-90). `noise`: optional (pop_size, dim) standard-normal draws."""
+        grad_mean, grad_sigma = _rank_weighted_step(self, noise, self.weights, x_is_population=False)
+        self.center = self.center + self.lrate_mean * self.sigma * grad_mean
+        self.sigma = self.sigma * torch.exp(self.lrate_sigma / 2 * grad_sigma)
+
+    def record_step(self):
+        return {"center": self.center, "sigma": self.sigma}
+
+
+class DES(Algorithm):
+    """Discovered evolution strategy (des.py:11-77): softmax rank weights, weighted mean and deviation."""
+
+    def __init__(self, pop_size: int, center_init: torch.Tensor, temperature: float = 12.5, sigma_init: float = 0.1,
+                 device: torch.device | None = None):
+        super().__init__()
+        device = torch.get_default_device() if device is None else torch.device(device)
+        assert pop_size > 1
+        self.temperature = Parameter(temperature, dtype=torch.float32, device=device)
+        self.sigma_init = Parameter(sigma_init, dtype=torch.float32, device=device)
+        self.lrate_mean = Parameter(1.0, dtype=torch.float32, device=device)
+        self.lrate_sigma = Parameter(0.1, dtype=torch.float32, device=device)
+        self.dim = center_init.shape[0]
+        self.pop_size = pop_size
+        self.ranks = torch.arange(pop_size, device=device) / (pop_size - 1) - 0.5
+        self.center = Mutable(center_init.to(device=device, dtype=torch.float32).contiguous().clone())
+        self.sigma = Mutable(sigma_init * torch.ones(self.dim, device=device))
+
+    def step(self, noise: torch.Tensor | None = None):
+        """One generation (des.py:57-72). `noise`: optional (pop_size, dim) standard-normal draws."""
+        weight = torch.nn.functional.softmax(-20 * torch.sigmoid(self.temperature * self.ranks), dim=0)
+        weight_mean, weight_sq = _rank_weighted_step(self, noise, weight, x_is_population=True)
+        weight_sigma = torch.sqrt(weight_sq + 1e-6)
+        self.center = self.center + self.lrate_mean * (weight_mean - self.center)
+        self.sigma = self.sigma + self.lrate_sigma * (weight_sigma - self.sigma)
+
+    def record_step(self):
+        return {"center": self.center, "sigma": self.sigma}
+
+
 class VirtualLoRAES(_ESBase):
     """ES over a virtual population: only the centre and one int64 seed per individual exist;
     perturbations are rank-r factors regenerated from the seeds."""

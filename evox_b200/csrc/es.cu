@@ -179,6 +179,38 @@ __global__ void __launch_bounds__(kThreads)
   }
 }
 
+// pop[i][l] = center[l] + noise[i][l] * sigma[l]: per-coordinate step sizes (snes.py:79, des.py:60).
+__global__ void __launch_bounds__(kThreads)
+    es_ask_diag_kernel(const float* __restrict__ center, const float* __restrict__ noise, const float* __restrict__ sigma, long long pop,
+                       long long n, float* __restrict__ out) {
+  const long long total = pop * n;
+  for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (long long)gridDim.x * blockDim.x) {
+    const long long l = e % n;
+    out[e] = __fadd_rn(center[l], __fmul_rn(noise[e], sigma[l]));
+  }
+}
+
+// Two row-weighted column sums of x (pop x n) in one pass:
+//   first[l] = sum_i w[i] * x[i][l],   second[l] = sum_i w[i] * ((x[i][l] - shift[l])^2 + offset)
+// (snes.py:83-84 with shift = 0, offset = -1 on the noise; des.py:66-67 with shift = center, offset = 0 on the
+// population). w[i] is the weight of row i's fitness rank.
+__global__ void __launch_bounds__(kThreads)
+    rank_weighted_moments_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ shift, float offset,
+                                 long long pop, long long n, float* __restrict__ first, float* __restrict__ second) {
+  for (long long l = (long long)blockIdx.x * blockDim.x + threadIdx.x; l < n; l += (long long)gridDim.x * blockDim.x) {
+    const float sh = shift ? shift[l] : 0.f;
+    float a = 0.f, b = 0.f;
+    for (long long i = 0; i < pop; ++i) {
+      const float v = x[i * n + l], wi = w[i];
+      const float dv = __fsub_rn(v, sh);
+      a = __fmaf_rn(wi, v, a);
+      b = __fmaf_rn(wi, __fadd_rn(__fmul_rn(dv, dv), offset), b);
+    }
+    first[l] = a;
+    second[l] = b;
+  }
+}
+
 // SGD: center -= lr * grad. Adam (adam_step.py:20-26, no bias correction, eps added after the root):
 // m = lerp(m, g, 1 - b1); v = v * b2 + g * g * (1 - b2); center -= lr * m / (sqrt(v) + eps).
 __global__ void __launch_bounds__(kThreads)
@@ -374,6 +406,26 @@ extern "C" int evox_pes_ask(const float* center, const float* noise, const float
   EVOX_REQUIRE(pop > 0 && dim > 0 && pop % 2 == 0, EVOX_ERR_INVALID, "pes_ask: pop must be positive and even");
   openes_ask_kernel<<<grid_for(pop * dim), kThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(center, noise, sigma, pop, dim,
                                                                                                pop / 2, population, pert_accum);
+  EVOX_LAUNCH_CHECK();
+  return EVOX_OK;
+}
+
+extern "C" int evox_es_ask_diag(const float* center, const float* noise, const float* sigma, int64_t pop, int64_t dim,
+                                float* population, void* stream) {
+  EVOX_REQUIRE(center && noise && sigma && population, EVOX_ERR_INVALID, "es_ask_diag: NULL pointer");
+  EVOX_REQUIRE(pop > 0 && dim > 0, EVOX_ERR_INVALID, "es_ask_diag: sizes must be positive");
+  es_ask_diag_kernel<<<grid_for(pop * dim), kThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(center, noise, sigma, pop, dim,
+                                                                                                population);
+  EVOX_LAUNCH_CHECK();
+  return EVOX_OK;
+}
+
+extern "C" int evox_rank_weighted_moments(const float* x, const float* row_weights, const float* shift, float offset, int64_t pop,
+                                          int64_t dim, float* first, float* second, void* stream) {
+  EVOX_REQUIRE(x && row_weights && first && second, EVOX_ERR_INVALID, "rank_weighted_moments: NULL pointer");
+  EVOX_REQUIRE(pop > 0 && dim > 0, EVOX_ERR_INVALID, "rank_weighted_moments: sizes must be positive");
+  rank_weighted_moments_kernel<<<grid_for(dim), kThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(x, row_weights, shift, offset,
+                                                                                                   pop, dim, first, second);
   EVOX_LAUNCH_CHECK();
   return EVOX_OK;
 }

@@ -363,6 +363,19 @@ int evox_openes_ask(const float* center, const float* noise, const float* sigma,
 int evox_pes_ask(const float* center, const float* noise, const float* sigma, int64_t pop, int64_t dim,
                  float* pert_accum, float* population, void* stream);
 
+/* population (pop x dim) = center + noise * sigma with one step size PER COORDINATE (sigma: dim
+ * floats), the sampling of SNES and DES (es_variants/snes.py:79, des.py:60). */
+int evox_es_ask_diag(const float* center, const float* noise, const float* sigma, int64_t pop, int64_t dim,
+                     float* population, void* stream);
+
+/* Two row-weighted column sums of x (pop x dim) in one pass over x:
+ *   first[l] = sum_i w_i x_il,   second[l] = sum_i w_i ((x_il - shift_l)^2 + offset),
+ * row_weights[i] being the weight of row i's fitness rank. SNES (snes.py:83-84): x = noise, shift = NULL,
+ * offset = -1 gives grad_mean and grad_sigma; DES (des.py:66-67): x = population, shift = center,
+ * offset = 0 gives the weighted mean and the weighted squared deviation. */
+int evox_rank_weighted_moments(const float* x, const float* row_weights, const float* shift, float offset,
+                               int64_t pop, int64_t dim, float* first, float* second, void* stream);
+
 /* grad (dim) = noise^T fitness / pop / sigma (open_es.py:70), same mirrored convention. */
 int evox_openes_gradient(const float* noise, const float* fitness, int64_t pop, int64_t dim,
                          int64_t noise_rows, float sigma, float* grad, void* stream);

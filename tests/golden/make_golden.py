@@ -523,8 +523,37 @@ def golden_de(out: dict):
                 out[f"{tag}_s{g + 2}_pop"], out[f"{tag}_s{g + 2}_fit"] = _np(wf.algorithm.state_dict()["pop"]), _np(wf.algorithm.state_dict()["fit"])
 
 
+def golden_snes_des(out: dict):
+    """SNES.step (both weight types) and DES.step with the normal draws fixed: three generations each on a
+    shifted sphere; centre and sigma after every step."""
+    from evox.algorithms import DES, SNES
+
+    import evox.algorithms.so.es_variants.des as dmod
+    import evox.algorithms.so.es_variants.snes as smod
+
+    g = torch.Generator().manual_seed(8642)
+    shift = torch.randn(18, generator=g)
+    cases = [("snes_temp", lambda c: SNES(14, c, sigma=0.5, weight_type="temp"), smod),
+             ("snes_recomb", lambda c: SNES(14, c, sigma=0.5, weight_type="recomb"), smod),
+             ("des", lambda c: DES(14, c, sigma_init=0.3), dmod)]
+    for tag, make, mod in cases:
+        center = torch.randn(18, generator=g)
+        algo = make(center.clone())
+        algo.evaluate = lambda pop: ((pop - shift) ** 2).sum(dim=1)
+        out[f"{tag}_center0"], out[f"{tag}_shift"] = _np(center), _np(shift)
+        for k in range(3):
+            z = torch.randn(14, 18, generator=g)
+            real = mod.torch.randn
+            mod.torch.randn = lambda *a, **kw: z
+            try:
+                algo.step()
+            finally:
+                mod.torch.randn = real
+            out[f"{tag}_z{k}"], out[f"{tag}_center{k + 1}"], out[f"{tag}_sigma{k + 1}"] = _np(z), _np(algo.center), _np(algo.sigma)
+
+
 GENERATORS = {"pso": golden_pso, "nds": golden_nds, "rvea": golden_rvea, "es": golden_es, "variation": golden_variation,
-              "cso": golden_cso, "ars": golden_ars, "clpso": golden_clpso, "pes": golden_pes, "slpso": golden_slpso, "rveaa": golden_rveaa, "de": golden_de}
+              "cso": golden_cso, "ars": golden_ars, "clpso": golden_clpso, "pes": golden_pes, "slpso": golden_slpso, "rveaa": golden_rveaa, "de": golden_de, "snes_des": golden_snes_des}
 
 
 def main():

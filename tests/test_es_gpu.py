@@ -186,6 +186,34 @@ def test_persistent_es_steps_golden(golden, cuda, opt):
     wf.step()  # default path draws its own noise
 
 
+@pytest.mark.parametrize("tag", ["snes_temp", "snes_recomb", "des"])
+def test_snes_des_steps_golden(golden, cuda, tag):
+    """SNES (both weight types) and DES: three teacher-forced generations against the reference's centres and
+    step sizes; then a run with its own draws must approach the optimum."""
+    from evox_b200.algorithms import DES, SNES
+    from evox_b200.core import Problem
+    from evox_b200.workflows import StdWorkflow
+
+    g = golden("snes_des")
+    shift = t(g[f"{tag}_shift"]).to(cuda)
+
+    class ShiftedSphere(Problem):
+        def evaluate(self, pop):
+            return ((pop - shift) ** 2).sum(dim=1)
+
+    c0 = t(g[f"{tag}_center0"])
+    algo = DES(14, c0, sigma_init=0.3, device=cuda) if tag == "des" else SNES(14, c0, sigma=0.5, weight_type=tag.split("_")[1], device=cuda)
+    wf = StdWorkflow(algo, ShiftedSphere(), device=cuda)
+    for k in range(3):
+        wf.algorithm.step(noise=t(g[f"{tag}_z{k}"]))
+        close(wf.algorithm.center, t(g[f"{tag}_center{k + 1}"]))
+        close(wf.algorithm.sigma, t(g[f"{tag}_sigma{k + 1}"]))
+    before = float(((wf.algorithm.center - shift) ** 2).sum())
+    for _ in range(150):
+        wf.step()
+    assert float(((wf.algorithm.center - shift) ** 2).sum()) < 0.2 * before
+
+
 def make_mlp(sizes, bias, gen):
     layers = []
     for i in range(len(sizes) - 1):
