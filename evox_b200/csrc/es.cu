@@ -148,19 +148,55 @@ __global__ void __launch_bounds__(kThreads)
 // out[l] = sum_i scale_i * noise[i][l], scale_i = fitness[i] * inv_scale   (1-D blocks, lora_noise.py:190-192;
 // also OpenES's noise^T fitness, open_es.py:70, with `sign_split` = pop/2 for mirrored sampling
 // where row i >= sign_split reuses noise row i - sign_split negated).
+// One block = 32 (or 128, as float4) columns x 8 warps; warp w walks rows w, w + 8, ... (a row's piece is one
+// coalesced 128- or 512-byte read), the eight partial sums are folded in warp order. The number of blocks grows with the
+// row length, the length of every dependent chain is pop / 8: short rows with many individuals no longer
+// serialise on one thread per column.
+template <int VEC>
 __global__ void __launch_bounds__(kThreads)
     weighted_rows_kernel(const float* __restrict__ fitness, const float* __restrict__ noise, long long pop, long long n,
                          long long noise_rows, float inv_scale, float* __restrict__ out) {
-  for (long long l = (long long)blockIdx.x * blockDim.x + threadIdx.x; l < n; l += (long long)gridDim.x * blockDim.x) {
-    float acc = 0.f;
-    for (long long i = 0; i < pop; ++i) {
-      const bool mirrored = i >= noise_rows;
-      const float z = noise[(mirrored ? i - noise_rows : i) * n + l];
-      acc = __fmaf_rn(fitness[i], mirrored ? -z : z, acc);
+  constexpr int kWarps = kThreads / 32, kTile = 32 * VEC;
+  __shared__ float part[kWarps][kTile];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (long long l0 = (long long)blockIdx.x * kTile; l0 < n; l0 += (long long)gridDim.x * kTile) {
+    const long long l = l0 + (long long)lane * VEC;
+    float acc[VEC];
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) acc[j] = 0.f;
+    if (l < n) {
+#pragma unroll 4
+      for (long long i = warp; i < pop; i += kWarps) {
+        const bool mirrored = i >= noise_rows;
+        const float f = mirrored ? -fitness[i] : fitness[i];  // f * (-z) and (-f) * z round alike
+        const float* row = noise + (mirrored ? i - noise_rows : i) * n + l;
+        if constexpr (VEC == 4) {
+          const float4 z = __ldg(reinterpret_cast<const float4*>(row));
+          acc[0] = __fmaf_rn(f, z.x, acc[0]);
+          acc[1] = __fmaf_rn(f, z.y, acc[1]);
+          acc[2] = __fmaf_rn(f, z.z, acc[2]);
+          acc[3] = __fmaf_rn(f, z.w, acc[3]);
+        } else {
+          acc[0] = __fmaf_rn(f, __ldg(row), acc[0]);
+        }
+      }
     }
-    out[l] = __fmul_rn(acc, inv_scale);
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) part[warp][lane * VEC + j] = acc[j];
+    __syncthreads();
+    for (int c = threadIdx.x; c < kTile; c += kThreads) {
+      if (l0 + c < n) {
+        float t = part[0][c];
+        for (int w = 1; w < kWarps; ++w) t += part[w][c];
+        out[l0 + c] = __fmul_rn(t, inv_scale);
+      }
+    }
+    __syncthreads();
   }
 }
+
+int launch_weighted_rows(const float* fitness, const float* noise, long long pop, long long n, long long noise_rows, float inv_scale,
+                         float* out, cudaStream_t s);
 
 // pop[i][l] = center[l] + sigma * (+-) noise[i mod rows][l]   (open_es.py:64-68); with `accum` the same
 // perturbation is also added to accum[i][l] (PersistentES, persistent_es.py:76-80).
@@ -197,17 +233,34 @@ __global__ void __launch_bounds__(kThreads)
 __global__ void __launch_bounds__(kThreads)
     rank_weighted_moments_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ shift, float offset,
                                  long long pop, long long n, float* __restrict__ first, float* __restrict__ second) {
-  for (long long l = (long long)blockIdx.x * blockDim.x + threadIdx.x; l < n; l += (long long)gridDim.x * blockDim.x) {
-    const float sh = shift ? shift[l] : 0.f;
+  // same decomposition as weighted_rows_kernel: 32 columns per block, rows dealt to the 8 warps
+  __shared__ float part[2][kThreads / 32][32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (long long l0 = (long long)blockIdx.x * 32; l0 < n; l0 += (long long)gridDim.x * 32) {
+    const long long l = l0 + lane;
     float a = 0.f, b = 0.f;
-    for (long long i = 0; i < pop; ++i) {
-      const float v = x[i * n + l], wi = w[i];
-      const float dv = __fsub_rn(v, sh);
-      a = __fmaf_rn(wi, v, a);
-      b = __fmaf_rn(wi, __fadd_rn(__fmul_rn(dv, dv), offset), b);
+    if (l < n) {
+      const float sh = shift ? shift[l] : 0.f;
+      for (long long i = warp; i < pop; i += kThreads / 32) {
+        const float v = x[i * n + l], wi = w[i];
+        const float dv = __fsub_rn(v, sh);
+        a = __fmaf_rn(wi, v, a);
+        b = __fmaf_rn(wi, __fadd_rn(__fmul_rn(dv, dv), offset), b);
+      }
     }
-    first[l] = a;
-    second[l] = b;
+    part[0][warp][lane] = a;
+    part[1][warp][lane] = b;
+    __syncthreads();
+    if (warp == 0 && l < n) {
+      float ta = part[0][0][lane], tb = part[1][0][lane];
+      for (int q = 1; q < kThreads / 32; ++q) {
+        ta += part[0][q][lane];
+        tb += part[1][q][lane];
+      }
+      first[l] = ta;
+      second[l] = tb;
+    }
+    __syncthreads();
   }
 }
 
@@ -303,6 +356,19 @@ __global__ void __launch_bounds__(kThreads)
   }
 }
 
+int grid_for(long long work, int per);
+
+int launch_weighted_rows(const float* fitness, const float* noise, long long pop, long long n, long long noise_rows, float inv_scale,
+                         float* out, cudaStream_t s) {
+  // float4 tiles need 128 columns per block: only when that still leaves a block or more per SM
+  if (n % 4 == 0 && aligned16(noise) && n >= 128ll * sm_count()) {
+    weighted_rows_kernel<4><<<grid_for(n, 128), kThreads, 0, s>>>(fitness, noise, pop, n, noise_rows, inv_scale, out);
+  } else {
+    weighted_rows_kernel<1><<<grid_for(n, 32), kThreads, 0, s>>>(fitness, noise, pop, n, noise_rows, inv_scale, out);
+  }
+  return 0;
+}
+
 int grid_for(long long work, int per = kThreads) {
   long long want = (work + per - 1) / per;
   const long long cap = (long long)sm_count() * 16;
@@ -363,7 +429,7 @@ extern "C" int evox_lora_gradient(const float* fitness, const float* A, const fl
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   const float inv_scale = 1.0f / ((float)pop * sigma);
   if (B == nullptr) {  // 1-D block: A is the (pop, k) noise
-    weighted_rows_kernel<<<grid_for(k), kThreads, 0, s>>>(fitness, A, pop, k, pop, inv_scale, grad);
+    launch_weighted_rows(fitness, A, pop, k, pop, inv_scale, grad, s);
   } else {
     EVOX_REQUIRE(d > 0 && r > 0 && r <= 64, EVOX_ERR_INVALID, "lora_gradient: rank must be in [1, 64], got %d", r);
     dim3 grid((unsigned)((k + 63) / 64), (unsigned)((d + 63) / 64));
@@ -424,7 +490,7 @@ extern "C" int evox_rank_weighted_moments(const float* x, const float* row_weigh
                                           int64_t dim, float* first, float* second, void* stream) {
   EVOX_REQUIRE(x && row_weights && first && second, EVOX_ERR_INVALID, "rank_weighted_moments: NULL pointer");
   EVOX_REQUIRE(pop > 0 && dim > 0, EVOX_ERR_INVALID, "rank_weighted_moments: sizes must be positive");
-  rank_weighted_moments_kernel<<<grid_for(dim), kThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(x, row_weights, shift, offset,
+  rank_weighted_moments_kernel<<<grid_for(dim, 32), kThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(x, row_weights, shift, offset,
                                                                                                    pop, dim, first, second);
   EVOX_LAUNCH_CHECK();
   return EVOX_OK;
@@ -436,8 +502,7 @@ extern "C" int evox_openes_gradient(const float* noise, const float* fitness, in
   EVOX_REQUIRE(pop > 0 && dim > 0 && (noise_rows == pop || 2 * noise_rows == pop), EVOX_ERR_INVALID,
                "openes_gradient: noise_rows must be pop or pop / 2");
   // grad = noise^T fitness / pop / sigma (open_es.py:70)
-  weighted_rows_kernel<<<grid_for(dim), kThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      fitness, noise, pop, dim, noise_rows, 1.0f / (float)pop / sigma, grad);
+  launch_weighted_rows(fitness, noise, pop, dim, noise_rows, 1.0f / (float)pop / sigma, grad, reinterpret_cast<cudaStream_t>(stream));
   EVOX_LAUNCH_CHECK();
   return EVOX_OK;
 }
