@@ -230,35 +230,57 @@ __global__ void __launch_bounds__(kThreads)
 //   first[l] = sum_i w[i] * x[i][l],   second[l] = sum_i w[i] * ((x[i][l] - shift[l])^2 + offset)
 // (snes.py:83-84 with shift = 0, offset = -1 on the noise; des.py:66-67 with shift = center, offset = 0 on the
 // population). w[i] is the weight of row i's fitness rank.
+template <int VEC>
 __global__ void __launch_bounds__(kThreads)
     rank_weighted_moments_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ shift, float offset,
                                  long long pop, long long n, float* __restrict__ first, float* __restrict__ second) {
-  // same decomposition as weighted_rows_kernel: 32 columns per block, rows dealt to the 8 warps
-  __shared__ float part[2][kThreads / 32][32];
+  // same decomposition as weighted_rows_kernel: a tile of 32 * VEC columns per block, rows dealt to the 8 warps
+  constexpr int kWarps = kThreads / 32, kTile = 32 * VEC;
+  __shared__ float part[2][kWarps][kTile];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  for (long long l0 = (long long)blockIdx.x * 32; l0 < n; l0 += (long long)gridDim.x * 32) {
-    const long long l = l0 + lane;
-    float a = 0.f, b = 0.f;
+  for (long long l0 = (long long)blockIdx.x * kTile; l0 < n; l0 += (long long)gridDim.x * kTile) {
+    const long long l = l0 + (long long)lane * VEC;
+    float a[VEC], b[VEC], sh[VEC];
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) {
+      a[j] = b[j] = 0.f;
+      sh[j] = (shift && l + j < n) ? shift[l + j] : 0.f;
+    }
     if (l < n) {
-      const float sh = shift ? shift[l] : 0.f;
-      for (long long i = warp; i < pop; i += kThreads / 32) {
-        const float v = x[i * n + l], wi = w[i];
-        const float dv = __fsub_rn(v, sh);
-        a = __fmaf_rn(wi, v, a);
-        b = __fmaf_rn(wi, __fadd_rn(__fmul_rn(dv, dv), offset), b);
+#pragma unroll 4
+      for (long long i = warp; i < pop; i += kWarps) {
+        const float wi = w[i];
+        float v[VEC];
+        if constexpr (VEC == 4) {
+          const float4 t = __ldg(reinterpret_cast<const float4*>(x + i * n + l));
+          v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+        } else {
+          v[0] = __ldg(x + i * n + l);
+        }
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) {
+          const float dv = __fsub_rn(v[j], sh[j]);
+          a[j] = __fmaf_rn(wi, v[j], a[j]);
+          b[j] = __fmaf_rn(wi, __fadd_rn(__fmul_rn(dv, dv), offset), b[j]);
+        }
       }
     }
-    part[0][warp][lane] = a;
-    part[1][warp][lane] = b;
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) {
+      part[0][warp][lane * VEC + j] = a[j];
+      part[1][warp][lane * VEC + j] = b[j];
+    }
     __syncthreads();
-    if (warp == 0 && l < n) {
-      float ta = part[0][0][lane], tb = part[1][0][lane];
-      for (int q = 1; q < kThreads / 32; ++q) {
-        ta += part[0][q][lane];
-        tb += part[1][q][lane];
+    for (int c = threadIdx.x; c < kTile; c += kThreads) {
+      if (l0 + c < n) {
+        float ta = part[0][0][c], tb = part[1][0][c];
+        for (int q = 1; q < kWarps; ++q) {
+          ta += part[0][q][c];
+          tb += part[1][q][c];
+        }
+        first[l0 + c] = ta;
+        second[l0 + c] = tb;
       }
-      first[l] = ta;
-      second[l] = tb;
     }
     __syncthreads();
   }
@@ -490,8 +512,11 @@ extern "C" int evox_rank_weighted_moments(const float* x, const float* row_weigh
                                           int64_t dim, float* first, float* second, void* stream) {
   EVOX_REQUIRE(x && row_weights && first && second, EVOX_ERR_INVALID, "rank_weighted_moments: NULL pointer");
   EVOX_REQUIRE(pop > 0 && dim > 0, EVOX_ERR_INVALID, "rank_weighted_moments: sizes must be positive");
-  rank_weighted_moments_kernel<<<grid_for(dim, 32), kThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(x, row_weights, shift, offset,
-                                                                                                   pop, dim, first, second);
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (dim % 4 == 0 && aligned16(x) && dim >= 128ll * sm_count())
+    rank_weighted_moments_kernel<4><<<grid_for(dim, 128), kThreads, 0, s>>>(x, row_weights, shift, offset, pop, dim, first, second);
+  else
+    rank_weighted_moments_kernel<1><<<grid_for(dim, 32), kThreads, 0, s>>>(x, row_weights, shift, offset, pop, dim, first, second);
   EVOX_LAUNCH_CHECK();
   return EVOX_OK;
 }

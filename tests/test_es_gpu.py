@@ -214,6 +214,30 @@ def test_snes_des_steps_golden(golden, cuda, tag):
     assert float(((wf.algorithm.center - shift) ** 2).sum()) < 0.2 * before
 
 
+@pytest.mark.parametrize("pop,dim", [(200, 1000), (64, 32768), (33, 20001), (7, 5)])
+def test_weighted_column_sums_vs_torch(cuda, pop, dim):
+    """Both tilings (32 columns, and float4 tiles of 128 for long aligned rows) of the two reductions behind
+    OpenES / ARS / PersistentES (noise^T fitness) and SNES / DES (two rank-weighted moments)."""
+    from evox_b200 import _cabi as c
+
+    g = torch.Generator().manual_seed(pop + dim)
+    x = torch.randn(pop, dim, generator=g).to(cuda)
+    w = torch.randn(pop, generator=g).to(cuda)
+    shift = torch.randn(dim, generator=g).to(cuda)
+    first, second = torch.empty(dim, device=cuda), torch.empty(dim, device=cuda)
+    for sh, off in ((None, -1.0), (shift, 0.0)):
+        c.check(c.lib.evox_rank_weighted_moments(c.ptr(x), c.ptr(w), c.ptr(sh), off, pop, dim, c.ptr(first), c.ptr(second), c.stream_ptr(cuda)))
+        xd, wd = x.double(), w.double()
+        close(first, (wd[:, None] * xd).sum(0).cpu())
+        dv = xd - (0 if sh is None else sh.double())
+        close(second, (wd[:, None] * (dv * dv + off)).sum(0).cpu())
+    if pop % 2 == 0:
+        grad = torch.empty(dim, device=cuda)
+        half = x[: pop // 2].contiguous()
+        c.check(c.lib.evox_openes_gradient(c.ptr(half), c.ptr(w), pop, dim, pop // 2, 0.25, c.ptr(grad), c.stream_ptr(cuda)))
+        close(grad, ((torch.cat([half, -half]).double().T @ w.double()) / pop / 0.25).cpu())
+
+
 def make_mlp(sizes, bias, gen):
     layers = []
     for i in range(len(sizes) - 1):
