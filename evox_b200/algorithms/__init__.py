@@ -1,4 +1,5 @@
 from .es import ARS, DES, SNES, OpenES, PersistentES, VirtualLoRAES
+from .hype import HypE
 from .mo import NSGA2, RVEA, RVEAa
 from .clpso import CLPSO
 from .cso import CSO
@@ -6,4 +7,4 @@ from .de import DE
 from .pso import PSO
 from .slpso import SLPSOGS, SLPSOUS
 
-__all__ = ["PSO", "CSO", "DE", "CLPSO", "SLPSOGS", "SLPSOUS", "OpenES", "ARS", "PersistentES", "SNES", "DES", "VirtualLoRAES", "NSGA2", "RVEA", "RVEAa"]
+__all__ = ["PSO", "CSO", "DE", "CLPSO", "SLPSOGS", "SLPSOUS", "OpenES", "ARS", "PersistentES", "SNES", "DES", "VirtualLoRAES", "NSGA2", "RVEA", "RVEAa", "HypE"]

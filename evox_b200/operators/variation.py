@@ -10,7 +10,7 @@ import torch
 
 from .. import _cabi
 
-__all__ = ["tournament_selection_multifit", "simulated_binary", "polynomial_mutation", "make_offspring"]
+__all__ = ["tournament_selection", "tournament_selection_multifit", "simulated_binary", "polynomial_mutation", "make_offspring"]
 
 CROSSOVER, MUTATION, CLAMP = 1, 2, 4
 
@@ -26,6 +26,12 @@ def tournament_selection_multifit(n_round: int, fitnesses: list[torch.Tensor], t
     _cabi.check(_cabi.lib.evox_tournament_multifit(_cabi.ptr(parents), n_round, tournament_size, _cabi.ptr(fit), fit.shape[0],
                                                    fit.shape[1], _cabi.ptr(out), _cabi.stream_ptr(dev)))
     return out
+
+
+def tournament_selection(n_round: int, fitness: torch.Tensor, tournament_size: int = 2, parents: torch.Tensor | None = None) -> torch.Tensor:
+    """The candidate with the smallest fitness of each round, the first one on ties
+    (tournament_selection.py:32-54): the multi-key kernel with one key."""
+    return tournament_selection_multifit(n_round, [fitness], tournament_size, parents)
 
 
 def make_offspring(pop: torch.Tensor, lb: torch.Tensor, ub: torch.Tensor, mating_pool: torch.Tensor | None = None,

@@ -215,6 +215,19 @@ int evox_de_trial(const float* pop, float* trial, float* trial_fit, const int64_
 int evox_de_select(const float* trial, const float* trial_fit, float* pop, float* fit, int64_t pop_size,
                    int32_t dim, void* stream);
 
+/* Monte-Carlo hypervolume contributions of HypE: replaces the table-building part of cal_hv
+ * (algorithms/mo/hype.py:28-38). fit (n x m) objective rows, samples (n_sample x m) sampling points,
+ * alpha (n) the weights of hype.py:14-24, volume a DEVICE scalar = prod(ref - f_min). For every sample s
+ * count_s = the number of rows with (fit - sample) <= 0 in every objective; then
+ *   hv[i] = (sum over the samples s that row i covers of alpha[count_s - 1]) * volume / n_sample.
+ * Nothing of size n x n_sample is stored; the counts are exact and the fp32 sum of one row's weights is
+ * taken in a fixed order (four interleaved chains per slice of samples, slices in order).
+ * 1 <= m <= 32. workspace: evox_hv_workspace_bytes(n, n_sample) bytes. */
+size_t evox_hv_workspace_bytes(int64_t n, int64_t n_sample);
+int evox_hv_contribution(const float* fit, const float* samples, const float* alpha, const float* volume,
+                         int64_t n, int32_t m, int64_t n_sample, float* hv, void* workspace,
+                         size_t workspace_bytes, void* stream);
+
 /* ------------------------------------------------------------------------------------------
  * P2. NSGA-II environmental selection.
  * ------------------------------------------------------------------------------------------ */

@@ -552,8 +552,64 @@ def golden_snes_des(out: dict):
             out[f"{tag}_z{k}"], out[f"{tag}_center{k + 1}"], out[f"{tag}_sigma{k + 1}"] = _np(z), _np(algo.center), _np(algo.sigma)
 
 
+def golden_hype(out: dict):
+    """cal_hv (algorithms/mo/hype.py:12-39) with its uniform draw recorded, on objective sets with duplicates
+    and with the population size given as a tensor (as the second call of HypE.step does); then HypE.init_step
+    and two teacher-forced HypE.step on DTLZ2 (every rand / randint result recorded in call order)."""
+    import evox.algorithms.mo.hype as hmod
+    from evox.problems.numerical import DTLZ2
+    from evox.workflows import StdWorkflow
+
+    g = torch.Generator().manual_seed(909)
+    cases = {"m3": (60, 3, 30, 500), "m2_tensor": (45, 2, torch.tensor(20), 300), "m6": (33, 6, 11, 257), "dup": (40, 3, 25, 400)}
+    for tag, (n, m, pop_size, n_sample) in cases.items():
+        fit = torch.rand(n, m, generator=g)
+        if tag == "dup":
+            fit = torch.round(fit * 4) / 4
+        ref = torch.full((m,), float(fit.max()) * 1.2)
+        draw = torch.rand(n_sample, m, generator=g)
+        real = torch.rand
+        hmod.torch.rand = lambda *a, **k: draw
+        try:
+            hv = hmod.cal_hv(fit, ref, pop_size, n_sample)
+        finally:
+            hmod.torch.rand = real
+        out[f"hv_{tag}_fit"], out[f"hv_{tag}_ref"], out[f"hv_{tag}_draw"], out[f"hv_{tag}_out"] = _np(fit), _np(ref), _np(draw), _np(hv)
+        out[f"hv_{tag}_pop_size"] = np.asarray(int(pop_size))
+
+    pop_size, d, m, n_sample = 24, 8, 3, 300
+    torch.manual_seed(31)
+    algo = hmod.HypE(pop_size, m, torch.zeros(d), torch.ones(d), n_sample=n_sample)
+    wf = StdWorkflow(algo, DTLZ2(d=d, m=m))
+    out["step_s0_pop"] = _np(wf.algorithm.state_dict()["pop"])
+    wf.init_step()
+    out["step_s1_fit"], out["step_ref"] = _np(wf.algorithm.state_dict()["fit"]), _np(wf.algorithm.state_dict()["ref"])
+    h = pop_size // 2
+    for it in range(2):
+        rec = {
+            "samples_a": torch.rand(n_sample, m, generator=g), "parents": torch.randint(0, pop_size, (pop_size, 2), generator=g),
+            "sbx_mu": torch.rand(h, d, generator=g), "sbx_sign": torch.randint(0, 2, (h, d), generator=g),
+            "sbx_half": torch.rand(h, d, generator=g), "sbx_pc": torch.rand(h, d, generator=g),
+            "pm_site": torch.rand(pop_size, d, generator=g) * 0.5, "pm_mu": torch.rand(pop_size, d, generator=g),
+            "samples_b": torch.rand(n_sample, m, generator=g),
+        }
+        rq = [rec[k] for k in ("samples_a", "sbx_mu", "sbx_half", "sbx_pc", "pm_site", "pm_mu", "samples_b")]
+        iq = [rec["parents"], rec["sbx_sign"]]
+        real_rand, real_randint = torch.rand, torch.randint
+        hmod.torch.rand = lambda *a, **k: rq.pop(0)
+        hmod.torch.randint = lambda *a, **k: iq.pop(0)
+        try:
+            wf.step()
+        finally:
+            hmod.torch.rand, hmod.torch.randint = real_rand, real_randint
+        assert not rq and not iq
+        for k, v in rec.items():
+            out[f"step_g{it}_{k}"] = _np(v)
+        out[f"step_g{it}_pop"], out[f"step_g{it}_fit"] = _np(wf.algorithm.state_dict()["pop"]), _np(wf.algorithm.state_dict()["fit"])
+
+
 GENERATORS = {"pso": golden_pso, "nds": golden_nds, "rvea": golden_rvea, "es": golden_es, "variation": golden_variation,
-              "cso": golden_cso, "ars": golden_ars, "clpso": golden_clpso, "pes": golden_pes, "slpso": golden_slpso, "rveaa": golden_rveaa, "de": golden_de, "snes_des": golden_snes_des}
+              "cso": golden_cso, "ars": golden_ars, "clpso": golden_clpso, "pes": golden_pes, "slpso": golden_slpso, "rveaa": golden_rveaa, "de": golden_de, "snes_des": golden_snes_des, "hype": golden_hype}
 
 
 def main():
