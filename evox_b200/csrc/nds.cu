@@ -20,8 +20,14 @@
 //                              witness position: the scan of its row resumes where it last found an
 //                              unranked dominator and never goes back, so each row of Dt is read
 //                              once in total (n^2 / 8 bytes), not once per front as the reference
-//                              does. A warp owns 32 columns; the mask is double buffered so one
-//                              bounded grid barrier separates two fronts.
+//                              does. A warp owns 32 columns; a lane whose witness left probes the
+//                              next 32 words of its row itself, the columns that need a longer scan
+//                              are queued per block and scanned by whichever warp is free; the mask
+//                              is double buffered so one bounded grid barrier separates two fronts.
+//   For 8192 rows or more the rows are first dealt into bins of descending first objective
+//   (nds_f1_range / bin_count / bin_scan / bin_scatter kernels): ranks do not depend on the row order,
+//   most tiles above the diagonal then need m - 1 comparisons per pair instead of 2 m, and a column's
+//   dominators all lie after its bin's first row.
 // Selection: histogram of ranks -> last admitted front -> per-objective stable radix sort of that
 // front -> neighbour gaps / range -> stable sorts by (rank) and (-crowding) -> gather.
 #include <math.h>
@@ -38,6 +44,8 @@ constexpr int kSortThreads = 1024;
 constexpr int kTileJ = 128;      // columns (dominated candidates) per dominance tile
 constexpr int kPad = 1024;       // population padded to a multiple of this (32 words = 128 B rows)
 constexpr unsigned kSpinLimit = 1u << 22;  // grid-barrier polls before giving up (~ seconds)
+constexpr int kBins = 4096;      // value bins of the first objective (row ordering for large populations)
+constexpr long long kOrderMinN = 8192;  // smaller populations have too few separated tiles to pay for the ordering
 
 // ---------------------------------------------------------------------------------------------
 // Workspace
@@ -55,7 +63,7 @@ struct Ctrl {
 };
 
 struct Layout {
-  size_t fs, dt, unranked, newfront, ptr, ctrl, hist, idx_a, key_a, idx_l, sortbuf, contrib, boundary, crowd, order, rank, total;
+  size_t fs, dt, unranked, newfront, ptr, ctrl, perm, bins, hist, idx_a, key_a, idx_l, sortbuf, contrib, boundary, crowd, order, rank, total;
   long long npad;
   int wp;
 };
@@ -77,6 +85,8 @@ Layout make_layout(long long n, int m, bool with_matrix) {
   L.unranked = take(sizeof(uint32_t) * L.wp);
   L.newfront = take(sizeof(uint32_t) * L.wp);
   L.ptr = take(sizeof(int) * (size_t)n);
+  L.perm = take(sizeof(uint32_t) * (size_t)n);
+  L.bins = take(sizeof(int) * (size_t)(2 * (kBins + 2) + 2));  // range keys, counts / offsets, cursors
   L.hist = take(sizeof(int) * (size_t)(n + 1));
   L.idx_a = take(sizeof(uint32_t) * (size_t)n);
   L.key_a = take(sizeof(uint32_t) * (size_t)n);
@@ -100,14 +110,107 @@ T* at(void* ws, size_t off) {
 // ---------------------------------------------------------------------------------------------
 // Rank
 // ---------------------------------------------------------------------------------------------
+// `perm` (optional): position p of the structure-of-arrays copy holds row perm[p].
 __global__ void nds_transpose_kernel(const float* __restrict__ f, long long n, int m, long long npad,
-                                     float* __restrict__ fs) {
+                                     const uint32_t* __restrict__ perm, float* __restrict__ fs) {
   const long long total = (long long)m * npad;
   for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
     const int k = (int)(t / npad);
     const long long i = t - (long long)k * npad;
-    fs[t] = (i < n) ? f[i * m + k] : __int_as_float(0x7fc00000);
+    fs[t] = (i < n) ? f[(perm ? (long long)perm[i] : i) * m + k] : __int_as_float(0x7fc00000);
   }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Row ordering for large populations. Ranks do not depend on the order of the rows, so the rows are
+// dealt into kBins value bins of the first objective (a counting sort: range, counts, offsets,
+// scatter, largest values first) and the matrix is built over that order. A row can only be dominated by
+// rows whose first objective is not larger, so most tiles above the diagonal then hold rows i whose
+// first objective lies strictly above that of every column j: there "i dominates j" is impossible and
+// "j dominates i" needs only the remaining m - 1 comparisons (nds_dominance_kernel tests this per tile, so any
+// order, also a poor one, gives the same bits). The order inside a bin is whatever the scatter's
+// atomics produce; the ranks, which is all that leaves the computation, do not depend on it.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t range_key(float x) {  // unsigned order = numeric order (finite values)
+  const uint32_t b = __float_as_uint(x);
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+__device__ __forceinline__ float range_value(uint32_t key) {
+  return __uint_as_float((key & 0x80000000u) ? (key ^ 0x80000000u) : ~key);
+}
+
+// range[0] = largest key of a finite first objective, range[1] = largest inverted key (= smallest value)
+__global__ void nds_f1_range_kernel(const float* __restrict__ f, long long n, int m, unsigned* range) {
+  unsigned hi = 0u, lo_inv = 0u;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const float x = f[i * m];
+    if (isfinite(x)) {
+      const unsigned key = range_key(x);
+      hi = max(hi, key);
+      lo_inv = max(lo_inv, ~key);
+    }
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    hi = max(hi, __shfl_xor_sync(0xffffffffu, hi, off));
+    lo_inv = max(lo_inv, __shfl_xor_sync(0xffffffffu, lo_inv, off));
+  }
+  if ((threadIdx.x & 31) == 0) {
+    if (hi) atomicMax(range, hi);
+    if (lo_inv) atomicMax(range + 1, lo_inv);
+  }
+}
+
+// Monotone DEcreasing in x: bins 0 .. kBins - 1 for numbers (+inf in the first, -inf in the last), kBins for
+// NaN. Large values come first, so the dominators of a row lie AFTER it and the peeling scan, which
+// walks a row of the matrix forward, meets the dominators nearest in the first objective first: those
+// tend to leave late, which keeps a column's witness alive for many fronts.
+__device__ __forceinline__ int f1_bin(float x, const unsigned* range) {
+  if (x != x) return kBins;
+  const float lo = range_value(~range[1]), hi = range_value(range[0]);
+  const float t = (x - lo) * ((float)kBins / (hi - lo));
+  const int up = t >= (float)kBins ? kBins - 1 : (t >= 0.f ? (int)t : 0);  // a NaN t (empty or zero range): 0
+  return kBins - 1 - up;
+}
+
+__global__ void nds_bin_count_kernel(const float* __restrict__ f, long long n, int m, const unsigned* __restrict__ range,
+                                     int* __restrict__ counts) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    atomicAdd(counts + f1_bin(f[i * m], range), 1);
+}
+
+// One block of 1024 threads: counts[0 .. kBins] -> exclusive offsets, copied to the scatter's cursors.
+__global__ void __launch_bounds__(1024) nds_bin_scan_kernel(int* __restrict__ counts, int* __restrict__ cursor) {
+  static_assert(kBins == 4096, "four bins per thread");
+  __shared__ int s_tot[1024];
+  const int t = threadIdx.x;
+  int c[4], sum = 0;
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    c[q] = counts[t * 4 + q];
+    sum += c[q];
+  }
+  s_tot[t] = sum;
+  __syncthreads();
+  for (int off = 1; off < 1024; off <<= 1) {
+    const int v = t >= off ? s_tot[t - off] : 0;
+    __syncthreads();
+    s_tot[t] += v;
+    __syncthreads();
+  }
+  int run = s_tot[t] - sum;
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    cursor[t * 4 + q] = run;
+    run += c[q];
+  }
+  if (t == 1023) cursor[kBins] = run;  // the NaN rows come last
+}
+
+__global__ void nds_bin_scatter_kernel(const float* __restrict__ f, long long n, int m, const unsigned* __restrict__ range,
+                                       int* __restrict__ cursor, uint32_t* __restrict__ perm) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    perm[atomicAdd(cursor + f1_bin(f[i * m], range), 1)] = (uint32_t)i;
 }
 
 // i dominates j: all(f_i <= f_j) and any(f_i < f_j) (non_dominate.py:20-24).
@@ -141,9 +244,14 @@ __device__ __forceinline__ void dominates_both(const float (&a)[M], const float 
 // dominators compute both directions of every pair at once and also emit the transposed bits
 // (row i, bits j); blocks whose columns all lie BEFORE their dominators have nothing left to do;
 // the blocks on the diagonal band compute the forward direction only, as every block used to.
+// `ordered` != 0 (rows dealt by their first objective, largest first): a block above the band first
+// compares the smallest first objective of its rows i with the largest one of its columns j; when the
+// latter is strictly smaller (and no NaN is involved) no i can dominate a j — zero words for the forward
+// direction — and "j dominates i" is all(f_j[k] <= f_i[k]) over the OTHER objectives: m - 1 comparisons
+// per pair instead of 2 m.
 template <int M, int R>
 __global__ void __launch_bounds__(kThreads)
-    nds_dominance_kernel(const float* __restrict__ fs, long long npad, long long n, uint32_t* __restrict__ Dt, int wp) {
+    nds_dominance_kernel(const float* __restrict__ fs, long long npad, long long n, uint32_t* __restrict__ Dt, int wp, int ordered) {
   constexpr int kWords = 8 * R;         // words of dominators per block (8 warps x R)
   constexpr int kRows = 32 * kWords;    // dominators per block
   __shared__ float sfj[M][kTileJ];
@@ -168,7 +276,57 @@ __global__ void __launch_bounds__(kThreads)
     sfj[k][jj] = (j < n) ? fs[(long long)k * npad + j] : __int_as_float(0x7fc00000);
   }
   __syncthreads();
-  if (!both) {
+  bool separated = false;
+  if (ordered && both) {  // block-uniform
+    __shared__ float s_imin[kThreads / 32], s_jmax[kThreads / 32];
+    float imin = INFINITY, jmax = -INFINITY;
+    int bad = 0;
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      bad |= (fi[r][0] != fi[r][0]);
+      imin = fminf(imin, fi[r][0]);
+    }
+    if (threadIdx.x < kTileJ) {
+      jmax = sfj[0][threadIdx.x];
+      bad |= (jmax != jmax);
+    }
+    bad = __syncthreads_or(bad);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+      imin = fminf(imin, __shfl_xor_sync(0xffffffffu, imin, off));
+      jmax = fmaxf(jmax, __shfl_xor_sync(0xffffffffu, jmax, off));
+    }
+    if (lane == 0) s_imin[warp] = imin, s_jmax[warp] = jmax;
+    __syncthreads();
+#pragma unroll
+    for (int w = 0; w < kThreads / 32; ++w) imin = fminf(imin, s_imin[w]), jmax = fmaxf(jmax, s_jmax[w]);
+    separated = !bad && jmax < imin;
+  }
+  if (separated) {
+    uint32_t back[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) back[r] = 0u;
+#pragma unroll 4
+    for (int jj = 0; jj < kTileJ; ++jj) {
+      float fj[M];
+#pragma unroll
+      for (int k = 1; k < M; ++k) fj[k] = sfj[k][jj];
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        bool le = true;
+#pragma unroll
+        for (int k = 1; k < M; ++k) le = le && (fj[k] <= fi[r][k]);
+        back[r] |= (uint32_t)le << (jj & 31);
+      }
+      if ((jj & 31) == 31) {
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          sback[jj >> 5][(warp * R + r) * 32 + lane] = back[r];
+          back[r] = 0u;
+        }
+      }
+    }
+  } else if (!both) {
 #pragma unroll 4
     for (int jj = 0; jj < kTileJ; ++jj) {
       float fj[M];
@@ -211,7 +369,7 @@ __global__ void __launch_bounds__(kThreads)
   for (int t = threadIdx.x; t < kTileJ * kWords; t += kThreads) {
     const int jj = t / kWords, w = t - jj * kWords;
     const long long j = j0 + jj;
-    if (j < n && w0 + w < wp) Dt[j * wp + w0 + w] = sout[jj][w];
+    if (j < n && w0 + w < wp) Dt[j * wp + w0 + w] = separated ? 0u : sout[jj][w];
   }
   if (both) {
     // row i of Dt, the four words that hold columns j0 .. j0 + 127 (16-byte aligned: j0 is a multiple of 128)
@@ -248,8 +406,12 @@ __global__ void __launch_bounds__(kThreads)
   }
 }
 
+// `bin_end` (optional, with `f1` = the first objective in matrix order and `range`): the rows were dealt
+// by descending first objective and bin_end[b] is one past the last position of bin b. Every dominator of
+// a column lies in the column's own bin or a later one, so its scan starts at its bin's first word.
 __global__ void nds_peel_init_kernel(long long n, int wp, uint32_t* unranked, uint32_t* unranked_alt, int* ptr, int* rank,
-                                     Ctrl* ctrl) {
+                                     Ctrl* ctrl, const float* __restrict__ f1, const unsigned* __restrict__ range,
+                                     const int* __restrict__ bin_end) {
   const long long t0 = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long w = t0; w < wp; w += stride) {
@@ -261,7 +423,12 @@ __global__ void nds_peel_init_kernel(long long n, int wp, uint32_t* unranked, ui
     unranked_alt[w] = bits;
   }
   for (long long j = t0; j < n; j += stride) {
-    ptr[j] = 0;
+    int start = 0;
+    if (bin_end) {
+      const int b = f1_bin(f1[j], range);
+      start = b ? bin_end[b - 1] : 0;
+    }
+    ptr[j] = start >> 5;
     rank[j] = -1;
   }
   if (t0 == 0) {
@@ -323,14 +490,20 @@ __device__ __forceinline__ int first_nonzero(const uint4& v) {
 // U[k & 1] as a snapshot and the owner of a word writes its successor into U[(k + 1) & 1], so one
 // grid barrier per front is enough and no atomics touch the masks. Each lane first re-tests its
 // column's witness word (where the last scan stopped); only columns whose witness cleared are
-// scanned on, 1024 words per step with 128-bit loads, and never backwards: over all fronts a row of
-// Dt is read once.
+// scanned on, and never backwards: over all fronts a row of Dt is read once. Measured per front at
+// 100,000 rows: about 1.4 us for the barrier itself, the rest is the slowest block's scans (late fronts:
+// few unranked rows are left, so the next unranked dominator of a column is far away).
 __global__ void __launch_bounds__(kThreads)
     nds_peel_kernel(const uint32_t* __restrict__ Dt, int wp, long long n, uint32_t* U0, uint32_t* U1, int* ptr,
-                    int* rank, Ctrl* ctrl, int mask_in_smem) {
+                    int* rank, Ctrl* ctrl, int mask_in_smem, const uint32_t* __restrict__ perm) {
   extern __shared__ __align__(16) uint32_t s_mask[];
   __shared__ unsigned s_cnt[kThreads / 32];
-  const int lane = threadIdx.x & 31;
+  __shared__ unsigned s_newly[kThreads / 32];  // per owning warp: columns ranked in this trip
+  __shared__ long long s_qj[kThreads];         // block queue of columns waiting for a warp-wide scan
+  __shared__ int s_qc[kThreads];
+  __shared__ unsigned short s_qowner[kThreads];
+  __shared__ int s_qn;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const long long gwarp = ((long long)blockIdx.x * kThreads + threadIdx.x) >> 5;
   const long long n_warps = ((long long)gridDim.x * kThreads) >> 5;
   const long long n_words = (n + 31) >> 5;
@@ -348,8 +521,15 @@ __global__ void __launch_bounds__(kThreads)
       Rs = s_mask;
     }
     unsigned ranked_here = 0;
-    for (long long wj = gwarp; wj < n_words; wj += n_warps) {
-      const uint32_t own = mask_word(Rs, (int)wj, mask_in_smem);
+    // Every warp of the block makes the same number of trips (the block synchronises inside).
+    const long long trips = (n_words + n_warps - 1) / n_warps;
+    for (long long trip = 0; trip < trips; ++trip) {
+      const long long wj = gwarp + trip * n_warps;
+      const bool have = wj < n_words;
+      if (threadIdx.x == 0) s_qn = 0;
+      if (lane == 0) s_newly[warp] = 0u;
+      __syncthreads();
+      const uint32_t own = have ? mask_word(Rs, (int)wj, mask_in_smem) : 0u;
       const long long j = wj * 32 + lane;
       const bool open = (own >> lane) & 1u;  // this lane's column is still unranked
       int c = 0;
@@ -358,16 +538,47 @@ __global__ void __launch_bounds__(kThreads)
         c = __ldcg(ptr + j);
         blocked = (__ldg(Dt + j * wp + c) & mask_word(Rs, c, mask_in_smem)) != 0u;
       }
-      unsigned todo = __ballot_sync(0xffffffffu, open && !blocked);
-      unsigned newly = 0;
-      while (todo) {
-        const int l = __ffs(todo) - 1;
-        todo &= todo - 1;
-        const long long jl = wj * 32 + l;
-        const int cl = __shfl_sync(0xffffffffu, c, l);
+      // Columns whose witness left: every such lane first probes the next 32 words of its own row by itself
+      // (eight independent 128-bit loads), which settles the columns with plenty of dominators left in one
+      // memory round trip for the whole warp. The others are queued for the block: the warp-wide scans of
+      // a front's new members would otherwise pile up in the few warps that own them.
+      if (open && !blocked) {
+        const int c4 = c & ~3;
+        const uint4* row4 = reinterpret_cast<const uint4*>(Dt + j * wp);
+        uint4 d[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          const int w = c4 + q * 4;
+          d[q] = (w < wp) ? __ldg(row4 + (w >> 2)) : make_uint4(0, 0, 0, 0);
+        }
+        int hit = -1;
+#pragma unroll
+        for (int q = 7; q >= 0; --q) {
+          const int w = c4 + q * 4;
+          if (w < wp) {
+            const uint4 u = mask_quad(Rs, w, mask_in_smem);
+            const int f = first_nonzero(make_uint4(d[q].x & u.x, d[q].y & u.y, d[q].z & u.z, d[q].w & u.w));
+            if (f >= 0) hit = w + f;
+          }
+        }
+        if (hit >= 0) {
+          ptr[j] = hit;
+        } else {
+          const int slot = atomicAdd(&s_qn, 1);
+          s_qj[slot] = j;
+          s_qc[slot] = min(c4 + 32, wp - 1);  // nothing up to here: the scan may skip these words
+          s_qowner[slot] = (unsigned short)threadIdx.x;
+        }
+      }
+      __syncthreads();
+      const int qn = s_qn;
+      for (int item = warp; item < qn; item += kThreads / 32) {
+        const long long jl = s_qj[item];
+        const int cl = s_qc[item];
         const uint4* row4 = reinterpret_cast<const uint4*>(Dt + jl * wp);
         int found = -1;
-        // 1024 words per step: eight independent 128-bit loads per lane are in flight together
+        // 1024 words per step: eight independent 128-bit loads per lane are in flight together. (Issuing the
+        // next step's loads before examining this one was measured slower: more registers, same waits.)
         for (int base = (cl & ~1023); base < wp && found < 0; base += 1024) {
           uint4 d[8];
 #pragma unroll
@@ -390,14 +601,19 @@ __global__ void __launch_bounds__(kThreads)
             }
           }
         }
-        if (found >= 0) {
-          if (lane == 0) ptr[jl] = found;
-        } else {
-          newly |= 1u << l;
-          if (lane == 0) rank[jl] = k;
+        if (lane == 0) {
+          if (found >= 0) {
+            ptr[jl] = found;
+          } else {
+            const unsigned owner = s_qowner[item];
+            atomicOr(&s_newly[owner >> 5], 1u << (owner & 31));
+            rank[perm ? (long long)perm[jl] : jl] = k;  // column jl of the matrix is row perm[jl]
+          }
         }
       }
-      if (lane == 0) W[wj] = own & ~newly;
+      __syncthreads();
+      const unsigned newly = s_newly[warp];
+      if (lane == 0 && have) W[wj] = own & ~newly;
       ranked_here += __popc(newly);
     }
     if (lane == 0) s_cnt[threadIdx.x >> 5] = ranked_here;
@@ -786,10 +1002,10 @@ __global__ void nds_gather_kernel(const uint32_t* __restrict__ order, long long 
 // Host side
 // ---------------------------------------------------------------------------------------------
 template <int M>
-void launch_dominance(const float* fs, long long npad, long long n, uint32_t* Dt, int wp, cudaStream_t s) {
+void launch_dominance(const float* fs, long long npad, long long n, uint32_t* Dt, int wp, int ordered, cudaStream_t s) {
   constexpr int R = (M <= 4) ? 4 : ((M <= 8) ? 2 : 1);
   dim3 grid((unsigned)((n + kTileJ - 1) / kTileJ), (unsigned)((npad + 256 * R - 1) / (256 * R)));
-  nds_dominance_kernel<M, R><<<grid, kThreads, 0, s>>>(fs, npad, n, Dt, wp);
+  nds_dominance_kernel<M, R><<<grid, kThreads, 0, s>>>(fs, npad, n, Dt, wp, ordered);
 }
 
 int grid_1d(long long work, int per_block = kThreads) {
@@ -805,10 +1021,26 @@ int run_rank(const float* f, long long n, int m, int* rank, void* ws, const Layo
   uint32_t* unranked = at<uint32_t>(ws, L.unranked);
   uint32_t* newfront = at<uint32_t>(ws, L.newfront);
   int* ptr = at<int>(ws, L.ptr);
-  nds_transpose_kernel<<<grid_1d((long long)m * L.npad), kThreads, 0, s>>>(f, n, m, L.npad, fs);
+  // large populations: deal the rows by their first objective (see nds_f1_range_kernel)
+  const uint32_t* perm = nullptr;
+  if (n >= kOrderMinN && m <= 16) {
+    unsigned* range = at<unsigned>(ws, L.bins);
+    int* counts = reinterpret_cast<int*>(range + 2);
+    int* cursor = counts + (kBins + 2);
+    uint32_t* perm_w = at<uint32_t>(ws, L.perm);
+    EVOX_CUDA(cudaMemsetAsync(range, 0, sizeof(int) * (size_t)(2 * (kBins + 2) + 2), s));
+    nds_f1_range_kernel<<<grid_1d(n), kThreads, 0, s>>>(f, n, m, range);
+    nds_bin_count_kernel<<<grid_1d(n), kThreads, 0, s>>>(f, n, m, range, counts);
+    nds_bin_scan_kernel<<<1, 1024, 0, s>>>(counts, cursor);
+    nds_bin_scatter_kernel<<<grid_1d(n), kThreads, 0, s>>>(f, n, m, range, cursor, perm_w);
+    EVOX_LAUNCH_CHECK();
+    perm = perm_w;
+  }
+  const int ordered = perm != nullptr;
+  nds_transpose_kernel<<<grid_1d((long long)m * L.npad), kThreads, 0, s>>>(f, n, m, L.npad, perm, fs);
   EVOX_LAUNCH_CHECK();
   switch (m) {
-#define EVOX_DOM(MM) case MM: launch_dominance<MM>(fs, L.npad, n, Dt, L.wp, s); break;
+#define EVOX_DOM(MM) case MM: launch_dominance<MM>(fs, L.npad, n, Dt, L.wp, ordered, s); break;
     EVOX_DOM(1) EVOX_DOM(2) EVOX_DOM(3) EVOX_DOM(4) EVOX_DOM(5) EVOX_DOM(6) EVOX_DOM(7) EVOX_DOM(8)
     EVOX_DOM(9) EVOX_DOM(10) EVOX_DOM(11) EVOX_DOM(12) EVOX_DOM(13) EVOX_DOM(14) EVOX_DOM(15) EVOX_DOM(16)
 #undef EVOX_DOM
@@ -816,7 +1048,12 @@ int run_rank(const float* f, long long n, int m, int* rank, void* ws, const Layo
       nds_dominance_generic_kernel<<<grid_1d(n * (long long)L.wp), kThreads, 0, s>>>(fs, L.npad, n, m, Dt, L.wp);
   }
   EVOX_LAUNCH_CHECK();
-  nds_peel_init_kernel<<<grid_1d(n), kThreads, 0, s>>>(n, L.wp, unranked, newfront, ptr, rank, ctrl);
+  {
+    const unsigned* range = at<unsigned>(ws, L.bins);
+    const int* bin_end = reinterpret_cast<const int*>(range + 2) + (kBins + 2);  // the scatter's cursors, now at the bin ends
+    nds_peel_init_kernel<<<grid_1d(n), kThreads, 0, s>>>(n, L.wp, unranked, newfront, ptr, rank, ctrl, fs, range,
+                                                         ordered ? bin_end : nullptr);
+  }
   EVOX_LAUNCH_CHECK();
   // persistent cooperative grid: every block must be resident for the grid barrier
   int per_sm = 0;
@@ -836,7 +1073,7 @@ int run_rank(const float* f, long long n, int m, int* rank, void* ws, const Layo
   int wp = L.wp;
   long long nn = n;
   void* args[] = {(void*)&Dt_c, (void*)&wp, (void*)&nn, (void*)&unranked, (void*)&newfront, (void*)&ptr, (void*)&rank, (void*)&ctrl,
-                  (void*)&mask_in_smem};
+                  (void*)&mask_in_smem, (void*)&perm};
   EVOX_CUDA(cudaLaunchCooperativeKernel((const void*)nds_peel_kernel, dim3((unsigned)blocks), dim3(kThreads), args, mask_bytes, s));
   return EVOX_OK;
 }

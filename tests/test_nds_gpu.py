@@ -63,6 +63,39 @@ def test_rank_many_objectives(cuda, m):
     assert torch.equal(got.cpu(), nds.non_dominate_rank(f))
 
 
+@pytest.mark.parametrize("case", ["ties", "nan_inf", "flat_first", "m1", "m2", "m5", "narrow_range", "huge_range"])
+def test_rank_ordered_rows_edge_cases(cuda, case):
+    """Populations of 8192 rows or more are dealt into bins of their first objective before the matrix is
+    built; the ranks must not notice: duplicates and ties in the first objective, NaN / +-inf there, a
+    constant first objective (one bin), one objective only, ranges that collapse or overflow the bins."""
+    from evox_b200.operators.selection import non_dominate_rank
+
+    n = 8700
+    gen = torch.Generator().manual_seed(len(case))
+    m = {"m1": 1, "m2": 2, "m5": 5}.get(case, 3)
+    f = torch.rand(n, m, generator=gen)
+    if case == "ties":
+        f = torch.round(f * 20) / 20
+    elif case == "nan_inf":
+        f[torch.randperm(n, generator=gen)[:300], 0] = float("nan")
+        f[torch.randperm(n, generator=gen)[:200], 0] = float("inf")
+        f[torch.randperm(n, generator=gen)[:200], 0] = float("-inf")
+        f[torch.randperm(n, generator=gen)[:100], 1] = float("nan")
+        f[5] = float("nan")
+    elif case == "flat_first":
+        f[:, 0] = 0.25
+    elif case == "m1":
+        f = torch.round(f * 500) / 500
+    elif case == "narrow_range":
+        f[:, 0] = 1.0 + torch.randint(0, 3, (n,), generator=gen) * 1.1920929e-07  # three adjacent floats
+    elif case == "huge_range":
+        f[:, 0] = (f[:, 0] - 0.5) * 6e38  # hi - lo overflows to inf
+        f[::7, 0] = 0.0
+        f[1::7, 0] = -0.0
+    got = non_dominate_rank(f.to(cuda), check=True)
+    assert torch.equal(got.cpu(), nds.non_dominate_rank(f))
+
+
 def test_chain_has_n_fronts(cuda):
     """A totally ordered set: n fronts of one row each — the worst case for the peeling loop."""
     from evox_b200.operators.selection import non_dominate_rank
