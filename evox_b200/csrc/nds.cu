@@ -504,7 +504,9 @@ __global__ void __launch_bounds__(kThreads)
   __shared__ unsigned short s_qowner[kThreads];
   __shared__ int s_qn;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const long long gwarp = ((long long)blockIdx.x * kThreads + threadIdx.x) >> 5;
+  // Words of 32 columns are dealt to the blocks first and to a block's warps second (word = block +
+  // blocks * (warp + 8 * trip)): with fewer words than warps every block still owns some, and its
+  // other warps help with the block's queue of long scans.
   const long long n_warps = ((long long)gridDim.x * kThreads) >> 5;
   const long long n_words = (n + 31) >> 5;
   long long remaining = n;
@@ -524,7 +526,7 @@ __global__ void __launch_bounds__(kThreads)
     // Every warp of the block makes the same number of trips (the block synchronises inside).
     const long long trips = (n_words + n_warps - 1) / n_warps;
     for (long long trip = 0; trip < trips; ++trip) {
-      const long long wj = gwarp + trip * n_warps;
+      const long long wj = (long long)blockIdx.x + (long long)gridDim.x * (warp + (kThreads / 32) * trip);
       const bool have = wj < n_words;
       if (threadIdx.x == 0) s_qn = 0;
       if (lane == 0) s_newly[warp] = 0u;
@@ -584,7 +586,7 @@ __global__ void __launch_bounds__(kThreads)
 #pragma unroll
           for (int q = 0; q < 8; ++q) {
             const int w = base + q * 128 + lane * 4;
-            d[q] = (w < wp) ? __ldg(row4 + (w >> 2)) : make_uint4(0, 0, 0, 0);
+            d[q] = (w < wp && w + 4 > cl) ? __ldg(row4 + (w >> 2)) : make_uint4(0, 0, 0, 0);  // words before cl are done
           }
 #pragma unroll
           for (int q = 0; q < 8; ++q) {
@@ -1067,7 +1069,7 @@ int run_rank(const float* f, long long n, int m, int* rank, void* ws, const Layo
   EVOX_REQUIRE(per_sm > 0, EVOX_ERR_CUDA, "nds_peel_kernel cannot be made resident");
   if (per_sm > 4) per_sm = 4;
   long long blocks = (long long)sm_count() * per_sm;
-  const long long useful = ((n + 31) / 32 + kThreads / 32 - 1) / (kThreads / 32);  // one warp per 32 columns
+  const long long useful = (n + 31) / 32;  // at least one word of 32 columns per block
   if (blocks > useful) blocks = useful < 1 ? 1 : useful;
   const uint32_t* Dt_c = Dt;
   int wp = L.wp;
