@@ -3,8 +3,9 @@
 // Reference semantics: cal_hv (evox/algorithms/mo/hype.py:12-39). For n objective rows and n_sample
 // sampling points the reference materialises the (n_sample, n) table "row i is <= sample s in every
 // objective" twice (as bool and as int64) and gathers alpha through it; here the table is never stored:
-//   hv_sample_weight_kernel   count_s = #rows that cover sample s; weight_s = alpha[count_s - 1] (0 if none)
-//   hv_row_sum_kernel         partial[slice][i] = sum of weight_s over the samples of the slice covered by row i
+//   hv_sample_count_kernel    count_s = #rows that cover sample s (row slices on grid y, integer atomics)
+//   hv_row_sum_kernel         partial[slice][i] = sum of weight_s = alpha[count_s - 1] (0 if nobody covers s)
+//                             over the samples of the slice covered by row i
 //   hv_finish_kernel          hv[i] = (sum over slices, in slice order) * volume / n_sample
 // The counts are integers and the cover test is the reference's (f - s) <= 0 in fp32, so the only
 // difference from the reference is the order in which the fp32 weights of one row are added.
@@ -49,11 +50,13 @@ struct Point<0> {
   __device__ __forceinline__ float get(int k) const { return p[(size_t)k * stride]; }
 };
 
-// rows: tile[k * tile_rows + i] (structure of arrays, so that a warp reads consecutive words)
+// rows: tile[k * tile_rows + i] (structure of arrays, so that a warp reads consecutive words).
+// blockIdx.y takes a slice of the rows; the integer counts of the slices meet in `count` (zeroed by the
+// caller) with atomicAdd, which is exact in any order.
 template <int M>
-__global__ void __launch_bounds__(kThreads) hv_sample_weight_kernel(const float* __restrict__ fit, const float* __restrict__ samples,
-                                                                    const float* __restrict__ alpha, long long n, int m_rt,
-                                                                    long long n_sample, float* __restrict__ weight) {
+__global__ void __launch_bounds__(kThreads) hv_sample_count_kernel(const float* __restrict__ fit, const float* __restrict__ samples,
+                                                                   long long n, int m_rt, long long n_sample, long long rows_per_slice,
+                                                                   int* __restrict__ count) {
   extern __shared__ __align__(16) float smem[];
   const int m = M ? M : m_rt;
   const int tile_rows = row_tile(m);
@@ -69,9 +72,11 @@ __global__ void __launch_bounds__(kThreads) hv_sample_weight_kernel(const float*
   Point<M> pt[kSamplesPerWarp];
 #pragma unroll
   for (int j = 0; j < kSamplesPerWarp; ++j) pt[j].load(smp + (warp * kSamplesPerWarp + j) * m, 1, m);
-  int count[kSamplesPerWarp] = {0, 0, 0, 0};
-  for (long long r0 = 0; r0 < n; r0 += tile_rows) {
-    const int rows = (int)((n - r0) < tile_rows ? (n - r0) : tile_rows);
+  int cnt[kSamplesPerWarp] = {0, 0, 0, 0};
+  const long long r_begin = (long long)blockIdx.y * rows_per_slice;
+  const long long r_end = (r_begin + rows_per_slice) < n ? (r_begin + rows_per_slice) : n;
+  for (long long r0 = r_begin; r0 < r_end; r0 += tile_rows) {
+    const int rows = (int)((r_end - r0) < tile_rows ? (r_end - r0) : tile_rows);
     __syncthreads();
     for (int e = threadIdx.x; e < rows * m; e += kThreads) {
       const int i = e / m, k = e - i * m;
@@ -80,24 +85,29 @@ __global__ void __launch_bounds__(kThreads) hv_sample_weight_kernel(const float*
     __syncthreads();
     for (int i = lane; i < rows; i += 32) {
       bool ok[kSamplesPerWarp] = {true, true, true, true};
-#pragma unroll 4
-      for (int k = 0; k < m; ++k) {
+      auto test = [&](int k) {
         const float f = tile[k * tile_rows + i];
 #pragma unroll
         for (int j = 0; j < kSamplesPerWarp; ++j) ok[j] &= (__fsub_rn(f, pt[j].get(k)) <= 0.f);  // no short circuit: no branches
+      };
+      if constexpr (M > 0) {
+#pragma unroll
+        for (int k = 0; k < M; ++k) test(k);
+      } else {
+#pragma unroll 4
+        for (int k = 0; k < m; ++k) test(k);
       }
 #pragma unroll
-      for (int j = 0; j < kSamplesPerWarp; ++j) count[j] += ok[j] ? 1 : 0;
+      for (int j = 0; j < kSamplesPerWarp; ++j) cnt[j] += ok[j] ? 1 : 0;
     }
   }
 #pragma unroll
   for (int j = 0; j < kSamplesPerWarp; ++j) {
-    int c = count[j];
+    int c = cnt[j];
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) c += __shfl_xor_sync(0xffffffffu, c, off);
     const long long s = s_block + warp * kSamplesPerWarp + j;
-    // hype.py:32-35: ds - 1 where ds > 0, then alpha[ds]; a sample nobody covers adds nothing
-    if (lane == 0 && s < n_sample) weight[s] = c > 0 ? alpha[c - 1] : 0.f;
+    if (lane == 0 && s < n_sample && c) atomicAdd(count + s, c);
   }
 }
 
@@ -109,8 +119,9 @@ __host__ __device__ constexpr int sample_stride(int M, int m) { return M ? ((M +
 // staged sample at the same time (shared-memory broadcast).
 template <int M>
 __global__ void __launch_bounds__(kThreads) hv_row_sum_kernel(const float* __restrict__ fit, const float* __restrict__ samples,
-                                                              const float* __restrict__ weight, long long n, int m_rt,
-                                                              long long n_sample, long long slice_len, float* __restrict__ partial) {
+                                                              const int* __restrict__ count, const float* __restrict__ alpha,
+                                                              long long n, int m_rt, long long n_sample, long long slice_len,
+                                                              float* __restrict__ partial) {
   extern __shared__ __align__(16) float smem[];
   const int m = M ? M : m_rt;
   const int stride = sample_stride(M, m);
@@ -134,7 +145,15 @@ __global__ void __launch_bounds__(kThreads) hv_row_sum_kernel(const float* __res
     __syncthreads();
     for (int e = threadIdx.x; e < cnt * stride; e += kThreads) {
       const int s = e / stride, k = e - s * stride;
-      tile[e] = k < m ? samples[(s0 + s) * m + k] : (k == m ? weight[s0 + s] : 0.f);
+      float v = 0.f;
+      if (k < m) {
+        v = samples[(s0 + s) * m + k];
+      } else if (k == m) {
+        // hype.py:32-35: ds - 1 where ds > 0, then alpha[ds]; a sample nobody covers adds nothing
+        const int c = count[s0 + s];
+        v = c > 0 ? alpha[c - 1] : 0.f;
+      }
+      tile[e] = v;
     }
     __syncthreads();
     // four accumulators dealt by sample number inside the tile: short chains, fixed order
@@ -191,15 +210,22 @@ int slices_for(long long n, long long n_sample) {
 
 template <int M>
 void launch_hv(const float* fit, const float* samples, const float* alpha, const float* volume, long long n, int m, long long n_sample,
-               float* hv, float* weight, float* partial, int slices, cudaStream_t s) {
+               float* hv, int* count, float* partial, int slices, cudaStream_t s) {
   const size_t smem1 = ((size_t)m * row_tile(m) + (size_t)kSamplesPerBlock * m) * sizeof(float);
   const size_t smem2 = (size_t)kTileFloats * sizeof(float);
-  if (smem1 > 48 * 1024) cudaFuncSetAttribute(hv_sample_weight_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1);
-  const unsigned g1 = (unsigned)((n_sample + kSamplesPerBlock - 1) / kSamplesPerBlock);
-  hv_sample_weight_kernel<M><<<g1, kThreads, smem1, s>>>(fit, samples, alpha, n, m, n_sample, weight);
+  if (smem1 > 48 * 1024) cudaFuncSetAttribute(hv_sample_count_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1);
+  const long long g1 = (n_sample + kSamplesPerBlock - 1) / kSamplesPerBlock;
+  // enough blocks for four per multiprocessor, but no row slice shorter than one staged tile
+  long long row_slices = (4LL * sm_count() + g1 - 1) / g1;
+  const long long max_slices = (n + row_tile(m) - 1) / row_tile(m);
+  row_slices = row_slices > max_slices ? max_slices : row_slices;
+  row_slices = row_slices > 65535 ? 65535 : (row_slices < 1 ? 1 : row_slices);
+  const long long rows_per_slice = (n + row_slices - 1) / row_slices;
+  cudaMemsetAsync(count, 0, sizeof(int) * (size_t)n_sample, s);
+  hv_sample_count_kernel<M><<<dim3((unsigned)g1, (unsigned)row_slices), kThreads, smem1, s>>>(fit, samples, n, m, n_sample, rows_per_slice, count);
   const long long slice_len = (n_sample + slices - 1) / slices;
   const dim3 g2((unsigned)((n + kThreads - 1) / kThreads), (unsigned)slices);
-  hv_row_sum_kernel<M><<<g2, kThreads, smem2, s>>>(fit, samples, weight, n, m, n_sample, slice_len, partial);
+  hv_row_sum_kernel<M><<<g2, kThreads, smem2, s>>>(fit, samples, count, alpha, n, m, n_sample, slice_len, partial);
   hv_finish_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(partial, slices, n, volume, n_sample, hv);
 }
 
@@ -219,16 +245,19 @@ extern "C" int evox_hv_contribution(const float* fit, const float* samples, cons
   EVOX_REQUIRE(n > 0 && n_sample > 0, EVOX_ERR_INVALID, "hv_contribution: sizes must be positive");
   EVOX_REQUIRE(m >= 1 && m <= kMaxObjectives, EVOX_ERR_INVALID, "hv_contribution: 1 <= m <= %d objectives, got %d", kMaxObjectives, m);
   EVOX_REQUIRE(workspace_bytes >= evox_hv_workspace_bytes(n, n_sample), EVOX_ERR_WORKSPACE, "hv_contribution: workspace too small");
-  float* weight = static_cast<float*>(workspace);
-  float* partial = weight + n_sample;
+  int* count = static_cast<int*>(workspace);
+  float* partial = reinterpret_cast<float*>(count + n_sample);
   const int slices = slices_for(n, n_sample);
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   switch (m) {
-    case 2: launch_hv<2>(fit, samples, alpha, volume, n, m, n_sample, hv, weight, partial, slices, s); break;
-    case 3: launch_hv<3>(fit, samples, alpha, volume, n, m, n_sample, hv, weight, partial, slices, s); break;
-    case 4: launch_hv<4>(fit, samples, alpha, volume, n, m, n_sample, hv, weight, partial, slices, s); break;
-    case 5: launch_hv<5>(fit, samples, alpha, volume, n, m, n_sample, hv, weight, partial, slices, s); break;
-    default: launch_hv<0>(fit, samples, alpha, volume, n, m, n_sample, hv, weight, partial, slices, s); break;
+    case 2: launch_hv<2>(fit, samples, alpha, volume, n, m, n_sample, hv, count, partial, slices, s); break;
+    case 3: launch_hv<3>(fit, samples, alpha, volume, n, m, n_sample, hv, count, partial, slices, s); break;
+    case 4: launch_hv<4>(fit, samples, alpha, volume, n, m, n_sample, hv, count, partial, slices, s); break;
+    case 5: launch_hv<5>(fit, samples, alpha, volume, n, m, n_sample, hv, count, partial, slices, s); break;
+    case 6: launch_hv<6>(fit, samples, alpha, volume, n, m, n_sample, hv, count, partial, slices, s); break;
+    case 7: launch_hv<7>(fit, samples, alpha, volume, n, m, n_sample, hv, count, partial, slices, s); break;
+    case 8: launch_hv<8>(fit, samples, alpha, volume, n, m, n_sample, hv, count, partial, slices, s); break;
+    default: launch_hv<0>(fit, samples, alpha, volume, n, m, n_sample, hv, count, partial, slices, s); break;
   }
   EVOX_LAUNCH_CHECK();
   return EVOX_OK;

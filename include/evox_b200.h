@@ -218,7 +218,7 @@ int evox_de_select(const float* trial, const float* trial_fit, float* pop, float
 /* Monte-Carlo hypervolume contributions of HypE: replaces the table-building part of cal_hv
  * (algorithms/mo/hype.py:28-38). fit (n x m) objective rows, samples (n_sample x m) sampling points,
  * alpha (n) the weights of hype.py:14-24, volume a DEVICE scalar = prod(ref - f_min). For every sample s
- * count_s = the number of rows with (fit - sample) <= 0 in every objective; then
+ * count_s = the number of rows with (fit - sample) <= 0 in every objective (integer, exact); then
  *   hv[i] = (sum over the samples s that row i covers of alpha[count_s - 1]) * volume / n_sample.
  * Nothing of size n x n_sample is stored; the counts are exact and the fp32 sum of one row's weights is
  * taken in a fixed order (four interleaved chains per slice of samples, slices in order).

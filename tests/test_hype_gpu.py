@@ -36,7 +36,7 @@ def test_cal_hv_golden(golden, cuda, tag):
 
 
 @pytest.mark.parametrize("n,m,n_sample,pop_size", [(1, 3, 40, 1), (257, 2, 1000, 100), (1000, 3, 4097, 500), (3000, 4, 2500, 1500),
-                                                  (700, 5, 999, 350), (300, 7, 1300, 100), (129, 32, 300, 64), (5000, 3, 10000, 2500)])
+                                                  (700, 5, 999, 350), (300, 7, 1300, 100), (400, 8, 900, 100), (350, 10, 800, 100), (129, 32, 300, 64), (5000, 3, 10000, 2500)])
 def test_cal_hv_vs_oracle(cuda, n, m, n_sample, pop_size):
     from evox_b200.algorithms.hype import cal_hv
 
