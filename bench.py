@@ -262,9 +262,22 @@ def run_ours(args):
     # timed region alone can be shorter than one nvidia-smi sampling period
     clocks = ClockSampler(physical_gpu_index(local))
     clocks.__enter__()
+    # The timed region carries a CUDA-event pair around every launch of the dominant kernel
+    # (pso_move_eval_kernel; the algorithm then issues its launches one C call at a time instead of
+    # through the single fused call — same kernels, same stream, same order), so the roofline below
+    # and `value` come from the same generations and the same clocks.
+    a = wf.algorithm
+    a._kernel_events = []
     for _ in range(max(args.warmup, 3)):
         wf.step()
+    a._kernel_events = []
     total_ms = timed(wf.step, args.steps)
+    kernel_ms = sum(e0.elapsed_time(e1) for e0, e1 in a._kernel_events) / len(a._kernel_events)
+    a._kernel_events = None
+    if world > 1:
+        t = torch.tensor([kernel_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        kernel_ms = t.item()
     launches_per_step = 2 if world == 1 else 3
     ms_per_step = total_ms / args.steps
     value = 1e3 / ms_per_step
@@ -273,7 +286,6 @@ def run_ours(args):
     hyper_host = torch.tensor([w, pp, pg], dtype=torch.float32).pin_memory()
     hyper_dev = torch.empty(3, dtype=torch.float32, device=dev)
     best_host = torch.empty((), dtype=torch.float32).pin_memory()
-    a = wf.algorithm
 
     def e2e_step():
         hyper_dev.copy_(hyper_host, non_blocking=True)
@@ -288,21 +300,7 @@ def run_ours(args):
         e2e_step()
     e2e_ms = timed(e2e_step, args.steps) / args.steps
 
-    # -- roofline of the dominant kernel: CUDA events around pso_move_eval_kernel inside K more real
-    #    generations (same stream, same neighbours; the algorithm then issues its launches one C call at a
-    #    time instead of through the single fused call) -------------------------------------------------
     n_local = a.local_size
-    a._kernel_events = []
-    barrier()
-    for _ in range(args.steps):
-        wf.step()
-    barrier()
-    kernel_ms = sum(e0.elapsed_time(e1) for e0, e1 in a._kernel_events) / len(a._kernel_events)
-    a._kernel_events = None
-    if world > 1:
-        t = torch.tensor([kernel_ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        kernel_ms = t.item()
     # nvidia-smi needs a few hundred milliseconds before its first sample: short runs (many GPUs, few steps)
     # keep stepping, untimed, until the clock record of the load has a few samples (every rank runs the same
     # number of extra generations: the count is agreed on rank 0's record)
