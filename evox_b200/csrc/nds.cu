@@ -502,6 +502,7 @@ __global__ void __launch_bounds__(kThreads)
   __shared__ long long s_qj[kThreads];         // block queue of columns waiting for a warp-wide scan
   __shared__ int s_qc[kThreads];
   __shared__ unsigned short s_qowner[kThreads];
+  __shared__ int s_found[kThreads];            // per owning thread: where its queued column's scan stopped
   __shared__ int s_qn;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   // Words of 32 columns are dealt to the blocks first and to a block's warps second (word = block +
@@ -510,6 +511,13 @@ __global__ void __launch_bounds__(kThreads)
   const long long n_warps = ((long long)gridDim.x * kThreads) >> 5;
   const long long n_words = (n + 31) >> 5;
   long long remaining = n;
+  const long long trips = (n_words + n_warps - 1) / n_warps;  // the same for every warp: the block synchronises inside
+  const bool single_trip = trips == 1;
+  int c_reg = 0;
+  if (single_trip) {
+    const long long j0 = ((long long)blockIdx.x + (long long)gridDim.x * warp) * 32 + lane;
+    if (j0 < n) c_reg = ptr[j0];
+  }
 
   for (int k = 0; k <= n; ++k) {
     const uint32_t* R = (k & 1) ? U1 : U0;
@@ -523,8 +531,6 @@ __global__ void __launch_bounds__(kThreads)
       Rs = s_mask;
     }
     unsigned ranked_here = 0;
-    // Every warp of the block makes the same number of trips (the block synchronises inside).
-    const long long trips = (n_words + n_warps - 1) / n_warps;
     for (long long trip = 0; trip < trips; ++trip) {
       const long long wj = (long long)blockIdx.x + (long long)gridDim.x * (warp + (kThreads / 32) * trip);
       const bool have = wj < n_words;
@@ -534,17 +540,16 @@ __global__ void __launch_bounds__(kThreads)
       const uint32_t own = have ? mask_word(Rs, (int)wj, mask_in_smem) : 0u;
       const long long j = wj * 32 + lane;
       const bool open = (own >> lane) & 1u;  // this lane's column is still unranked
+      // One memory round trip settles most columns: a lane reads 32 words of its own row from its
+      // witness position on (eight independent 128-bit loads; the witness word is among them) and takes the
+      // first word that still holds an unranked dominator as the new witness. When every word of a
+      // block's warps is visited once per front (one trip), the witness position lives in a register
+      // and is not re-read from memory. Columns with nothing in those 32 words are queued for the block:
+      // the warp-wide scans of a front's new members would otherwise pile up in the warps that own them.
       int c = 0;
-      bool blocked = false;
+      bool queued = false;
       if (open) {
-        c = __ldcg(ptr + j);
-        blocked = (__ldg(Dt + j * wp + c) & mask_word(Rs, c, mask_in_smem)) != 0u;
-      }
-      // Columns whose witness left: every such lane first probes the next 32 words of its own row by itself
-      // (eight independent 128-bit loads), which settles the columns with plenty of dominators left in one
-      // memory round trip for the whole warp. The others are queued for the block: the warp-wide scans of
-      // a front's new members would otherwise pile up in the few warps that own them.
-      if (open && !blocked) {
+        c = single_trip ? c_reg : __ldcg(ptr + j);
         const int c4 = c & ~3;
         const uint4* row4 = reinterpret_cast<const uint4*>(Dt + j * wp);
         uint4 d[8];
@@ -564,12 +569,16 @@ __global__ void __launch_bounds__(kThreads)
           }
         }
         if (hit >= 0) {
-          ptr[j] = hit;
+          if (hit != c) {
+            ptr[j] = hit;
+            c_reg = hit;
+          }
         } else {
           const int slot = atomicAdd(&s_qn, 1);
           s_qj[slot] = j;
           s_qc[slot] = min(c4 + 32, wp - 1);  // nothing up to here: the scan may skip these words
           s_qowner[slot] = (unsigned short)threadIdx.x;
+          queued = true;
         }
       }
       __syncthreads();
@@ -604,6 +613,7 @@ __global__ void __launch_bounds__(kThreads)
           }
         }
         if (lane == 0) {
+          s_found[s_qowner[item]] = found;
           if (found >= 0) {
             ptr[jl] = found;
           } else {
@@ -614,6 +624,7 @@ __global__ void __launch_bounds__(kThreads)
         }
       }
       __syncthreads();
+      if (queued && s_found[threadIdx.x] >= 0) c_reg = s_found[threadIdx.x];
       const unsigned newly = s_newly[warp];
       if (lane == 0 && have) W[wj] = own & ~newly;
       ranked_here += __popc(newly);
