@@ -303,28 +303,28 @@ __global__ void __launch_bounds__(kThreads)
     separated = !bad && jmax < imin;
   }
   if (separated) {
-    uint32_t back[R];
+    // 32 columns per word with the bit position known at compile time: two compares and one predicated
+    // OR per pair
+#pragma unroll 1
+    for (int jw = 0; jw < kTileJ / 32; ++jw) {
+      uint32_t back[R];
 #pragma unroll
-    for (int r = 0; r < R; ++r) back[r] = 0u;
-#pragma unroll 4
-    for (int jj = 0; jj < kTileJ; ++jj) {
-      float fj[M];
+      for (int r = 0; r < R; ++r) back[r] = 0u;
 #pragma unroll
-      for (int k = 1; k < M; ++k) fj[k] = sfj[k][jj];
+      for (int jb = 0; jb < 32; ++jb) {
+        float fj[M];
 #pragma unroll
-      for (int r = 0; r < R; ++r) {
-        bool le = true;
-#pragma unroll
-        for (int k = 1; k < M; ++k) le = le && (fj[k] <= fi[r][k]);
-        back[r] |= (uint32_t)le << (jj & 31);
-      }
-      if ((jj & 31) == 31) {
+        for (int k = 1; k < M; ++k) fj[k] = sfj[k][jw * 32 + jb];
 #pragma unroll
         for (int r = 0; r < R; ++r) {
-          sback[jj >> 5][(warp * R + r) * 32 + lane] = back[r];
-          back[r] = 0u;
+          bool le = true;
+#pragma unroll
+          for (int k = 1; k < M; ++k) le = le && (fj[k] <= fi[r][k]);
+          if (le) back[r] |= 1u << jb;
         }
       }
+#pragma unroll
+      for (int r = 0; r < R; ++r) sback[jw][(warp * R + r) * 32 + lane] = back[r];
     }
   } else if (!both) {
 #pragma unroll 4
