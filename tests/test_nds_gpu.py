@@ -41,7 +41,7 @@ def test_golden(golden, cuda, case):
     assert same(scrowd, torch.from_numpy(g[f"{case}_sel_crowd"]))
 
 
-@pytest.mark.parametrize("n", [1, 2, 31, 32, 33, 127, 128, 129, 1023, 1024, 1025, 3000])
+@pytest.mark.parametrize("n", [1, 2, 31, 32, 33, 127, 128, 129, 1023, 1024, 1025, 3000, 8191, 8192, 8193])  # 8192: rows get ordered
 @pytest.mark.parametrize("m", [2, 3])
 def test_rank_sizes(cuda, n, m):
     from evox_b200.operators.selection import non_dominate_rank
