@@ -155,7 +155,8 @@ def test_config1_full_size(cuda):
     assert same(got[3], want[3])
 
 
-def test_metric_size_properties(cuda):
+@pytest.mark.parametrize("n", [100_000, 160_000])  # 160,000: more 32-column words than resident warps (two trips per front)
+def test_metric_size_properties(cuda, n):
     """2N = 100,000 rows, 3 objectives (the size the selection metric is quoted on): the CPU oracle needs
     minutes there, so the ranks are checked through their defining properties on the device:
     (a) relabelling the rows permutes the ranks the same way; (b) no row of a front dominates another
@@ -163,7 +164,6 @@ def test_metric_size_properties(cuda):
     both verified exhaustively for a sample of 400 rows against ALL rows with torch ops."""
     from evox_b200.operators.selection import non_dominate_rank
 
-    n = 100_000
     gen = torch.Generator().manual_seed(5)
     x = torch.rand(n, 12, generator=gen)
     f = nds.dtlz2_objectives(x, 3).to(cuda)
