@@ -41,6 +41,7 @@ namespace {
 
 constexpr int kThreads = 256;
 constexpr int kSortThreads = 1024;
+constexpr int kPeelThreads = 512;   // threads per block of the peeling kernel (256: 2.37 / 0.435 ms per rank at 1e5 / 2e4 rows, 512: 2.34 / 0.426, 1024: 2.32 / 0.460)
 constexpr int kTileJ = 128;      // columns (dominated candidates) per dominance tile
 constexpr int kPad = 1024;       // population padded to a multiple of this (32 words = 128 B rows)
 constexpr unsigned kSpinLimit = 1u << 22;  // grid-barrier polls before giving up (~ seconds)
@@ -493,22 +494,22 @@ __device__ __forceinline__ int first_nonzero(const uint4& v) {
 // scanned on, and never backwards: over all fronts a row of Dt is read once. Measured per front at
 // 100,000 rows: about 1.4 us for the barrier itself, the rest is the slowest block's scans (late fronts:
 // few unranked rows are left, so the next unranked dominator of a column is far away).
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kPeelThreads)
     nds_peel_kernel(const uint32_t* __restrict__ Dt, int wp, long long n, uint32_t* U0, uint32_t* U1, int* ptr,
                     int* rank, Ctrl* ctrl, int mask_in_smem, const uint32_t* __restrict__ perm) {
   extern __shared__ __align__(16) uint32_t s_mask[];
-  __shared__ unsigned s_cnt[kThreads / 32];
-  __shared__ unsigned s_newly[kThreads / 32];  // per owning warp: columns ranked in this trip
-  __shared__ long long s_qj[kThreads];         // block queue of columns waiting for a warp-wide scan
-  __shared__ int s_qc[kThreads];
-  __shared__ unsigned short s_qowner[kThreads];
-  __shared__ int s_found[kThreads];            // per owning thread: where its queued column's scan stopped
+  __shared__ unsigned s_cnt[kPeelThreads / 32];
+  __shared__ unsigned s_newly[kPeelThreads / 32];  // per owning warp: columns ranked in this trip
+  __shared__ long long s_qj[kPeelThreads];         // block queue of columns waiting for a warp-wide scan
+  __shared__ int s_qc[kPeelThreads];
+  __shared__ unsigned short s_qowner[kPeelThreads];
+  __shared__ int s_found[kPeelThreads];            // per owning thread: where its queued column's scan stopped
   __shared__ int s_qn;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   // Words of 32 columns are dealt to the blocks first and to a block's warps second (word = block +
   // blocks * (warp + 8 * trip)): with fewer words than warps every block still owns some, and its
   // other warps help with the block's queue of long scans.
-  const long long n_warps = ((long long)gridDim.x * kThreads) >> 5;
+  const long long n_warps = ((long long)gridDim.x * kPeelThreads) >> 5;
   const long long n_words = (n + 31) >> 5;
   long long remaining = n;
   const long long trips = (n_words + n_warps - 1) / n_warps;  // the same for every warp: the block synchronises inside
@@ -525,14 +526,14 @@ __global__ void __launch_bounds__(kThreads)
     // this pass's snapshot of the unranked mask, staged in shared memory when it fits
     const uint32_t* Rs = R;
     if (mask_in_smem) {
-      for (int w = threadIdx.x * 4; w < wp; w += kThreads * 4)
+      for (int w = threadIdx.x * 4; w < wp; w += kPeelThreads * 4)
         *reinterpret_cast<uint4*>(s_mask + w) = __ldcg(reinterpret_cast<const uint4*>(R + w));
       __syncthreads();
       Rs = s_mask;
     }
     unsigned ranked_here = 0;
     for (long long trip = 0; trip < trips; ++trip) {
-      const long long wj = (long long)blockIdx.x + (long long)gridDim.x * (warp + (kThreads / 32) * trip);
+      const long long wj = (long long)blockIdx.x + (long long)gridDim.x * (warp + (kPeelThreads / 32) * trip);
       const bool have = wj < n_words;
       if (threadIdx.x == 0) s_qn = 0;
       if (lane == 0) s_newly[warp] = 0u;
@@ -583,7 +584,7 @@ __global__ void __launch_bounds__(kThreads)
       }
       __syncthreads();
       const int qn = s_qn;
-      for (int item = warp; item < qn; item += kThreads / 32) {
+      for (int item = warp; item < qn; item += kPeelThreads / 32) {
         const long long jl = s_qj[item];
         const int cl = s_qc[item];
         const uint4* row4 = reinterpret_cast<const uint4*>(Dt + jl * wp);
@@ -633,7 +634,7 @@ __global__ void __launch_bounds__(kThreads)
     __syncthreads();
     if (threadIdx.x == 0) {
       unsigned tot = 0;
-      for (int i = 0; i < kThreads / 32; ++i) tot += s_cnt[i];
+      for (int i = 0; i < kPeelThreads / 32; ++i) tot += s_cnt[i];
       if (tot) atomicAdd(&ctrl->ranked[k & 3], tot);
       if (blockIdx.x == 0) ctrl->ranked[(k + 2) & 3] = 0;  // last read two barriers ago
     }
@@ -1076,7 +1077,7 @@ int run_rank(const float* f, long long n, int m, int* rank, void* ws, const Layo
   if (mask_bytes > 40 * 1024) {
     EVOX_CUDA(cudaFuncSetAttribute(nds_peel_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
   }
-  EVOX_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, nds_peel_kernel, kThreads, mask_bytes));
+  EVOX_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, nds_peel_kernel, kPeelThreads, mask_bytes));
   EVOX_REQUIRE(per_sm > 0, EVOX_ERR_CUDA, "nds_peel_kernel cannot be made resident");
   if (per_sm > 4) per_sm = 4;
   {
@@ -1084,7 +1085,7 @@ int run_rank(const float* f, long long n, int m, int* rank, void* ws, const Layo
     // warps, but no more: the grid barrier gets slower with every block that takes part (measured at
     // 20,000 rows: 0.47 ms per rank with four blocks per multiprocessor, 0.44 ms with one).
     const long long words = (n + 31) / 32;
-    const long long need = (words + (long long)sm_count() * (kThreads / 32) - 1) / ((long long)sm_count() * (kThreads / 32));
+    const long long need = (words + (long long)sm_count() * (kPeelThreads / 32) - 1) / ((long long)sm_count() * (kPeelThreads / 32));
     const int want = need <= 1 ? 1 : (int)(need + 1);
     if (want < per_sm) per_sm = want;
   }
@@ -1096,7 +1097,7 @@ int run_rank(const float* f, long long n, int m, int* rank, void* ws, const Layo
   long long nn = n;
   void* args[] = {(void*)&Dt_c, (void*)&wp, (void*)&nn, (void*)&unranked, (void*)&newfront, (void*)&ptr, (void*)&rank, (void*)&ctrl,
                   (void*)&mask_in_smem, (void*)&perm};
-  EVOX_CUDA(cudaLaunchCooperativeKernel((const void*)nds_peel_kernel, dim3((unsigned)blocks), dim3(kThreads), args, mask_bytes, s));
+  EVOX_CUDA(cudaLaunchCooperativeKernel((const void*)nds_peel_kernel, dim3((unsigned)blocks), dim3(kPeelThreads), args, mask_bytes, s));
   return EVOX_OK;
 }
 
