@@ -52,9 +52,9 @@ constexpr long long kOrderMinN = 8192;  // smaller populations have too few sepa
 // Workspace
 // ---------------------------------------------------------------------------------------------
 struct Ctrl {
-  unsigned bar_count;
-  unsigned bar_gen;
-  unsigned ranked[4];  // columns ranked in pass k, slot k & 3
+  unsigned long long bar_word;      // arrivals of the current barrier (low half) + rows they ranked (high half)
+  unsigned long long release_word;  // (barrier number << 32) | rows ranked before it; bit 63: a wait gave up
+  unsigned spare[2];
   int status;        // 0 ok, 1 barrier timed out, 2 no progress
   int n_fronts;
   int worst_rank;    // last admitted front
@@ -433,43 +433,62 @@ __global__ void nds_peel_init_kernel(long long n, int wp, uint32_t* unranked, ui
     rank[j] = -1;
   }
   if (t0 == 0) {
-    ctrl->bar_count = 0;
-    ctrl->bar_gen = 0;
-    for (int i = 0; i < 4; ++i) ctrl->ranked[i] = 0;
+    ctrl->bar_word = 0ull;
+    ctrl->release_word = 0ull;
     ctrl->status = 0;
     ctrl->n_fronts = 0;
   }
 }
 
-// Grid-wide barrier for a cooperative (co-resident) launch. The wait is bounded: a block that
-// polls kSpinLimit times records status 1 and every block leaves at its next check.
-__device__ __forceinline__ bool grid_barrier(Ctrl* ctrl, unsigned n_blocks) {
+// Grid-wide barrier number `number` (1, 2, ...) of a cooperative (co-resident) launch, which also adds up
+// `mine` (the rows this block ranked in the pass) over the grid: the sum comes back in *total. The
+// wait is bounded: a block that polls kSpinLimit times records status 1 and every block leaves at its
+// next check. Thread 0 makes three dependent trips to memory per barrier (release fence, arrival
+// atomic, the poll that sees the release); the barrier number is known to every block, the sum rides
+// on the arrival word and comes back with the release word, and a failed wait shows in the same word.
+__device__ __forceinline__ bool grid_barrier_sum(Ctrl* ctrl, unsigned n_blocks, unsigned number, unsigned mine, unsigned* total) {
   __shared__ int ok;
-  __syncthreads();
+  __shared__ unsigned s_total;
   if (threadIdx.x == 0) {
-    volatile unsigned* gen_p = &ctrl->bar_gen;
-    volatile int* status_p = &ctrl->status;
-    const unsigned gen = *gen_p;
+    constexpr unsigned long long kFailed = 1ull << 63;
+    volatile unsigned long long* rel_p = &ctrl->release_word;
     __threadfence();
-    const unsigned arrived = atomicAdd(&ctrl->bar_count, 1u) + 1u;
-    if (arrived == n_blocks) {
-      ctrl->bar_count = 0;
+    const unsigned long long old = atomicAdd(&ctrl->bar_word, 1ull | ((unsigned long long)mine << 32));
+    bool good = true;
+    if ((unsigned)(old & 0xffffffffull) + 1u == n_blocks) {
+      const unsigned sum = (unsigned)(old >> 32) + mine;
+      ctrl->bar_word = 0ull;
       __threadfence();
-      atomicAdd(&ctrl->bar_gen, 1u);
+      // keeps a failure flag that a block which gave up may have set meanwhile
+      const unsigned long long before = atomicMax(&ctrl->release_word, ((unsigned long long)number << 32) | sum);
+      good = !(before & kFailed);
+      s_total = sum;
     } else {
       unsigned spins = 0;
-      while (*gen_p == gen && *status_p == 0) {
+      for (;;) {
+        const unsigned long long w = *rel_p;
+        if (w & kFailed) {
+          good = false;
+          break;
+        }
+        if ((unsigned)(w >> 32) == number) {
+          s_total = (unsigned)w;
+          break;
+        }
         __nanosleep(32);
         if (++spins > kSpinLimit) {
           atomicExch(&ctrl->status, 1);
+          atomicOr(&ctrl->release_word, kFailed);
+          good = false;
           break;
         }
       }
     }
     __threadfence();
-    ok = (*status_p == 0);
+    ok = good;
   }
   __syncthreads();
+  *total = s_total;
   return ok != 0;
 }
 
@@ -632,14 +651,12 @@ __global__ void __launch_bounds__(kPeelThreads)
     }
     if (lane == 0) s_cnt[threadIdx.x >> 5] = ranked_here;
     __syncthreads();
+    unsigned tot = 0;
     if (threadIdx.x == 0) {
-      unsigned tot = 0;
       for (int i = 0; i < kPeelThreads / 32; ++i) tot += s_cnt[i];
-      if (tot) atomicAdd(&ctrl->ranked[k & 3], tot);
-      if (blockIdx.x == 0) ctrl->ranked[(k + 2) & 3] = 0;  // last read two barriers ago
     }
-    if (!grid_barrier(ctrl, gridDim.x)) return;
-    const unsigned got = *((volatile unsigned*)&ctrl->ranked[k & 3]);
+    unsigned got = 0;
+    if (!grid_barrier_sum(ctrl, gridDim.x, (unsigned)k + 1u, tot, &got)) return;
     remaining -= got;
     if (remaining <= 0) {
       if (blockIdx.x == 0 && threadIdx.x == 0) ctrl->n_fronts = k + 1;
