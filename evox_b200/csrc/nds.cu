@@ -829,28 +829,47 @@ __global__ void __launch_bounds__(kSortThreads)
   if (tid == 0) s_worst = (s_worst_u == 0xffffffffu) ? (int)n : (int)s_worst_u;
   __syncthreads();
   const int worst = s_worst;
-  for (long long s = 0; s < n; s += kSortThreads) {
-    const long long i = s + tid;
-    const int r = (i < n) ? rank[i] : 0x7fffffff;
-    const bool in_a = r < worst, in_l = r == worst;
-    const unsigned ma = __ballot_sync(0xffffffffu, in_a), ml = __ballot_sync(0xffffffffu, in_l);
-    if (lane == 0) {
-      s_wsum[warp][0] = __popc(ma);
-      s_wsum[warp][1] = __popc(ml);
+  // four consecutive rows per thread and tile: the lists stay in index order (a thread's rows are
+  // consecutive, the threads of a warp and the warps of the block follow each other)
+  for (long long s = 0; s < n; s += 4 * kSortThreads) {
+    const long long i0 = s + (long long)tid * 4;
+    int r[4];
+    unsigned ca = 0, cl = 0;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      r[q] = (i0 + q < n) ? rank[i0 + q] : 0x7fffffff;
+      ca += r[q] < worst;
+      cl += r[q] == worst;
+    }
+    unsigned ia = ca, il = cl;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const unsigned ta = __shfl_up_sync(0xffffffffu, ia, off), tl = __shfl_up_sync(0xffffffffu, il, off);
+      if (lane >= off) {
+        ia += ta;
+        il += tl;
+      }
+    }
+    if (lane == 31) {
+      s_wsum[warp][0] = ia;
+      s_wsum[warp][1] = il;
     }
     __syncthreads();
-    unsigned off_a = s_base[0], off_l = s_base[1];
+    unsigned off_a = s_base[0] + (ia - ca), off_l = s_base[1] + (il - cl);
     for (int w = 0; w < warp; ++w) {
       off_a += s_wsum[w][0];
       off_l += s_wsum[w][1];
     }
-    const unsigned lt = (1u << lane) - 1u;
-    if (in_a) {
-      const unsigned p = off_a + __popc(ma & lt);
-      idx_a[p] = (uint32_t)i;
-      key_a[p] = (uint32_t)r;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      if (r[q] < worst) {
+        idx_a[off_a] = (uint32_t)(i0 + q);
+        key_a[off_a] = (uint32_t)r[q];
+        ++off_a;
+      } else if (r[q] == worst) {
+        idx_l[off_l++] = (uint32_t)(i0 + q);
+      }
     }
-    if (in_l) idx_l[off_l + __popc(ml & lt)] = (uint32_t)i;
     __syncthreads();
     if (tid == 0) {
       unsigned ta = 0, tl = 0;
