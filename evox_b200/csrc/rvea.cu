@@ -64,14 +64,21 @@ __global__ void __launch_bounds__(kThreads)
   const long long stride = (long long)gridDim.x * blockDim.x;
   const long long step = stride - (stride % m);  // keep each thread on one column
   long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (t >= step) return;
-  const int col = (int)(t % m);
-  float mn = INFINITY;
-  for (; t < total; t += step) {
-    const float v = f[t];
-    if (v == v) mn = fminf(mn, v);
+  // the block's threads meet in shared memory first (m <= 32): one global atomic per column and block
+  __shared__ uint32_t s_key[32];
+  if (threadIdx.x < 32) s_key[threadIdx.x] = 0xffffffffu;
+  __syncthreads();
+  if (t < step) {
+    const int col = (int)(t % m);
+    float mn = INFINITY;
+    for (; t < total; t += step) {
+      const float v = f[t];
+      if (v == v) mn = fminf(mn, v);
+    }
+    atomicMin(s_key + col, order_key(mn));
   }
-  atomicMin(zmin_key + col, order_key(mn));
+  __syncthreads();
+  if (threadIdx.x < m && s_key[threadIdx.x] != 0xffffffffu) atomicMin(zmin_key + threadIdx.x, s_key[threadIdx.x]);
 }
 
 // vn = v / max(|v|, eps), one thread per vector.
