@@ -6,6 +6,7 @@ Run ``python -m evox_b200._build`` to (re)build; ``--force`` ignores the up-to-d
 
 from __future__ import annotations
 
+import fcntl
 import hashlib
 import os
 import shutil
@@ -61,8 +62,21 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     """Build the shared library if any source changed; return its path."""
     if not force and is_current():
         return LIB_PATH
-    nvcc = _nvcc()
     LIB_DIR.mkdir(exist_ok=True)
+    # several ranks of one job may import the package at once on a fresh checkout: one of them builds,
+    # the others wait on the lock and then find the library current
+    with open(LIB_DIR / "build.lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if not force and is_current():
+                return LIB_PATH
+            return _build_locked(verbose)
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+
+
+def _build_locked(verbose: bool) -> Path:
+    nvcc = _nvcc()
     obj_dir = LIB_DIR / "obj"
     obj_dir.mkdir(exist_ok=True)
     extra = ["-Xptxas", "-v"] if verbose else []
@@ -79,10 +93,13 @@ def build(force: bool = False, verbose: bool = False) -> Path:
 
     with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as ex:
         objs = list(ex.map(compile_one, _sources()))
-    link = [nvcc, "-shared", "-o", str(LIB_PATH), *map(str, objs), "-gencode", "arch=compute_100a,code=sm_100a"]
+    # link under a temporary name and move it into place: a reader never maps a half-written library
+    tmp = LIB_DIR / (LIB_PATH.name + ".tmp")
+    link = [nvcc, "-shared", "-o", str(tmp), *map(str, objs), "-gencode", "arch=compute_100a,code=sm_100a"]
     res = subprocess.run(link, capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")
+    os.replace(tmp, LIB_PATH)
     (LIB_DIR / "fingerprint.txt").write_text(_fingerprint())
     return LIB_PATH
 

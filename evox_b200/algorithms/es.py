@@ -56,11 +56,14 @@ class _ESBase(Algorithm):
             self.beta2 = Parameter(0.999, dtype=torch.float32, device=device)
 
     def sigma(self) -> float:
-        """Host copy of noise_stdev; refreshed (one sync) only when the parameter was modified."""
-        ver = self.noise_stdev._version
-        if getattr(self, "_sigma_version", None) != ver:
-            self._sigma_host = float(self.noise_stdev)
-            self._sigma_version = ver
+        """Host copy of noise_stdev; refreshed (one sync) when the parameter was modified in place OR rebound to
+        another tensor (a fresh tensor's version counter can equal the cached one, so the key also holds the
+        tensor's identity and storage address)."""
+        t = self.noise_stdev
+        key = (id(t), t.data_ptr(), t._version)
+        if getattr(self, "_sigma_key", None) != key:
+            self._sigma_host = float(t)
+            self._sigma_key = key
         return self._sigma_host
 
     def record_step(self):

@@ -63,6 +63,26 @@ class _MOBase(Algorithm):
         self.seed = int(torch.randint(0, 2**62, (), device="cpu"))
         self.generation = 0
 
+    # -- checkpointing: the position in the random stream travels with the state_dict --------------
+    def get_extra_state(self):
+        return {"seed": self.seed, "generation": self.generation}
+
+    def set_extra_state(self, state):
+        self.seed = int(state["seed"])
+        self.generation = int(state["generation"])
+
+    def load_state_dict(self, state_dict, strict: bool = True, assign: bool = False):
+        # a state_dict written by the reference has no random-stream entry: keep ours
+        if "_extra_state" not in state_dict:
+            state_dict = dict(state_dict)
+            state_dict["_extra_state"] = self.get_extra_state()
+        out = super().load_state_dict(state_dict, strict=strict, assign=assign)
+        self._after_load()
+        return out
+
+    def _after_load(self) -> None:
+        pass
+
     def _variation(self, pop: torch.Tensor, mating_pool: torch.Tensor | None, draws: dict | None) -> torch.Tensor:
         """crossover -> mutation -> clamp (nsga2.py:95-97). Fused kernel unless custom operators are set."""
         if self.crossover is None and self.mutation is None:
@@ -117,7 +137,7 @@ class RVEA(_MOBase):
         self.alpha = Parameter(alpha, dtype=torch.float32, device=device)
         self.fr = Parameter(fr, dtype=torch.float32, device=device)
         self.max_gen = Parameter(max_gen, dtype=torch.float32, device=device)
-        self._adapt_every = max(int(round(1.0 / fr)), 1)
+        self._schedule = None  # host copies of (generation count, adaptation period, last generation)
         v, n = uniform_sampling(pop_size, n_objs)
         v = v.to(device)
         self.pop_size = n
@@ -127,7 +147,22 @@ class RVEA(_MOBase):
         self.init_v = v
         self.gen = Mutable(torch.tensor(0, dtype=torch.int64, device=device))
 
+    def _sync_schedule(self) -> None:
+        """Host copies of what decides WHEN vectors adapt and when RVEAa truncates: the `gen` buffer and the
+        `fr` / `max_gen` Parameters (rvea.py:107: the period is recomputed from `fr` in init_step; rveaa.py:181
+        compares `gen` with `max_gen`). Read once here — in init_step and after a load_state_dict — and counted
+        on the host afterwards, so a generation needs no device-to-host copy."""
+        period = torch.max(torch.round(1 / self.fr), torch.tensor(1.0, device=self.fr.device))
+        self._gen_host = int(self.gen)
+        self._adapt_every = int(period)
+        self._max_gen_host = int(self.max_gen)
+        self._schedule = True
+
+    def _after_load(self) -> None:
+        self._schedule = None  # gen, fr or max_gen may have changed
+
     def init_step(self):
+        self._sync_schedule()
         self.fit = self.evaluate(self.pop)
 
     def _mating_rows(self, picks: torch.Tensor | None) -> torch.Tensor:
@@ -143,8 +178,10 @@ class RVEA(_MOBase):
     def step(self, picks: torch.Tensor | None = None, draws: dict | None = None):
         """One generation (rvea.py:135-154). `picks` (pop_size,) in [0, #valid rows) and `draws` replace
         the random draws of the mating pool and of crossover / mutation."""
+        if self._schedule is None:
+            self._sync_schedule()
         self.gen = self.gen + 1
-        self._gen_host = getattr(self, "_gen_host", 0) + 1
+        self._gen_host += 1
         mating = self._mating_rows(picks)
         # NaN rows never enter the pool, so the fused kernel can gather straight from pop
         offspring = self._variation(self.pop, mating, draws)
@@ -176,7 +213,6 @@ class RVEAa(RVEA):
         super().__init__(pop_size, n_objs, lb, ub, alpha, fr, max_gen, selection_op, mutation_op, crossover_op, device)
         extra = torch.rand(self.pop_size, n_objs, device=self.reference_vector.device)
         self.reference_vector = Mutable(torch.cat([self.reference_vector, extra], dim=0))
-        self._max_gen_host = int(max_gen)
 
     @staticmethod
     def _rv_regeneration(pop_obj: torch.Tensor, v: torch.Tensor, draw: torch.Tensor | None = None) -> torch.Tensor:
@@ -204,8 +240,10 @@ class RVEAa(RVEA):
         """One generation (rveaa.py:189-212)."""
         from ..operators.selection import non_dominate_rank
 
+        if self._schedule is None:
+            self._sync_schedule()
         self.gen = self.gen + 1
-        self._gen_host = getattr(self, "_gen_host", 0) + 1
+        self._gen_host += 1
         mating = self._mating_rows(picks)
         offspring = self._variation(self.pop, mating, draws)
         off_fit = self.evaluate(offspring)

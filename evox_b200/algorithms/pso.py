@@ -1,4 +1,4 @@
-"""Particle swarm optimisation with the whole generation in two kernel launches.
+"""Particle swarm optimisation with the whole generation in one kernel launch.
 
 Drop-in for the reference's `PSO` (evox/algorithms/so/pso_variants/pso.py:9-115): same
 constructor arguments, same state names (`pop`, `velocity`, `fit`, `local_best_location`,
@@ -13,6 +13,13 @@ constructor arguments, same state names (`pop`, `velocity`, `fit`, `local_best_l
 * with `shard=True` under an initialised `torch.distributed` group each rank holds only its
   rows; one allgather of a (dim + 4)-word best-particle record per generation keeps the
   global best identical on all ranks.
+
+The global-best search of generation g + 1 (min_by over the fitness generation g produced,
+pso.py:92-95) rides on the kernel of generation g: its tail leaves this shard's best-particle
+record, the head of the next launch folds the records into the running best. The record is
+only trusted while `pop` and `fit` are the tensors the kernel left (same storage, same
+version counter); after a `load_state_dict`, a torch-side write or an evaluation outside the
+kernel it is rebuilt from `fit` with one extra launch.
 """
 
 from __future__ import annotations
@@ -95,8 +102,11 @@ class PSO(Algorithm):
         self.global_best_location = Mutable(pop[0].clone())
         self.global_best_fit = Mutable(torch.tensor(torch.inf, device=device))
         self._scratch: dict[str, torch.Tensor] = {}
-        # measurement hook: when a list, step() issues its launches one C call at a time and appends a
-        # (start, end) CUDA-event pair around the update kernel of every generation
+        self._checked_ptrs = None  # storage addresses of the state the last argument check saw
+        self._cur = 0              # which of the two record buffers holds this shard's latest record
+        self._pending = None       # (swarm key, gathered records) left by the last fused generation
+        # measurement hook: when a list, step() appends a (start, end) CUDA-event pair around the
+        # generation kernel (on several GPUs the allgather that follows stays outside the pair)
         self._kernel_events: list | None = None
 
     # -- checkpointing of the random stream position ------------------------------------------
@@ -115,11 +125,13 @@ class PSO(Algorithm):
         return super().load_state_dict(state_dict, strict=strict, assign=assign)
 
     # -- kernel plumbing -----------------------------------------------------------------------
+    _STATE = ("pop", "velocity", "local_best_location", "local_best_fit", "fit", "global_best_location", "global_best_fit")
+
     def _buffers_ready(self) -> torch.device:
         dev = self.pop.device
         if dev.type != "cuda":
             raise _cabi.EvoxKernelError("PSO.step needs its state on a CUDA device; evox_b200 has no CPU path")
-        for name in ("pop", "velocity", "local_best_location", "local_best_fit", "fit", "global_best_location", "global_best_fit"):
+        for name in self._STATE:
             t = getattr(self, name)
             if not t.is_contiguous() or t.dtype != torch.float32:
                 setattr(self, name, t.to(torch.float32).contiguous())
@@ -130,33 +142,60 @@ class PSO(Algorithm):
             nbytes = _cabi.lib.evox_pso_workspace_bytes(self.local_size, self.dim)
             self._scratch["ws"] = torch.zeros(nbytes, dtype=torch.uint8, device=dev)
             words = _cabi.lib.evox_pso_candidate_words(self.dim)
-            self._scratch["cand"] = torch.zeros(words, dtype=torch.int32, device=dev)
+            # two records of this shard (the kernel reads one generation's while it writes the next one's)
+            self._scratch["cand"] = torch.zeros(2, words, dtype=torch.int32, device=dev)
+            self._scratch["gathered"] = torch.zeros(self.world_size, words, dtype=torch.int32, device=dev)
+            self._pending = None
         return dev
 
     def _fused_plan(self):
         planner = getattr(self, "_workflow_fused_plan", None)
         return planner() if planner is not None else None
 
-    def _update_global_best(self, dev: torch.device, have_previous: bool) -> None:
-        ws, cand = self._scratch["ws"], self._scratch["cand"]
-        lib, s = _cabi.lib, _cabi.stream_ptr(dev)
+    def _swarm_key(self):
+        pop, fit = self.pop, self.fit
+        return (pop.data_ptr(), pop._version, fit.data_ptr(), fit._version)
+
+    def _gather(self, record: torch.Tensor) -> torch.Tensor:
+        """Every shard's record in rank order: the record itself on one GPU, one allgather otherwise."""
+        if self.world_size == 1:
+            return record
+        return allgather_records(record, self.group, out=self._scratch["gathered"])
+
+    def _rebuild_records(self, dev: torch.device) -> torch.Tensor:
+        """This shard's best-particle record from `fit` and `pop` as they are now, gathered."""
+        ws, cand = self._scratch["ws"], self._scratch["cand"][self._cur]
         _cabi.check(
-            lib.evox_pso_local_best(
+            _cabi.lib.evox_pso_local_best(
                 _cabi.ptr(self.fit), _cabi.ptr(self.pop), self.local_size, self.dim, self.row_start,
-                _cabi.ptr(cand), _cabi.ptr(ws), ws.numel(), s,
+                _cabi.ptr(cand), _cabi.ptr(ws), ws.numel(), _cabi.stream_ptr(dev),
             )
         )
-        records = allgather_records(cand, self.group)
+        return self._gather(cand)
+
+    def _update_global_best(self, dev: torch.device, have_previous: bool) -> torch.Tensor:
+        records = self._rebuild_records(dev)
         _cabi.check(
-            lib.evox_pso_merge_best(
+            _cabi.lib.evox_pso_merge_best(
                 _cabi.ptr(records), self.world_size, self.dim, int(have_previous),
-                _cabi.ptr(self.global_best_location), _cabi.ptr(self.global_best_fit), s,
+                _cabi.ptr(self.global_best_location), _cabi.ptr(self.global_best_fit), _cabi.stream_ptr(dev),
             )
         )
+        return records
 
     def step(self, rg: torch.Tensor | None = None, rp: torch.Tensor | None = None):
         """One generation (pso.py:71-106). `rg`, `rp`: optional (local_size, dim) uniform draws."""
-        dev = self._buffers_ready()
+        ptrs = tuple(getattr(self, n).data_ptr() for n in self._STATE)
+        if ptrs != self._checked_ptrs:
+            dev = self._buffers_ready()
+            self._checked_ptrs = tuple(getattr(self, n).data_ptr() for n in self._STATE)
+            self._static_args = (
+                _cabi.ptr(self.lb, torch.float32, "lb"), _cabi.ptr(self.ub, torch.float32, "ub"),
+                _cabi.ptr(self.w, torch.float32, "w"), _cabi.ptr(self.phi_p, torch.float32, "phi_p"),
+                _cabi.ptr(self.phi_g, torch.float32, "phi_g"),
+            )
+            self._device = dev
+        dev = self._device
         plan = self._fused_plan()
         fitness_id, params = plan if plan is not None else (FIT_SPHERE, (0.0, 0.0, 0.0))
         if (rg is None) != (rp is None):
@@ -166,36 +205,36 @@ class PSO(Algorithm):
             assert rg.shape == self.pop.shape and rp.shape == self.pop.shape
         lib, s = _cabi.lib, _cabi.stream_ptr(dev)
         ws = self._scratch["ws"]
+        state = tuple(_cabi.ptr(getattr(self, n)) for n in self._STATE)
         args = (
-            _cabi.ptr(self.lb, torch.float32, "lb"), _cabi.ptr(self.ub, torch.float32, "ub"),
-            _cabi.ptr(self.w, torch.float32, "w"), _cabi.ptr(self.phi_p, torch.float32, "phi_p"),
-            _cabi.ptr(self.phi_g, torch.float32, "phi_g"),
-            _cabi.ptr(rg, torch.float32, "rg"), _cabi.ptr(rp, torch.float32, "rp"),
+            *self._static_args, _cabi.ptr(rg, torch.float32, "rg"), _cabi.ptr(rp, torch.float32, "rp"),
             self.local_size, self.dim, fitness_id, _cabi.host_floats(params), self.seed, self.generation,
         )
-        if self.world_size == 1 and self._kernel_events is None:
-            _cabi.check(
-                lib.evox_pso_step(
-                    _cabi.ptr(self.pop), _cabi.ptr(self.velocity), _cabi.ptr(self.local_best_location),
-                    _cabi.ptr(self.local_best_fit), _cabi.ptr(self.fit), _cabi.ptr(self.global_best_location),
-                    _cabi.ptr(self.global_best_fit), *args, _cabi.ptr(ws), ws.numel(), s,
-                )
-            )
-        else:
+        if plan is None:
+            # the problem is evaluated outside: two launches, nothing carried to the next generation
             self._update_global_best(dev, have_previous=True)
+            _cabi.check(lib.evox_pso_move_eval(*state[:6], *args, self.row_start, s))
+            self._pending = None
+        else:
+            if self._pending is None or self._pending[0] != self._swarm_key():
+                records = self._rebuild_records(dev)
+            else:
+                records = self._pending[1]
+            self._cur ^= 1
+            out = self._scratch["cand"][self._cur]
             if self._kernel_events is not None:
                 pair = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
                 pair[0].record()
             _cabi.check(
-                lib.evox_pso_move_eval(
-                    _cabi.ptr(self.pop), _cabi.ptr(self.velocity), _cabi.ptr(self.local_best_location),
-                    _cabi.ptr(self.local_best_fit), _cabi.ptr(self.fit), _cabi.ptr(self.global_best_location),
-                    *args, self.row_start, s,
+                lib.evox_pso_generation(
+                    *state, *args, self.row_start, _cabi.ptr(records), self.world_size, _cabi.ptr(out),
+                    _cabi.ptr(ws), ws.numel(), s,
                 )
             )
             if self._kernel_events is not None:
                 pair[1].record()
                 self._kernel_events.append(pair)
+            self._pending = (self._swarm_key(), self._gather(out))
         self.generation += 1
         if plan is None:
             self.fit = self.evaluate(self.pop)
@@ -219,7 +258,9 @@ class PSO(Algorithm):
             )
             self._workflow_notify(self.pop, self.fit)
         self.local_best_fit.copy_(self.fit)
-        self._update_global_best(dev, have_previous=False)
+        records = self._update_global_best(dev, have_previous=False)
+        # the first generation folds the same records again: a tie, which the stored best wins
+        self._pending = (self._swarm_key(), records) if plan is not None else None
 
     def _workflow_notify(self, pop: torch.Tensor, fit: torch.Tensor) -> None:
         notify = getattr(self, "_workflow_fused_notify", None)

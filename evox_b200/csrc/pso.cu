@@ -4,13 +4,17 @@
 // min_by (pso_variants/utils.py:6-25), clamp (evox/utils/jit_fix_operator.py:24-44),
 // ackley_func / rastrigin_func (evox/problems/numerical/basic.py:66-69, 115-116).
 //
-// One generation is two launches on one stream:
-//   1. pso_local_best_kernel  — argmin over fit (4 bytes per particle), finished by the last
-//      block to arrive; it also folds the result into the running global best (single GPU) or
-//      writes a candidate record for an allgather (sharded swarm).
-//   2. pso_move_eval_kernel   — one warp per particle, 128-bit loads: personal-best update,
-//      velocity / position update, relu-form clamps and the fitness of the moved particle, with
-//      a fixed-order shuffle reduction so results do not depend on scheduling.
+// One generation is ONE launch (evox_pso_generation): pso_move_eval_kernel<.., FUSED = true>
+//   head  — every warp folds the best-particle records left by the previous generation (one per
+//           shard) into the running global best: the winner's row is the social attractor;
+//   body  — one warp per particle, 128-bit loads: personal-best update, velocity / position
+//           update, relu-form clamps and the fitness of the moved particle, with a fixed-order
+//           shuffle reduction so results do not depend on scheduling;
+//   tail  — per-block (min, row) of the NEW fitness; the last block to arrive (atomic ticket)
+//           stores the folded global best and writes this shard's record for the next generation.
+// The two-launch form (pso_local_best_kernel, then the un-fused move kernel) is kept: it starts a
+// run (init_step), recovers when something else wrote to the swarm between two generations, and
+// serves callers that evaluate the fitness themselves.
 // HBM traffic per particle-dimension: 12 B read (pop, velocity, personal best) + 8 B written
 // (pop, velocity), + 8 B read when rg / rp are supplied as tensors instead of Philox.
 #include <math.h>
@@ -95,7 +99,69 @@ struct MoveArgs {
   RoundKeys rk;
   uint64_t generation;
   long long row_offset;
+  // read only by the FUSED instantiations
+  const uint32_t* cands;    // n_cands records of (4 + d) words left by the previous generation
+  int n_cands;
+  float* gbest_fit;         // running best fitness: read by every warp, stored by the last block
+  float* gbest_loc_out;     // the array gbest_loc points at, writable
+  uint32_t* cand_out;       // this shard's record of the new swarm (never inside cands)
+  unsigned int* ticket;
+  MinIdx* partials;
 };
+
+constexpr long long kNoRow = 0x7fffffffffffffffLL;
+
+// true when argmin would report b before a (smaller key, then lower index)
+__device__ __forceinline__ bool comes_first(const MinIdx& b, const MinIdx& a) {
+  return key_less(b.v, a.v) || (!key_less(a.v, b.v) && b.i < a.i);
+}
+
+// min_by over [old best, records] (pso_variants/utils.py:18-25): the old best wins ties, then the lowest
+// GLOBAL row index. Every lane returns the same answer: the attractor row, whether a record replaced the old
+// best, and that record's fitness.
+__device__ __forceinline__ const float* fold_candidates(const MoveArgs& a, int lane, bool* take, float* best_fit) {
+  const int words = 4 + a.d;
+  MinIdx m{INFINITY, kNoRow};
+  int rec = 0;
+  for (int r = lane; r < a.n_cands; r += 32) {
+    const uint32_t* c = a.cands + (size_t)r * words;
+    const MinIdx o{__uint_as_float(__ldg(c)), (long long)(((unsigned long long)__ldg(c + 2) << 32) | __ldg(c + 1))};
+    if (comes_first(o, m)) {
+      m = o;
+      rec = r;
+    }
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    MinIdx o;
+    o.v = __shfl_xor_sync(0xffffffffu, m.v, off);
+    o.i = __shfl_xor_sync(0xffffffffu, m.i, off);
+    const int orec = __shfl_xor_sync(0xffffffffu, rec, off);
+    if (comes_first(o, m)) {
+      m = o;
+      rec = orec;
+    }
+  }
+  *take = key_less(m.v, *a.gbest_fit);
+  *best_fit = m.v;
+  return *take ? reinterpret_cast<const float*>(a.cands + (size_t)rec * words + 4) : a.gbest_loc;
+}
+
+__device__ __forceinline__ MinIdx block_min_idx(MinIdx m, MinIdx* smem) {
+  m = warp_min_idx(m);
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  if (lane == 0) smem[wid] = m;
+  __syncthreads();
+  if (wid == 0) {
+    MinIdx t = (lane < (int)(blockDim.x >> 5)) ? smem[lane] : MinIdx{INFINITY, kNoRow};
+    t = warp_min_idx(t);
+    if (lane == 0) smem[0] = t;
+  }
+  __syncthreads();
+  MinIdx r = smem[0];
+  __syncthreads();
+  return r;
+}
 
 // One particle-dimension of PSO.step (pso.py:98-105). Returns the clamped position.
 __device__ __forceinline__ float move_one(float x, float& v, float pb, float gb, float lb, float ub,
@@ -109,10 +175,18 @@ __device__ __forceinline__ float move_one(float x, float& v, float pb, float gb,
   return relu_clamp(xn, lb, ub);
 }
 
-template <int VEC, bool PHILOX, int FIT>
+template <int VEC, bool PHILOX, int FIT, bool FUSED>
 __global__ void __launch_bounds__(kThreads, MOVE_BLOCKS_PER_SM) pso_move_eval_kernel(const MoveArgs a) {
   const int lane = threadIdx.x & 31;
   const long long warp0 = (long long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  __shared__ MinIdx s_warp_min[FUSED ? kWarpsPerBlock : 1];
+  const float* gbest_row = a.gbest_loc;
+  if constexpr (FUSED) {
+    bool take;
+    float best;
+    gbest_row = fold_candidates(a, lane, &take, &best);
+    if (lane == 0) s_warp_min[threadIdx.x >> 5] = MinIdx{INFINITY, kNoRow};
+  }
   const long long n_warps = (long long)gridDim.x * kWarpsPerBlock;
   const float w = *a.w, phi_p = *a.phi_p, phi_g = *a.phi_g;
   // vector path in Philox mode: the draws arrive as 24-bit integers, 2^-24 rides on phi (exact)
@@ -132,7 +206,7 @@ __global__ void __launch_bounds__(kThreads, MOVE_BLOCKS_PER_SM) pso_move_eval_ke
       float4* pop4 = reinterpret_cast<float4*>(a.pop + base);
       float4* vel4 = reinterpret_cast<float4*>(a.vel + base);
       float4* pb4 = reinterpret_cast<float4*>(a.pbest_loc + base);
-      const float4* gb4 = reinterpret_cast<const float4*>(a.gbest_loc);
+      const float4* gb4 = reinterpret_cast<const float4*>(gbest_row);
       const float4* lb4 = reinterpret_cast<const float4*>(a.lb);
       const float4* ub4 = reinterpret_cast<const float4*>(a.ub);
       const float4* rg4 = PHILOX ? nullptr : reinterpret_cast<const float4*>(a.rg + base);
@@ -180,7 +254,7 @@ __global__ void __launch_bounds__(kThreads, MOVE_BLOCKS_PER_SM) pso_move_eval_ke
           rg = a.rg[base + e];
           rp = a.rp[base + e];
         }
-        const float xo = move_one(x, v, pb, a.gbest_loc[e], a.lb[e], a.ub[e], rg, rp, w, phi_p, phi_g);
+        const float xo = move_one(x, v, pb, gbest_row[e], a.lb[e], a.ub[e], rg, rp, w, phi_p, phi_g);
         if (better) a.pbest_loc[base + e] = x;
         a.pop[base + e] = xo;
         a.vel[base + e] = v;
@@ -189,9 +263,58 @@ __global__ void __launch_bounds__(kThreads, MOVE_BLOCKS_PER_SM) pso_move_eval_ke
     }
     acc.reduce();
     if (lane == 0) {
-      a.fit[row] = acc.finish(d, a.fp);     // pso.py:106
+      const float f_new = acc.finish(d, a.fp);
+      a.fit[row] = f_new;                    // pso.py:106
       if (better) a.pbest_fit[row] = f_old;  // pso.py:91
+      if constexpr (FUSED) {
+        // a warp meets its rows in ascending order: a strict comparison keeps the first minimum
+        MinIdx* mine = &s_warp_min[threadIdx.x >> 5];
+        if (mine->i == kNoRow || key_less(f_new, mine->v)) *mine = MinIdx{f_new, row};
+      }
     }
+  }
+  if constexpr (FUSED) {
+    __shared__ MinIdx s_red[32];
+    __shared__ bool s_last;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      MinIdx t = (lane < kWarpsPerBlock) ? s_warp_min[lane] : MinIdx{INFINITY, kNoRow};
+      t = warp_min_idx(t);
+      if (lane == 0) {
+        a.partials[blockIdx.x] = t;
+        __threadfence();
+        s_last = (atomicAdd(a.ticket, 1u) == gridDim.x - 1);
+      }
+    }
+    __syncthreads();
+    if (!s_last) return;
+    // Every other block has finished its rows: nobody reads the records or the global best any more.
+    __threadfence();
+    MinIdx f{INFINITY, kNoRow};
+    for (int i = threadIdx.x; i < (int)gridDim.x; i += blockDim.x) {
+      const volatile MinIdx* p = a.partials + i;
+      f = min_idx_combine(f, MinIdx{p->v, p->i});
+    }
+    f = block_min_idx(f, s_red);
+    // store the global best this generation moved towards (pso.py:92-95) ...
+    bool take;
+    float best;
+    const float* src = fold_candidates(a, lane, &take, &best);
+    if (take) {
+      for (int e = threadIdx.x; e < d; e += blockDim.x) a.gbest_loc_out[e] = src[e];
+    }
+    __syncthreads();  // ... before its record may be overwritten
+    if (threadIdx.x == 0) {
+      if (take) *a.gbest_fit = best;
+      *a.ticket = 0u;  // ready for the next launch
+      const long long g = f.i + a.row_offset;
+      a.cand_out[0] = __float_as_uint(f.v);
+      a.cand_out[1] = (uint32_t)((unsigned long long)g & 0xffffffffull);
+      a.cand_out[2] = (uint32_t)((unsigned long long)g >> 32);
+      a.cand_out[3] = 0u;
+    }
+    const float* row = a.pop + (size_t)f.i * (size_t)d;  // written by another block of this launch: read past L1
+    for (int e = threadIdx.x; e < d; e += blockDim.x) a.cand_out[4 + e] = __float_as_uint(__ldcg(row + e));
   }
 }
 
@@ -238,28 +361,12 @@ struct BestArgs {
   MinIdx* partials;
 };
 
-__device__ __forceinline__ MinIdx block_min_idx(MinIdx m, MinIdx* smem) {
-  m = warp_min_idx(m);
-  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-  if (lane == 0) smem[wid] = m;
-  __syncthreads();
-  if (wid == 0) {
-    MinIdx t = (lane < (int)(blockDim.x >> 5)) ? smem[lane] : MinIdx{INFINITY, 0x7fffffffffffffffLL};
-    t = warp_min_idx(t);
-    if (lane == 0) smem[0] = t;
-  }
-  __syncthreads();
-  MinIdx r = smem[0];
-  __syncthreads();
-  return r;
-}
-
 __global__ void __launch_bounds__(kThreads) pso_local_best_kernel(const BestArgs a) {
   __shared__ MinIdx smem[32];
   __shared__ bool is_last;
   // +inf with the largest index loses against every real entry (an all-+inf shard still
   // reports index 0 because equal keys resolve to the lower index).
-  MinIdx m{INFINITY, 0x7fffffffffffffffLL};
+  MinIdx m{INFINITY, kNoRow};
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < a.P; i += (long long)gridDim.x * blockDim.x) {
     m = min_idx_combine(m, MinIdx{a.fit[i], i});
   }
@@ -273,7 +380,7 @@ __global__ void __launch_bounds__(kThreads) pso_local_best_kernel(const BestArgs
   __syncthreads();
   if (!is_last) return;
   __threadfence();
-  MinIdx f{INFINITY, 0x7fffffffffffffffLL};
+  MinIdx f{INFINITY, kNoRow};
   for (int i = threadIdx.x; i < (int)gridDim.x; i += blockDim.x) {
     const volatile MinIdx* p = a.partials + i;
     f = min_idx_combine(f, MinIdx{p->v, p->i});
@@ -307,7 +414,7 @@ __global__ void __launch_bounds__(kThreads)
   __shared__ int winner;
   const int words = 4 + d;
   if (threadIdx.x == 0) {
-    MinIdx best{INFINITY, 0x7fffffffffffffffLL};
+    MinIdx best{INFINITY, kNoRow};
     int bi = 0;
     for (int r = 0; r < n; ++r) {
       const uint32_t* c = cands + (size_t)r * words;
@@ -391,18 +498,29 @@ int check_fit(int fitness_id, const float* params, FitParams* fp) {
   return EVOX_OK;
 }
 
-template <int VEC, bool PHILOX>
+template <int VEC, bool PHILOX, bool FUSED>
 void launch_move(int fitness_id, int grid, cudaStream_t s, const MoveArgs& a) {
   switch (fitness_id) {
     case EVOX_FIT_ACKLEY:
-      pso_move_eval_kernel<VEC, PHILOX, EVOX_FIT_ACKLEY><<<grid, kThreads, 0, s>>>(a);
+      pso_move_eval_kernel<VEC, PHILOX, EVOX_FIT_ACKLEY, FUSED><<<grid, kThreads, 0, s>>>(a);
       break;
     case EVOX_FIT_RASTRIGIN:
-      pso_move_eval_kernel<VEC, PHILOX, EVOX_FIT_RASTRIGIN><<<grid, kThreads, 0, s>>>(a);
+      pso_move_eval_kernel<VEC, PHILOX, EVOX_FIT_RASTRIGIN, FUSED><<<grid, kThreads, 0, s>>>(a);
       break;
     default:
-      pso_move_eval_kernel<VEC, PHILOX, EVOX_FIT_SPHERE><<<grid, kThreads, 0, s>>>(a);
+      pso_move_eval_kernel<VEC, PHILOX, EVOX_FIT_SPHERE, FUSED><<<grid, kThreads, 0, s>>>(a);
       break;
+  }
+}
+
+template <bool FUSED>
+void launch_move_any(bool vec, bool philox, int fitness_id, int grid, cudaStream_t s, const MoveArgs& a) {
+  if (vec) {
+    if (philox) launch_move<4, true, FUSED>(fitness_id, grid, s, a);
+    else launch_move<4, false, FUSED>(fitness_id, grid, s, a);
+  } else {
+    if (philox) launch_move<1, true, FUSED>(fitness_id, grid, s, a);
+    else launch_move<1, false, FUSED>(fitness_id, grid, s, a);
   }
 }
 
@@ -492,51 +610,107 @@ extern "C" int evox_pso_merge_best(const uint32_t* candidates, int32_t n_candida
   return EVOX_OK;
 }
 
-extern "C" int evox_pso_move_eval(float* pop, float* velocity, float* local_best_location,
-                                  float* local_best_fit, float* fit, const float* global_best_location,
-                                  const float* lb, const float* ub, const float* w, const float* phi_p,
-                                  const float* phi_g, const float* rg, const float* rp, int64_t pop_size,
-                                  int32_t dim, int32_t fitness_id, const float* params, uint64_t seed,
-                                  uint64_t generation, int64_t row_offset, void* stream) {
+namespace {
+
+// Argument checks and packing shared by the two forms of the update kernel.
+int fill_move_args(MoveArgs* a, bool* vec, float* pop, float* velocity, float* local_best_location, float* local_best_fit,
+                   float* fit, const float* global_best_location, const float* lb, const float* ub, const float* w,
+                   const float* phi_p, const float* phi_g, const float* rg, const float* rp, int64_t pop_size,
+                   int32_t dim, int32_t fitness_id, const float* params, uint64_t seed, uint64_t generation,
+                   int64_t row_offset) {
   if (int rc = check_shape(pop_size, dim)) return rc;
   EVOX_REQUIRE(pop && velocity && local_best_location && local_best_fit && fit && global_best_location && lb &&
                    ub && w && phi_p && phi_g,
                EVOX_ERR_INVALID, "pso_move_eval: NULL pointer");
   EVOX_REQUIRE((rg == nullptr) == (rp == nullptr), EVOX_ERR_INVALID,
                "pso_move_eval: rg and rp must both be given or both be NULL");
+  if (int rc = check_fit(fitness_id, params, &a->fp)) return rc;
+  a->pop = pop;
+  a->vel = velocity;
+  a->pbest_loc = local_best_location;
+  a->pbest_fit = local_best_fit;
+  a->fit = fit;
+  a->gbest_loc = global_best_location;
+  a->lb = lb;
+  a->ub = ub;
+  a->w = w;
+  a->phi_p = phi_p;
+  a->phi_g = phi_g;
+  a->rg = rg;
+  a->rp = rp;
+  a->P = pop_size;
+  a->d = dim;
+  a->rk = make_round_keys(seed);
+  a->generation = generation;
+  a->row_offset = row_offset;
+  a->cands = nullptr;
+  a->n_cands = 0;
+  a->gbest_fit = nullptr;
+  a->gbest_loc_out = nullptr;
+  a->cand_out = nullptr;
+  a->ticket = nullptr;
+  a->partials = nullptr;
+  *vec = (dim % 4 == 0) && aligned16(pop) && aligned16(velocity) && aligned16(local_best_location) &&
+         aligned16(global_best_location) && aligned16(lb) && aligned16(ub);
+  if (rg != nullptr) *vec = *vec && aligned16(rg) && aligned16(rp);
+  return EVOX_OK;
+}
+
+}  // namespace
+
+extern "C" int evox_pso_move_eval(float* pop, float* velocity, float* local_best_location,
+                                  float* local_best_fit, float* fit, const float* global_best_location,
+                                  const float* lb, const float* ub, const float* w, const float* phi_p,
+                                  const float* phi_g, const float* rg, const float* rp, int64_t pop_size,
+                                  int32_t dim, int32_t fitness_id, const float* params, uint64_t seed,
+                                  uint64_t generation, int64_t row_offset, void* stream) {
   MoveArgs a;
-  if (int rc = check_fit(fitness_id, params, &a.fp)) return rc;
-  a.pop = pop;
-  a.vel = velocity;
-  a.pbest_loc = local_best_location;
-  a.pbest_fit = local_best_fit;
-  a.fit = fit;
-  a.gbest_loc = global_best_location;
-  a.lb = lb;
-  a.ub = ub;
-  a.w = w;
-  a.phi_p = phi_p;
-  a.phi_g = phi_g;
-  a.rg = rg;
-  a.rp = rp;
-  a.P = pop_size;
-  a.d = dim;
-  a.rk = make_round_keys(seed);
-  a.generation = generation;
-  a.row_offset = row_offset;
+  bool vec;
+  if (int rc = fill_move_args(&a, &vec, pop, velocity, local_best_location, local_best_fit, fit, global_best_location,
+                              lb, ub, w, phi_p, phi_g, rg, rp, pop_size, dim, fitness_id, params, seed, generation,
+                              row_offset))
+    return rc;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  const int grid = row_grid(pop_size, MOVE_BLOCKS_PER_SM);
-  const bool philox = (rg == nullptr);
-  bool vec = (dim % 4 == 0) && aligned16(pop) && aligned16(velocity) && aligned16(local_best_location) &&
-             aligned16(global_best_location) && aligned16(lb) && aligned16(ub);
-  if (!philox) vec = vec && aligned16(rg) && aligned16(rp);
-  if (vec) {
-    if (philox) launch_move<4, true>(fitness_id, grid, s, a);
-    else launch_move<4, false>(fitness_id, grid, s, a);
-  } else {
-    if (philox) launch_move<1, true>(fitness_id, grid, s, a);
-    else launch_move<1, false>(fitness_id, grid, s, a);
+  launch_move_any<false>(vec, rg == nullptr, fitness_id, row_grid(pop_size, MOVE_BLOCKS_PER_SM), s, a);
+  EVOX_LAUNCH_CHECK();
+  return EVOX_OK;
+}
+
+extern "C" int evox_pso_generation(float* pop, float* velocity, float* local_best_location, float* local_best_fit,
+                                   float* fit, float* global_best_location, float* global_best_fit, const float* lb,
+                                   const float* ub, const float* w, const float* phi_p, const float* phi_g,
+                                   const float* rg, const float* rp, int64_t pop_size, int32_t dim,
+                                   int32_t fitness_id, const float* params, uint64_t seed, uint64_t generation,
+                                   int64_t row_offset, const uint32_t* candidates, int32_t n_candidates,
+                                   uint32_t* candidate_out, void* workspace, size_t workspace_bytes, void* stream) {
+  MoveArgs a;
+  bool vec;
+  if (int rc = fill_move_args(&a, &vec, pop, velocity, local_best_location, local_best_fit, fit, global_best_location,
+                              lb, ub, w, phi_p, phi_g, rg, rp, pop_size, dim, fitness_id, params, seed, generation,
+                              row_offset))
+    return rc;
+  EVOX_REQUIRE(global_best_fit && candidates && candidate_out, EVOX_ERR_INVALID, "pso_generation: NULL pointer");
+  EVOX_REQUIRE(n_candidates > 0, EVOX_ERR_INVALID, "pso_generation: n_candidates must be positive, got %d", n_candidates);
+  {
+    const uintptr_t c0 = reinterpret_cast<uintptr_t>(candidates), o0 = reinterpret_cast<uintptr_t>(candidate_out);
+    const uintptr_t rec = sizeof(uint32_t) * (size_t)(4 + dim);
+    EVOX_REQUIRE(o0 + rec <= c0 || c0 + rec * (size_t)n_candidates <= o0, EVOX_ERR_INVALID,
+                 "pso_generation: candidates and candidate_out overlap");
   }
+  Workspace ws;
+  if (int rc = carve(workspace, workspace_bytes, &ws)) return rc;
+  // the attractor row is read with 16-byte loads straight out of a record: row start = record + 16 bytes
+  vec = vec && aligned16(candidates);
+  a.cands = candidates;
+  a.n_cands = n_candidates;
+  a.gbest_fit = global_best_fit;
+  a.gbest_loc_out = global_best_location;
+  a.cand_out = candidate_out;
+  a.ticket = ws.ticket;
+  a.partials = ws.partials;
+  const int grid = row_grid(pop_size, MOVE_BLOCKS_PER_SM);
+  EVOX_REQUIRE(grid <= kMaxPartials, EVOX_ERR_INVALID, "pso_generation: grid of %d blocks exceeds %d partials", grid, kMaxPartials);
+  launch_move_any<true>(vec, rg == nullptr, fitness_id, grid, reinterpret_cast<cudaStream_t>(stream), a);
   EVOX_LAUNCH_CHECK();
   return EVOX_OK;
 }

@@ -29,11 +29,13 @@ def group_info(group=None) -> tuple[int, int]:
     return 0, 1
 
 
-def allgather_records(record: torch.Tensor, group=None) -> torch.Tensor:
-    """Concatenate every rank's 1-D record in rank order (one small allgather)."""
+def allgather_records(record: torch.Tensor, group=None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Concatenate every rank's 1-D record in rank order (one small allgather). `out`, when given,
+    receives the result (world_size * record.numel() elements) instead of a fresh tensor."""
     rank, world = group_info(group)
     if world == 1:
         return record
-    out = torch.empty(world * record.numel(), dtype=record.dtype, device=record.device)
-    dist.all_gather_into_tensor(out, record, group=group)
+    if out is None:
+        out = torch.empty(world * record.numel(), dtype=record.dtype, device=record.device)
+    dist.all_gather_into_tensor(out.view(-1), record, group=group)
     return out

@@ -93,13 +93,36 @@ int evox_pso_move_eval(float* pop, float* velocity, float* local_best_location,
                        int32_t dim, int32_t fitness_id, const float* params, uint64_t seed,
                        uint64_t generation, int64_t row_offset, void* stream);
 
-/* One whole single-GPU generation: local_best + merge_best + move_eval (PSO.step, pso.py:71-106). */
+/* One whole single-GPU generation as two launches: local_best + merge_best, then move_eval
+ * (PSO.step, pso.py:71-106). Needs no record carried from one call to the next. */
 int evox_pso_step(float* pop, float* velocity, float* local_best_location, float* local_best_fit,
                   float* fit, float* global_best_location, float* global_best_fit,
                   const float* lb, const float* ub, const float* w, const float* phi_p,
                   const float* phi_g, const float* rg, const float* rp, int64_t pop_size,
                   int32_t dim, int32_t fitness_id, const float* params, uint64_t seed,
                   uint64_t generation, void* workspace, size_t workspace_bytes, void* stream);
+
+/* One whole generation of a swarm shard in ONE launch (PSO.step, pso.py:71-106, with min_by of
+ * pso_variants/utils.py:6-25 split across two consecutive calls): the kernel of evox_pso_move_eval with
+ *  - a head in which every warp folds `candidates` (n_candidates records in rank order, the
+ *    fitness minima of the swarm as the PREVIOUS call left it) into the running global best —
+ *    the old best wins ties, then the lowest global row index, exactly as evox_pso_merge_best —
+ *    and moves towards the winner;
+ *  - a tail in which the last block to finish stores that winner in global_best_location /
+ *    global_best_fit and writes this shard's record of the NEW fit and pop to `candidate_out`
+ *    (the layout of evox_pso_local_best), ready to be gathered and passed to the next call.
+ * The records must describe fit and pop as they are when the call starts: after anything else
+ * wrote to them, rebuild the record with evox_pso_local_best. `candidates` and `candidate_out`
+ * must not overlap (alternate two buffers on a single GPU; with several shards `candidates` is
+ * the gathered array). Other arguments as evox_pso_move_eval; workspace as evox_pso_local_best. */
+int evox_pso_generation(float* pop, float* velocity, float* local_best_location, float* local_best_fit,
+                        float* fit, float* global_best_location, float* global_best_fit,
+                        const float* lb, const float* ub, const float* w, const float* phi_p,
+                        const float* phi_g, const float* rg, const float* rp, int64_t pop_size,
+                        int32_t dim, int32_t fitness_id, const float* params, uint64_t seed,
+                        uint64_t generation, int64_t row_offset, const uint32_t* candidates,
+                        int32_t n_candidates, uint32_t* candidate_out, void* workspace,
+                        size_t workspace_bytes, void* stream);
 
 /* PSO.init_step (pso.py:108-115): fit = f(pop); local_best_fit = fit; global best = min_by. */
 int evox_pso_init_step(const float* pop, float* fit, float* local_best_fit,
@@ -471,12 +494,26 @@ int evox_neg_mse_from_partials(const float* row_partial, int64_t pop, int64_t ba
  * the call fails with EVOX_ERR_INVALID and evox_nd_rank must be used. Same results as
  * evox_nd_rank; `f`, `rank` and the optional `status` are still the caller's buffers.
  * The first call on each device looks up the array's device address (with that device
- * current); make that first call before starting any stream capture. All calls on a device
+ * current); make that first call before starting any stream capture. The address is kept for
+ * the life of that device's primary context: after a cudaDeviceReset (or any other teardown of
+ * the context) in the same process the entry point must not be called again. All calls on a device
  * share the one array and it keeps the previous call's contents (everything that is read is
  * rewritten first), so two calls must not overlap on the GPU: issue them on one stream, or
  * order them with events. */
 int evox_nd_rank_static(const float* f, int64_t n, int32_t m, int32_t* rank, int32_t* status,
                         void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Measurement support.
+ * ------------------------------------------------------------------------------------------ */
+
+/* Issue-rate microbenchmark for the roofline of the dominance phase of non_dominate_rank
+ * (operators/selection/non_dominate.py:6-26: m * n^2 fp32 comparisons on kilobytes of input).
+ * Every one of evox_bench_compare_rate_threads() threads performs 64 * iterations fp32 "<=" comparisons
+ * combined into predicates; `in` holds 1,024 floats (in[1023] is the per-iteration increment of the
+ * compared values), `out` receives one word per thread. The caller times the call with CUDA events. */
+int64_t evox_bench_compare_rate_threads(void);
+int evox_bench_compare_rate(const float* in, uint32_t* out, int32_t iterations, void* stream);
 
 #ifdef __cplusplus
 }

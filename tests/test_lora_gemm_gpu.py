@@ -163,3 +163,90 @@ def test_fused_next_layer_projection(cuda, pop):
     a, _ = lora.generate_lora_factors(seeds.cpu(), (d, d), 8, next_counter)
     ref = torch.bmm(y.float().cpu(), a.transpose(1, 2))
     assert rel_err(t_next, ref) <= 1e-4
+
+
+# ---------------------------------------------------------------------------------------------
+# The layer shape of the virtual-LoRA benchmark configuration: K = N = 4096 (64 k-blocks per tile,
+# 16 column tiles, 32 slices of the fused next-layer projection), few individuals so that the fp32
+# oracle stays cheap.
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("pop", [8, 6])  # 512 rows: CTA pairs; 384 rows: single-CTA tiles
+def test_layer_at_benchmark_width(cuda, pop):
+    from evox_b200.lora_kernels import lora_layer_bf16
+
+    g = torch.Generator().manual_seed(4096 + pop)
+    batch, k, d, sigma, counter, next_counter = 64, 4096, 4096, 0.02, 65536, 131072
+    h = torch.randn(pop, batch, k, generator=g).bfloat16()
+    w = (torch.randn(d, k, generator=g) / k**0.5).bfloat16()
+    seeds = torch.randint(0, 2**31, (pop,), generator=g, dtype=torch.int64)
+    want = reference_layer(h, w, seeds, counter, sigma, None, None, True)
+    y, t_next = lora_layer_bf16(h.to(cuda), w.to(cuda), seeds.to(cuda), counter, sigma, relu=True, next_counter=next_counter)
+    torch.cuda.synchronize()
+    assert int(lora_layer_bf16.last_error_flag) == 0
+    assert rel_err(y.float(), want) <= 2e-2
+    # the projection for the next layer, from the bf16 activations the kernel stored
+    a, _ = lora.generate_lora_factors(seeds, (d, d), 8, next_counter)
+    assert rel_err(t_next, torch.bmm(y.float().cpu(), a.transpose(1, 2))) <= 1e-4
+    # fused squared error of a last layer of that width
+    target = torch.randn(batch, d, generator=g)
+    want_mse = -((reference_layer(h, w, seeds, counter, sigma, None, None, False) - target) ** 2).mean(dim=(1, 2))
+    got_mse = lora_layer_bf16(h.to(cuda), w.to(cuda), seeds.to(cuda), counter, sigma, target=target.to(cuda))
+    torch.cuda.synchronize()
+    assert int(lora_layer_bf16.last_error_flag) == 0
+    assert rel_err(got_mse, want_mse) <= 2e-3
+
+
+def test_problem_at_benchmark_width(cuda):
+    """Three 4096 -> 4096 layers with ReLU between them, eight individuals with their own 64 x 4096 batch, the
+    squared error reduced in the last layer's epilogue: the benchmark configuration's network, against the fp32
+    oracle forward on the same bf16-rounded operands (2e-2 relative on the fitness)."""
+    from torch import nn
+
+    from evox_b200.lora_kernels import lora_layer_bf16
+    from evox_b200.problems import VirtualLoRAProblem
+
+    g = torch.Generator().manual_seed(11)
+    pop, batch, width, rank, sigma = 8, 64, 4096, 8, 0.02
+    layers = []
+    for i in range(3):
+        lin = nn.Linear(width, width, bias=False)
+        with torch.no_grad():
+            lin.weight.copy_((torch.randn(width, width, generator=g) / width**0.5).bfloat16().float())
+        layers += [lin] + ([nn.ReLU()] if i < 2 else [])
+    model = nn.Sequential(*layers)
+    x = torch.randn(pop, batch, width, generator=g).bfloat16()
+    target = torch.randn(batch, width, generator=g)
+    prob = VirtualLoRAProblem(model, [(x, target)], nn.MSELoss(reduction="none"), rank, device=cuda, compute_dtype=torch.bfloat16)
+    center = torch.cat([p.detach().reshape(-1) for p in model.parameters()])
+    seeds = torch.randint(0, 2**31, (pop,), generator=g, dtype=torch.int64)
+    got = prob.evaluate((center.to(cuda), seeds.to(cuda), sigma))
+    torch.cuda.synchronize()
+    assert int(lora_layer_bf16.last_error_flag) == 0
+    weights = [m.weight.detach() for m in model if isinstance(m, nn.Linear)]
+    out = lora.virtual_forward(x.float(), weights, [None] * 3, seeds, prob.counter_offsets, prob.param_shapes, rank, sigma)
+    want = ((out - target) ** 2).mean(dim=(1, 2))
+    assert got.shape == (pop,)
+    assert rel_err(got, want) <= 2e-2
+
+
+def test_tensor_core_gradient_at_benchmark_block(cuda):
+    """One full 4096 x 4096 gradient block at 1,024 individuals — 256 pair tiles walked by 74 CTA pairs over
+    several waves, the long K split between two work items per tile — against the fp64 einsum
+    (lora_noise.py:188-196) on 320 sampled rows: 1e-5 of the largest entry."""
+    from evox_b200.lora_kernels import lora_gradient_from_seeds
+
+    g = torch.Generator().manual_seed(77)
+    pop, d, k, counter, sigma = 1024, 4096, 4096, 65536, 0.02
+    seeds = torch.randint(0, 2**31, (pop,), generator=g, dtype=torch.int64)
+    fit = torch.rand(pop, generator=g) - 0.5
+    got = lora_gradient_from_seeds(fit.to(cuda), seeds.to(cuda), (d, k), 8, counter, pop, sigma)
+    torch.cuda.synchronize()
+    assert int(lora_gradient_from_seeds.last_error_flag) == 0
+    assert got.shape == (d, k)
+    a, b = lora.generate_lora_factors(seeds, (d, k), 8, counter)
+    # rows from every 256-row tile, first and last rows of tiles included
+    rows = torch.cat([torch.arange(0, d, 256), torch.arange(255, d, 256), torch.randint(0, d, (288,), generator=g)]).unique()
+    fb = (fit.double()[:, None, None] * b[:, rows, :].double()).permute(1, 0, 2).reshape(rows.numel(), pop * 8)
+    want = fb @ a.double().reshape(pop * 8, k) / (pop * sigma)
+    err = float((got[rows.to(cuda)].double().cpu() - want).abs().max() / want.abs().max())
+    assert err <= 1e-5, err

@@ -184,3 +184,29 @@ def test_metric_size_properties(cuda, n):
     assert bool(has_parent[rs > 0].all())
     # nothing of an EARLIER front may be dominated-free: rows of front 0 have no dominator at all
     assert not dom[rs == 0].any()
+
+
+@pytest.mark.parametrize("tag,n,fronts", [("config1", 20_000, None), ("metric", 100_000, 77)])
+def test_every_rank_at_the_benchmark_sizes(golden, cuda, tag, n, fronts):
+    """All n ranks against tests/golden/nds_large.npz: at 2N = 20,000 the ranks the reference itself computed,
+    at 2N = 100,000 (the size the rank metric is quoted on, beyond what the reference can hold in memory) the
+    ranks of the blocked bit-packed CPU restatement, which the generator first required to reproduce the
+    reference at 20,000. The stored objectives are used, so the check does not depend on this host's libm."""
+    from evox_b200.operators.selection import nd_environmental_selection, non_dominate_rank
+
+    g = golden("nds_large")
+    f = torch.from_numpy(g[f"{tag}_f"])
+    want = torch.from_numpy(g[f"{tag}_rank"]).to(torch.int32)
+    assert f.shape == (n, 3) and want.shape == (n,)
+    if fronts is not None:
+        assert int(want.max()) + 1 == fronts
+    got = non_dominate_rank(f.to(cuda), check=True)
+    assert torch.equal(got.cpu(), want)
+    # the selection built on those ranks: the kept rows are exactly the fronts before the cut, plus part of the cut front
+    k = n // 2
+    sel = nd_environmental_selection(f.to(cuda), f.to(cuda), k, return_index=True, check=True)
+    idx = sel[4].cpu()
+    cut = int(torch.sort(want).values[k - 1])
+    assert torch.equal(torch.sort(idx[want[idx] < cut]).values, torch.nonzero(want < cut).flatten())
+    assert bool((want[idx] <= cut).all()) and idx.unique().numel() == k
+    assert torch.equal(sel[2].cpu(), want[idx])

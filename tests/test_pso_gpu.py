@@ -62,6 +62,27 @@ class Swarm:
         )
         torch.cuda.synchronize()
 
+    def local_best(self, record, row_offset=0):
+        c = self.c
+        c.check(c.lib.evox_pso_local_best(self.p("fit"), self.p("pop"), self.P, self.d, row_offset, c.ptr(record),
+                                          c.ptr(self.ws), self.ws.numel(), c.stream_ptr(self.dev)))
+
+    def generation(self, prob, records, n_records, out, rg=None, rp=None, seed=0, generation=0, row_offset=0):
+        """evox_pso_generation: fold `records`, move, leave this shard's next record in `out`."""
+        c = self.c
+        rg_d = None if rg is None else rg.to(self.dev).contiguous()
+        rp_d = None if rp is None else rp.to(self.dev).contiguous()
+        c.check(
+            c.lib.evox_pso_generation(
+                self.p("pop"), self.p("velocity"), self.p("local_best_location"), self.p("local_best_fit"),
+                self.p("fit"), self.p("global_best_location"), self.p("global_best_fit"), self.p("lb"), self.p("ub"),
+                self.p("w"), self.p("phi_p"), self.p("phi_g"), c.ptr(rg_d), c.ptr(rp_d), self.P, self.d,
+                FIT_ID[prob], c.host_floats(PARAMS[prob]), seed, generation, row_offset, c.ptr(records), n_records,
+                c.ptr(out), c.ptr(self.ws), self.ws.numel(), c.stream_ptr(self.dev),
+            )
+        )
+        torch.cuda.synchronize()
+
     def init_step(self, prob):
         c = self.c
         c.check(
@@ -233,6 +254,130 @@ def test_sharded_candidates_match_single(cuda):
         assert torch.equal(sh.t["global_best_fit"], single.t["global_best_fit"])
 
 
+@pytest.mark.parametrize("prob,P,d,philox", [("ackley", 10_000, 500, True), ("rastrigin", 4097, 1000, False),
+                                             ("sphere", 77, 10, True), ("ackley", 5, 3, False), ("ackley", 1, 1, True)])
+def test_one_launch_generation_equals_two_launch_form(cuda, prob, P, d, philox):
+    """evox_pso_generation carries the arg-min of the fitness it produces to the next call; five
+    generations of it must leave every state entry, after every generation, bit-identical to the
+    two-launch evox_pso_step (same update arithmetic, so the fitness is compared exactly too)."""
+    from evox_b200 import _cabi as c
+
+    lo, hi = (-32.768, 32.768) if prob == "ackley" else (-5.12, 5.12)
+    s0 = opso.init_step(opso.make_state(P, d, lo, hi, 0.6, 2.5, 0.8, seed=3), opso.FITNESS[prob])
+    two, one = Swarm(s0, cuda), Swarm(s0, cuda)
+    words = c.lib.evox_pso_candidate_words(d)
+    rec = torch.zeros(2, words, dtype=torch.int32, device=cuda)
+    one.local_best(rec[0])
+    for g in range(5):
+        rg, rp = (None, None) if philox else opso.draws(P, d, 50 + g)
+        two.step(prob, rg, rp, seed=9, generation=g)
+        one.generation(prob, rec[g % 2], 1, rec[(g + 1) % 2], rg, rp, seed=9, generation=g)
+        for n in NAMES:
+            assert torch.equal(one.t[n], two.t[n]), (g, n)
+        # the record left behind describes the new swarm
+        want = opso.candidate_record(one.t["fit"].cpu(), one.t["pop"].cpu(), 0)
+        assert torch.equal(rec[(g + 1) % 2].cpu(), want), g
+
+
+def test_one_launch_generation_tie_and_nan_rules(cuda):
+    """The head of evox_pso_generation applies min_by's rules: the stored best wins ties, the lowest
+    global row wins among records, NaN counts as the minimum."""
+    from evox_b200 import _cabi as c
+
+    P, d = 300, 8
+    s = opso.make_state(P, d, -1.0, 1.0, 0.6, 2.5, 0.8, seed=5)
+    s["fit"] = torch.full((P,), 3.0)
+    s["fit"][[17, 200]] = 1.0
+    s["local_best_fit"] = s["fit"].clone()
+    s["global_best_location"] = torch.full((d,), 0.25)
+    rg, rp = opso.draws(P, d, 1)
+    words = c.lib.evox_pso_candidate_words(d)
+    for old, nan_row in ((1.0, None), (2.0, None), (2.0, 250), (float("nan"), 250)):
+        s["global_best_fit"] = torch.tensor(old)
+        if nan_row is not None:
+            s["fit"][nan_row] = float("nan")
+        sw = Swarm(s, cuda)
+        rec = torch.zeros(2, words, dtype=torch.int32, device=cuda)
+        sw.local_best(rec[0])
+        sw.generation("sphere", rec[0], 1, rec[1], rg, rp)
+        want = opso.step(s, rg, rp, opso.sphere)
+        assert torch.equal(sw.t["global_best_location"].cpu(), want["global_best_location"]), (old, nan_row)
+        assert torch.equal(torch.nan_to_num(sw.t["global_best_fit"].cpu(), nan=-7.0), torch.nan_to_num(want["global_best_fit"], nan=-7.0))
+        assert torch.equal(sw.t["pop"].cpu(), want["pop"])
+
+
+def test_one_launch_generation_sharded_matches_single(cuda):
+    """Three uneven shards emulated on one GPU: each runs evox_pso_generation over the gathered records of all
+    shards (built here by placing every shard's record in one array, which is what the allgather does); after
+    four generations the concatenated shards equal the unsharded swarm bit for bit."""
+    from evox_b200 import _cabi as c
+
+    P, d = 5001, 40
+    s = opso.init_step(opso.make_state(P, d, -5.12, 5.12, 0.7, 1.5, 1.5, seed=9), opso.rastrigin)
+    single = Swarm(s, cuda)
+    words = c.lib.evox_pso_candidate_words(d)
+    bounds = [(0, 1700), (1700, 3401), (3401, P)]
+    shards = []
+    for a, b in bounds:
+        part = {k: (v[a:b] if (v.ndim >= 1 and v.shape[0] == P) else v) for k, v in s.items()}
+        shards.append(Swarm(part, cuda))
+    gathered = torch.zeros(len(bounds), words, dtype=torch.int32, device=cuda)
+    mine = torch.zeros(len(bounds), words, dtype=torch.int32, device=cuda)
+    for r, (a, b) in enumerate(bounds):
+        shards[r].local_best(gathered[r], row_offset=a)
+    rec1 = torch.zeros(2, words, dtype=torch.int32, device=cuda)
+    single.local_best(rec1[0])
+    for g in range(4):
+        single.generation("rastrigin", rec1[g % 2], 1, rec1[(g + 1) % 2], seed=4, generation=g)
+        for r, (a, b) in enumerate(bounds):
+            shards[r].generation("rastrigin", gathered, len(bounds), mine[r], seed=4, generation=g, row_offset=a)
+        gathered.copy_(mine)
+        for n in ("pop", "velocity", "fit", "local_best_location", "local_best_fit"):
+            assert torch.equal(torch.cat([sh.t[n] for sh in shards]), single.t[n]), (g, n)
+        for sh in shards:
+            assert torch.equal(sh.t["global_best_location"], single.t["global_best_location"]), g
+            assert torch.equal(sh.t["global_best_fit"], single.t["global_best_fit"]), g
+
+
+def test_generation_rejects_overlapping_records(cuda):
+    from evox_b200 import _cabi as c
+
+    s = opso.init_step(opso.make_state(64, 8, -1.0, 1.0, 0.6, 2.5, 0.8, seed=1), opso.sphere)
+    sw = Swarm(s, cuda)
+    rec = torch.zeros(2, c.lib.evox_pso_candidate_words(8), dtype=torch.int32, device=cuda)
+    with pytest.raises(c.EvoxKernelError, match="overlap"):
+        sw.generation("sphere", rec, 2, rec[1])
+
+
+def test_step_sees_writes_between_generations(cuda):
+    """The record carried from one generation to the next is dropped when something else writes to `fit`
+    or `pop`: the next step must find the global best of the swarm as it is then (pso.py:92-95)."""
+    from evox_b200.algorithms import PSO
+    from evox_b200.problems.numerical import Sphere
+    from evox_b200.workflows import StdWorkflow
+
+    d = 16
+    algo = PSO(1000, torch.full((d,), -1.0), torch.full((d,), 1.0), device=cuda, seed=2)
+    wf = StdWorkflow(algo, Sphere(), device=cuda)
+    wf.init_step()
+    wf.step()
+    wf.step()
+    algo = wf.algorithm
+    algo.fit[123] = -5.0  # an in-place torch write
+    row = algo.pop[123].clone()
+    wf.step()
+    assert float(algo.global_best_fit) == -5.0
+    assert torch.equal(algo.global_best_location, row)
+    # a loaded state: the stored bests come from the dict, the record is rebuilt from its fit
+    sd = {k: v.clone() for k, v in algo.state_dict().items() if isinstance(v, torch.Tensor)}
+    sd["fit"][7] = -9.0
+    row = sd["pop"][7].clone()
+    algo.load_state_dict(sd)
+    wf.step()
+    assert float(algo.global_best_fit) == -9.0
+    assert torch.equal(algo.global_best_location, row)
+
+
 def test_workflow_fused_equals_unfused(cuda):
     """StdWorkflow(PSO, Ackley): the fused step and the path through Problem.evaluate agree,
     and the swarm improves."""
@@ -296,10 +441,9 @@ def test_reference_state_dict_loads(golden, cuda):
 
 
 def test_headline_size_properties(cuda):
-    """1,000,000 x 1,000 (the headline workload, 12 GB of state), checked through properties that do not
-    need the CPU oracle at that size: (a) every row's update depends only on that row, the global best and
-    its position in the random stream — four row blocks re-run as small swarms with `row_offset` must
-    reproduce the big run bit for bit; (b) the stored fitness is the fitness of the stored positions;
+    """1,000,000 x 1,000 (the headline workload, 12 GB of state): (a) every row's update depends only on that
+    row, the global best and its position in the random stream — four row blocks re-run as small swarms with
+    `row_offset` must reproduce the big run bit for bit, and the CPU oracle must reproduce them too (a'); (b) the stored fitness is the fitness of the stored positions;
     (c) positions stay inside the bounds; (d) the global best is the smallest fitness seen so far and
     never gets worse."""
     from evox_b200 import _cabi as c
@@ -322,6 +466,7 @@ def test_headline_size_properties(cuda):
     blocks = [(0, 513), (123_456, 124_000), (500_000, 500_257), (P - 300, P)]
     names = ("pop", "velocity", "local_best_location", "local_best_fit", "fit")
     saved = [{n: getattr(algo, n)[a:b].clone() for n in names} for a, b in blocks]
+    saved_before = [{n: t.clone() for n, t in part.items()} for part in saved]
     gen = algo.generation
     min_fit_before = float(algo.fit.min())
     wf.step()
@@ -336,6 +481,22 @@ def test_headline_size_properties(cuda):
             None, None, b - a, d, fid, c.host_floats(params), algo.seed, gen, a, c.stream_ptr(cuda)))
         for n in names:
             assert torch.equal(part[n], getattr(algo, n)[a:b]), (a, n)
+    # (a') the same four row blocks through the CPU oracle of PSO.step (pso.py:89-106), fed with the draws of the
+    # run's random stream at those rows and the run's global best: positions, velocities and personal bests
+    # bit for bit, fitness to 1e-5
+    hyper = {"lb": algo.lb.cpu(), "ub": algo.ub.cpu(), "w": algo.w.detach().cpu(), "phi_p": algo.phi_p.detach().cpu(),
+             "phi_g": algo.phi_g.detach().cpu()}
+    for (a, b), before in zip(blocks, saved_before):
+        st = {**{n: t.cpu() for n, t in before.items()}, **hyper,
+              # min_by over [stored best, block] must keep the run's global best: it is the minimum of the whole swarm
+              "global_best_location": gbest.cpu(), "global_best_fit": algo.global_best_fit.cpu()}
+        rg = opso.pso_uniform(b - a, d, algo.seed, gen, 0, row_offset=a)
+        rp = opso.pso_uniform(b - a, d, algo.seed, gen, 1, row_offset=a)
+        want = opso.step(st, rg, rp, opso.ackley)
+        for n in ("pop", "velocity", "local_best_location"):
+            assert torch.equal(getattr(algo, n)[a:b].cpu(), want[n]), (a, n)
+        for n in ("fit", "local_best_fit"):
+            assert_fitness_close(getattr(algo, n)[a:b], want[n], "ackley", d)
     # (b) re-evaluation of the stored positions, in slabs to bound memory
     for a in range(0, P, 250_000):
         again = prob.evaluate(algo.pop[a:a + 250_000])
