@@ -34,3 +34,12 @@ def test_rank_crowding_selection(golden, case):
 def test_blocking_does_not_change_ranks():
     f = nds.dtlz2_objectives(torch.rand(700, 12, generator=torch.Generator().manual_seed(1)))
     assert torch.equal(nds.non_dominate_rank(f, block=37), nds.non_dominate_rank(f, block=4096))
+
+
+def test_restatement_reproduces_the_reference_at_configuration_1(golden):
+    """2N = 20,000 DTLZ2-shaped rows: the ranks stored in nds_large.npz were computed by the reference itself;
+    the blocked bit-packed restatement (the source of the stored ranks at 2N = 100,000) must give the same."""
+    g = golden("nds_large")
+    f = torch.from_numpy(g["config1_f"])
+    assert torch.equal(nds.non_dominate_rank(f), torch.from_numpy(g["config1_rank"]).to(torch.int32))
+    assert g["metric_f"].shape == (100_000, 3) and g["metric_rank"].shape == (100_000,)
