@@ -21,6 +21,12 @@ def _update_center(algo, grad: torch.Tensor, start: int = 0, count: int | None =
     lr = algo.learning_rate if lr is None else lr
     adam = algo.optimizer == "adam"
     count = algo.center.numel() - start if count is None else count
+    if torch.compiler.is_compiling():  # traced: one registered operator that declares what it updates in place
+        from .. import ops
+
+        ops.es_update(algo.center, grad, lr, algo.exp_avg if adam else None, algo.exp_avg_sq if adam else None,
+                      algo.beta1 if adam else None, algo.beta2 if adam else None, start, count)
+        return
     assert grad.numel() == count and grad.is_contiguous()
 
     def at(t):
@@ -59,6 +65,8 @@ class _ESBase(Algorithm):
         """Host copy of noise_stdev; refreshed (one sync) when the parameter was modified in place OR rebound to
         another tensor (a fresh tensor's version counter can equal the cached one, so the key also holds the
         tensor's identity and storage address)."""
+        if torch.compiler.is_compiling():
+            return self._sigma_host  # a traced step cannot look at storage or version counters; it uses the last value read
         t = self.noise_stdev
         key = (id(t), t.data_ptr(), t._version)
         if getattr(self, "_sigma_key", None) != key:
@@ -100,6 +108,13 @@ class OpenES(_ESBase):
             noise = torch.randn(rows, self.dim, device=dev)
         noise = noise.to(torch.float32).contiguous()
         assert noise.shape == (rows, self.dim)
+        if torch.compiler.is_compiling():  # traced: the same three kernels as registered operators
+            from .. import ops
+
+            pop = ops.openes_ask(self.center, noise, self.noise_stdev, self.pop_size)
+            fitness = self.evaluate(pop)
+            _update_center(self, ops.openes_gradient(noise, fitness, self.pop_size, self.sigma()))
+            return
         pop = torch.empty(self.pop_size, self.dim, dtype=torch.float32, device=dev)
         lib, s = _cabi.lib, _cabi.stream_ptr(dev)
         _cabi.check(lib.evox_openes_ask(_cabi.ptr(self.center), _cabi.ptr(noise), _cabi.ptr(self.noise_stdev), self.pop_size, self.dim, rows, _cabi.ptr(pop), s))

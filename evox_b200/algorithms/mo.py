@@ -76,6 +76,12 @@ class _MOBase(Algorithm):
         if "_extra_state" not in state_dict:
             state_dict = dict(state_dict)
             state_dict["_extra_state"] = self.get_extra_state()
+        # some populations change their row count while they run (RVEAa keeps 2 * pop_size rows after its first
+        # generation, rveaa.py:189-212): a buffer whose stored shape differs is re-created before the copy
+        for name, buf in list(self.named_buffers(recurse=False)):
+            src = state_dict.get(name)
+            if isinstance(src, torch.Tensor) and src.shape != buf.shape:
+                setattr(self, name, torch.empty(src.shape, dtype=buf.dtype, device=buf.device))
         out = super().load_state_dict(state_dict, strict=strict, assign=assign)
         self._after_load()
         return out

@@ -69,7 +69,9 @@ class PSO(Algorithm):
         self.local_size = self.row_end - self.row_start
         assert self.local_size > 0, "every rank needs at least one particle"
         self.seed = int(torch.randint(0, 2**62, (), device="cpu")) if seed is None else int(seed)
-        self.generation = 0
+        # position in the random stream: a 0-d HOST tensor, so that a traced step can hand it to the operator
+        # that reads and advances it (`generation` below is its integer view)
+        self._generation = torch.zeros((), dtype=torch.int64)
         # hyper-parameters stay 0-d device tensors: the kernels read them without a host sync
         self.w = Parameter(w, dtype=torch.float32, device=device)
         self.phi_p = Parameter(phi_p, dtype=torch.float32, device=device)
@@ -108,6 +110,14 @@ class PSO(Algorithm):
         # measurement hook: when a list, step() appends a (start, end) CUDA-event pair around the
         # generation kernel (on several GPUs the allgather that follows stays outside the pair)
         self._kernel_events: list | None = None
+
+    @property
+    def generation(self) -> int:
+        return int(self._generation)
+
+    @generation.setter
+    def generation(self, value: int) -> None:
+        self._generation.fill_(int(value))
 
     # -- checkpointing of the random stream position ------------------------------------------
     def get_extra_state(self):
@@ -185,6 +195,8 @@ class PSO(Algorithm):
 
     def step(self, rg: torch.Tensor | None = None, rp: torch.Tensor | None = None):
         """One generation (pso.py:71-106). `rg`, `rp`: optional (local_size, dim) uniform draws."""
+        if torch.compiler.is_compiling():
+            return self._step_traced(rg, rp)
         ptrs = tuple(getattr(self, n).data_ptr() for n in self._STATE)
         if ptrs != self._checked_ptrs:
             dev = self._buffers_ready()
@@ -236,6 +248,25 @@ class PSO(Algorithm):
                 self._kernel_events.append(pair)
             self._pending = (self._swarm_key(), self._gather(out))
         self.generation += 1
+        if plan is None:
+            self.fit = self.evaluate(self.pop)
+        else:
+            self._workflow_notify(self.pop, self.fit)
+
+    def _step_traced(self, rg, rp):
+        """The generation as ONE registered operator (`evox_b200::pso_step`), for torch.compile: no storage
+        addresses, version counters or Python integers are read here. It is the two-launch form, which carries
+        nothing between calls; the operator bumps the version counters of the state it writes, so an eager step
+        afterwards rebuilds its best-particle record."""
+        from .. import ops
+
+        if self.world_size != 1:
+            raise _cabi.EvoxKernelError("a traced PSO.step runs on one GPU; step a sharded swarm eagerly")
+        plan = self._fused_plan()
+        fitness_id, params = plan if plan is not None else (FIT_SPHERE, (0.0, 0.0, 0.0))
+        ops.pso_step(self.pop, self.velocity, self.local_best_location, self.local_best_fit, self.fit, self.global_best_location,
+                     self.global_best_fit, self.lb, self.ub, self.w, self.phi_p, self.phi_g, rg, rp, fitness_id,
+                     [float(p) for p in params], self.seed, self._generation)
         if plan is None:
             self.fit = self.evaluate(self.pop)
         else:

@@ -9,11 +9,19 @@
 //                          angle between v_j and v_k, the diagonal counted as cosine 0
 //                          (rvea_selection.py:63-71).
 //   3. rvea_assign_kernel  4 lanes per individual: translate, normalise, cosine against every
-//                          vector from shared memory, arccos, first-minimum association, APD, and
+//                          vector from shared memory, first-minimum association by angle, APD, and
 //                          a 64-bit atomicMin of (APD bits, row) per vector — APD is positive, so
 //                          its bit pattern orders like the value and the lowest row wins ties, as
-//                          torch.argmin does.
+//                          torch.argmin does. The arccosine is taken only where it can matter: the
+//                          sweep keeps the largest and the second largest cosine, and a row whose
+//                          two largest cosines differ by more than 2e-6 is associated with the
+//                          largest one (arccos falls at least as fast as its argument rises, and
+//                          the device routine is accurate to 4e-7, so no other vector can have the
+//                          smaller computed angle); the few other rows repeat the sweep with the
+//                          arccosine of every cosine, exactly as the reference orders them.
 //   4. rvea_gather_kernel  rows of x and f for every vector, NaN for vectors nobody joined.
+// The unit vectors and gamma stay in the workspace: a caller that passes the same vectors again
+// says so and steps 2 are skipped.
 // Bytes that must move: n*m*4 (objectives) + nv*(dx+m)*4 (outputs); the pass is latency-bound at
 // the benchmark's 2 MB input.
 #include <math.h>
@@ -31,7 +39,9 @@ __device__ __forceinline__ uint32_t order_key(float x) {
   const uint32_t b = __float_as_uint(x);
   return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
 }
+// 0xffffffff (the byte pattern a memset leaves) stands for "no number seen": +inf, as nanmin reports it
 __device__ __forceinline__ float order_key_inv(uint32_t k) {
+  if (k == 0xffffffffu) return INFINITY;
   return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
 }
 
@@ -48,12 +58,6 @@ __global__ void rvea_decode_ideal_kernel(const uint32_t* zmin_key, int m, float*
 __global__ void rvea_encode_ideal_kernel(const float* zmin, int m, uint32_t* zmin_key) {
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
   if (t < m) zmin_key[t] = order_key(zmin[t]);
-}
-
-__global__ void rvea_init_kernel(uint32_t* zmin_key, int m, unsigned long long* best, int nv) {
-  const int t = blockIdx.x * blockDim.x + threadIdx.x;
-  if (t < m) zmin_key[t] = order_key(INFINITY);
-  if (t < nv) best[t] = 0xffffffffffffffffull;
 }
 
 // nanmin over rows (jit_fix_operator.py:289-292): NaN counts as +inf.
@@ -116,13 +120,44 @@ __global__ void __launch_bounds__(kThreads)
   }
 }
 
+// One output element of the gather: rows of x and f for every vector, NaN for vectors nobody joined.
+// sharded: x and f hold rows [row_begin, row_begin + row_count); rows of other shards and empty vectors
+// contribute 0 so that a sum over the shards reproduces the gathered row.
+__device__ __forceinline__ void gather_element(long long t, unsigned long long key, const float* __restrict__ x, long long dx,
+                                               const float* __restrict__ f, int m, float* __restrict__ next_x,
+                                               float* __restrict__ next_f, long long* __restrict__ next_index,
+                                               long long row_begin, long long row_count, int sharded) {
+  const long long per = dx + m;
+  const int j = (int)(t / per);
+  const long long c = t - (long long)j * per;
+  const bool empty = key == 0xffffffffffffffffull;
+  // a vector whose members all have APD = +inf: argmin over an all-inf column is row 0
+  const bool all_inf = !empty && (uint32_t)(key >> 32) == 0x7f800000u;
+  const long long src = all_inf ? 0 : (long long)(uint32_t)key;
+  const float nanv = __int_as_float(0x7fc00000);
+  const long long loc = src - row_begin;
+  const bool mine = !empty && loc >= 0 && loc < row_count;
+  if (c < dx) next_x[(long long)j * dx + c] = sharded ? (mine ? x[loc * dx + c] : 0.0f) : (empty ? nanv : x[src * dx + c]);
+  else next_f[(long long)j * m + (c - dx)] = sharded ? (mine ? f[loc * m + (c - dx)] : 0.0f) : (empty ? nanv : f[src * m + (c - dx)]);
+  if (c == 0 && next_index) next_index[j] = empty ? -1 : src;
+}
+
+constexpr float kCosMargin = 2e-6f;
+
+constexpr int kRowsPerGroup = 4;  // rows a group of kLanesPerRow lanes carries through one sweep of the vectors
+
+// A group of four lanes owns kRowsPerGroup consecutive rows and deals the vectors among its lanes: every vector
+// a lane reads from shared memory (three 16-byte loads for twelve objectives) is used for all of the group's
+// rows. (With one row per group the sweep was bound by shared-memory bandwidth: 48 bytes per row-vector pair,
+// 2.1 ms at 5,000,000 rows.)
 template <int MP>
 __global__ void __launch_bounds__(kThreads)
     rvea_assign_kernel(const float* __restrict__ f, long long n, int m, const uint32_t* __restrict__ zmin_key,
                        const float* __restrict__ vn, const float* __restrict__ gamma, int nv,
                        const float* __restrict__ theta_p, unsigned long long* best, int* __restrict__ associate,
                        long long row_offset) {
-  extern __shared__ float s_vn[];  // nv x MP, zero padded
+  constexpr int R = kRowsPerGroup;
+  extern __shared__ __align__(16) float s_vn[];  // nv x MP, zero padded
   for (int t = threadIdx.x; t < nv * MP; t += blockDim.x) {
     const int j = t / MP, k = t - j * MP;
     s_vn[t] = (k < m) ? vn[j * m + k] : 0.0f;
@@ -130,64 +165,142 @@ __global__ void __launch_bounds__(kThreads)
   __syncthreads();
   const float m_theta = __fmul_rn((float)m, *theta_p);  // rvea_selection.py:26: obj.size(1) * theta
   const int sub = threadIdx.x & (kLanesPerRow - 1);
-  const long long rows_per_pass = (long long)gridDim.x * (kThreads / kLanesPerRow);
-  const long long n_pad = (n + rows_per_pass - 1) / rows_per_pass * rows_per_pass;  // keep whole warps in the shuffles
-  for (long long row = (long long)blockIdx.x * (kThreads / kLanesPerRow) + (threadIdx.x / kLanesPerRow); row < n_pad;
-       row += rows_per_pass) {
-    const bool live = row < n;
-    float obj[MP];
-    bool has_nan = false;
-    float sq = 0.f;
+  // only the four lanes of a group meet in the shuffles below (the groups of a warp run different numbers of trips)
+  const unsigned group_lanes = ((1u << kLanesPerRow) - 1u) << (threadIdx.x & 31 & ~(kLanesPerRow - 1));
+  const long long groups_per_pass = (long long)gridDim.x * (kThreads / kLanesPerRow);
+  const long long n_groups = (n + R - 1) / R;
+  for (long long grp = (long long)blockIdx.x * (kThreads / kLanesPerRow) + (threadIdx.x / kLanesPerRow); grp < n_groups;
+       grp += groups_per_pass) {
+    float obj[R][MP];
+    float norm[R];
+    bool has_nan[R];
 #pragma unroll
-    for (int k = 0; k < MP; ++k) {
-      float o = 0.f;
-      if (live && k < m) {
-        o = __fsub_rn(f[row * m + k], order_key_inv(zmin_key[k]));
-        o = __fadd_rn(o, fmaxf(__fsub_rn(1e-32f, o), 0.0f));  // maximum(obj, 1e-32), relu form
-        has_nan = has_nan || (o != o);
-        sq = __fmaf_rn(o, o, sq);
+    for (int r = 0; r < R; ++r) {
+      const long long row = grp * R + r;
+      const bool live = row < n;
+      has_nan[r] = false;
+      float sq = 0.f;
+#pragma unroll
+      for (int k = 0; k < MP; ++k) {
+        float o = 0.f;
+        if (live && k < m) {
+          o = __fsub_rn(f[row * m + k], order_key_inv(zmin_key[k]));
+          o = __fadd_rn(o, fmaxf(__fsub_rn(1e-32f, o), 0.0f));  // maximum(obj, 1e-32), relu form
+          has_nan[r] = has_nan[r] || (o != o);
+          sq = __fmaf_rn(o, o, sq);
+        }
+        obj[r][k] = o;
       }
-      obj[k] = o;
-    }
-    const float norm = sqrtf(sq);
-    const float inv_den = fmaxf(norm, kEps);
+      norm[r] = sqrtf(sq);
+      const float inv_den = fmaxf(norm[r], kEps);
 #pragma unroll
-    for (int k = 0; k < MP; ++k) obj[k] = __fdiv_rn(obj[k], inv_den);
-    float best_angle = INFINITY;
-    int best_j = 0x7fffffff;
+      for (int k = 0; k < MP; ++k) obj[r][k] = __fdiv_rn(obj[r][k], inv_den);
+    }
+    // sweep 1: per row the largest cosine (first index among equals) and the largest cosine of all the others
+    float c1[R], c2[R];
+    int j1[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      c1[r] = -INFINITY;
+      c2[r] = -INFINITY;
+      j1[r] = 0x7fffffff;
+    }
+#pragma unroll 2
     for (int j = sub; j < nv; j += kLanesPerRow) {
-      const float* vj = s_vn + j * MP;
-      float c = 0.f;
+      float vj[MP];
+      if constexpr (MP % 4 == 0) {
 #pragma unroll
-      for (int k = 0; k < MP; ++k) c = __fmaf_rn(obj[k], vj[k], c);
-      const float a = acosf(relu_clamp01(c));
-      if (a < best_angle) {
-        best_angle = a;
-        best_j = j;
-      }
-    }
-#pragma unroll
-    for (int off = 1; off < kLanesPerRow; off <<= 1) {
-      const float oa = __shfl_xor_sync(0xffffffffu, best_angle, off);
-      const int oj = __shfl_xor_sync(0xffffffffu, best_j, off);
-      if (oa < best_angle || (oa == best_angle && oj < best_j)) {
-        best_angle = oa;
-        best_j = oj;
-      }
-    }
-    if (live && sub == 0) {
-      if (has_nan || best_j >= nv) {
-        associate[row] = -1;  // rvea_selection.py:81-83
+        for (int k = 0; k < MP; k += 4) {
+          const float4 q = *reinterpret_cast<const float4*>(s_vn + j * MP + k);
+          vj[k] = q.x;
+          vj[k + 1] = q.y;
+          vj[k + 2] = q.z;
+          vj[k + 3] = q.w;
+        }
       } else {
-        associate[row] = best_j;
-        // rvea_selection.py:25-29: (1 + m * theta * angle) / gamma * |obj|
-        const float left = __fdiv_rn(__fadd_rn(1.0f, __fmul_rn(m_theta, best_angle)), gamma[best_j]);
-        const float apd = __fmul_rn(left, norm);
-        // NaN sorts first (torch.argmin); +inf keeps its bit pattern and is resolved at gather time
-        const unsigned long long grow = (unsigned long long)(row + row_offset);  // row number in the whole population
-        const unsigned long long key =
-            (apd != apd) ? grow : (((unsigned long long)__float_as_uint(apd) << 32) | (grow & 0xffffffffull));
-        atomicMin(best + best_j, key);
+        static_assert(MP % 2 == 0, "vector rows are read with 8- or 16-byte loads");
+#pragma unroll
+        for (int k = 0; k < MP; k += 2) {
+          const float2 q = *reinterpret_cast<const float2*>(s_vn + j * MP + k);
+          vj[k] = q.x;
+          vj[k + 1] = q.y;
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        float c = 0.f;
+#pragma unroll
+        for (int k = 0; k < MP; ++k) c = __fmaf_rn(obj[r][k], vj[k], c);
+        c2[r] = fmaxf(c2[r], fminf(c, c1[r]));  // a NaN cosine leaves both untouched
+        if (c > c1[r]) {
+          c1[r] = c;
+          j1[r] = j;
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+#pragma unroll
+      for (int off = 1; off < kLanesPerRow; off <<= 1) {
+        const float o1 = __shfl_xor_sync(group_lanes, c1[r], off);
+        const float o2 = __shfl_xor_sync(group_lanes, c2[r], off);
+        const int oj = __shfl_xor_sync(group_lanes, j1[r], off);
+        c2[r] = fmaxf(fmaxf(c2[r], o2), fminf(c1[r], o1));
+        if (o1 > c1[r] || (o1 == c1[r] && oj < j1[r])) {
+          c1[r] = o1;
+          j1[r] = oj;
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const long long row = grp * R + r;
+      if (row >= n) continue;  // the same for the group's four lanes
+      float best_angle;
+      int best_j;
+      // compared after the clamp to [0, 1] the angle is taken of: all cosines below 0 share the angle pi / 2
+      if (!(fminf(fmaxf(c1[r], 0.0f), 1.0f) - fminf(fmaxf(c2[r], 0.0f), 1.0f) > kCosMargin)) {
+        // near tie (or no usable cosine at all): the reference's own order, arccosine of every cosine
+        best_angle = INFINITY;
+        best_j = 0x7fffffff;
+        for (int j = sub; j < nv; j += kLanesPerRow) {
+          const float* vj = s_vn + j * MP;
+          float c = 0.f;
+#pragma unroll
+          for (int k = 0; k < MP; ++k) c = __fmaf_rn(obj[r][k], vj[k], c);
+          const float a = acosf(relu_clamp01(c));
+          if (a < best_angle) {
+            best_angle = a;
+            best_j = j;
+          }
+        }
+#pragma unroll
+        for (int off = 1; off < kLanesPerRow; off <<= 1) {
+          const float oa = __shfl_xor_sync(group_lanes, best_angle, off);
+          const int oj = __shfl_xor_sync(group_lanes, best_j, off);
+          if (oa < best_angle || (oa == best_angle && oj < best_j)) {
+            best_angle = oa;
+            best_j = oj;
+          }
+        }
+      } else {
+        best_j = j1[r];
+        best_angle = acosf(relu_clamp01(c1[r]));
+      }
+      if (sub == 0) {
+        if (has_nan[r] || best_j >= nv) {
+          associate[row] = -1;  // rvea_selection.py:81-83
+        } else {
+          associate[row] = best_j;
+          // rvea_selection.py:25-29: (1 + m * theta * angle) / gamma * |obj|
+          const float left = __fdiv_rn(__fadd_rn(1.0f, __fmul_rn(m_theta, best_angle)), gamma[best_j]);
+          const float apd = __fmul_rn(left, norm[r]);
+          // NaN sorts first (torch.argmin); +inf keeps its bit pattern and is resolved at gather time
+          const unsigned long long grow = (unsigned long long)(row + row_offset);  // row number in the whole population
+          const unsigned long long key =
+              (apd != apd) ? grow : (((unsigned long long)__float_as_uint(apd) << 32) | (grow & 0xffffffffull));
+          atomicMin(best + best_j, key);
+        }
       }
     }
   }
@@ -197,29 +310,13 @@ __global__ void rvea_gather_kernel(const unsigned long long* __restrict__ best, 
                                    long long dx, const float* __restrict__ f, int m, float* __restrict__ next_x,
                                    float* __restrict__ next_f, long long* __restrict__ next_index, long long row_begin,
                                    long long row_count, int sharded) {
-  const long long per = dx + m;
-  const long long total = (long long)nv * per;
-  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
-    const int j = (int)(t / per);
-    const long long c = t - (long long)j * per;
-    const unsigned long long key = best[j];
-    const bool empty = key == 0xffffffffffffffffull;
-    // a vector whose members all have APD = +inf: argmin over an all-inf column is row 0
-    const bool all_inf = !empty && (uint32_t)(key >> 32) == 0x7f800000u;
-    const long long src = all_inf ? 0 : (long long)(uint32_t)key;
-    const float nanv = __int_as_float(0x7fc00000);
-    // sharded: x and f hold rows [row_begin, row_begin + row_count); rows of other shards and empty
-    // vectors contribute 0 so that a sum over the shards reproduces the gathered row
-    const long long loc = src - row_begin;
-    const bool mine = !empty && loc >= 0 && loc < row_count;
-    if (c < dx) next_x[(long long)j * dx + c] = sharded ? (mine ? x[loc * dx + c] : 0.0f) : (empty ? nanv : x[src * dx + c]);
-    else next_f[(long long)j * m + (c - dx)] = sharded ? (mine ? f[loc * m + (c - dx)] : 0.0f) : (empty ? nanv : f[src * m + (c - dx)]);
-    if (c == 0 && next_index) next_index[j] = empty ? -1 : src;
-  }
+  const long long total = (long long)nv * (dx + m);
+  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x)
+    gather_element(t, best[(int)(t / (dx + m))], x, dx, f, m, next_x, next_f, next_index, row_begin, row_count, sharded);
 }
 
 struct Layout {
-  size_t zmin, best, vn, gamma, associate, total;
+  size_t zmin, best, clear_bytes, vn, gamma, associate, total;
 };
 
 Layout make_layout(long long n, int m, int nv) {
@@ -230,8 +327,10 @@ Layout make_layout(long long n, int m, int nv) {
     off = (off + bytes + 255) / 256 * 256;
     return at;
   };
+  // [zmin | best] start every call as all-ones bytes: one memset
   L.zmin = take(sizeof(uint32_t) * (size_t)m);
   L.best = take(sizeof(unsigned long long) * (size_t)nv);
+  L.clear_bytes = off;
   L.vn = take(sizeof(float) * (size_t)nv * m);
   L.gamma = take(sizeof(float) * (size_t)nv);
   L.associate = take(sizeof(int) * (size_t)n);
@@ -247,7 +346,7 @@ int launch_assign(const float* f, long long n, int m, const uint32_t* zmin, cons
   if (smem > 48 * 1024) {
     EVOX_CUDA(cudaFuncSetAttribute(rvea_assign_kernel<MP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   }
-  const long long rows_per_block = kThreads / kLanesPerRow;
+  const long long rows_per_block = (kThreads / kLanesPerRow) * kRowsPerGroup;
   long long blocks = (n + rows_per_block - 1) / rows_per_block;
   const long long cap = (long long)sm_count() * 8;
   if (blocks > cap) blocks = cap;
@@ -266,9 +365,25 @@ extern "C" size_t evox_rvea_workspace_bytes(int64_t n, int32_t m, int32_t nv) {
   return make_layout(n, m, nv).total;
 }
 
+namespace {
+
+template <class... A>
+int dispatch_assign(int m, A... args) {
+  if (m <= 2) return launch_assign<2>(args...);
+  if (m <= 4) return launch_assign<4>(args...);
+  if (m <= 6) return launch_assign<6>(args...);
+  if (m <= 8) return launch_assign<8>(args...);
+  if (m <= 10) return launch_assign<10>(args...);
+  if (m <= 12) return launch_assign<12>(args...);
+  if (m <= 16) return launch_assign<16>(args...);
+  return launch_assign<32>(args...);
+}
+
+}  // namespace
+
 extern "C" int evox_ref_vec_guided(const float* x, int64_t dx, const float* f, int64_t n, int32_t m,
-                                   const float* v, int32_t nv, const float* theta, float* next_x,
-                                   float* next_f, int64_t* next_index, void* workspace,
+                                   const float* v, int32_t nv, const float* theta, int32_t vectors_ready,
+                                   float* next_x, float* next_f, int64_t* next_index, void* workspace,
                                    size_t workspace_bytes, void* stream) {
   EVOX_REQUIRE(x && f && v && theta && next_x && next_f, EVOX_ERR_INVALID, "ref_vec_guided: NULL pointer");
   EVOX_REQUIRE(n > 0 && n < (1ll << 32), EVOX_ERR_INVALID, "ref_vec_guided: n must be in [1, 2^32), got %lld", (long long)n);
@@ -285,9 +400,8 @@ extern "C" int evox_ref_vec_guided(const float* x, int64_t dx, const float* f, i
   float* gamma = reinterpret_cast<float*>(ws + L.gamma);
   int* associate = reinterpret_cast<int*>(ws + L.associate);
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  const int init_n = m > nv ? m : nv;
-  rvea_init_kernel<<<(init_n + kThreads - 1) / kThreads, kThreads, 0, s>>>(zmin, m, best, nv);
-  EVOX_LAUNCH_CHECK();
+  // column minima and the per-vector winners start as all-ones bytes
+  EVOX_CUDA(cudaMemsetAsync(ws + L.zmin, 0xff, L.clear_bytes - L.zmin, s));
   {
     long long want = (n * m + kThreads * 8 - 1) / (kThreads * 8);
     const long long cap = (long long)sm_count() * 4;
@@ -295,16 +409,14 @@ extern "C" int evox_ref_vec_guided(const float* x, int64_t dx, const float* f, i
     rvea_ideal_kernel<<<grid, kThreads, 0, s>>>(f, n, m, zmin);
     EVOX_LAUNCH_CHECK();
   }
-  rvea_vectors_kernel<<<(nv + kThreads - 1) / kThreads, kThreads, 0, s>>>(v, nv, m, vn);
-  rvea_gamma_kernel<<<nv, kThreads, 0, s>>>(vn, nv, m, gamma);
-  EVOX_LAUNCH_CHECK();
-  int rc;
-  if (m <= 4) rc = launch_assign<4>(f, n, m, zmin, vn, gamma, nv, theta, best, associate, 0, s);
-  else if (m <= 8) rc = launch_assign<8>(f, n, m, zmin, vn, gamma, nv, theta, best, associate, 0, s);
-  else if (m <= 12) rc = launch_assign<12>(f, n, m, zmin, vn, gamma, nv, theta, best, associate, 0, s);
-  else if (m <= 16) rc = launch_assign<16>(f, n, m, zmin, vn, gamma, nv, theta, best, associate, 0, s);
-  else rc = launch_assign<32>(f, n, m, zmin, vn, gamma, nv, theta, best, associate, 0, s);
-  if (rc) return rc;
+  if (!vectors_ready) {
+    rvea_vectors_kernel<<<(nv + kThreads - 1) / kThreads, kThreads, 0, s>>>(v, nv, m, vn);
+    rvea_gamma_kernel<<<nv, kThreads, 0, s>>>(vn, nv, m, gamma);
+    EVOX_LAUNCH_CHECK();
+  }
+  if (int rc = dispatch_assign(m, f, (long long)n, (int)m, (const uint32_t*)zmin, (const float*)vn, (const float*)gamma, (int)nv,
+                               theta, best, associate, 0ll, s))
+    return rc;
   {
     const long long total = (long long)nv * (dx + m);
     const long long cap = (long long)sm_count() * 8;
@@ -340,8 +452,8 @@ extern "C" int evox_ref_vec_guided_phase(int32_t phase, const float* x, int64_t 
   int* associate = reinterpret_cast<int*>(ws + L.associate);
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (phase == 1) {  // this shard's column minima -> ideal (m floats)
-    const int init_n = m > nv ? m : nv;
-    rvea_init_kernel<<<(init_n + kThreads - 1) / kThreads, kThreads, 0, s>>>(zmin, m, best, nv);
+    EVOX_CUDA(cudaMemsetAsync(zmin, 0xff, sizeof(uint32_t) * (size_t)m, s));
+    EVOX_CUDA(cudaMemsetAsync(best, 0xff, sizeof(unsigned long long) * (size_t)nv, s));
     long long want = (n * m + kThreads * 8 - 1) / (kThreads * 8);
     const long long cap = (long long)sm_count() * 4;
     rvea_ideal_kernel<<<(int)(want < 1 ? 1 : (want < cap ? want : cap)), kThreads, 0, s>>>(f, n, m, zmin);
@@ -355,11 +467,8 @@ extern "C" int evox_ref_vec_guided_phase(int32_t phase, const float* x, int64_t 
     rvea_vectors_kernel<<<(nv + kThreads - 1) / kThreads, kThreads, 0, s>>>(v, nv, m, vn);
     rvea_gamma_kernel<<<nv, kThreads, 0, s>>>(vn, nv, m, gamma);
     EVOX_LAUNCH_CHECK();
-    if (m <= 4) return launch_assign<4>(f, n, m, zmin, vn, gamma, nv, theta, best, associate, row_offset, s);
-    if (m <= 8) return launch_assign<8>(f, n, m, zmin, vn, gamma, nv, theta, best, associate, row_offset, s);
-    if (m <= 12) return launch_assign<12>(f, n, m, zmin, vn, gamma, nv, theta, best, associate, row_offset, s);
-    if (m <= 16) return launch_assign<16>(f, n, m, zmin, vn, gamma, nv, theta, best, associate, row_offset, s);
-    return launch_assign<32>(f, n, m, zmin, vn, gamma, nv, theta, best, associate, row_offset, s);
+    return dispatch_assign(m, f, (long long)n, (int)m, (const uint32_t*)zmin, (const float*)vn, (const float*)gamma, (int)nv, theta,
+                           best, associate, (long long)row_offset, s);
   }
   // phase 3: best_keys = minimum over all shards -> this shard's rows of the winners (others 0)
   EVOX_REQUIRE(x && next_x && next_f && dx > 0, EVOX_ERR_INVALID, "ref_vec_guided_phase: NULL pointer");

