@@ -278,7 +278,8 @@ __device__ __forceinline__ void dominates_both(const float (&a)[M], const float 
 // per pair instead of 2 m.
 template <int M, int R>
 __global__ void __launch_bounds__(kThreads)
-    nds_dominance_kernel(const float* __restrict__ fs, long long npad, long long n, uint32_t* __restrict__ Dt, int wp, int ordered) {
+    nds_dominance_kernel(const float* __restrict__ fs, long long npad, long long n, uint32_t* __restrict__ Dt, int wp, int ordered,
+                         long long s_begin, long long s_end) {
   constexpr int kWords = 8 * R;         // words of dominators per block (8 warps x R)
   constexpr int kRows = 32 * kWords;    // dominators per block
   __shared__ float sfj[M][kTileJ];
@@ -289,6 +290,11 @@ __global__ void __launch_bounds__(kThreads)
   const long long j0 = (long long)blockIdx.x * kTileJ;
   if (j0 + kTileJ <= i0) return;              // covered by the transposed output of the mirrored block
   const bool both = j0 >= i0 + kRows;         // every column index exceeds every dominator index
+  // Only rows [s_begin, s_end) of the matrix are kept (all of them unless the matrix is split over several GPUs;
+  // the bounds are multiples of the tile sizes): the forward words belong to the rows j, the mirrored ones to the rows i.
+  const bool keep_fwd = j0 >= s_begin && j0 < s_end;
+  const bool keep_back = both && i0 >= s_begin && i0 < s_end;
+  if (!keep_fwd && !keep_back) return;
 
   float fi[R][M];
 #pragma unroll
@@ -393,18 +399,20 @@ __global__ void __launch_bounds__(kThreads)
   }
   __syncthreads();
   const int w0 = (int)(i0 >> 5);
-  for (int t = threadIdx.x; t < kTileJ * kWords; t += kThreads) {
-    const int jj = t / kWords, w = t - jj * kWords;
-    const long long j = j0 + jj;
-    if (j < n && w0 + w < wp) Dt[j * wp + w0 + w] = separated ? 0u : sout[jj][w];
+  if (keep_fwd) {
+    for (int t = threadIdx.x; t < kTileJ * kWords; t += kThreads) {
+      const int jj = t / kWords, w = t - jj * kWords;
+      const long long j = j0 + jj;
+      if (j < n && w0 + w < wp) Dt[(j - s_begin) * wp + w0 + w] = separated ? 0u : sout[jj][w];
+    }
   }
-  if (both) {
+  if (keep_back) {
     // row i of Dt, the four words that hold columns j0 .. j0 + 127 (16-byte aligned: j0 is a multiple of 128)
     const int wj = (int)(j0 >> 5);
     for (int il = threadIdx.x; il < kRows; il += kThreads) {
       const long long i = i0 + il;
       if (i < n && wj + 3 < wp) {
-        *reinterpret_cast<uint4*>(Dt + i * wp + wj) = make_uint4(sback[0][il], sback[1][il], sback[2][il], sback[3][il]);
+        *reinterpret_cast<uint4*>(Dt + (i - s_begin) * wp + wj) = make_uint4(sback[0][il], sback[1][il], sback[2][il], sback[3][il]);
       }
     }
   }
@@ -1379,10 +1387,11 @@ __global__ void nds_gather_kernel(const uint32_t* __restrict__ order, long long 
 // Host side
 // ---------------------------------------------------------------------------------------------
 template <int M>
-void launch_dominance(const float* fs, long long npad, long long n, uint32_t* Dt, int wp, int ordered, cudaStream_t s) {
+void launch_dominance(const float* fs, long long npad, long long n, uint32_t* Dt, int wp, int ordered, cudaStream_t s,
+                      long long s_begin = 0, long long s_end = (1ll << 62)) {
   constexpr int R = (M <= 4) ? 4 : ((M <= 8) ? 2 : 1);
   dim3 grid((unsigned)((n + kTileJ - 1) / kTileJ), (unsigned)((npad + 256 * R - 1) / (256 * R)));
-  nds_dominance_kernel<M, R><<<grid, kThreads, 0, s>>>(fs, npad, n, Dt, wp, ordered);
+  nds_dominance_kernel<M, R><<<grid, kThreads, 0, s>>>(fs, npad, n, Dt, wp, ordered, s_begin, s_end);
 }
 
 int grid_1d(long long work, int per_block = kThreads) {
@@ -1588,6 +1597,175 @@ extern "C" int evox_nd_environmental_selection(const float* x, int64_t dx, const
                                                                       out_rank, out_crowd, (long long*)out_index);
   EVOX_LAUNCH_CHECK();
   if (status) EVOX_CUDA(cudaMemcpyAsync(status, &ctrl->status, 2 * sizeof(int), cudaMemcpyDeviceToDevice, s));
+  return EVOX_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Rank with the dominance matrix split over several GPUs (rows of the matrix = dominated columns).
+//
+// Every GPU holds all objectives (kilobytes to megabytes) and the rows [shard_begin, shard_begin + shard_rows)
+// of the bit matrix, in the row order `perm` all GPUs agree on. One front = one launch of nds_shard_front_kernel
+// on every GPU (its columns are tested against the whole unranked mask, exactly as in nds_peel_kernel: witness
+// word first, then a forward scan of the row) followed by an allgather of the GPUs' slices of the next mask: the
+// one exchange per peeling round, n / 8 bytes in total. The matrix (n^2 / 8 bytes) and the comparisons that
+// build it are what is divided; the chain of fronts is not.
+// ---------------------------------------------------------------------------------------------
+namespace evox {
+namespace {
+
+struct ShardLayout {
+  size_t fs, dt, ptr, total;
+  int wp;
+};
+
+ShardLayout make_shard_layout(long long n_cols, int m, long long shard_rows) {
+  ShardLayout L;
+  L.wp = (int)(n_cols / 32);
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    size_t at = off;
+    off = align_up(off + bytes);
+    return at;
+  };
+  L.fs = take(sizeof(float) * (size_t)m * (size_t)n_cols);
+  L.ptr = take(sizeof(int) * (size_t)shard_rows);
+  L.dt = take(sizeof(uint32_t) * (size_t)shard_rows * (size_t)L.wp);
+  L.total = off;
+  return L;
+}
+
+__global__ void nds_shard_init_kernel(long long n, long long shard_begin, long long shard_rows, const int* __restrict__ start_word,
+                                      int* __restrict__ ptr, uint32_t* __restrict__ mask_slice, int* __restrict__ rank_local) {
+  const long long t0 = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long w = t0; w < shard_rows / 32; w += stride) {
+    const long long lo = shard_begin + w * 32;
+    uint32_t bits = 0;
+    if (lo + 32 <= n) bits = 0xffffffffu;
+    else if (lo < n) bits = (1u << (int)(n - lo)) - 1u;
+    mask_slice[w] = bits;
+  }
+  for (long long j = t0; j < shard_rows; j += stride) {
+    ptr[j] = start_word ? start_word[j] : 0;
+    rank_local[j] = -1;
+  }
+}
+
+// One front for this GPU's columns. A warp owns 32 consecutive columns; `mask` is the whole unranked mask
+// (mask_words words, read-only here), the successor of the warp's own word goes to mask_slice_out.
+__global__ void __launch_bounds__(256)
+    nds_shard_front_kernel(const uint32_t* __restrict__ Dt, int wp, long long shard_rows, const uint32_t* __restrict__ mask,
+                           long long shard_begin, int front, int* __restrict__ ptr, uint32_t* __restrict__ mask_slice_out,
+                           int* __restrict__ rank_local) {
+  const int lane = threadIdx.x & 31;
+  const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long n_warps = ((long long)gridDim.x * blockDim.x) >> 5;
+  for (long long w = warp; w < shard_rows / 32; w += n_warps) {
+    const uint32_t own = __ldg(mask + shard_begin / 32 + w);
+    const long long jl = w * 32 + lane;  // local row of the matrix
+    const bool open = (own >> lane) & 1u;
+    int c = 0;
+    bool cleared = false;
+    if (open) {
+      c = ptr[jl];
+      cleared = (__ldg(Dt + jl * wp + c) & __ldg(mask + c)) == 0u;
+    }
+    unsigned todo = __ballot_sync(0xffffffffu, cleared);
+    uint32_t newly = 0u;
+    while (todo) {
+      const int src = __ffs(todo) - 1;
+      todo &= todo - 1;
+      const int cs = __shfl_sync(0xffffffffu, c, src);
+      const uint4* row4 = reinterpret_cast<const uint4*>(Dt + (w * 32 + src) * wp);
+      int found = -1;
+      for (int base = cs & ~1023; base < wp && found < 0; base += 1024) {
+        uint4 d[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          const int x = base + q * 128 + lane * 4;
+          d[q] = (x < wp && x + 4 > cs) ? __ldg(row4 + (x >> 2)) : make_uint4(0u, 0u, 0u, 0u);  // words before cs are done
+        }
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          const int x = base + q * 128 + lane * 4;
+          int f = -1;
+          if (x < wp) f = tail_first_nonzero(and4(d[q], __ldg(reinterpret_cast<const uint4*>(mask + x))));
+          const unsigned hit = __ballot_sync(0xffffffffu, f >= 0);
+          if (hit && found < 0) {
+            const int l = __ffs(hit) - 1;
+            found = base + q * 128 + l * 4 + __shfl_sync(0xffffffffu, f, l);
+          }
+        }
+      }
+      if (found >= 0) {
+        if (lane == src) ptr[jl] = found;
+      } else {
+        newly |= 1u << src;
+      }
+    }
+    if ((newly >> lane) & 1u) rank_local[jl] = front;
+    if (lane == 0) mask_slice_out[w] = own & ~newly;
+  }
+}
+
+}  // namespace
+}  // namespace evox
+
+extern "C" size_t evox_nds_shard_workspace_bytes(int64_t n_cols, int32_t m, int64_t shard_rows) {
+  if (n_cols <= 0 || m <= 0 || shard_rows <= 0) return 0;
+  return make_shard_layout(n_cols, m, shard_rows).total;
+}
+
+extern "C" int evox_nd_rank_shard_begin(const float* f, int64_t n, int32_t m, const uint32_t* perm, int64_t n_cols,
+                                        int64_t shard_begin, int64_t shard_rows, const int32_t* start_word,
+                                        uint32_t* mask_slice, int32_t* rank_local, void* workspace,
+                                        size_t workspace_bytes, void* stream) {
+  if (int rc = check_nm("nd_rank_shard_begin", n, m)) return rc;
+  EVOX_REQUIRE(f && mask_slice && rank_local, EVOX_ERR_INVALID, "nd_rank_shard_begin: NULL pointer");
+  EVOX_REQUIRE(m <= 16, EVOX_ERR_INVALID, "nd_rank_shard_begin: at most 16 objectives, got %d", m);
+  EVOX_REQUIRE(shard_rows > 0 && shard_rows % kPad == 0 && shard_begin >= 0 && shard_begin % shard_rows == 0 && n_cols % shard_rows == 0 &&
+                   n_cols >= n && shard_begin + shard_rows <= n_cols,
+               EVOX_ERR_INVALID, "nd_rank_shard_begin: shards must be equal multiples of %d rows that cover the population", kPad);
+  const ShardLayout L = make_shard_layout(n_cols, m, shard_rows);
+  EVOX_REQUIRE(workspace != nullptr && ((uintptr_t)workspace & 255u) == 0 && workspace_bytes >= L.total, EVOX_ERR_WORKSPACE,
+               "nd_rank_shard_begin: workspace missing, misaligned or smaller than %zu bytes", L.total);
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  float* fs = at<float>(workspace, L.fs);
+  uint32_t* Dt = at<uint32_t>(workspace, L.dt);
+  nds_transpose_kernel<<<grid_1d((long long)m * n_cols), kThreads, 0, s>>>(f, n, m, n_cols, perm, fs);
+  EVOX_LAUNCH_CHECK();
+  // columns at or beyond n (padding) dominate nothing and are never open: their rows of the matrix are never read
+  switch (m) {
+#define EVOX_DOM(MM) case MM: launch_dominance<MM>(fs, n_cols, n, Dt, L.wp, 1, s, shard_begin, shard_begin + shard_rows); break;
+    EVOX_DOM(1) EVOX_DOM(2) EVOX_DOM(3) EVOX_DOM(4) EVOX_DOM(5) EVOX_DOM(6) EVOX_DOM(7) EVOX_DOM(8)
+    EVOX_DOM(9) EVOX_DOM(10) EVOX_DOM(11) EVOX_DOM(12) EVOX_DOM(13) EVOX_DOM(14) EVOX_DOM(15) EVOX_DOM(16)
+#undef EVOX_DOM
+  }
+  EVOX_LAUNCH_CHECK();
+  nds_shard_init_kernel<<<grid_1d(shard_rows), kThreads, 0, s>>>(n, shard_begin, shard_rows, start_word, at<int>(workspace, L.ptr),
+                                                                mask_slice, rank_local);
+  EVOX_LAUNCH_CHECK();
+  return EVOX_OK;
+}
+
+extern "C" int evox_nd_rank_shard_front(int64_t n_cols, int32_t m, int64_t shard_begin, int64_t shard_rows, const uint32_t* mask_full,
+                                        int32_t front, uint32_t* mask_slice_out, int32_t* rank_local, void* workspace,
+                                        size_t workspace_bytes, void* stream) {
+  EVOX_REQUIRE(mask_full && mask_slice_out && rank_local, EVOX_ERR_INVALID, "nd_rank_shard_front: NULL pointer");
+  EVOX_REQUIRE(n_cols > 0 && m > 0 && shard_rows > 0 && shard_rows % kPad == 0 && n_cols % shard_rows == 0 && shard_begin >= 0 &&
+                   shard_begin + shard_rows <= n_cols,
+               EVOX_ERR_INVALID, "nd_rank_shard_front: bad shard geometry");
+  EVOX_REQUIRE(((uintptr_t)mask_full & 15u) == 0, EVOX_ERR_INVALID, "nd_rank_shard_front: the mask must be 16-byte aligned");
+  const ShardLayout L = make_shard_layout(n_cols, m, shard_rows);
+  EVOX_REQUIRE(workspace != nullptr && workspace_bytes >= L.total, EVOX_ERR_WORKSPACE, "nd_rank_shard_front: workspace too small");
+  const long long warps = shard_rows / 32;
+  const long long cap = (long long)sm_count() * 8;
+  long long blocks = (warps + 7) / 8;
+  if (blocks > cap) blocks = cap;
+  nds_shard_front_kernel<<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      at<uint32_t>(workspace, L.dt), L.wp, shard_rows, mask_full, shard_begin, front, at<int>(workspace, L.ptr), mask_slice_out,
+      rank_local);
+  EVOX_LAUNCH_CHECK();
   return EVOX_OK;
 }
 

@@ -10,8 +10,8 @@ import torch
 
 from .. import _cabi
 
-__all__ = ["non_dominate_rank", "crowding_distance", "nd_environmental_selection", "ref_vec_guided", "ref_vec_guided_sharded",
-           "raise_on_kernel_errors"]
+__all__ = ["non_dominate_rank", "non_dominate_rank_sharded", "crowding_distance", "nd_environmental_selection", "ref_vec_guided",
+           "ref_vec_guided_sharded", "raise_on_kernel_errors"]
 
 _workspaces: dict[tuple[str, torch.device], torch.Tensor] = {}
 _rvea_vectors: dict[torch.device, tuple | None] = {}  # per device: (reference-vector tensor, its version, workspace address)
@@ -81,6 +81,97 @@ def non_dominate_rank(x: torch.Tensor, check: bool = False) -> torch.Tensor:
     else:
         _remember(status)
     return rank
+
+
+def _shard_geometry(n: int, world: int) -> tuple[int, int]:
+    """(rows per shard, columns of the split matrix): equal shards of a multiple of 1,024 rows that cover n."""
+    shard_rows = -(-n // (world * 1024)) * 1024
+    return shard_rows, shard_rows * world
+
+
+def non_dominate_rank_sharded(x: torch.Tensor, group=None, check_every: int = 8, _emulate: tuple[int, int] | None = None):
+    """`non_dominate_rank` with the dominance matrix split over the ranks of `group`: every rank passes the same
+    `x` (n, m) and gets the same ranks back. Rank r builds and keeps only its rows of the bit matrix
+    (n^2 / 8 / world bytes) and peels its columns; after every front the ranks allgather their slices of the
+    unranked mask (n / 8 bytes in all) — the one exchange per peeling round. The host looks at the mask every
+    `check_every` fronts (one synchronisation) to see whether anything is left.
+
+    `_emulate=(rank, world)` runs one shard without a process group and returns its state (tests drive several
+    shards on one GPU with it and do the gather themselves)."""
+    import torch.distributed as dist
+
+    f = _check_objectives(x, "x")
+    n, m = f.shape
+    dev = f.device
+    if _emulate is not None:
+        rank_id, world = _emulate
+    elif dist.is_available() and dist.is_initialized():
+        rank_id, world = dist.get_rank(group), dist.get_world_size(group)
+    else:
+        rank_id, world = 0, 1
+    if n == 0:
+        return torch.empty(0, dtype=torch.int32, device=dev)
+    shard_rows, n_cols = _shard_geometry(n, world)
+    begin = rank_id * shard_rows
+    # a row order every rank derives alike: first objective descending (NaN last), ties in index order; a row's
+    # dominators then start at the first row with the same first objective
+    key = torch.where(torch.isnan(f[:, 0]), -torch.inf, f[:, 0])
+    perm = torch.argsort(key, descending=True, stable=True)
+    sorted_key = key[perm]
+    first_equal = torch.searchsorted(-sorted_key, -sorted_key, side="left")
+    start_word = torch.zeros(shard_rows, dtype=torch.int32, device=dev)
+    hi = min(begin + shard_rows, n)
+    if hi > begin:
+        start_word[: hi - begin] = (first_equal[begin:hi] // 32).to(torch.int32)
+    perm32 = perm.to(torch.int32).contiguous()
+    nbytes = _cabi.lib.evox_nds_shard_workspace_bytes(n_cols, m, shard_rows)
+    ws = _workspace("nds_shard", dev, nbytes)
+    mask_slice = torch.empty(shard_rows // 32, dtype=torch.int32, device=dev)
+    rank_local = torch.empty(shard_rows, dtype=torch.int32, device=dev)
+    s = _cabi.stream_ptr(dev)
+    _cabi.check(
+        _cabi.lib.evox_nd_rank_shard_begin(
+            _cabi.ptr(f), n, m, _cabi.ptr(perm32), n_cols, begin, shard_rows, _cabi.ptr(start_word), _cabi.ptr(mask_slice),
+            _cabi.ptr(rank_local), _cabi.ptr(ws), ws.numel(), s,
+        )
+    )
+
+    def front(mask_full: torch.Tensor, k: int) -> None:
+        _cabi.check(
+            _cabi.lib.evox_nd_rank_shard_front(n_cols, m, begin, shard_rows, _cabi.ptr(mask_full), k, _cabi.ptr(mask_slice),
+                                               _cabi.ptr(rank_local), _cabi.ptr(ws), ws.numel(), _cabi.stream_ptr(dev))
+        )
+
+    if _emulate is not None:
+        return {"front": front, "mask_slice": mask_slice, "rank_local": rank_local, "perm": perm, "begin": begin,
+                "shard_rows": shard_rows, "n_cols": n_cols}
+    mask_full = torch.empty(n_cols // 32, dtype=torch.int32, device=dev)
+
+    def gather() -> None:
+        if world > 1:
+            dist.all_gather_into_tensor(mask_full, mask_slice, group=group)
+        else:
+            mask_full.copy_(mask_slice)
+
+    gather()
+    k = 0
+    while True:
+        for _ in range(check_every):
+            front(mask_full, k)
+            gather()
+            k += 1
+        if k > n or not bool(mask_full.any()):  # a strict partial order ranks somebody in every front
+            break
+    if world > 1:
+        ranks_all = torch.empty(n_cols, dtype=torch.int32, device=dev)
+        dist.all_gather_into_tensor(ranks_all, rank_local, group=group)
+    else:
+        ranks_all = rank_local
+    out = torch.empty(n, dtype=torch.int32, device=dev)
+    out[perm] = ranks_all[:n]
+    if bool((out < 0).any()):
+        raise _cabi.EvoxKernelError("sharded non-dominated sort did not finish: no progress")
+    return out
 
 
 def crowding_distance(costs: torch.Tensor, mask: torch.Tensor | None = None) -> torch.Tensor:
@@ -163,9 +254,8 @@ def ref_vec_guided(x: torch.Tensor, f: torch.Tensor, v: torch.Tensor, theta: tor
         th = theta
     else:
         th = torch.as_tensor(theta, dtype=torch.float32, device=dev).reshape(())
-    # one allocation for both gathered tables (the kernel wants two dense arrays: they lie behind each other)
-    out = torch.empty(nv * (dx + m), dtype=torch.float32, device=dev)
-    next_x, next_f = out[: nv * dx].view(nv, dx), out[nv * dx :].view(nv, m)
+    next_x = torch.empty(nv, dx, dtype=torch.float32, device=dev)
+    next_f = torch.empty(nv, m, dtype=torch.float32, device=dev)
     next_index = torch.empty(nv, dtype=torch.int64, device=dev)
     nbytes = _cabi.lib.evox_rvea_workspace_bytes(n, m, nv)
     ws = _workspace("rvea", dev, nbytes)

@@ -285,6 +285,29 @@ int evox_nd_environmental_selection(const float* x, int64_t dx, const float* f, 
                                     float* out_crowd, int64_t* out_index, int32_t* status,
                                     void* workspace, size_t workspace_bytes, void* stream);
 
+/* Non-dominated rank with the dominance matrix split over several GPUs: the per-front exchange the
+ * reference's distributed workflow has no counterpart for (it replicates the whole selection on every rank,
+ * workflows/std_workflow.py:167-189); the arithmetic is dominate_relation and the peeling loop of
+ * non_dominate_rank (operators/selection/non_dominate.py:6-26, 151-169).
+ * All GPUs hold f (n x m) and agree on a row order `perm` (uint32[n], position -> row of f; NULL = identity)
+ * and on n_cols = number of shards * shard_rows >= n, shard_rows a multiple of 1,024. A GPU keeps rows
+ * [shard_begin, shard_begin + shard_rows) of the bit matrix (shard_rows * n_cols / 8 bytes) in its workspace.
+ *   evox_nd_rank_shard_begin  builds them, sets rank_local (int32[shard_rows]) to -1 and writes the shard's
+ *       slice of the unranked mask (shard_rows / 32 words). start_word (optional, int32[shard_rows]): first word
+ *       of each row that can hold a dominator.
+ *   evox_nd_rank_shard_front  peels one front: mask_full (n_cols / 32 words = every shard's slice, gathered)
+ *       -> rank_local = `front` for the shard's columns that join it, and the shard's slice of the next mask.
+ * The caller gathers the slices after every front and stops when the gathered mask is empty; the ranks in
+ * the caller's order are rank[perm[shard_begin + a]] = rank_local[a]. */
+size_t evox_nds_shard_workspace_bytes(int64_t n_cols, int32_t m, int64_t shard_rows);
+int evox_nd_rank_shard_begin(const float* f, int64_t n, int32_t m, const uint32_t* perm, int64_t n_cols,
+                             int64_t shard_begin, int64_t shard_rows, const int32_t* start_word,
+                             uint32_t* mask_slice, int32_t* rank_local, void* workspace,
+                             size_t workspace_bytes, void* stream);
+int evox_nd_rank_shard_front(int64_t n_cols, int32_t m, int64_t shard_begin, int64_t shard_rows,
+                             const uint32_t* mask_full, int32_t front, uint32_t* mask_slice_out,
+                             int32_t* rank_local, void* workspace, size_t workspace_bytes, void* stream);
+
 /* ------------------------------------------------------------------------------------------
  * P3. RVEA reference-vector-guided selection.
  * ------------------------------------------------------------------------------------------ */

@@ -5,8 +5,9 @@
 
 Every rank runs the sharded algorithm on its GPU and, next to it, the single-GPU algorithm on the same
 GPU; after a few generations the gathered sharded state must equal the single-GPU state bit for bit
-(PSO), the centre of the sharded virtual-LoRA ES must equal the single-GPU centre, and the
-row-sharded RVEA selection must pick and gather the same rows as the single call. Prints
+(PSO), the centre of the sharded virtual-LoRA ES must equal the single-GPU centre, the
+row-sharded RVEA selection must pick and gather the same rows as the single call, and the non-dominated
+rank with its matrix split over the GPUs must equal the single-GPU rank. Prints
 "multigpu ok" from rank 0 and exits non-zero on any mismatch.
 """
 import os
@@ -92,6 +93,17 @@ def check_rvea(dev, rank, world):
         assert torch.equal(torch.nan_to_num(g, nan=-1.0), torch.nan_to_num(w, nan=-1.0)), f"rank {rank}: gathered rows differ"
 
 
+def check_nds(dev, rank, world):
+    from evox_b200.operators.selection import non_dominate_rank, non_dominate_rank_sharded
+    from oracle import nds
+
+    f = nds.dtlz2_objectives(torch.rand(30_001, 12, generator=torch.Generator().manual_seed(4)), 3).to(dev)
+    want = non_dominate_rank(f, check=True)
+    got = non_dominate_rank_sharded(f)
+    torch.cuda.synchronize()
+    assert torch.equal(got, want), f"rank {rank}: split-matrix ranks differ"
+
+
 def main():
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
@@ -101,6 +113,7 @@ def main():
         check_pso(dev, rank, world)
         check_lora_es(dev, rank, world)
         check_rvea(dev, rank, world)
+        check_nds(dev, rank, world)
         dist.barrier()
         if rank == 0:
             print("multigpu ok", flush=True)

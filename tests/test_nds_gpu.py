@@ -210,3 +210,50 @@ def test_every_rank_at_the_benchmark_sizes(golden, cuda, tag, n, fronts):
     assert torch.equal(torch.sort(idx[want[idx] < cut]).values, torch.nonzero(want < cut).flatten())
     assert bool((want[idx] <= cut).all()) and idx.unique().numel() == k
     assert torch.equal(sel[2].cpu(), want[idx])
+
+
+@pytest.mark.parametrize("n,m,world", [(5000, 3, 3), (2049, 2, 2), (700, 5, 4), (20_000, 3, 2)])
+def test_split_matrix_rank_emulated_on_one_gpu(cuda, n, m, world):
+    """The rank with the dominance matrix split by rows over `world` shards, all driven on one GPU: every shard
+    peels its own columns against the gathered unranked mask (the gather is done here by concatenating the
+    slices, which is what the allgather does). Ranks must equal the single-matrix kernel's bit for bit."""
+    from evox_b200.operators.selection import non_dominate_rank, non_dominate_rank_sharded
+
+    gen = torch.Generator().manual_seed(n + world)
+    f = nds.dtlz2_objectives(torch.rand(n, 12, generator=gen), 3) if m == 3 else torch.round(torch.rand(n, m, generator=gen) * 50) / 50
+    if n > 1000:
+        f[5] = float("nan")
+        f[77, 0] = float("inf")
+    fd = f.to(cuda)
+    want = non_dominate_rank(fd, check=True)
+    # every shard needs its own workspace here (on several GPUs each process has one)
+    from evox_b200.operators import selection as sel
+
+    shards = []
+    for r in range(world):
+        sel._workspaces.pop(("nds_shard", cuda), None)
+        shards.append(non_dominate_rank_sharded(fd, _emulate=(r, world)))
+        shards[-1]["ws"] = sel._workspaces[("nds_shard", cuda)]
+    k = 0
+    mask_full = torch.cat([s["mask_slice"] for s in shards])
+    while bool(mask_full.any()):
+        assert k <= n
+        for s in shards:
+            sel._workspaces[("nds_shard", cuda)] = s["ws"]
+            s["front"](mask_full, k)
+        torch.cuda.synchronize()
+        mask_full = torch.cat([s["mask_slice"] for s in shards])
+        k += 1
+    ranks = torch.cat([s["rank_local"] for s in shards])[:n]
+    got = torch.empty(n, dtype=torch.int32, device=cuda)
+    got[shards[0]["perm"]] = ranks
+    assert torch.equal(got, want)
+    assert k == int(want.max()) + 1
+
+
+def test_split_matrix_rank_single_process(cuda):
+    """The public function without a process group (one shard): same ranks as non_dominate_rank."""
+    from evox_b200.operators.selection import non_dominate_rank, non_dominate_rank_sharded
+
+    f = nds.dtlz2_objectives(torch.rand(9000, 12, generator=torch.Generator().manual_seed(2)), 3).to(cuda)
+    assert torch.equal(non_dominate_rank_sharded(f), non_dominate_rank(f, check=True))
