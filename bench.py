@@ -369,7 +369,7 @@ def nds_floor_ms(n: int, m: int, compare_rate: float | None) -> dict:
     return {"hbm_floor_ms": hbm_ms, "alu_floor_ms": alu_ms, "floor_ms": max(hbm_ms, alu_ms or 0.0)}
 
 
-def measure_nds(n: int, reps: int, dev: torch.device, compare_rate: float | None, cpu: bool) -> dict:
+def measure_nds(n: int, reps: int, dev: torch.device, compare_rate: float | None, cpu: bool, selection: bool = True) -> dict:
     """Non-dominated rank and the full environmental selection on DTLZ2-shaped objectives (benchmark
     configuration 1 at 2N = 20,000; the metric's 2N = 100,000)."""
     from evox_b200.operators.selection import nd_environmental_selection, non_dominate_rank
@@ -379,8 +379,8 @@ def measure_nds(n: int, reps: int, dev: torch.device, compare_rate: float | None
     f = onds.dtlz2_objectives(x, 3)
     xd, fd = x.to(dev), f.to(dev)
     with ClockSampler(physical_gpu_index(dev.index or 0)) as clocks:
-        rank_ms = timed_ms(lambda: non_dominate_rank(fd), reps)
-        sel_ms = timed_ms(lambda: nd_environmental_selection(xd, fd, n // 2), reps)
+        rank_ms = timed_ms(lambda: non_dominate_rank(fd), reps, warmup=3 if n <= 100_000 else 1)
+        sel_ms = timed_ms(lambda: nd_environmental_selection(xd, fd, n // 2), reps) if selection else None
     rank = non_dominate_rank(fd, check=True)
     floor = nds_floor_ms(n, 3, compare_rate)
     out = {
@@ -645,13 +645,14 @@ def run_ours(args):
     # nvidia-smi needs a few hundred milliseconds before its first sample: short runs (many GPUs, few steps)
     # keep stepping, untimed, until the clock record of the load has a few samples (every rank runs the same
     # number of extra generations: the count is agreed on rank 0's record)
-    for _ in range(20):
-        enough = torch.tensor([1 if clocks.sample_count() >= 4 else 0], device=dev)
+    t_wait = time.perf_counter()
+    while True:
+        enough = torch.tensor([1 if (clocks.sample_count() >= 4 or time.perf_counter() - t_wait > 5.0) else 0], device=dev)
         if world > 1:
             dist.broadcast(enough, src=0)
         if int(enough.item()):
             break
-        for _ in range(max(args.steps // 2, 10)):
+        for _ in range(100):
             wf.step()
         barrier()
     clocks.__exit__(None, None, None)
@@ -718,6 +719,9 @@ def run_ours(args):
         cpu = not args.no_cpu_baseline
         sec["nds_rank_1e5"] = measure_nds(100_000, 20, dev, rate, cpu)
         sec["nds_rank_2e4"] = measure_nds(20_000, 50, dev, rate, cpu)
+        # the size at which one GPU's bit matrix is 20 GB: the single-GPU side of the split-matrix comparison
+        sec["nds_rank_4e5"] = measure_nds(400_000, 3, dev, rate, False, selection=False)
+        torch.cuda.empty_cache()
         sec["rvea_config2"] = measure_rvea(50_000, 100, dev, cpu)
         sec["rvea_5e6"] = measure_rvea(5_000_000, 20, dev, False)
         torch.cuda.empty_cache()

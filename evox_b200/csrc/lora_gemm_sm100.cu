@@ -465,7 +465,25 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         for (int ci = 0; ci < 4; ++ci)
 #pragma unroll
           for (int j = 0; j < 32; ++j) sum[ci][j] = 0.f;
+        float* o = a.out_f32 + (m0 + row_in_tile) * a.ld_out + n0 + col_half * (BN / 2);
+        const float os = a.out_scale_dev ? a.out_scale * __ldg(a.out_scale_dev) : a.out_scale;
+        // The chunk sums of a tile always leave as TWO rounded halves, chunks [0, n/2) and [n/2, n), added once:
+        // either by two work items (k_split = 2, atomicAdd into the zero-filled output: two addends, any order) or
+        // by this one, which stores the first half when it reaches the middle and adds the second at the end.
+        // The result then does not depend on how many tiles the launch has (a row shard of a block gives the same
+        // bits as the whole block).
+        const int mid = (k_split == 1 && n_chunks >= 2) ? n_chunks / 2 : -1;
         for (int chunk = ch0; chunk < ch1; ++chunk, ++it) {
+          if (chunk == mid && ok) {
+#pragma unroll
+            for (int ci = 0; ci < 4; ++ci)
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) {
+                *reinterpret_cast<float4*>(o + ci * 32 + j) =
+                    make_float4(sum[ci][j] * os, sum[ci][j + 1] * os, sum[ci][j + 2] * os, sum[ci][j + 3] * os);
+                sum[ci][j] = sum[ci][j + 1] = sum[ci][j + 2] = sum[ci][j + 3] = 0.f;
+              }
+          }
           const int buf = (int)(it & 1);
           const uint32_t acc_ph = (uint32_t)((it >> 1) & 1);
           if (ok && !mbar_wait(tfull_bar(buf), acc_ph, a.error_flag, 4)) ok = false;
@@ -484,17 +502,20 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           if constexpr (PAIR) mbar_arrive_cluster(leader_tempty0 + 8u * buf); else mbar_arrive(tempty_bar(buf));
         }
         if (ok) {
-          float* o = a.out_f32 + (m0 + row_in_tile) * a.ld_out + n0 + col_half * (BN / 2);
-          const float os = a.out_scale_dev ? a.out_scale * __ldg(a.out_scale_dev) : a.out_scale;
 #pragma unroll
           for (int ci = 0; ci < 4; ++ci)
 #pragma unroll
             for (int j = 0; j < 32; j += 4) {
               const float4 r = make_float4(sum[ci][j] * os, sum[ci][j + 1] * os, sum[ci][j + 2] * os, sum[ci][j + 3] * os);
-              if (k_split > 1)
-                atomicAdd(reinterpret_cast<float4*>(o + ci * 32 + j), r);
-              else
-                *reinterpret_cast<float4*>(o + ci * 32 + j) = r;
+              float4* dst = reinterpret_cast<float4*>(o + ci * 32 + j);
+              if (k_split > 1) {
+                atomicAdd(dst, r);
+              } else if (mid >= 0) {
+                const float4 first = *dst;  // this thread stored it at the middle chunk
+                *dst = make_float4(__fadd_rn(first.x, r.x), __fadd_rn(first.y, r.y), __fadd_rn(first.z, r.z), __fadd_rn(first.w, r.w));
+              } else {
+                *dst = r;
+              }
             }
         }
         continue;
