@@ -24,9 +24,10 @@
 //                              next 32 words of its row itself, the columns that need a longer scan
 //                              are queued per block and scanned by whichever warp is free; the mask
 //                              is double buffered so one bounded grid barrier separates two fronts.
-//   For 8192 rows or more the rows are first dealt into bins of descending first objective
-//   (nds_f1_range / bin_count / bin_scan / bin_scatter kernels): ranks do not depend on the row order,
-//   most tiles above the diagonal then need m - 1 comparisons per pair instead of 2 m, and a column's
+//   For 8192 rows or more the rows are first dealt into bands of descending first objective and, inside a band,
+//   into bins of descending second objective (nds_range / bin_count / group / key_count / bin_scan / bin_scatter
+//   kernels): ranks do not depend on the row order, a tile of the matrix is then narrow in both objectives, most
+//   tiles above the diagonal need m - 1, m - 2 or no comparisons per pair instead of 2 m, and a column's
 //   dominators all lie after its bin's first row.
 // Selection: histogram of ranks -> last admitted front -> per-objective stable radix sort of that
 // front -> neighbour gaps / range -> stable sorts by (rank) and (-crowding) -> gather.
@@ -107,7 +108,7 @@ Layout make_layout(long long n, int m, bool with_matrix, bool selection = true) 
   L.newfront = take(sizeof(uint32_t) * L.wp);
   L.ptr = take(sizeof(int) * (size_t)n);
   L.perm = take(sizeof(uint32_t) * (size_t)n);
-  L.bins = take(sizeof(int) * (size_t)(2 * (kBins + 2) + 2));  // range keys, counts / offsets, cursors
+  L.bins = take(sizeof(int) * (size_t)(3 * (kBins + 2) + 4));  // range keys, band of each value bin, counts / offsets, cursors
   L.hist = take(sizeof(int) * (size_t)(n + 1));
   L.idx_a = take(sizeof(uint32_t) * (size_t)n);
   L.key_a = take(sizeof(uint32_t) * (size_t)n);
@@ -119,7 +120,7 @@ Layout make_layout(long long n, int m, bool with_matrix, bool selection = true) 
   L.order = take(sizeof(uint32_t) * (size_t)n);
   L.rank = take(sizeof(int) * (size_t)n);
   L.whist = selection ? take(sizeof(int) * (size_t)kRankWarps * kRankBuckets) : off;
-  L.rank_off = selection ? take(sizeof(int) * (size_t)kRankBuckets) : off;
+  L.rank_off = selection ? take(sizeof(int) * (size_t)kRankBuckets * 2) : off;  // offsets, then totals
   // populations too large for the cluster kernel to peel alone: the compacted sub-matrix of the last rows
   const bool compact = with_matrix && n > kTailDirectMaxN;
   L.tail_ids = compact ? take(sizeof(uint32_t) * kTailCompactRows) : off;
@@ -166,44 +167,98 @@ __device__ __forceinline__ float range_value(uint32_t key) {
   return __uint_as_float((key & 0x80000000u) ? (key ^ 0x80000000u) : ~key);
 }
 
-// range[0] = largest key of a finite first objective, range[1] = largest inverted key (= smallest value)
-__global__ void nds_f1_range_kernel(const float* __restrict__ f, long long n, int m, unsigned* range) {
-  unsigned hi = 0u, lo_inv = 0u;
+// range[2k] = largest key of a finite objective k, range[2k + 1] = largest inverted key (= smallest value), k = 0, 1
+__global__ void nds_range_kernel(const float* __restrict__ f, long long n, int m, unsigned* range) {
+  unsigned hi[2] = {0u, 0u}, lo_inv[2] = {0u, 0u};
+  const int objs = m >= 2 ? 2 : 1;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
-    const float x = f[i * m];
-    if (isfinite(x)) {
-      const unsigned key = range_key(x);
-      hi = max(hi, key);
-      lo_inv = max(lo_inv, ~key);
+    for (int k = 0; k < objs; ++k) {
+      const float x = f[i * m + k];
+      if (isfinite(x)) {
+        const unsigned key = range_key(x);
+        hi[k] = max(hi[k], key);
+        lo_inv[k] = max(lo_inv[k], ~key);
+      }
     }
   }
 #pragma unroll
-  for (int off = 16; off > 0; off >>= 1) {
-    hi = max(hi, __shfl_xor_sync(0xffffffffu, hi, off));
-    lo_inv = max(lo_inv, __shfl_xor_sync(0xffffffffu, lo_inv, off));
-  }
-  if ((threadIdx.x & 31) == 0) {
-    if (hi) atomicMax(range, hi);
-    if (lo_inv) atomicMax(range + 1, lo_inv);
+  for (int k = 0; k < 2; ++k) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+      hi[k] = max(hi[k], __shfl_xor_sync(0xffffffffu, hi[k], off));
+      lo_inv[k] = max(lo_inv[k], __shfl_xor_sync(0xffffffffu, lo_inv[k], off));
+    }
+    if ((threadIdx.x & 31) == 0) {
+      if (hi[k]) atomicMax(range + 2 * k, hi[k]);
+      if (lo_inv[k]) atomicMax(range + 2 * k + 1, lo_inv[k]);
+    }
   }
 }
 
-// Monotone DEcreasing in x: bins 0 .. kBins - 1 for numbers (+inf in the first, -inf in the last), kBins for
-// NaN. Large values come first, so the dominators of a row lie AFTER it and the peeling scan, which
-// walks a row of the matrix forward, meets the dominators nearest in the first objective first: those
-// tend to leave late, which keeps a column's witness alive for many fronts.
-__device__ __forceinline__ int f1_bin(float x, const unsigned* range) {
-  if (x != x) return kBins;
+// Monotone DEcreasing in x: bins 0 .. n_bins - 1 for numbers (+inf in the first, -inf in the last); the caller
+// sends NaN elsewhere. Large values come first, so the dominators of a row lie AFTER it.
+__device__ __forceinline__ int value_bin(float x, const unsigned* range, int n_bins) {
   const float lo = range_value(~range[1]), hi = range_value(range[0]);
-  const float t = (x - lo) * ((float)kBins / (hi - lo));
-  const int up = t >= (float)kBins ? kBins - 1 : (t >= 0.f ? (int)t : 0);  // a NaN t (empty or zero range): 0
-  return kBins - 1 - up;
+  const float t = (x - lo) * ((float)n_bins / (hi - lo));
+  const int up = t >= (float)n_bins ? n_bins - 1 : (t >= 0.f ? (int)t : 0);  // a NaN t (empty or zero range): 0
+  return n_bins - 1 - up;
+}
+__device__ __forceinline__ int f1_bin(float x, const unsigned* range) { return (x != x) ? kBins : value_bin(x, range, kBins); }
+
+// Position of a row in the matrix order: `groups` bands of descending first objective (unions of its kBins value
+// bins holding about the same number of rows: group_of_bin), and inside a band kBins / groups bins of descending
+// second objective. Rows with a NaN in either go last (bin kBins). With one objective: its value bin.
+__device__ __forceinline__ int order_key(const float* __restrict__ row, int m, const unsigned* range, const int* __restrict__ group_of_bin,
+                                         int groups) {
+  const float x0 = row[0];
+  if (x0 != x0) return kBins;
+  if (m < 2) return value_bin(x0, range, kBins);
+  const float x1 = row[1];
+  if (x1 != x1) return kBins;
+  const int per = kBins / groups;
+  return group_of_bin[value_bin(x0, range, kBins)] * per + value_bin(x1, range + 2, per);
 }
 
 __global__ void nds_bin_count_kernel(const float* __restrict__ f, long long n, int m, const unsigned* __restrict__ range,
                                      int* __restrict__ counts) {
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
     atomicAdd(counts + f1_bin(f[i * m], range), 1);
+}
+
+// One block of 1024 threads: counts of the first objective's value bins -> the band each bin belongs to
+// (bands of about equal row counts, in place).
+__global__ void __launch_bounds__(1024) nds_group_kernel(int* __restrict__ counts, int groups) {
+  static_assert(kBins == 4096, "four bins per thread");
+  __shared__ int s_tot[1024];
+  const int t = threadIdx.x;
+  int c[4], sum = 0;
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    c[q] = counts[t * 4 + q];
+    sum += c[q];
+  }
+  s_tot[t] = sum;
+  __syncthreads();
+  for (int off = 1; off < 1024; off <<= 1) {
+    const int v = t >= off ? s_tot[t - off] : 0;
+    __syncthreads();
+    s_tot[t] += v;
+    __syncthreads();
+  }
+  const long long total = s_tot[1023];
+  long long run = s_tot[t] - sum;
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const long long g = total > 0 ? run * groups / total : 0;
+    counts[t * 4 + q] = (int)(g < groups ? g : groups - 1);
+    run += c[q];
+  }
+}
+
+__global__ void nds_key_count_kernel(const float* __restrict__ f, long long n, int m, const unsigned* __restrict__ range,
+                                     const int* __restrict__ group_of_bin, int groups, int* __restrict__ counts) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    atomicAdd(counts + order_key(f + i * m, m, range, group_of_bin, groups), 1);
 }
 
 // One block of 1024 threads: counts[0 .. kBins] -> exclusive offsets, copied to the scatter's cursors.
@@ -235,9 +290,10 @@ __global__ void __launch_bounds__(1024) nds_bin_scan_kernel(int* __restrict__ co
 }
 
 __global__ void nds_bin_scatter_kernel(const float* __restrict__ f, long long n, int m, const unsigned* __restrict__ range,
-                                       int* __restrict__ cursor, uint32_t* __restrict__ perm) {
+                                       const int* __restrict__ group_of_bin, int groups, int* __restrict__ cursor,
+                                       uint32_t* __restrict__ perm) {
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
-    perm[atomicAdd(cursor + f1_bin(f[i * m], range), 1)] = (uint32_t)i;
+    perm[atomicAdd(cursor + order_key(f + i * m, m, range, group_of_bin, groups), 1)] = (uint32_t)i;
 }
 
 // i dominates j: all(f_i <= f_j) and any(f_i < f_j) (non_dominate.py:20-24).
@@ -265,6 +321,36 @@ __device__ __forceinline__ void dominates_both(const float (&a)[M], const float 
   }
   a_dom_b = ab && !ba;
   b_dom_a = ba && !ab;
+}
+
+// Words of "column j dominates row i" for a tile whose columns lie strictly below its rows in one objective:
+// the comparison all(f_j[k] <= f_i[k]) runs over the objectives k in CMP only (a compile-time bit set).
+template <int M, int R, unsigned CMP>
+__device__ __forceinline__ void separated_words(const float (&fi)[R][M], const float (*sfj)[kTileJ], uint32_t (*sback)[32 * 8 * R + 1],
+                                                int warp, int lane) {
+#pragma unroll 1
+  for (int jw = 0; jw < kTileJ / 32; ++jw) {
+    uint32_t back[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) back[r] = 0u;
+#pragma unroll
+    for (int jb = 0; jb < 32; ++jb) {
+      float fj[M];
+#pragma unroll
+      for (int k = 0; k < M; ++k)
+        if ((CMP >> k) & 1u) fj[k] = sfj[k][jw * 32 + jb];
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        bool le = true;
+#pragma unroll
+        for (int k = 0; k < M; ++k)
+          if ((CMP >> k) & 1u) le = le && (fj[k] <= fi[r][k]);
+        if (le) back[r] |= 1u << jb;
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) sback[jw][(warp * R + r) * 32 + lane] = back[r];
+  }
 }
 
 // One block = (32 * 8 * R dominators i) x (128 columns j). Blocks whose columns all lie AFTER their
@@ -309,55 +395,75 @@ __global__ void __launch_bounds__(kThreads)
     sfj[k][jj] = (j < n) ? fs[(long long)k * npad + j] : __int_as_float(0x7fc00000);
   }
   __syncthreads();
-  bool separated = false;
-  if (ordered && both) {  // block-uniform
-    __shared__ float s_imin[kThreads / 32], s_jmax[kThreads / 32];
-    float imin = INFINITY, jmax = -INFINITY;
+  // Tile classes (block-uniform). kFull: every comparison. The others need one of the first two objectives, s, in
+  // which every column lies strictly below every row: then no row dominates a column (zero forward words) and
+  // column j dominates row i iff f_j <= f_i in every OTHER objective. In the other one of the first two, t:
+  // columns all above the rows -> nobody dominates anybody (kZero); columns all at or below -> t needs no
+  // comparison either (kSkip01); otherwise t is compared (kSkip0 for s = 0, kSkip1 for s = 1).
+  enum { kFull, kZero, kSkip0, kSkip1, kSkip01 };
+  int tile_class = kFull;
+  if (ordered && both) {
+    constexpr int kObj = M >= 2 ? 2 : 1;
+    __shared__ float s_stat[kThreads / 32][8];
+    float st[8];  // per objective k < 2: min over rows, -max over rows, min over columns, -max over columns (all as minima)
     int bad = 0;
 #pragma unroll
-    for (int r = 0; r < R; ++r) {
-      bad |= (fi[r][0] != fi[r][0]);
-      imin = fminf(imin, fi[r][0]);
-    }
-    if (threadIdx.x < kTileJ) {
-      jmax = sfj[0][threadIdx.x];
-      bad |= (jmax != jmax);
+    for (int k = 0; k < 2; ++k) {
+      float imin = INFINITY, imaxn = INFINITY, jmin = INFINITY, jmaxn = INFINITY;
+      if (k < kObj) {
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          bad |= (fi[r][k] != fi[r][k]);
+          imin = fminf(imin, fi[r][k]);
+          imaxn = fminf(imaxn, -fi[r][k]);
+        }
+        if (threadIdx.x < kTileJ) {
+          const float v = sfj[k][threadIdx.x];
+          bad |= (v != v);
+          jmin = v;
+          jmaxn = -v;
+        }
+      }
+      st[4 * k] = imin, st[4 * k + 1] = imaxn, st[4 * k + 2] = jmin, st[4 * k + 3] = jmaxn;
     }
     bad = __syncthreads_or(bad);
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) {
-      imin = fminf(imin, __shfl_xor_sync(0xffffffffu, imin, off));
-      jmax = fmaxf(jmax, __shfl_xor_sync(0xffffffffu, jmax, off));
+    for (int q = 0; q < 8; ++q) {
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) st[q] = fminf(st[q], __shfl_xor_sync(0xffffffffu, st[q], off));
     }
-    if (lane == 0) s_imin[warp] = imin, s_jmax[warp] = jmax;
+    if (lane == 0) {
+#pragma unroll
+      for (int q = 0; q < 8; ++q) s_stat[warp][q] = st[q];
+    }
     __syncthreads();
 #pragma unroll
-    for (int w = 0; w < kThreads / 32; ++w) imin = fminf(imin, s_imin[w]), jmax = fmaxf(jmax, s_jmax[w]);
-    separated = !bad && jmax < imin;
-  }
-  if (separated) {
-    // 32 columns per word with the bit position known at compile time: two compares and one predicated
-    // OR per pair
-#pragma unroll 1
-    for (int jw = 0; jw < kTileJ / 32; ++jw) {
-      uint32_t back[R];
+    for (int q = 0; q < 8; ++q) {
 #pragma unroll
-      for (int r = 0; r < R; ++r) back[r] = 0u;
-#pragma unroll
-      for (int jb = 0; jb < 32; ++jb) {
-        float fj[M];
-#pragma unroll
-        for (int k = 1; k < M; ++k) fj[k] = sfj[k][jw * 32 + jb];
-#pragma unroll
-        for (int r = 0; r < R; ++r) {
-          bool le = true;
-#pragma unroll
-          for (int k = 1; k < M; ++k) le = le && (fj[k] <= fi[r][k]);
-          if (le) back[r] |= 1u << jb;
-        }
+      for (int w = 0; w < kThreads / 32; ++w) st[q] = fminf(st[q], s_stat[w][q]);
+    }
+    if (!bad) {
+      const float imin0 = st[0], imax0 = -st[1], jmin0 = st[2], jmax0 = -st[3];
+      const float imin1 = st[4], imax1 = -st[5], jmin1 = st[6], jmax1 = -st[7];
+      if (jmax0 < imin0) {
+        tile_class = (kObj == 2 && jmin1 > imax1) ? kZero : ((kObj == 2 && jmax1 <= imin1) ? kSkip01 : kSkip0);
+      } else if (kObj == 2 && jmax1 < imin1) {
+        tile_class = (jmin0 > imax0) ? kZero : ((jmax0 <= imin0) ? kSkip01 : kSkip1);
       }
-#pragma unroll
-      for (int r = 0; r < R; ++r) sback[jw][(warp * R + r) * 32 + lane] = back[r];
+    }
+  }
+  const bool separated = tile_class != kFull;
+  if (separated) {
+    // 32 columns per word with the bit position known at compile time: the comparisons of the class and one
+    // predicated OR per pair
+    if (tile_class == kZero) {
+      for (int t = threadIdx.x; t < (kTileJ / 32) * kRows; t += kThreads) sback[t / kRows][t % kRows] = 0u;
+    } else if (tile_class == kSkip0) {
+      separated_words<M, R, ((1u << M) - 1u) & ~1u>(fi, sfj, sback, warp, lane);
+    } else if (tile_class == kSkip1) {
+      separated_words<M, R, ((1u << M) - 1u) & ~2u>(fi, sfj, sback, warp, lane);
+    } else {
+      separated_words<M, R, ((1u << M) - 1u) & ~3u>(fi, sfj, sback, warp, lane);
     }
   } else if (!both) {
 #pragma unroll 4
@@ -441,11 +547,13 @@ __global__ void __launch_bounds__(kThreads)
   }
 }
 
-// `bin_end` (optional, with `f1` = the first objective in matrix order and `range`): the rows were dealt
-// by descending first objective and bin_end[b] is one past the last position of bin b. Every dominator of
-// a column lies in the column's own bin or a later one, so its scan starts at its bin's first word.
+// `bin_end` (optional, with `fs` = the objectives in matrix order, structure of arrays with row length npad, and
+// the tables of the row order): bin_end[b] is one past the last position of order bin b. Every dominator of a
+// column is no larger in the first AND in the second objective, so it lies in the column's own bin or a later
+// one: the column's scan starts at its bin's first word.
 __global__ void nds_peel_init_kernel(long long n, int wp, uint32_t* unranked, uint32_t* unranked_alt, int* ptr, int* rank,
-                                     Ctrl* ctrl, const float* __restrict__ f1, const unsigned* __restrict__ range,
+                                     Ctrl* ctrl, const float* __restrict__ fs, long long npad, int m,
+                                     const unsigned* __restrict__ range, const int* __restrict__ group_of_bin, int groups,
                                      const int* __restrict__ bin_end, int tail_rows) {
   const long long t0 = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long stride = (long long)gridDim.x * blockDim.x;
@@ -460,7 +568,8 @@ __global__ void nds_peel_init_kernel(long long n, int wp, uint32_t* unranked, ui
   for (long long j = t0; j < n; j += stride) {
     int start = 0;
     if (bin_end) {
-      const int b = f1_bin(f1[j], range);
+      const float key[2] = {fs[j], m >= 2 ? fs[npad + j] : 0.0f};
+      const int b = order_key(key, m, range, group_of_bin, groups);
       start = b ? bin_end[b - 1] : 0;
     }
     ptr[j] = start >> 5;
@@ -1008,9 +1117,9 @@ __global__ void nds_hist_kernel(const int* __restrict__ rank, long long n, int* 
 // before the last admitted front in (rank, index) order and that front's rows in index order. Both are
 // stable bucket placements keyed by rank, done by kRankWarps warps that each own a contiguous range of rows:
 //   count  per-warp histogram of the ranks of its rows                       (kRankWarps x fronts table)
-//   scan   one block: per rank an exclusive prefix over the warps, the rank totals, their prefix over
-//          ranks, and from it the last admitted front (torch.topk(rank, k, largest=False)[0][-1],
-//          non_dominate.py:250)
+//   scan   a warp per rank: exclusive prefix over the row ranges and the rank's total; then one block: prefix
+//          of the totals over the ranks and from it the last admitted front
+//          (torch.topk(rank, k, largest=False)[0][-1], non_dominate.py:250)
 //   place  every warp walks its rows in index order again and writes each to its bucket's next slot.
 // No atomics on shared addresses and no sort: two passes over the ranks.
 // ---------------------------------------------------------------------------------------------
@@ -1039,11 +1148,44 @@ __global__ void __launch_bounds__(256) nds_rank_count_kernel(const int* __restri
     if (in && (peers & ((1u << lane) - 1u)) == 0u) s_cnt[warp][r] += __popc(peers);  // one lane per distinct rank
     __syncwarp();
   }
-  for (int r = lane; r < fronts; r += 32) whist[(size_t)gw * kRankBuckets + r] = s_cnt[warp][r];
+  for (int r = lane; r < fronts; r += 32) whist[(size_t)r * kRankWarps + gw] = s_cnt[warp][r];  // rank-major: the scan reads a rank's row
 }
 
-__global__ void __launch_bounds__(kRankBuckets) nds_rank_scan_kernel(long long topk, Ctrl* ctrl, int* __restrict__ whist,
-                                                                       int* __restrict__ rank_off) {
+// One warp per rank: exclusive prefix of the rank's counts over the kRankWarps row ranges (in place) and the
+// rank's total.
+__global__ void __launch_bounds__(256) nds_rank_scan_kernel(const Ctrl* ctrl, int* __restrict__ whist, int* __restrict__ rank_total) {
+  const int fronts = ctrl->n_fronts;
+  if (fronts > kRankBuckets || fronts <= 0) return;
+  const int lane = threadIdx.x & 31;
+  const int r = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (r >= fronts) return;
+  constexpr int kPer = kRankWarps / 32;  // consecutive row ranges per lane
+  int* row = whist + (size_t)r * kRankWarps + lane * kPer;
+  int c[kPer], sum = 0;
+#pragma unroll
+  for (int q = 0; q < kPer; ++q) {
+    c[q] = row[q];
+    sum += c[q];
+  }
+  int incl = sum;
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const int t = __shfl_up_sync(0xffffffffu, incl, off);
+    if (lane >= off) incl += t;
+  }
+  int run = incl - sum;
+#pragma unroll
+  for (int q = 0; q < kPer; ++q) {
+    row[q] = run;  // rows of this rank owned by earlier ranges
+    run += c[q];
+  }
+  if (lane == 31) rank_total[r] = incl;
+}
+
+// One block: prefix of the rank totals over the ranks, and from it the last admitted front: the first rank whose
+// inclusive count reaches topk.
+__global__ void __launch_bounds__(kRankBuckets) nds_rank_offsets_kernel(long long topk, Ctrl* ctrl, const int* __restrict__ rank_total,
+                                                                          int* __restrict__ rank_off) {
   const int fronts = ctrl->n_fronts;
   if (fronts > kRankBuckets || fronts <= 0) return;
   __shared__ int s_scan[kRankBuckets];
@@ -1053,16 +1195,7 @@ __global__ void __launch_bounds__(kRankBuckets) nds_rank_scan_kernel(long long t
     ctrl->n_before = 0;
     ctrl->n_last = 0;
   }
-  __syncthreads();
-  int total = 0;
-  if (r < fronts) {
-#pragma unroll 8
-    for (int w = 0; w < kRankWarps; ++w) {
-      const int c = whist[(size_t)w * kRankBuckets + r];
-      whist[(size_t)w * kRankBuckets + r] = total;  // rows of this rank owned by earlier warps
-      total += c;
-    }
-  }
+  const int total = r < fronts ? rank_total[r] : 0;
   s_scan[r] = total;
   __syncthreads();
   for (int off = 1; off < kRankBuckets; off <<= 1) {
@@ -1074,7 +1207,6 @@ __global__ void __launch_bounds__(kRankBuckets) nds_rank_scan_kernel(long long t
   const int before = s_scan[r] - total;  // rows of better ranks
   if (r < fronts) {
     rank_off[r] = before;
-    // the last admitted front: the first rank whose inclusive count reaches topk
     if ((long long)before < topk && (long long)before + total >= topk) {
       ctrl->worst_rank = r;
       ctrl->n_before = before;
@@ -1093,7 +1225,7 @@ __global__ void __launch_bounds__(256) nds_rank_place_kernel(const int* __restri
   const int gw = blockIdx.x * 8 + warp;
   const int worst = ctrl->worst_rank;
   for (int r = lane; r <= worst; r += 32)
-    s_cur[warp][r] = whist[(size_t)gw * kRankBuckets + r] + (r < worst ? rank_off[r] : 0);
+    s_cur[warp][r] = whist[(size_t)r * kRankWarps + gw] + (r < worst ? rank_off[r] : 0);
   __syncwarp();
   long long begin, end;
   rank_warp_range(n, gw, &begin, &end);
@@ -1407,18 +1539,27 @@ int run_rank(const float* f, long long n, int m, int* rank, void* ws, const Layo
   uint32_t* unranked = at<uint32_t>(ws, L.unranked);
   uint32_t* newfront = at<uint32_t>(ws, L.newfront);
   int* ptr = at<int>(ws, L.ptr);
-  // large populations: deal the rows by their first objective (see nds_f1_range_kernel)
+  // large populations: deal the rows into bands of the first objective and, inside a band, by the second one
+  // (see order_key): about eight tiles of 1,024 rows per band, so that a tile is narrow in both objectives
   const uint32_t* perm = nullptr;
+  unsigned* range = at<unsigned>(ws, L.bins);
+  int* group_of_bin = reinterpret_cast<int*>(range + 4);
+  int* counts = group_of_bin + (kBins + 2);
+  int* cursor = counts + (kBins + 2);
+  int groups = (int)(n / 8192);
+  groups = groups < 1 ? 1 : (groups > 16 ? 16 : groups);
+  while (kBins % groups) --groups;
   if (n >= kOrderMinN && m <= 16) {
-    unsigned* range = at<unsigned>(ws, L.bins);
-    int* counts = reinterpret_cast<int*>(range + 2);
-    int* cursor = counts + (kBins + 2);
     uint32_t* perm_w = at<uint32_t>(ws, L.perm);
-    EVOX_CUDA(cudaMemsetAsync(range, 0, sizeof(int) * (size_t)(2 * (kBins + 2) + 2), s));
-    nds_f1_range_kernel<<<grid_1d(n), kThreads, 0, s>>>(f, n, m, range);
-    nds_bin_count_kernel<<<grid_1d(n), kThreads, 0, s>>>(f, n, m, range, counts);
+    EVOX_CUDA(cudaMemsetAsync(range, 0, sizeof(int) * (size_t)(3 * (kBins + 2) + 4), s));
+    nds_range_kernel<<<grid_1d(n), kThreads, 0, s>>>(f, n, m, range);
+    if (m >= 2) {
+      nds_bin_count_kernel<<<grid_1d(n), kThreads, 0, s>>>(f, n, m, range, group_of_bin);
+      nds_group_kernel<<<1, 1024, 0, s>>>(group_of_bin, groups);
+    }
+    nds_key_count_kernel<<<grid_1d(n), kThreads, 0, s>>>(f, n, m, range, group_of_bin, groups, counts);
     nds_bin_scan_kernel<<<1, 1024, 0, s>>>(counts, cursor);
-    nds_bin_scatter_kernel<<<grid_1d(n), kThreads, 0, s>>>(f, n, m, range, cursor, perm_w);
+    nds_bin_scatter_kernel<<<grid_1d(n), kThreads, 0, s>>>(f, n, m, range, group_of_bin, groups, cursor, perm_w);
     EVOX_LAUNCH_CHECK();
     perm = perm_w;
   }
@@ -1434,12 +1575,9 @@ int run_rank(const float* f, long long n, int m, int* rank, void* ws, const Layo
       nds_dominance_generic_kernel<<<grid_1d(n * (long long)L.wp), kThreads, 0, s>>>(fs, L.npad, n, m, Dt, L.wp);
   }
   EVOX_LAUNCH_CHECK();
-  {
-    const unsigned* range = at<unsigned>(ws, L.bins);
-    const int* bin_end = reinterpret_cast<const int*>(range + 2) + (kBins + 2);  // the scatter's cursors, now at the bin ends
-    nds_peel_init_kernel<<<grid_1d(n), kThreads, 0, s>>>(n, L.wp, unranked, newfront, ptr, rank, ctrl, fs, range,
-                                                         ordered ? bin_end : nullptr, n <= kTailDirectMaxN ? (int)n : 0);
-  }
+  // the scatter's cursors are now at the bin ends
+  nds_peel_init_kernel<<<grid_1d(n), kThreads, 0, s>>>(n, L.wp, unranked, newfront, ptr, rank, ctrl, fs, L.npad, m, range, group_of_bin,
+                                                       groups, ordered ? cursor : nullptr, n <= kTailDirectMaxN ? (int)n : 0);
   EVOX_LAUNCH_CHECK();
   if (n <= kTailDirectMaxN) {
     // small population: one cluster peels every front straight from the matrix (measured against the grid kernel:
@@ -1578,7 +1716,8 @@ extern "C" int evox_nd_environmental_selection(const float* x, int64_t dx, const
     int* whist = at<int>(ws, L.whist);
     int* rank_off = at<int>(ws, L.rank_off);
     nds_rank_count_kernel<<<kRankWarps / 8, 256, 0, s>>>(rank, n, ctrl, whist);
-    nds_rank_scan_kernel<<<1, kRankBuckets, 0, s>>>(topk, ctrl, whist, rank_off);
+    nds_rank_scan_kernel<<<kRankBuckets / 8, 256, 0, s>>>(ctrl, whist, rank_off + kRankBuckets);
+    nds_rank_offsets_kernel<<<1, kRankBuckets, 0, s>>>(topk, ctrl, rank_off + kRankBuckets, rank_off);
     nds_rank_place_kernel<<<kRankWarps / 8, 256, 0, s>>>(rank, n, ctrl, whist, rank_off, order, idx_l);
     EVOX_LAUNCH_CHECK();
   }

@@ -250,3 +250,23 @@ def test_tensor_core_gradient_at_benchmark_block(cuda):
     want = fb @ a.double().reshape(pop * 8, k) / (pop * sigma)
     err = float((got[rows.to(cuda)].double().cpu() - want).abs().max() / want.abs().max())
     assert err <= 1e-5, err
+
+
+@pytest.mark.parametrize("pop,d,k,parts", [(64, 2048, 2048, 8), (1024, 4096, 4096, 8), (16, 512, 512, 2)])
+def test_row_shards_of_a_gradient_block_give_the_whole_block_bit_for_bit(cuda, pop, d, k, parts):
+    """A GPU of a sharded VirtualLoRAES computes its rows of every gradient block; the launch then has a
+    different number of tiles than the whole block's, and may divide a tile's chunk list between one or two
+    work items differently. The chunk sums are always combined as the same two rounded halves, so the rows
+    must equal the whole block's rows exactly — which is what lets the sharded centre equal the single-GPU one."""
+    from evox_b200.lora_kernels import lora_gradient_from_seeds
+
+    g = torch.Generator().manual_seed(pop + d)
+    seeds = torch.randint(0, 2**31, (pop,), generator=g, dtype=torch.int64).to(cuda)
+    fit = (torch.rand(pop, generator=g) - 0.5).to(cuda)
+    whole = lora_gradient_from_seeds(fit, seeds, (d, k), 8, 40, pop, 0.02).clone()
+    step = d // parts
+    for i in range(parts):
+        part = lora_gradient_from_seeds(fit, seeds, (d, k), 8, 40, pop, 0.02, rows=(i * step, (i + 1) * step))
+        assert torch.equal(part, whole[i * step:(i + 1) * step]), i
+    torch.cuda.synchronize()
+    assert int(lora_gradient_from_seeds.last_error_flag) == 0
