@@ -43,7 +43,10 @@ namespace {
 
 constexpr int kThreads = 256;
 constexpr int kSortThreads = 1024;
-constexpr int kPeelThreads = 512;   // threads per block of the peeling kernel (256: 2.37 / 0.435 ms per rank at 1e5 / 2e4 rows, 512: 2.34 / 0.426, 1024: 2.32 / 0.460)
+// threads per block of the grid peeling kernel: 512, or 1024 when that lets every warp own ONE word of 32 columns
+// per front (earlier measurements with one size for every population: 256: 2.37 / 0.435 ms per rank at 1e5 / 2e4
+// rows, 512: 2.34 / 0.426, 1024: 2.32 / 0.460)
+constexpr int kPeelThreadsSmall = 512, kPeelThreadsLarge = 1024;
 constexpr int kTileJ = 128;      // columns (dominated candidates) per dominance tile
 constexpr int kPad = 1024;       // population padded to a multiple of this (32 words = 128 B rows)
 constexpr unsigned kSpinLimit = 1u << 22;  // grid-barrier polls before giving up (~ seconds)
@@ -692,6 +695,7 @@ __device__ __forceinline__ int first_nonzero(const uint4& v) {
 // scanned on, and never backwards: over all fronts a row of Dt is read once. Measured per front at
 // 100,000 rows: about 1.4 us for the barrier itself, the rest is the slowest block's scans (late fronts:
 // few unranked rows are left, so the next unranked dominator of a column is far away).
+template <int kPeelThreads>
 __global__ void __launch_bounds__(kPeelThreads)
     nds_peel_kernel(const uint32_t* __restrict__ Dt, int wp, long long n, uint32_t* U0, uint32_t* U1, int* ptr,
                     int* rank, Ctrl* ctrl, int mask_in_smem, const uint32_t* __restrict__ perm, int tail_limit) {
@@ -1625,18 +1629,23 @@ int run_rank(const float* f, long long n, int m, int* rank, void* ws, const Layo
   size_t mask_bytes = sizeof(uint32_t) * (size_t)L.wp;
   int mask_in_smem = mask_bytes <= 64 * 1024 ? 1 : 0;  // larger masks are read through L2
   if (!mask_in_smem) mask_bytes = 0;
-  if (mask_bytes > 40 * 1024) {
-    EVOX_CUDA(cudaFuncSetAttribute(nds_peel_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
-  }
-  EVOX_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, nds_peel_kernel, kPeelThreads, mask_bytes));
+  const long long words = (n + 31) / 32;
+  // 1024-thread blocks when 512-thread ones would make every warp visit two words per front but 1024-thread ones
+  // only one (the witness position then stays in a register and a front has one trip of block barriers, not two:
+  // 1.84 against 1.89 ms per rank at 100,000 rows)
+  const long long warps512 = (long long)sm_count() * (kPeelThreadsSmall / 32);
+  const bool large = words > warps512 && words <= 2 * warps512;
+  const int threads = large ? kPeelThreadsLarge : kPeelThreadsSmall;
+  const void* kernel = large ? (const void*)nds_peel_kernel<kPeelThreadsLarge> : (const void*)nds_peel_kernel<kPeelThreadsSmall>;
+  if (mask_bytes > 40 * 1024) EVOX_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
+  EVOX_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, mask_bytes));
   EVOX_REQUIRE(per_sm > 0, EVOX_ERR_CUDA, "nds_peel_kernel cannot be made resident");
   if (per_sm > 4) per_sm = 4;
   {
     // Enough blocks for one word of 32 columns per warp (one trip per front) plus a share of helper
     // warps, but no more: the grid barrier gets slower with every block that takes part (measured at
     // 20,000 rows: 0.47 ms per rank with four blocks per multiprocessor, 0.44 ms with one).
-    const long long words = (n + 31) / 32;
-    const long long need = (words + (long long)sm_count() * (kPeelThreads / 32) - 1) / ((long long)sm_count() * (kPeelThreads / 32));
+    const long long need = (words + (long long)sm_count() * (threads / 32) - 1) / ((long long)sm_count() * (threads / 32));
     const int want = need <= 1 ? 1 : (int)(need + 1);
     if (want < per_sm) per_sm = want;
   }
@@ -1650,7 +1659,7 @@ int run_rank(const float* f, long long n, int m, int* rank, void* ws, const Layo
   int tail_limit = kTailCompactRows;
   void* args[] = {(void*)&Dt_c, (void*)&wp, (void*)&nn, (void*)&unranked, (void*)&newfront, (void*)&ptr, (void*)&rank, (void*)&ctrl,
                   (void*)&mask_in_smem, (void*)&perm, (void*)&tail_limit};
-  EVOX_CUDA(cudaLaunchCooperativeKernel((const void*)nds_peel_kernel, dim3((unsigned)blocks), dim3(kPeelThreads), args, mask_bytes, s));
+  EVOX_CUDA(cudaLaunchCooperativeKernel(kernel, dim3((unsigned)blocks), dim3(threads), args, mask_bytes, s));
   uint32_t* ids = at<uint32_t>(ws, L.tail_ids);
   uint32_t* sub = at<uint32_t>(ws, L.tail_sub);
   nds_tail_ids_kernel<<<1, 1024, 0, s>>>(unranked, newfront, L.wp, ctrl, ids);
