@@ -176,7 +176,7 @@ def pso_config(workload: str, world: int) -> dict:
         "random_draws": "in-kernel Philox4x32-10 (the reference arm: torch.rand, as the reference draws them)",
         "l2": "state per GPU (%.1f GB) is larger than L2, no flush needed" % (12.0 * rows * d / 1e9)
         if 12.0 * rows * d > 4 * 126e6 else "state fits in L2: numbers are L2-resident",
-        "sharding": "rows over ranks, one best-particle allgather per generation" if world > 1 else "single GPU",
+        "sharding": "rows over ranks, every shard's best-particle record exchanged once per generation" if world > 1 else "single GPU",
     }
 
 
@@ -598,10 +598,11 @@ def run_ours(args):
         extras["sharded_checks"] = checks
         extras["nccl_allgather_4k"] = measure_allgather_latency(dev)
 
-    def pso_run(workload, steps, warmup, with_e2e=True):
+    def pso_run(workload, steps, warmup, with_e2e=True, peer_exchange=True):
         fit_name, P, d, lb, ub, w, pp, pg = WORKLOADS[workload]
         torch.manual_seed(0)
-        algo = PSO(P, torch.full((d,), lb), torch.full((d,), ub), w, pp, pg, device=dev, shard=world > 1, seed=2026)
+        algo = PSO(P, torch.full((d,), lb), torch.full((d,), ub), w, pp, pg, device=dev, shard=world > 1, seed=2026,
+                   peer_exchange=peer_exchange)
         algo.velocity.mul_(0.2)  # the benchmark configurations start with velocities in +-0.2 * range
         wf = StdWorkflow(algo, Ackley() if fit_name == "ackley" else Rastrigin(), device=dev)
         assert wf._fused_plan() is not None
@@ -619,7 +620,10 @@ def run_ours(args):
             t = torch.tensor([kernel_ms], device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             kernel_ms = t.item()
-        res = {"ms_per_step": total_ms / steps, "kernel_ms": kernel_ms, "rows": a.local_size, "P": P, "d": d}
+        res = {"ms_per_step": total_ms / steps, "kernel_ms": kernel_ms, "rows": a.local_size, "P": P, "d": d,
+               "exchange": "single GPU" if world == 1 else ("peer stores by the generation kernel" if a._peer else "NCCL allgather")}
+        if a.exchange_status() != 0:
+            raise RuntimeError("PSO: a wait for another GPU's best-particle record gave up during the timed run")
         if with_e2e:
             # end to end: host inputs in (three pinned scalars), result out, every step
             host = [torch.tensor(v, dtype=torch.float32).pin_memory() for v in (w, pp, pg)]
@@ -665,7 +669,8 @@ def run_ours(args):
     pk = peaks()
     alg_bytes = PSO_BYTES_PER_ELEM * n_local * d
     achieved = alg_bytes / (main["kernel_ms"] * 1e-3) / 1e9
-    launches_per_step = 1 if world == 1 else 2  # the generation kernel (+ NCCL's allgather kernel)
+    # the generation kernel (+ NCCL's allgather kernel when the records do not travel by peer stores)
+    launches_per_step = 2 if main["exchange"] == "NCCL allgather" else 1
 
     if world > 1 and args.workload == "pso_ackley_1e6x1000" and not args.no_secondary:
         # benchmark configuration 4 names Rastrigin (w = 0.7, phi = 1.5 / 1.5) for the sharded swarm
@@ -673,10 +678,16 @@ def run_ours(args):
             r4, wf4 = pso_run("pso_rastrigin_1e6x1000", args.steps, warmup)
         wf4 = None
         torch.cuda.empty_cache()
+        # the headline swarm again with the records exchanged by one NCCL allgather per generation
+        rn, wfn = pso_run(args.workload, args.steps, warmup, with_e2e=False, peer_exchange=False)
+        wfn = None
+        torch.cuda.empty_cache()
+        extras["pso_ackley_nccl_exchange"] = {"value": 1e3 / rn["ms_per_step"], "unit": "gens/s", "ms_per_step": rn["ms_per_step"],
+                                              "kernel_ms": rn["kernel_ms"], "exchange": rn["exchange"]}
         extras["pso_rastrigin_1e6x1000"] = {
             "value": 1e3 / r4["ms_per_step"], "unit": "gens/s", "ms_per_step": r4["ms_per_step"], "kernel_ms": r4["kernel_ms"],
             "e2e": {"value": 1e3 / r4["e2e_ms"], "unit": "gens/s", "h2d_bytes_per_step": 12, "d2h_bytes_per_step": 4},
-            "config": pso_config("pso_rastrigin_1e6x1000", world), "clocks": c4.summary(),
+            "config": pso_config("pso_rastrigin_1e6x1000", world), "clocks": c4.summary(), "exchange": r4["exchange"],
         }
         sec = {}
         from evox_b200.operators.selection import ref_vec_guided_sharded
@@ -753,6 +764,7 @@ def run_ours(args):
                 "note": "StdWorkflow.step(); swarm state is device-resident by design, host inputs are the hyper-parameters",
             },
             "gpu_launches": launches_per_step * args.steps,
+            "exchange": main["exchange"],
             "roofline": {
                 "bound": "hbm", "kernel": "pso_move_eval_kernel (fused generation)", "achieved": achieved, "peak": pk["hbm_gbs"],
                 "unit": "GB/s", "frac": achieved / pk["hbm_gbs"], "peak_kind": pk["kind"],

@@ -24,6 +24,8 @@ kernel it is rebuilt from `fit` with one extra launch.
 
 from __future__ import annotations
 
+import ctypes
+
 import torch
 
 from .. import _cabi
@@ -47,6 +49,7 @@ class PSO(Algorithm):
         shard: bool = False,
         group=None,
         seed: int | None = None,
+        peer_exchange: bool = True,
     ):
         """
         :param pop_size: number of particles (of the WHOLE swarm when `shard=True`).
@@ -54,6 +57,9 @@ class PSO(Algorithm):
         :param w, phi_p, phi_g: inertia, cognitive and social weights.
         :param device: where the state lives; must be a CUDA device to step.
         :param shard: split the particles over the ranks of `group`.
+        :param peer_exchange: sharded swarms only: let the generation kernels write their best-particle records
+            straight into the other GPUs' memory (one launch per generation, no collective call); falls back to
+            one NCCL allgather per generation when the ranks cannot map each other's memory.
         :param seed: key of the in-kernel random stream; drawn from torch's CPU generator if None,
             so `torch.manual_seed` makes runs repeatable (and equal on every rank).
         """
@@ -107,6 +113,10 @@ class PSO(Algorithm):
         self._checked_ptrs = None  # storage addresses of the state the last argument check saw
         self._cur = 0              # which of the two record buffers holds this shard's latest record
         self._pending = None       # (swarm key, gathered records) left by the last fused generation
+        # sharded swarm: the records are exchanged by the kernels themselves over peer memory when the ranks can
+        # map each other's exchange buffers (None: not tried yet, False: unavailable -> NCCL allgather)
+        self.peer_exchange = peer_exchange
+        self._peer = None
         # measurement hook: when a list, step() appends a (start, end) CUDA-event pair around the
         # generation kernel (on several GPUs the allgather that follows stays outside the pair)
         self._kernel_events: list | None = None
@@ -172,6 +182,41 @@ class PSO(Algorithm):
             return record
         return allgather_records(record, self.group, out=self._scratch["gathered"])
 
+    def _setup_peer_exchange(self, dev: torch.device) -> None:
+        """Exchange buffers the ranks can write into each other (torch's symmetric memory: plain peer mappings
+        over NVLink; no multicast object is bound). Every rank ends with the same answer."""
+        import os
+
+        import torch.distributed as dist
+
+        ok, peer = 1, None
+        try:
+            if self.world_size > 16:
+                raise RuntimeError("the peer exchange serves at most 16 ranks")
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+            import torch.distributed._symmetric_memory as symm_mem
+
+            words = (_cabi.lib.evox_pso_exchange_words(self.dim, self.world_size) + 3) // 4 * 4
+            buf = symm_mem.empty(words, dtype=torch.int32, device=dev)
+            handle = symm_mem.rendezvous(buf, self.group if self.group is not None else dist.group.WORLD)
+            buf.zero_()
+            ptrs = [int(p) for p in handle.buffer_ptrs]
+            if len(ptrs) != self.world_size or any(p == 0 for p in ptrs):
+                raise RuntimeError("symmetric memory gave no peer addresses")
+            peer = {"buf": buf, "handle": handle, "ptrs": (ctypes.c_uint64 * self.world_size)(*ptrs),
+                    "status": torch.zeros(1, dtype=torch.int32, device=dev), "tag": 1}
+        except Exception as exc:  # unavailable on this machine / build: the NCCL path serves
+            ok, self._peer_error = 0, f"{type(exc).__name__}: {exc}"
+        flag = torch.tensor([ok], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)  # also orders the zero-fill before any peer write
+        torch.cuda.synchronize(dev)
+        dist.barrier(group=self.group)
+        self._peer = peer if int(flag.item()) == 1 else False
+
+    def exchange_status(self) -> int:
+        """0, or 1 when a kernel's wait for another GPU's record ran out (synchronises the device)."""
+        return int(self._peer["status"]) if self._peer else 0
+
     def _rebuild_records(self, dev: torch.device) -> torch.Tensor:
         """This shard's best-particle record from `fit` and `pop` as they are now, gathered."""
         ws, cand = self._scratch["ws"], self._scratch["cand"][self._cur]
@@ -228,25 +273,57 @@ class PSO(Algorithm):
             _cabi.check(lib.evox_pso_move_eval(*state[:6], *args, self.row_start, s))
             self._pending = None
         else:
-            if self._pending is None or self._pending[0] != self._swarm_key():
-                records = self._rebuild_records(dev)
-            else:
-                records = self._pending[1]
-            self._cur ^= 1
-            out = self._scratch["cand"][self._cur]
-            if self._kernel_events is not None:
-                pair = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
-                pair[0].record()
-            _cabi.check(
-                lib.evox_pso_generation(
-                    *state, *args, self.row_start, _cabi.ptr(records), self.world_size, _cabi.ptr(out),
-                    _cabi.ptr(ws), ws.numel(), s,
+            if self.world_size > 1 and self.peer_exchange and self._peer is None:
+                self._setup_peer_exchange(dev)
+            stale = self._pending is None or self._pending[0] != self._swarm_key()
+            if self.world_size > 1 and self._peer:
+                peer = self._peer
+                tag = peer["tag"]
+                if stale or self._pending[1] is not None:
+                    # The records are not in the exchange buffer (first generation, or the swarm was written
+                    # between generations): take them from init_step or rebuild them (one launch + one NCCL
+                    # allgather, which also orders every rank's earlier kernels before this write) and place them
+                    # where the kernel's head looks: slot (tag & 1) of this rank's buffer, flags = tag. Every rank
+                    # must take this branch in the same generation, as with any collective.
+                    records = self._rebuild_records(dev) if stale else self._pending[1]
+                    words, g = records.shape[1], self.world_size
+                    base = (tag & 1) * g * words
+                    peer["buf"][base : base + g * words].copy_(records.view(-1))
+                    flags = 2 * g * words + (tag & 1) * g
+                    peer["buf"][flags : flags + g].fill_(tag if tag < 2**31 else tag - 2**32)
+                if self._kernel_events is not None:
+                    pair = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+                    pair[0].record()
+                _cabi.check(
+                    lib.evox_pso_generation_peer(
+                        *state, *args, self.row_start, peer["ptrs"], self.world_size, self.rank, tag, _cabi.ptr(peer["status"]),
+                        _cabi.ptr(ws), ws.numel(), s,
+                    )
                 )
-            )
-            if self._kernel_events is not None:
-                pair[1].record()
-                self._kernel_events.append(pair)
-            self._pending = (self._swarm_key(), self._gather(out))
+                if self._kernel_events is not None:
+                    pair[1].record()
+                    self._kernel_events.append(pair)
+                peer["tag"] = 1 if tag == 2**32 - 1 else tag + 1
+                self._pending = (self._swarm_key(), None)
+                if self.generation % 4096 == 4095 and int(peer["status"]) != 0:
+                    raise _cabi.EvoxKernelError("PSO: a wait for another GPU's best-particle record timed out")
+            else:
+                records = self._rebuild_records(dev) if stale else self._pending[1]
+                self._cur ^= 1
+                out = self._scratch["cand"][self._cur]
+                if self._kernel_events is not None:
+                    pair = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+                    pair[0].record()
+                _cabi.check(
+                    lib.evox_pso_generation(
+                        *state, *args, self.row_start, _cabi.ptr(records), self.world_size, _cabi.ptr(out),
+                        _cabi.ptr(ws), ws.numel(), s,
+                    )
+                )
+                if self._kernel_events is not None:
+                    pair[1].record()
+                    self._kernel_events.append(pair)
+                self._pending = (self._swarm_key(), self._gather(out))
         self.generation += 1
         if plan is None:
             self.fit = self.evaluate(self.pop)

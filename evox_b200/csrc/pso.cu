@@ -107,9 +107,38 @@ struct MoveArgs {
   uint32_t* cand_out;       // this shard's record of the new swarm (never inside cands)
   unsigned int* ticket;
   MinIdx* partials;
+  // Sharded swarm with the records exchanged by the kernels themselves (n_peers > 0): every rank holds an
+  // exchange buffer of the same layout — records[2][n_peers][4 + d] then flags[2][n_peers], all 32-bit words —
+  // and peer_base[p] is rank p's buffer as THIS device addresses it (peer memory over NVLink). The tail stores
+  // this shard's record into slot (tag_out & 1, my_rank) of every rank's buffer and then the flag tag_out; the
+  // head waits until its own buffer's flags of parity tag_in & 1 all read tag_in. cands / cand_out are unused.
+  unsigned long long peer_base[16];
+  int n_peers;
+  int my_rank;
+  unsigned int tag_in;
+  int* status;  // set to 1 when a wait for a peer's flag gave up
 };
 
 constexpr long long kNoRow = 0x7fffffffffffffffLL;
+// A wait for another GPU's record ends after two seconds (or this many polls, whichever comes first): the kernel
+// then sets its status word and goes on, and later launches that find the word set do not wait at all.
+constexpr unsigned kPeerSpinLimit = 1u << 24;
+constexpr unsigned long long kPeerWaitNs = 2000000000ull;
+
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+__device__ __forceinline__ unsigned int load_acquire_sys(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void store_release_sys(unsigned int* p, unsigned int v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 
 // true when argmin would report b before a (smaller key, then lower index)
 __device__ __forceinline__ bool comes_first(const MinIdx& b, const MinIdx& a) {
@@ -121,11 +150,36 @@ __device__ __forceinline__ bool comes_first(const MinIdx& b, const MinIdx& a) {
 // best, and that record's fitness.
 __device__ __forceinline__ const float* fold_candidates(const MoveArgs& a, int lane, bool* take, float* best_fit) {
   const int words = 4 + a.d;
+  const uint32_t* cands = a.cands;
+  int n_cands = a.n_cands;
+  if (a.n_peers > 0) {
+    // the records of the previous generation arrive from the other GPUs: wait (bounded) for every rank's flag
+    const uint32_t* mine = reinterpret_cast<const uint32_t*>(a.peer_base[a.my_rank]);
+    const unsigned parity = a.tag_in & 1u;
+    const unsigned int* flags = mine + (size_t)2 * a.n_peers * words + (size_t)parity * a.n_peers;
+    for (int r = lane; r < a.n_peers; r += 32) {
+      if (load_acquire_sys(flags + r) == a.tag_in) continue;
+      if (*reinterpret_cast<const volatile int*>(a.status) != 0) continue;  // an earlier wait gave up: do not wait again
+      const unsigned long long t0 = global_timer_ns();
+      unsigned spins = 0;
+      while (load_acquire_sys(flags + r) != a.tag_in) {
+        if (++spins > kPeerSpinLimit || global_timer_ns() - t0 > kPeerWaitNs) {
+          atomicExch(a.status, 1);
+          break;
+        }
+        __nanosleep(200);
+      }
+    }
+    __syncwarp();
+    cands = mine + (size_t)parity * a.n_peers * words;
+    n_cands = a.n_peers;
+  }
   MinIdx m{INFINITY, kNoRow};
   int rec = 0;
-  for (int r = lane; r < a.n_cands; r += 32) {
-    const uint32_t* c = a.cands + (size_t)r * words;
-    const MinIdx o{__uint_as_float(__ldg(c)), (long long)(((unsigned long long)__ldg(c + 2) << 32) | __ldg(c + 1))};
+  for (int r = lane; r < n_cands; r += 32) {
+    const uint32_t* c = cands + (size_t)r * words;
+    // plain loads: in peer mode another GPU wrote these words while this kernel may already have been running
+    const MinIdx o{__uint_as_float(c[0]), (long long)(((unsigned long long)c[2] << 32) | c[1])};
     if (comes_first(o, m)) {
       m = o;
       rec = r;
@@ -144,7 +198,7 @@ __device__ __forceinline__ const float* fold_candidates(const MoveArgs& a, int l
   }
   *take = key_less(m.v, *a.gbest_fit);
   *best_fit = m.v;
-  return *take ? reinterpret_cast<const float*>(a.cands + (size_t)rec * words + 4) : a.gbest_loc;
+  return *take ? reinterpret_cast<const float*>(cands + (size_t)rec * words + 4) : a.gbest_loc;
 }
 
 __device__ __forceinline__ MinIdx block_min_idx(MinIdx m, MinIdx* smem) {
@@ -227,7 +281,7 @@ __global__ void __launch_bounds__(kThreads, MOVE_BLOCKS_PER_SM) pso_move_eval_ke
           rg = __ldcs(rg4 + c);
           rp = __ldcs(rp4 + c);
         }
-        const float4 gb = __ldg(gb4 + c);
+        const float4 gb = FUSED ? gb4[c] : __ldg(gb4 + c);  // fused: may be a record a peer wrote during this launch
         const float4 lb = __ldg(lb4 + c);
         const float4 ub = __ldg(ub4 + c);
         float4 xo;
@@ -307,14 +361,38 @@ __global__ void __launch_bounds__(kThreads, MOVE_BLOCKS_PER_SM) pso_move_eval_ke
     if (threadIdx.x == 0) {
       if (take) *a.gbest_fit = best;
       *a.ticket = 0u;  // ready for the next launch
-      const long long g = f.i + a.row_offset;
-      a.cand_out[0] = __float_as_uint(f.v);
-      a.cand_out[1] = (uint32_t)((unsigned long long)g & 0xffffffffull);
-      a.cand_out[2] = (uint32_t)((unsigned long long)g >> 32);
-      a.cand_out[3] = 0u;
     }
+    const long long g = f.i + a.row_offset;
     const float* row = a.pop + (size_t)f.i * (size_t)d;  // written by another block of this launch: read past L1
-    for (int e = threadIdx.x; e < d; e += blockDim.x) a.cand_out[4 + e] = __float_as_uint(__ldcg(row + e));
+    if (a.n_peers == 0) {
+      if (threadIdx.x == 0) {
+        a.cand_out[0] = __float_as_uint(f.v);
+        a.cand_out[1] = (uint32_t)((unsigned long long)g & 0xffffffffull);
+        a.cand_out[2] = (uint32_t)((unsigned long long)g >> 32);
+        a.cand_out[3] = 0u;
+      }
+      for (int e = threadIdx.x; e < d; e += blockDim.x) a.cand_out[4 + e] = __float_as_uint(__ldcg(row + e));
+    } else {
+      // this shard's record goes straight into every rank's exchange buffer (peer stores), then the flags
+      const int words = 4 + d;
+      const unsigned tag_out = a.tag_in + 1u == 0u ? 1u : a.tag_in + 1u;  // never 0: a cleared buffer holds no tag
+      const size_t slot = ((size_t)(tag_out & 1u) * a.n_peers + a.my_rank) * words;
+      for (int e = threadIdx.x; e < words; e += blockDim.x) {
+        uint32_t v;
+        if (e == 0) v = __float_as_uint(f.v);
+        else if (e == 1) v = (uint32_t)((unsigned long long)g & 0xffffffffull);
+        else if (e == 2) v = (uint32_t)((unsigned long long)g >> 32);
+        else if (e == 3) v = 0u;
+        else v = __float_as_uint(__ldcg(row + (e - 4)));
+        for (int p = 0; p < a.n_peers; ++p) reinterpret_cast<uint32_t*>(a.peer_base[p])[slot + e] = v;
+      }
+      __threadfence_system();
+      __syncthreads();
+      if ((int)threadIdx.x < a.n_peers) {
+        unsigned int* flags = reinterpret_cast<uint32_t*>(a.peer_base[threadIdx.x]) + (size_t)2 * a.n_peers * words;
+        store_release_sys(flags + (size_t)(tag_out & 1u) * a.n_peers + a.my_rank, tag_out);
+      }
+    }
   }
 }
 
@@ -650,6 +728,11 @@ int fill_move_args(MoveArgs* a, bool* vec, float* pop, float* velocity, float* l
   a->cand_out = nullptr;
   a->ticket = nullptr;
   a->partials = nullptr;
+  a->n_peers = 0;
+  a->my_rank = 0;
+  a->tag_in = 0u;
+  a->status = nullptr;
+  for (int p = 0; p < 16; ++p) a->peer_base[p] = 0ull;
   *vec = (dim % 4 == 0) && aligned16(pop) && aligned16(velocity) && aligned16(local_best_location) &&
          aligned16(global_best_location) && aligned16(lb) && aligned16(ub);
   if (rg != nullptr) *vec = *vec && aligned16(rg) && aligned16(rp);
@@ -710,6 +793,52 @@ extern "C" int evox_pso_generation(float* pop, float* velocity, float* local_bes
   a.partials = ws.partials;
   const int grid = row_grid(pop_size, MOVE_BLOCKS_PER_SM);
   EVOX_REQUIRE(grid <= kMaxPartials, EVOX_ERR_INVALID, "pso_generation: grid of %d blocks exceeds %d partials", grid, kMaxPartials);
+  launch_move_any<true>(vec, rg == nullptr, fitness_id, grid, reinterpret_cast<cudaStream_t>(stream), a);
+  EVOX_LAUNCH_CHECK();
+  return EVOX_OK;
+}
+
+extern "C" size_t evox_pso_exchange_words(int32_t dim, int32_t n_ranks) {
+  if (dim <= 0 || n_ranks <= 0) return 0;
+  return (size_t)2 * n_ranks * (4 + (size_t)dim) + (size_t)2 * n_ranks;
+}
+
+extern "C" int evox_pso_generation_peer(float* pop, float* velocity, float* local_best_location, float* local_best_fit,
+                                        float* fit, float* global_best_location, float* global_best_fit, const float* lb,
+                                        const float* ub, const float* w, const float* phi_p, const float* phi_g,
+                                        const float* rg, const float* rp, int64_t pop_size, int32_t dim,
+                                        int32_t fitness_id, const float* params, uint64_t seed, uint64_t generation,
+                                        int64_t row_offset, const uint64_t* peer_buffers, int32_t n_ranks, int32_t my_rank,
+                                        uint32_t tag, int32_t* status, void* workspace, size_t workspace_bytes,
+                                        void* stream) {
+  MoveArgs a;
+  bool vec;
+  if (int rc = fill_move_args(&a, &vec, pop, velocity, local_best_location, local_best_fit, fit, global_best_location,
+                              lb, ub, w, phi_p, phi_g, rg, rp, pop_size, dim, fitness_id, params, seed, generation,
+                              row_offset))
+    return rc;
+  EVOX_REQUIRE(global_best_fit && peer_buffers && status, EVOX_ERR_INVALID, "pso_generation_peer: NULL pointer");
+  EVOX_REQUIRE(n_ranks >= 1 && n_ranks <= 16, EVOX_ERR_INVALID, "pso_generation_peer: 1 to 16 ranks, got %d", n_ranks);
+  EVOX_REQUIRE(my_rank >= 0 && my_rank < n_ranks, EVOX_ERR_INVALID, "pso_generation_peer: rank %d outside [0, %d)", my_rank, n_ranks);
+  EVOX_REQUIRE(tag != 0u, EVOX_ERR_INVALID, "pso_generation_peer: tag 0 is reserved for a cleared buffer");
+  Workspace ws;
+  if (int rc = carve(workspace, workspace_bytes, &ws)) return rc;
+  for (int p = 0; p < n_ranks; ++p) {
+    EVOX_REQUIRE(peer_buffers[p] != 0 && (peer_buffers[p] & 15u) == 0, EVOX_ERR_INVALID,
+                 "pso_generation_peer: exchange buffer of rank %d is NULL or not 16-byte aligned", p);
+    a.peer_base[p] = peer_buffers[p];
+  }
+  // the attractor row is read with 16-byte loads out of a record: records are (4 + dim) words, dim % 4 == 0 here
+  a.n_peers = n_ranks;
+  a.my_rank = my_rank;
+  a.tag_in = tag;
+  a.status = status;
+  a.gbest_fit = global_best_fit;
+  a.gbest_loc_out = global_best_location;
+  a.ticket = ws.ticket;
+  a.partials = ws.partials;
+  const int grid = row_grid(pop_size, MOVE_BLOCKS_PER_SM);
+  EVOX_REQUIRE(grid <= kMaxPartials, EVOX_ERR_INVALID, "pso_generation_peer: grid of %d blocks exceeds %d partials", grid, kMaxPartials);
   launch_move_any<true>(vec, rg == nullptr, fitness_id, grid, reinterpret_cast<cudaStream_t>(stream), a);
   EVOX_LAUNCH_CHECK();
   return EVOX_OK;

@@ -124,6 +124,29 @@ int evox_pso_generation(float* pop, float* velocity, float* local_best_location,
                         int32_t n_candidates, uint32_t* candidate_out, void* workspace,
                         size_t workspace_bytes, void* stream);
 
+/* evox_pso_generation for a swarm sharded over the GPUs of one node, with the one exchange of a generation — the
+ * allgather of the best-particle records — done by the kernels themselves over peer memory (NVLink), so that a
+ * generation is one launch and no library collective. Every rank owns an exchange buffer of
+ * evox_pso_exchange_words(dim, n_ranks) 32-bit words, zero-filled once: records[2][n_ranks][4 + dim], then
+ * flags[2][n_ranks]. `peer_buffers` is a HOST array of n_ranks device addresses: rank p's buffer as this device
+ * addresses it (its own buffer at index my_rank). The head waits until the flags of parity (tag & 1) in its own
+ * buffer all read `tag` (the caller writes the records and flags of the first call itself), the tail stores this
+ * shard's record of the new swarm into slot ((tag + 1) & 1, my_rank) of EVERY rank's buffer and then the flag
+ * tag + 1: pass tag, tag + 1, tag + 2, ... on consecutive calls, never 0. Waits are bounded (about a quarter of a
+ * second): a rank whose peer never writes sets *status = 1 and finishes the generation with what it has; the
+ * caller reads `status` (device int32) when it synchronises. Replaces the same reference code as
+ * evox_pso_generation; the reference's own distributed mode gathers fitness lists with torch.distributed
+ * (workflows/std_workflow.py:185-189). */
+size_t evox_pso_exchange_words(int32_t dim, int32_t n_ranks);
+int evox_pso_generation_peer(float* pop, float* velocity, float* local_best_location, float* local_best_fit,
+                             float* fit, float* global_best_location, float* global_best_fit, const float* lb,
+                             const float* ub, const float* w, const float* phi_p, const float* phi_g,
+                             const float* rg, const float* rp, int64_t pop_size, int32_t dim,
+                             int32_t fitness_id, const float* params, uint64_t seed, uint64_t generation,
+                             int64_t row_offset, const uint64_t* peer_buffers, int32_t n_ranks, int32_t my_rank,
+                             uint32_t tag, int32_t* status, void* workspace, size_t workspace_bytes,
+                             void* stream);
+
 /* PSO.init_step (pso.py:108-115): fit = f(pop); local_best_fit = fit; global best = min_by. */
 int evox_pso_init_step(const float* pop, float* fit, float* local_best_fit,
                        float* global_best_location, float* global_best_fit, int64_t pop_size,

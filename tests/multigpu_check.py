@@ -32,16 +32,29 @@ def check_pso(dev, rank, world):
     shard = StdWorkflow(PSO(P, lb, ub, 0.7, 1.5, 1.5, device=dev, seed=7, shard=True), Rastrigin(), device=dev)
     a, b = shard.algorithm.row_start, shard.algorithm.row_end
     assert torch.equal(shard.algorithm.pop, single.algorithm.pop[a:b])  # the initial swarm does not depend on the sharding
-    for wf in (single, shard):
+    # the same sharded swarm with the records exchanged by one NCCL allgather per generation instead
+    nccl = StdWorkflow(PSO(P, lb, ub, 0.7, 1.5, 1.5, device=dev, seed=7, shard=True, peer_exchange=False), Rastrigin(), device=dev)
+    for wf in (single, shard, nccl):
         wf.init_step()
         for _ in range(5):
             wf.step()
+        # the swarm is written between generations: the next step must see it (records rebuilt on every rank)
+        wf.algorithm.pop.mul_(0.5)
+        for _ in range(4):
+            wf.step()
     torch.cuda.synchronize()
-    s, f = shard.algorithm, single.algorithm
-    for name in ("pop", "velocity", "fit", "local_best_location", "local_best_fit"):
-        assert torch.equal(getattr(s, name), getattr(f, name)[a:b]), f"rank {rank}: {name}"
-    assert torch.equal(s.global_best_location, f.global_best_location)
-    assert torch.equal(s.global_best_fit, f.global_best_fit)
+    f = single.algorithm
+    for s in (shard.algorithm, nccl.algorithm):
+        for name in ("pop", "velocity", "fit", "local_best_location", "local_best_fit"):
+            assert torch.equal(getattr(s, name), getattr(f, name)[a:b]), f"rank {rank}: {name}"
+        assert torch.equal(s.global_best_location, f.global_best_location)
+        assert torch.equal(s.global_best_fit, f.global_best_fit)
+    assert nccl.algorithm._peer is None
+    if shard.algorithm._peer:
+        assert shard.algorithm.exchange_status() == 0, f"rank {rank}: a wait for a peer's record gave up"
+    if rank == 0:
+        how = "kernels over peer memory" if shard.algorithm._peer else f"NCCL ({getattr(shard.algorithm, '_peer_error', '')})"
+        print(f"pso records exchanged by: {how}", flush=True)
 
 
 def check_lora_es(dev, rank, world):

@@ -83,6 +83,25 @@ class Swarm:
         )
         torch.cuda.synchronize()
 
+    def generation_peer(self, prob, buffers, rank, tag, status, rg=None, rp=None, seed=0, generation=0, row_offset=0):
+        """evox_pso_generation_peer: records come from and go to the ranks' exchange buffers."""
+        import ctypes
+
+        c = self.c
+        rg_d = None if rg is None else rg.to(self.dev).contiguous()
+        rp_d = None if rp is None else rp.to(self.dev).contiguous()
+        ptrs = (ctypes.c_uint64 * len(buffers))(*[b.data_ptr() for b in buffers])
+        c.check(
+            c.lib.evox_pso_generation_peer(
+                self.p("pop"), self.p("velocity"), self.p("local_best_location"), self.p("local_best_fit"),
+                self.p("fit"), self.p("global_best_location"), self.p("global_best_fit"), self.p("lb"), self.p("ub"),
+                self.p("w"), self.p("phi_p"), self.p("phi_g"), c.ptr(rg_d), c.ptr(rp_d), self.P, self.d,
+                FIT_ID[prob], c.host_floats(PARAMS[prob]), seed, generation, row_offset, ptrs, len(buffers), rank,
+                tag, c.ptr(status), c.ptr(self.ws), self.ws.numel(), c.stream_ptr(self.dev),
+            )
+        )
+        torch.cuda.synchronize()
+
     def init_step(self, prob):
         c = self.c
         c.check(
@@ -337,6 +356,78 @@ def test_one_launch_generation_sharded_matches_single(cuda):
         for sh in shards:
             assert torch.equal(sh.t["global_best_location"], single.t["global_best_location"]), g
             assert torch.equal(sh.t["global_best_fit"], single.t["global_best_fit"]), g
+
+
+@pytest.mark.parametrize("P,d,prob", [(5001, 40, "rastrigin"), (999, 10, "ackley")])
+def test_peer_exchange_generation_matches_single(cuda, P, d, prob):
+    """evox_pso_generation_peer with three ranks emulated on one GPU: every rank has its own exchange buffer
+    and the kernels write their records into all three. The ranks run one after the other within a generation,
+    so every wait finds its flag already set. After five generations the concatenated shards equal the
+    unsharded swarm bit for bit and no wait gave up."""
+    from evox_b200 import _cabi as c
+
+    lo, hi = (-32.768, 32.768) if prob == "ackley" else (-5.12, 5.12)
+    s = opso.init_step(opso.make_state(P, d, lo, hi, 0.7, 1.5, 1.5, seed=9), opso.FITNESS[prob])
+    single = Swarm(s, cuda)
+    words = c.lib.evox_pso_candidate_words(d)
+    bounds = [(0, P // 3), (P // 3, 2 * P // 3 + 1), (2 * P // 3 + 1, P)]
+    g_ranks = len(bounds)
+    shards = []
+    for a, b in bounds:
+        part = {k: (v[a:b] if (v.ndim >= 1 and v.shape[0] == P) else v) for k, v in s.items()}
+        shards.append(Swarm(part, cuda))
+    n_words = c.lib.evox_pso_exchange_words(d, g_ranks)
+    assert n_words == 2 * g_ranks * words + 2 * g_ranks
+    buffers = [torch.zeros((n_words + 3) // 4 * 4, dtype=torch.int32, device=cuda) for _ in bounds]
+    status = torch.zeros(1, dtype=torch.int32, device=cuda)
+    # generation 0 reads tag 1: seed parity slot 1 of every buffer with the gathered records, flags = 1
+    first = torch.zeros(g_ranks, words, dtype=torch.int32, device=cuda)
+    for r, (a, b) in enumerate(bounds):
+        shards[r].local_best(first[r], row_offset=a)
+    for buf in buffers:
+        buf[g_ranks * words: 2 * g_ranks * words].copy_(first.view(-1))
+        buf[2 * g_ranks * words + g_ranks: 2 * g_ranks * words + 2 * g_ranks].fill_(1)
+    rec1 = torch.zeros(2, words, dtype=torch.int32, device=cuda)
+    single.local_best(rec1[0])
+    for g in range(5):
+        single.generation(prob, rec1[g % 2], 1, rec1[(g + 1) % 2], seed=4, generation=g)
+        for r, (a, b) in enumerate(bounds):
+            shards[r].generation_peer(prob, buffers, r, g + 1, status, seed=4, generation=g, row_offset=a)
+        for n in ("pop", "velocity", "fit", "local_best_location", "local_best_fit"):
+            assert torch.equal(torch.cat([sh.t[n] for sh in shards]), single.t[n]), (g, n)
+        for sh in shards:
+            assert torch.equal(sh.t["global_best_location"], single.t["global_best_location"]), g
+            assert torch.equal(sh.t["global_best_fit"], single.t["global_best_fit"]), g
+        assert torch.equal(buffers[0], buffers[1]) and torch.equal(buffers[0], buffers[2])
+    assert int(status) == 0
+
+
+def test_peer_exchange_wait_gives_up(cuda):
+    """A flag that nothing sets: the wait ends by itself after its time limit, the kernel reports through the
+    status word and returns, the context stays usable, and the next launch does not wait again."""
+    import time
+
+    from evox_b200 import _cabi as c
+
+    P, d = 256, 8
+    s = opso.init_step(opso.make_state(P, d, -1.0, 1.0, 0.6, 2.5, 0.8, seed=1), opso.sphere)
+    sw = Swarm(s, cuda)
+    n_words = c.lib.evox_pso_exchange_words(d, 2)
+    buffers = [torch.zeros((n_words + 3) // 4 * 4, dtype=torch.int32, device=cuda) for _ in range(2)]
+    status = torch.zeros(1, dtype=torch.int32, device=cuda)
+    t0 = time.perf_counter()
+    sw.generation_peer("sphere", buffers, 0, 5, status)  # nobody wrote tag 5
+    first = time.perf_counter() - t0
+    assert int(status) == 1
+    assert first < 30.0
+    t0 = time.perf_counter()
+    sw.generation_peer("sphere", buffers, 0, 6, status)
+    assert time.perf_counter() - t0 < first / 2 + 0.5
+    assert torch.isfinite(sw.t["pop"]).all()
+    with pytest.raises(c.EvoxKernelError, match="tag 0"):
+        sw.generation_peer("sphere", buffers, 0, 0, status)
+    with pytest.raises(c.EvoxKernelError, match="rank"):
+        sw.generation_peer("sphere", buffers, 2, 1, status)
 
 
 def test_generation_rejects_overlapping_records(cuda):
