@@ -146,10 +146,36 @@ constexpr float kCosMargin = 2e-6f;
 
 constexpr int kRowsPerGroup = 4;  // rows a group of kLanesPerRow lanes carries through one sweep of the vectors
 
-// A group of four lanes owns kRowsPerGroup consecutive rows and deals the vectors among its lanes: every vector
-// a lane reads from shared memory (three 16-byte loads for twelve objectives) is used for all of the group's
-// rows. (With one row per group the sweep was bound by shared-memory bandwidth: 48 bytes per row-vector pair,
-// 2.1 ms at 5,000,000 rows.)
+static_assert(kRowsPerGroup == kLanesPerRow, "lane r of a group prepares and finishes row r of the group");
+
+// Floats between two vectors in shared memory: the next multiple of four, so that every vector starts on a
+// 16-byte boundary (ten objectives: two 16-byte loads and one 8-byte load instead of five 8-byte loads).
+template <int MP>
+constexpr int kVecStride = (MP + 3) / 4 * 4;
+
+template <int MP>
+__device__ __forceinline__ void load_vector(const float* __restrict__ row, float (&vj)[MP]) {
+  static_assert(MP % 2 == 0, "vector rows are read with 8- or 16-byte loads");
+#pragma unroll
+  for (int k = 0; k + 4 <= MP; k += 4) {
+    const float4 q = *reinterpret_cast<const float4*>(row + k);
+    vj[k] = q.x;
+    vj[k + 1] = q.y;
+    vj[k + 2] = q.z;
+    vj[k + 3] = q.w;
+  }
+  if constexpr (MP % 4 == 2) {
+    const float2 q = *reinterpret_cast<const float2*>(row + MP - 2);
+    vj[MP - 2] = q.x;
+    vj[MP - 1] = q.y;
+  }
+}
+
+// A group of four lanes owns four consecutive rows. Lane r translates and normalises row r once and hands it to
+// the group by shuffles; in the sweep the vectors are dealt among the lanes and every vector a lane reads from
+// shared memory is used for all four rows (with one row per group the sweep was bound by shared-memory
+// bandwidth: 48 bytes per row-vector pair, 2.1 ms at 5,000,000 rows); lane r then finishes row r (arccosine,
+// angle-penalised distance, the atomic minimum of its vector).
 template <int MP>
 __global__ void __launch_bounds__(kThreads)
     rvea_assign_kernel(const float* __restrict__ f, long long n, int m, const uint32_t* __restrict__ zmin_key,
@@ -157,11 +183,14 @@ __global__ void __launch_bounds__(kThreads)
                        const float* __restrict__ theta_p, unsigned long long* best, int* __restrict__ associate,
                        long long row_offset) {
   constexpr int R = kRowsPerGroup;
-  extern __shared__ __align__(16) float s_vn[];  // nv x MP, zero padded
-  for (int t = threadIdx.x; t < nv * MP; t += blockDim.x) {
-    const int j = t / MP, k = t - j * MP;
+  constexpr int VS = kVecStride<MP>;
+  extern __shared__ __align__(16) float s_vn[];  // nv x VS, zero padded
+  __shared__ float s_zmin[MP];
+  for (int t = threadIdx.x; t < nv * VS; t += blockDim.x) {
+    const int j = t / VS, k = t - j * VS;
     s_vn[t] = (k < m) ? vn[j * m + k] : 0.0f;
   }
+  if (threadIdx.x < MP) s_zmin[threadIdx.x] = threadIdx.x < m ? order_key_inv(zmin_key[threadIdx.x]) : 0.0f;
   __syncthreads();
   const float m_theta = __fmul_rn((float)m, *theta_p);  // rvea_selection.py:26: obj.size(1) * theta
   const int sub = threadIdx.x & (kLanesPerRow - 1);
@@ -171,32 +200,34 @@ __global__ void __launch_bounds__(kThreads)
   const long long n_groups = (n + R - 1) / R;
   for (long long grp = (long long)blockIdx.x * (kThreads / kLanesPerRow) + (threadIdx.x / kLanesPerRow); grp < n_groups;
        grp += groups_per_pass) {
+    // this lane's row: translate by the ideal point, floor at 1e-32, normalise
+    const long long my_row = grp * R + sub;
+    const bool my_live = my_row < n;
+    float mine[MP];
+    bool my_nan = false;
+    float sq = 0.f;
+#pragma unroll
+    for (int k = 0; k < MP; ++k) {
+      float o = 0.f;
+      if (my_live && k < m) {
+        o = __fsub_rn(f[my_row * m + k], s_zmin[k]);
+        o = __fadd_rn(o, fmaxf(__fsub_rn(1e-32f, o), 0.0f));  // maximum(obj, 1e-32), relu form
+        my_nan = my_nan || (o != o);
+        sq = __fmaf_rn(o, o, sq);
+      }
+      mine[k] = o;
+    }
+    const float my_norm = sqrtf(sq);
+    const float den = fmaxf(my_norm, kEps);
+#pragma unroll
+    for (int k = 0; k < MP; ++k) mine[k] = __fdiv_rn(mine[k], den);
     float obj[R][MP];
-    float norm[R];
-    bool has_nan[R];
 #pragma unroll
     for (int r = 0; r < R; ++r) {
-      const long long row = grp * R + r;
-      const bool live = row < n;
-      has_nan[r] = false;
-      float sq = 0.f;
 #pragma unroll
-      for (int k = 0; k < MP; ++k) {
-        float o = 0.f;
-        if (live && k < m) {
-          o = __fsub_rn(f[row * m + k], order_key_inv(zmin_key[k]));
-          o = __fadd_rn(o, fmaxf(__fsub_rn(1e-32f, o), 0.0f));  // maximum(obj, 1e-32), relu form
-          has_nan[r] = has_nan[r] || (o != o);
-          sq = __fmaf_rn(o, o, sq);
-        }
-        obj[r][k] = o;
-      }
-      norm[r] = sqrtf(sq);
-      const float inv_den = fmaxf(norm[r], kEps);
-#pragma unroll
-      for (int k = 0; k < MP; ++k) obj[r][k] = __fdiv_rn(obj[r][k], inv_den);
+      for (int k = 0; k < MP; ++k) obj[r][k] = __shfl_sync(group_lanes, mine[k], r, kLanesPerRow);
     }
-    // sweep 1: per row the largest cosine (first index among equals) and the largest cosine of all the others
+    // the sweep: per row the largest cosine (first index among equals) and the largest cosine of all the others
     float c1[R], c2[R];
     int j1[R];
 #pragma unroll
@@ -208,24 +239,7 @@ __global__ void __launch_bounds__(kThreads)
 #pragma unroll 2
     for (int j = sub; j < nv; j += kLanesPerRow) {
       float vj[MP];
-      if constexpr (MP % 4 == 0) {
-#pragma unroll
-        for (int k = 0; k < MP; k += 4) {
-          const float4 q = *reinterpret_cast<const float4*>(s_vn + j * MP + k);
-          vj[k] = q.x;
-          vj[k + 1] = q.y;
-          vj[k + 2] = q.z;
-          vj[k + 3] = q.w;
-        }
-      } else {
-        static_assert(MP % 2 == 0, "vector rows are read with 8- or 16-byte loads");
-#pragma unroll
-        for (int k = 0; k < MP; k += 2) {
-          const float2 q = *reinterpret_cast<const float2*>(s_vn + j * MP + k);
-          vj[k] = q.x;
-          vj[k + 1] = q.y;
-        }
-      }
+      load_vector<MP>(s_vn + j * VS, vj);
 #pragma unroll
       for (int r = 0; r < R; ++r) {
         float c = 0.f;
@@ -252,19 +266,26 @@ __global__ void __launch_bounds__(kThreads)
         }
       }
     }
+    // Every lane now holds the same c1 / c2 / j1 of the four rows. Lane r keeps row r's; a row whose two largest
+    // cosines are close is first settled by the whole group in the reference's own order.
+    float my_c1 = c1[0];
+    int my_j = j1[0];
+    float my_angle = 0.f;
+    bool my_slow = false;
 #pragma unroll
     for (int r = 0; r < R; ++r) {
-      const long long row = grp * R + r;
-      if (row >= n) continue;  // the same for the group's four lanes
-      float best_angle;
-      int best_j;
+      if (r > 0 && sub == r) {
+        my_c1 = c1[r];
+        my_j = j1[r];
+      }
       // compared after the clamp to [0, 1] the angle is taken of: all cosines below 0 share the angle pi / 2
-      if (!(fminf(fmaxf(c1[r], 0.0f), 1.0f) - fminf(fmaxf(c2[r], 0.0f), 1.0f) > kCosMargin)) {
-        // near tie (or no usable cosine at all): the reference's own order, arccosine of every cosine
-        best_angle = INFINITY;
-        best_j = 0x7fffffff;
+      const bool near = !(fminf(fmaxf(c1[r], 0.0f), 1.0f) - fminf(fmaxf(c2[r], 0.0f), 1.0f) > kCosMargin);
+      if (near && grp * R + r < n) {  // the same for the group's four lanes
+        // near tie (or no usable cosine at all): arccosine of every cosine, first minimum
+        float best_angle = INFINITY;
+        int best_j = 0x7fffffff;
         for (int j = sub; j < nv; j += kLanesPerRow) {
-          const float* vj = s_vn + j * MP;
+          const float* vj = s_vn + j * VS;
           float c = 0.f;
 #pragma unroll
           for (int k = 0; k < MP; ++k) c = __fmaf_rn(obj[r][k], vj[k], c);
@@ -283,24 +304,27 @@ __global__ void __launch_bounds__(kThreads)
             best_j = oj;
           }
         }
-      } else {
-        best_j = j1[r];
-        best_angle = acosf(relu_clamp01(c1[r]));
-      }
-      if (sub == 0) {
-        if (has_nan[r] || best_j >= nv) {
-          associate[row] = -1;  // rvea_selection.py:81-83
-        } else {
-          associate[row] = best_j;
-          // rvea_selection.py:25-29: (1 + m * theta * angle) / gamma * |obj|
-          const float left = __fdiv_rn(__fadd_rn(1.0f, __fmul_rn(m_theta, best_angle)), gamma[best_j]);
-          const float apd = __fmul_rn(left, norm[r]);
-          // NaN sorts first (torch.argmin); +inf keeps its bit pattern and is resolved at gather time
-          const unsigned long long grow = (unsigned long long)(row + row_offset);  // row number in the whole population
-          const unsigned long long key =
-              (apd != apd) ? grow : (((unsigned long long)__float_as_uint(apd) << 32) | (grow & 0xffffffffull));
-          atomicMin(best + best_j, key);
+        if (sub == r) {
+          my_slow = true;
+          my_angle = best_angle;
+          my_j = best_j;
         }
+      }
+    }
+    if (my_live) {
+      if (!my_slow) my_angle = acosf(relu_clamp01(my_c1));
+      if (my_nan || my_j >= nv) {
+        associate[my_row] = -1;  // rvea_selection.py:81-83
+      } else {
+        associate[my_row] = my_j;
+        // rvea_selection.py:25-29: (1 + m * theta * angle) / gamma * |obj|
+        const float left = __fdiv_rn(__fadd_rn(1.0f, __fmul_rn(m_theta, my_angle)), gamma[my_j]);
+        const float apd = __fmul_rn(left, my_norm);
+        // NaN sorts first (torch.argmin); +inf keeps its bit pattern and is resolved at gather time
+        const unsigned long long grow = (unsigned long long)(my_row + row_offset);  // row number in the whole population
+        const unsigned long long key =
+            (apd != apd) ? grow : (((unsigned long long)__float_as_uint(apd) << 32) | (grow & 0xffffffffull));
+        atomicMin(best + my_j, key);
       }
     }
   }
@@ -341,7 +365,7 @@ Layout make_layout(long long n, int m, int nv) {
 template <int MP>
 int launch_assign(const float* f, long long n, int m, const uint32_t* zmin, const float* vn, const float* gamma, int nv,
                   const float* theta, unsigned long long* best, int* associate, long long row_offset, cudaStream_t s) {
-  const size_t smem = sizeof(float) * (size_t)nv * MP;
+  const size_t smem = sizeof(float) * (size_t)nv * kVecStride<MP>;
   EVOX_REQUIRE(smem <= 200 * 1024, EVOX_ERR_INVALID, "ref_vec_guided: %d reference vectors x %d objectives do not fit in shared memory", nv, m);
   if (smem > 48 * 1024) {
     EVOX_CUDA(cudaFuncSetAttribute(rvea_assign_kernel<MP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
