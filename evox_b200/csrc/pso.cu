@@ -266,9 +266,12 @@ __global__ void __launch_bounds__(kThreads, MOVE_BLOCKS_PER_SM) pso_move_eval_ke
       const float4* rg4 = PHILOX ? nullptr : reinterpret_cast<const float4*>(a.rg + base);
       const float4* rp4 = PHILOX ? nullptr : reinterpret_cast<const float4*>(a.rp + base);
       const uint64_t q0 = (uint64_t)(a.row_offset + row) * (uint64_t)n_call;
-      // Plain loop: with four blocks of eight warps per SM the other warps cover a chunk's load latency; a
-      // register double buffer (next chunk's loads issued ahead) measured 4 % slower here, and three blocks
-      // per SM 15 % slower.
+      // Plain loop: with four blocks of eight warps per SM the other warps cover a chunk's load latency. Measured
+      // and dropped: a register double buffer (next chunk's loads issued ahead) 4 % slower; the loads of two chunks
+      // issued together 3 % slower at four blocks per SM and 13 % slower at three; four chunks at two blocks per SM
+      // 20 % slower; lanes holding half chunks (8-byte loads, 40 registers, six blocks per SM, the two lanes of a
+      // chunk swapping halves of their Philox draws) 25 % slower. The pace follows the instruction count and the
+      // number of resident warps, not the bytes in flight.
       for (int c = lane; c < n_call; c += 32) {
         const float4 x = __ldcs(pop4 + c);
         float4 v = __ldcs(vel4 + c);
