@@ -15,6 +15,7 @@ import torch
 
 from .. import _cabi
 from ..core import Algorithm, Mutable, Parameter
+from ..core.functional import replica_seed
 
 __all__ = ["CLPSO"]
 
@@ -144,7 +145,7 @@ class CLPSO(Algorithm):
                 _cabi.ptr(self.pop), _cabi.ptr(self.velocity), _cabi.ptr(self.personal_best_location), _cabi.ptr(self.fit),
                 _cabi.ptr(source_rows), _cabi.ptr(self.lb, torch.float32, "lb"), _cabi.ptr(self.ub, torch.float32, "ub"),
                 _cabi.ptr(self.w, torch.float32, "w"), _cabi.ptr(self.c, torch.float32, "c"), _cabi.ptr(random_coefficient),
-                n, self.dim, fitness_id, _cabi.host_floats(params), self.seed, self.generation, s,
+                n, self.dim, fitness_id, _cabi.host_floats(params), replica_seed(self.seed), self.generation, s,
             )
         )
         self.generation += 1

@@ -21,6 +21,7 @@ import torch
 
 from .. import _cabi
 from ..core import Algorithm, Mutable, Parameter
+from ..core.functional import replica_seed
 from ..problems.numerical import _relu_clamp_rows
 
 __all__ = ["CSO"]
@@ -159,7 +160,7 @@ class CSO(Algorithm):
                 _cabi.ptr(self.pop), _cabi.ptr(self.velocity), int(self.store_velocity), _cabi.ptr(self.fit), _cabi.ptr(perm),
                 _cabi.ptr(self.lb, torch.float32, "lb"), _cabi.ptr(self.ub, torch.float32, "ub"),
                 _cabi.ptr(self.phi, torch.float32, "phi"), _cabi.ptr(lambdas), self.pop_size, self.dim, fitness_id,
-                _cabi.host_floats(params), self.seed, self.generation, int(self._center_stamp == stamp),
+                _cabi.host_floats(params), replica_seed(self.seed), self.generation, int(self._center_stamp == stamp),
                 _cabi.ptr(candidates), _cabi.ptr(students), _cabi.ptr(self._ws), self._ws.numel(),
                 ctypes.byref(next_ready), _cabi.stream_ptr(dev),
             )

@@ -16,6 +16,7 @@ import torch
 
 from .. import _cabi
 from ..core import Algorithm, Mutable, Parameter
+from ..core.functional import replica_seed
 from ..problems.numerical import _relu_clamp_rows
 
 __all__ = ["DE"]
@@ -142,7 +143,7 @@ class DE(Algorithm):
                 _cabi.ptr(rows_a), _cabi.ptr(rows_b), _cabi.ptr(forced), _cabi.ptr(self.lb, torch.float32, "lb"),
                 _cabi.ptr(self.ub, torch.float32, "ub"), _cabi.ptr(self.differential_weight, torch.float32, "differential_weight"),
                 _cabi.ptr(self.cross_probability, torch.float32, "cross_probability"), _cabi.ptr(cross_prob), n, self.dim,
-                fitness_id, _cabi.host_floats(params), self.seed, self.generation, s,
+                fitness_id, _cabi.host_floats(params), replica_seed(self.seed), self.generation, s,
             )
         )
         self.generation += 1

@@ -12,7 +12,8 @@ from typing import Callable, Optional
 import torch
 
 from ..core import Algorithm, Mutable, Parameter
-from ..operators.selection import nd_environmental_selection, raise_on_kernel_errors, ref_vec_guided
+from ..core.functional import replica_seed
+from ..operators.selection import nd_environmental_selection, non_dominate_rank, raise_on_kernel_errors, ref_vec_guided
 from ..operators.variation import make_offspring, tournament_selection_multifit
 from ..problems.numerical import _relu_clamp_rows
 
@@ -92,7 +93,7 @@ class _MOBase(Algorithm):
     def _variation(self, pop: torch.Tensor, mating_pool: torch.Tensor | None, draws: dict | None) -> torch.Tensor:
         """crossover -> mutation -> clamp (nsga2.py:95-97). Fused kernel unless custom operators are set."""
         if self.crossover is None and self.mutation is None:
-            return make_offspring(pop, self.lb, self.ub, mating_pool, draws, seed=self.seed, generation=self.generation)
+            return make_offspring(pop, self.lb, self.ub, mating_pool, draws, seed=replica_seed(self.seed), generation=self.generation)
         from ..operators.variation import polynomial_mutation, simulated_binary
 
         parents = pop if mating_pool is None else pop[mating_pool]
@@ -131,6 +132,145 @@ class NSGA2(_MOBase):
         merge_fit = torch.cat([self.fit, off_fit], dim=0)
         self.pop, self.fit, self.rank, self.dis = nd_environmental_selection(merge_pop, merge_fit, self.pop_size)
         self.generation += 1
+
+
+def _masked_assign(target: torch.Tensor, index: torch.Tensor, mask: torch.Tensor, value) -> torch.Tensor:
+    """`target` with `value` written at `index[mask]`, INCLUDING what the reference's helper of that name does
+    with the entries outside the mask (nsga3.py:56-72): every entry writes to its index clamped into the
+    target, the target's old value where the mask does not hold, and among entries that meet at one index the
+    LAST one stands, as on the reference's sequential CPU path (a plain `index_copy` with duplicates is not
+    deterministic on a GPU). An assignment can thus be undone by a later entry outside the mask that is
+    clamped onto the same index; generations of the reference depend on it."""
+    n = target.shape[0]
+    idx = index.clamp(0, n - 1).to(torch.int64)
+    pos = torch.arange(idx.shape[0], device=target.device)
+    last = torch.full((n,), -1, dtype=torch.int64, device=target.device).scatter_reduce(0, idx, pos, "amax", include_self=True)
+    wins = last[idx] == pos
+    write = torch.where(mask, torch.as_tensor(value, dtype=target.dtype, device=target.device), target[idx])
+    out = target.clone()
+    out[idx[wins]] = write[wins]
+    return out
+
+
+class NSGA3(_MOBase):
+    """NSGA-III (algorithms/mo/nsga3.py:75-286): non-dominated rank by the dominance / peel kernels, then
+    reference-point niching over the last admitted front. Constructor arguments and state names are the
+    reference's; `data_type` other than float32 is not supported."""
+
+    def __init__(self, pop_size: int, n_objs: int, lb: torch.Tensor, ub: torch.Tensor, selection_op: Optional[Callable] = None,
+                 mutation_op: Optional[Callable] = None, crossover_op: Optional[Callable] = None,
+                 data_type: Optional[torch.dtype] = None, device: torch.device | None = None):
+        super().__init__()
+        assert data_type in (None, torch.float32), "NSGA3: only float32 decision variables"
+        device = torch.get_default_device() if device is None else torch.device(device)
+        self.pop_size = pop_size
+        self._setup(pop_size, n_objs, lb, ub, selection_op, mutation_op, crossover_op, device)
+        pop = (self.ub - self.lb) * torch.rand(pop_size, self.dim, device=device) + self.lb
+        self.pop = Mutable(pop)
+        self.fit = Mutable(torch.full((pop_size, n_objs), torch.inf, device=device))
+        self.rank = Mutable(torch.full((pop_size,), torch.inf, device=device))
+        self.ref = uniform_sampling(pop_size, n_objs)[0].to(device)
+
+    def init_step(self):
+        self.fit = self.evaluate(self.pop)
+        self.rank = non_dominate_rank(self.fit)
+
+    def step(self, parents: torch.Tensor | None = None, draws: dict | None = None, perm_merge: torch.Tensor | None = None,
+             perm_ref: torch.Tensor | None = None):
+        """One generation (nsga3.py:155-266). `parents`, `draws`, `perm_merge`, `perm_ref` replace the random
+        draws of the tournament, of crossover / mutation and of the two permutations."""
+        raise_on_kernel_errors()
+        select = self.selection or tournament_selection_multifit
+        kwargs = {"parents": parents} if (self.selection is None and parents is not None) else {}
+        mating_pool = select(self.pop_size, [self.rank.to(torch.float32)], **kwargs)
+        offspring = self._variation(self.pop, mating_pool, draws)
+        off_fit = self.evaluate(offspring)
+        self.environmental_selection(offspring, off_fit, perm_merge, perm_ref)
+        self.generation += 1
+
+    @staticmethod
+    def _normalise(fit: torch.Tensor) -> torch.Tensor:
+        """Ideal-point translation and hyperplane intercepts of the extreme points (nsga3.py:176-188)."""
+        m = fit.shape[1]
+        f = fit - fit.min(dim=0).values
+        w = torch.eye(m, device=f.device) + 1e-6
+        # per objective j the row with the smallest achievement value max_k f[i, k] / w[j, k]
+        extreme = f[(f.unsqueeze(0) / w.unsqueeze(1)).max(dim=2).values.argmin(dim=1)]
+        if int(torch.linalg.matrix_rank(extreme)) == m:
+            intercepts = 1.0 / torch.linalg.solve(extreme, torch.ones(m, device=f.device))
+        else:
+            intercepts = f.max(dim=0).values
+        return f / intercepts
+
+    @staticmethod
+    def _distances(fit: torch.Tensor, ref: torch.Tensor) -> torch.Tensor:
+        """|f| * sqrt(1 - cos^2) of every (row, reference point) pair (nsga3.py:272-286)."""
+        mag = torch.norm(fit, dim=1, keepdim=True).clamp_min(1e-10)
+        cos = torch.matmul(fit / mag, (ref / torch.norm(ref, dim=1, keepdim=True).clamp_min(1e-10)).T)
+        return mag * torch.sqrt((1 - cos**2).clamp_min(1e-10))
+
+    def environmental_selection(self, offspring: torch.Tensor, off_fit: torch.Tensor, perm_merge: torch.Tensor | None = None,
+                                perm_ref: torch.Tensor | None = None) -> None:
+        dev, n_keep = self.pop.device, self.pop_size
+        merge_pop = torch.cat([self.pop, offspring], dim=0)
+        merge_fit = torch.cat([self.fit, off_fit], dim=0)
+        perm_merge = torch.randperm(merge_pop.shape[0], device=dev) if perm_merge is None else perm_merge.to(dev)
+        merge_pop, merge_fit = merge_pop[perm_merge], merge_fit[perm_merge]
+        rank = non_dominate_rank(merge_fit)
+        worst = torch.sort(rank).values[n_keep]  # rank of the (pop_size + 1)-th best row
+        keep = torch.nonzero(rank <= worst).flatten()
+        merge_pop, merge_fit, rank = merge_pop[keep], merge_fit[keep], rank[keep]
+        c, n_ref = merge_pop.shape[0], self.ref.shape[0]
+        perm_ref = torch.randperm(n_ref, device=dev) if perm_ref is None else perm_ref.to(dev)
+        group_dist, group_id = self._distances(self._normalise(merge_fit), self.ref[perm_ref]).min(dim=1)
+        big = c + merge_pop.shape[1] + merge_fit.shape[1] + 1  # the reference's upper_bound sentinel
+        in_last = rank == worst
+        zeros = torch.zeros(n_ref, dtype=torch.int64, device=dev)
+        rho = zeros.scatter_add(0, group_id, (~in_last).to(torch.int64))  # rows already admitted, per reference point
+        rho_last = zeros.scatter_add(0, group_id, in_last.to(torch.int64))  # candidates of the last front
+        selected_num = int(rho.sum())
+        rho = torch.where(rho_last == 0, big, rho)
+        group_id = torch.where(in_last, group_id, big)
+        rows = torch.arange(c, device=dev)
+
+        # first stage: reference points nobody was admitted for take their closest candidate (first minimum);
+        # candidates ordered by (reference point, distance, index): a group's first entry is that minimum
+        selected_ref = rho == 0
+        by_dist = torch.argsort(group_dist, stable=True)
+        order = by_dist[torch.argsort(group_id[by_dist], stable=True)]
+        first = torch.full((n_ref + 1,), c, dtype=torch.int64, device=dev).scatter_reduce(
+            0, group_id[order].clamp(max=n_ref), rows, "amin", include_self=True)[:n_ref]
+        candi = torch.where(selected_ref, order[first.clamp(max=c - 1)], 0)  # the others: argmin of an all-inf column = 0
+        rank = _masked_assign(rank, candi, selected_ref, worst - 1)
+        rho_last = torch.where(selected_ref, rho_last - 1, rho_last)
+        rho = torch.where(selected_ref, 1, rho)
+        rho = torch.where(rho_last == 0, big, rho)
+        selected_num += int(selected_ref.sum())
+
+        # second stage: per reference point its remaining candidates in index order, one per round for the
+        # reference points with the fewest admitted rows
+        group_id = _masked_assign(group_id, candi, selected_ref, big)
+        order = torch.argsort(group_id, stable=True)  # by (reference point, index); rows outside the last front at the end
+        counts = zeros.scatter_add(0, group_id.clamp(max=n_ref - 1), (group_id < big).to(torch.int64))
+        start = torch.cumsum(counts, 0) - counts
+        cursor = torch.zeros_like(counts)
+        while selected_num < n_keep:
+            selected_ref = rho == rho.min()
+            level = rho.min()
+            candi = torch.where(cursor < counts, order[(start + cursor).clamp(max=c - 1)], big)
+            rank = _masked_assign(rank, candi, selected_ref, worst - 1)
+            cursor = torch.where(selected_ref, cursor + 1, cursor)
+            rho_last = torch.where(selected_ref, rho_last - 1, rho_last)
+            rho = torch.where(selected_ref, level + 1, rho)
+            rho = torch.where(rho_last == 0, big, rho)
+            selected_num += int(selected_ref.sum())
+
+        # the last round may admit too many: its lowest indices leave again
+        dif = selected_num - n_keep
+        leaving = torch.sort(torch.where(selected_ref, candi, big)).values
+        rank = _masked_assign(rank, leaving, torch.arange(n_ref, device=dev) < dif, worst)
+        final = rank < worst
+        self.pop, self.fit, self.rank = merge_pop[final], merge_fit[final], rank[final]
 
 
 class RVEA(_MOBase):

@@ -30,6 +30,7 @@ import torch
 
 from .. import _cabi
 from ..core import Algorithm, Mutable, Parameter
+from ..core.functional import replica_seed
 from ..problems.numerical import FIT_SPHERE
 from ..sharding import allgather_records, group_info, shard_bounds
 
@@ -265,7 +266,7 @@ class PSO(Algorithm):
         state = tuple(_cabi.ptr(getattr(self, n)) for n in self._STATE)
         args = (
             *self._static_args, _cabi.ptr(rg, torch.float32, "rg"), _cabi.ptr(rp, torch.float32, "rp"),
-            self.local_size, self.dim, fitness_id, _cabi.host_floats(params), self.seed, self.generation,
+            self.local_size, self.dim, fitness_id, _cabi.host_floats(params), replica_seed(self.seed), self.generation,
         )
         if plan is None:
             # the problem is evaluated outside: two launches, nothing carried to the next generation

@@ -17,6 +17,7 @@ import torch
 
 from .. import _cabi
 from ..core import Algorithm, Mutable, Parameter
+from ..core.functional import replica_seed
 
 __all__ = ["SLPSOGS", "SLPSOUS"]
 
@@ -137,7 +138,7 @@ class _SLPSO(Algorithm):
                 _cabi.ptr(self.lb, torch.float32, "lb"), _cabi.ptr(self.ub, torch.float32, "ub"),
                 _cabi.ptr(self.social_influence_factor, torch.float32, "social_influence_factor"),
                 _cabi.ptr(draws[0]), _cabi.ptr(draws[1]), _cabi.ptr(draws[2]), n, self.dim, fitness_id, _cabi.host_floats(params),
-                self.seed, self.generation, int(self._center_stamp == stamp), _cabi.ptr(sc["ws"]), sc["ws"].numel(),
+                replica_seed(self.seed), self.generation, int(self._center_stamp == stamp), _cabi.ptr(sc["ws"]), sc["ws"].numel(),
                 ctypes.byref(next_ready), s,
             )
         )

@@ -608,6 +608,51 @@ def golden_hype(out: dict):
         out[f"step_g{it}_pop"], out[f"step_g{it}_fit"] = _np(wf.algorithm.state_dict()["pop"]), _np(wf.algorithm.state_dict()["fit"])
 
 
+def golden_nsga3(out: dict):
+    """NSGA3.step (algorithms/mo/nsga3.py:155-266) on DTLZ2, the environmental part in isolation: per recorded
+    generation the state before the step, the offspring and their objectives (taken at the `evaluate` call),
+    the two permutations the step draws (merged population, reference points), and the state after it."""
+    import evox.algorithms.mo.nsga3 as nmod
+    from evox.problems.numerical import DTLZ2
+    from evox.workflows import StdWorkflow
+
+    for tag, (pop_size, d, m, gens, seed) in {"m3": (60, 12, 3, 4, 11), "m4": (84, 9, 4, 3, 12), "m2": (30, 6, 2, 3, 13)}.items():
+        torch.manual_seed(seed)
+        algo = nmod.NSGA3(pop_size, m, torch.zeros(d), torch.ones(d))
+        wf = StdWorkflow(algo, DTLZ2(d=d, m=m))
+        wf.init_step()
+        out[f"{tag}_ref"] = _np(wf.algorithm.ref)
+        out[f"{tag}_gens"] = np.asarray(gens)
+        out[f"{tag}_pop_size"] = np.asarray(pop_size)  # the population itself may hold fewer rows (see oracle/nsga3.py)
+        for g in range(gens):
+            st = wf.algorithm.state_dict()
+            out[f"{tag}_g{g}_pop"], out[f"{tag}_g{g}_fit"], out[f"{tag}_g{g}_rank"] = _np(st["pop"]), _np(st["fit"]), _np(st["rank"])
+            perms, evals = [], []
+            real_randperm, real_eval = torch.randperm, wf.algorithm.evaluate
+
+            def randperm(*a, **k):
+                perms.append(real_randperm(*a, **k))
+                return perms[-1]
+
+            def evaluate(x):
+                f = real_eval(x)
+                evals.append((x.clone(), f.clone()))
+                return f
+
+            nmod.torch.randperm = randperm
+            wf.algorithm.evaluate = evaluate
+            try:
+                wf.step()
+            finally:
+                nmod.torch.randperm = real_randperm
+                wf.algorithm.evaluate = real_eval
+            assert len(perms) == 2 and len(evals) == 1
+            out[f"{tag}_g{g}_offspring"], out[f"{tag}_g{g}_off_fit"] = _np(evals[0][0]), _np(evals[0][1])
+            out[f"{tag}_g{g}_perm_merge"], out[f"{tag}_g{g}_perm_ref"] = _np(perms[0]), _np(perms[1])
+            st = wf.algorithm.state_dict()
+            out[f"{tag}_g{g}_next_pop"], out[f"{tag}_g{g}_next_fit"], out[f"{tag}_g{g}_next_rank"] = _np(st["pop"]), _np(st["fit"]), _np(st["rank"])
+
+
 def golden_nds_large(out: dict):
     """Ranks at the sizes the benchmark quotes. 2N = 20,000 (benchmark configuration 1) comes from the reference
     itself (about 3 GB of temporaries and half a minute on CPU). 2N = 100,000 is beyond what the reference can
@@ -635,7 +680,7 @@ def golden_nds_large(out: dict):
 
 GENERATORS = {"pso": golden_pso, "nds": golden_nds, "rvea": golden_rvea, "es": golden_es, "variation": golden_variation,
               "cso": golden_cso, "ars": golden_ars, "clpso": golden_clpso, "pes": golden_pes, "slpso": golden_slpso, "rveaa": golden_rveaa, "de": golden_de, "snes_des": golden_snes_des, "hype": golden_hype,
-              "nds_large": golden_nds_large}
+              "nsga3": golden_nsga3, "nds_large": golden_nds_large}
 SLOW = {"nds_large"}  # only when named in --only
 
 
