@@ -306,7 +306,7 @@ class PSO(Algorithm):
                     self._kernel_events.append(pair)
                 peer["tag"] = 1 if tag == 2**32 - 1 else tag + 1
                 self._pending = (self._swarm_key(), None)
-                if self.generation % 4096 == 4095 and int(peer["status"]) != 0:
+                if self.generation % 256 == 255 and int(peer["status"]) != 0:  # one host read per 256 generations
                     raise _cabi.EvoxKernelError("PSO: a wait for another GPU's best-particle record timed out")
             else:
                 records = self._rebuild_records(dev) if stale else self._pending[1]
