@@ -110,10 +110,13 @@ def _replica(index: int):
         _REPLICA = old
 
 
-def vmap(func: Callable, in_dims: int | tuple = 0, out_dims: int | tuple = 0, randomness: str = "error", **_ignored) -> Callable:
+def vmap(func: Callable, in_dims: int | tuple = 0, out_dims: int | tuple = 0, randomness: str = "error", *,
+         chunk_size: int | None = None) -> Callable:
     """Map `func` over dimension `in_dims` of its tensor arguments, slice by slice (see the module text).
     `in_dims` / `out_dims`: one integer or `None` for all arguments / results, or a tuple with one entry
-    per positional argument / result; an entry applies to every tensor inside that argument."""
+    per positional argument / result; an entry applies to every tensor inside that argument. `chunk_size` is
+    accepted for `torch.vmap`'s signature; the slices run one at a time whatever it says."""
+    del chunk_size
     if randomness not in ("error", "different", "same"):
         raise ValueError(f"randomness must be 'error', 'different' or 'same', got {randomness!r}")
     module = getattr(func, "_evox_module", None)
