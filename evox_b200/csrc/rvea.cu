@@ -244,7 +244,7 @@ __global__ void __launch_bounds__(kThreads)
       c2[r] = -INFINITY;
       j1[r] = 0x7fffffff;
     }
-#pragma unroll 2
+#pragma unroll 4
     for (int j = sub; j < nv; j += kLanesPerRow) {
       float vj[MP];
       load_vector<MP>(s_vn + j * VS, vj);
