@@ -30,8 +30,13 @@ namespace {
 constexpr int kWarpsPerBlock = 8;
 constexpr int kThreads = kWarpsPerBlock * 32;
 constexpr int kMaxPartials = 2048;
+// The generation kernel runs 32 warps per SM as ONE block of 1,024 threads: measured in one GPU call at
+// 1,000,000 x 1,000, 282.5 generations/s against 279-282 with two blocks of 512 and 276 with four blocks of 256
+// (fewer blocks also mean fewer partial minima for the last block to fold).
+constexpr int kMoveWarps = 32;
+constexpr int kMoveThreads = kMoveWarps * 32;
 #ifndef MOVE_BLOCKS_PER_SM
-#define MOVE_BLOCKS_PER_SM 4
+#define MOVE_BLOCKS_PER_SM 1
 #endif
 
 // --------------------------------------------------------------------------------------------
@@ -231,10 +236,10 @@ __device__ __forceinline__ float move_one(float x, float& v, float pb, float gb,
 }
 
 template <int VEC, bool PHILOX, int FIT, bool FUSED>
-__global__ void __launch_bounds__(kThreads, MOVE_BLOCKS_PER_SM) pso_move_eval_kernel(const MoveArgs a) {
+__global__ void __launch_bounds__(kMoveThreads, MOVE_BLOCKS_PER_SM) pso_move_eval_kernel(const MoveArgs a) {
   const int lane = threadIdx.x & 31;
-  const long long warp0 = (long long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
-  __shared__ MinIdx s_warp_min[FUSED ? kWarpsPerBlock : 1];
+  const long long warp0 = (long long)blockIdx.x * kMoveWarps + (threadIdx.x >> 5);
+  __shared__ MinIdx s_warp_min[FUSED ? kMoveWarps : 1];
   const float* gbest_row = a.gbest_loc;
   if constexpr (FUSED) {
     bool take;
@@ -242,7 +247,7 @@ __global__ void __launch_bounds__(kThreads, MOVE_BLOCKS_PER_SM) pso_move_eval_ke
     gbest_row = fold_candidates(a, lane, &take, &best);
     if (lane == 0) s_warp_min[threadIdx.x >> 5] = MinIdx{INFINITY, kNoRow};
   }
-  const long long n_warps = (long long)gridDim.x * kWarpsPerBlock;
+  const long long n_warps = (long long)gridDim.x * kMoveWarps;
   const float w = *a.w, phi_p = *a.phi_p, phi_g = *a.phi_g;
   // vector path in Philox mode: the draws arrive as 24-bit integers, 2^-24 rides on phi (exact)
   const float phi_p_v = (PHILOX && VEC == 4) ? phi_p * 5.9604644775390625e-08f : phi_p;
@@ -270,7 +275,7 @@ __global__ void __launch_bounds__(kThreads, MOVE_BLOCKS_PER_SM) pso_move_eval_ke
       // The loop exists twice, for rows whose position becomes their personal best (no load of the old best, one
       // more store) and for the others: written out like this (instead of a select and a predicated store inside
       // one loop) the kernel is 10 % faster (0.78 -> 0.86 of the measured copy bandwidth at 1,000,000 x 1,000).
-      // Plain loop: with four blocks of eight warps per SM the other warps cover a chunk's load latency. Measured
+      // Plain loop: with 32 warps per SM the other warps cover a chunk's load latency. Measured
       // and dropped: a register double buffer (next chunk's loads issued ahead) 4 % slower; the loads of two chunks
       // issued together 3 % slower at four blocks per SM and 13 % slower at three; four chunks at two blocks per SM
       // 20 % slower; lanes holding half chunks (8-byte loads, 40 registers, six blocks per SM, the two lanes of a
@@ -345,7 +350,7 @@ __global__ void __launch_bounds__(kThreads, MOVE_BLOCKS_PER_SM) pso_move_eval_ke
     __shared__ bool s_last;
     __syncthreads();
     if (threadIdx.x < 32) {
-      MinIdx t = (lane < kWarpsPerBlock) ? s_warp_min[lane] : MinIdx{INFINITY, kNoRow};
+      MinIdx t = (lane < kMoveWarps) ? s_warp_min[lane] : MinIdx{INFINITY, kNoRow};
       t = warp_min_idx(t);
       if (lane == 0) {
         a.partials[blockIdx.x] = t;
@@ -569,9 +574,9 @@ int carve(void* ws, size_t bytes, Workspace* out) {
   return EVOX_OK;
 }
 
-int row_grid(long long P, int blocks_per_sm = 8) {
+int row_grid(long long P, int blocks_per_sm = 8, int warps_per_block = kWarpsPerBlock) {
   // persistent grid of exactly the resident blocks (one wave), never more rows than exist
-  const long long want = (P + kWarpsPerBlock - 1) / kWarpsPerBlock;
+  const long long want = (P + warps_per_block - 1) / warps_per_block;
   const long long cap = (long long)sm_count() * blocks_per_sm;
   return (int)(want < cap ? (want < 1 ? 1 : want) : cap);
 }
@@ -593,13 +598,13 @@ template <int VEC, bool PHILOX, bool FUSED>
 void launch_move(int fitness_id, int grid, cudaStream_t s, const MoveArgs& a) {
   switch (fitness_id) {
     case EVOX_FIT_ACKLEY:
-      pso_move_eval_kernel<VEC, PHILOX, EVOX_FIT_ACKLEY, FUSED><<<grid, kThreads, 0, s>>>(a);
+      pso_move_eval_kernel<VEC, PHILOX, EVOX_FIT_ACKLEY, FUSED><<<grid, kMoveThreads, 0, s>>>(a);
       break;
     case EVOX_FIT_RASTRIGIN:
-      pso_move_eval_kernel<VEC, PHILOX, EVOX_FIT_RASTRIGIN, FUSED><<<grid, kThreads, 0, s>>>(a);
+      pso_move_eval_kernel<VEC, PHILOX, EVOX_FIT_RASTRIGIN, FUSED><<<grid, kMoveThreads, 0, s>>>(a);
       break;
     default:
-      pso_move_eval_kernel<VEC, PHILOX, EVOX_FIT_SPHERE, FUSED><<<grid, kThreads, 0, s>>>(a);
+      pso_move_eval_kernel<VEC, PHILOX, EVOX_FIT_SPHERE, FUSED><<<grid, kMoveThreads, 0, s>>>(a);
       break;
   }
 }
@@ -767,7 +772,7 @@ extern "C" int evox_pso_move_eval(float* pop, float* velocity, float* local_best
                               row_offset))
     return rc;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  launch_move_any<false>(vec, rg == nullptr, fitness_id, row_grid(pop_size, MOVE_BLOCKS_PER_SM), s, a);
+  launch_move_any<false>(vec, rg == nullptr, fitness_id, row_grid(pop_size, MOVE_BLOCKS_PER_SM, kMoveWarps), s, a);
   EVOX_LAUNCH_CHECK();
   return EVOX_OK;
 }
@@ -804,7 +809,7 @@ extern "C" int evox_pso_generation(float* pop, float* velocity, float* local_bes
   a.cand_out = candidate_out;
   a.ticket = ws.ticket;
   a.partials = ws.partials;
-  const int grid = row_grid(pop_size, MOVE_BLOCKS_PER_SM);
+  const int grid = row_grid(pop_size, MOVE_BLOCKS_PER_SM, kMoveWarps);
   EVOX_REQUIRE(grid <= kMaxPartials, EVOX_ERR_INVALID, "pso_generation: grid of %d blocks exceeds %d partials", grid, kMaxPartials);
   launch_move_any<true>(vec, rg == nullptr, fitness_id, grid, reinterpret_cast<cudaStream_t>(stream), a);
   EVOX_LAUNCH_CHECK();
@@ -850,7 +855,7 @@ extern "C" int evox_pso_generation_peer(float* pop, float* velocity, float* loca
   a.gbest_loc_out = global_best_location;
   a.ticket = ws.ticket;
   a.partials = ws.partials;
-  const int grid = row_grid(pop_size, MOVE_BLOCKS_PER_SM);
+  const int grid = row_grid(pop_size, MOVE_BLOCKS_PER_SM, kMoveWarps);
   EVOX_REQUIRE(grid <= kMaxPartials, EVOX_ERR_INVALID, "pso_generation_peer: grid of %d blocks exceeds %d partials", grid, kMaxPartials);
   launch_move_any<true>(vec, rg == nullptr, fitness_id, grid, reinterpret_cast<cudaStream_t>(stream), a);
   EVOX_LAUNCH_CHECK();
