@@ -201,13 +201,14 @@ int launch_weighted_rows(const float* fitness, const float* noise, long long pop
 // pop[i][l] = center[l] + sigma * (+-) noise[i mod rows][l]   (open_es.py:64-68); with `accum` the same
 // perturbation is also added to accum[i][l] (PersistentES, persistent_es.py:76-80).
 // Rows on blockIdx.y, VEC consecutive columns per thread: no index division, 16-byte accesses when VEC = 4.
-template <int VEC>
+// MIRRORED (row i + noise_rows is row i with the perturbation negated: one read, two writes) and ACCUM are template
+// arguments: as run-time conditions inside the column loop they cost the kernel a tenth of its bandwidth.
+template <int VEC, bool MIRRORED, bool ACCUM>
 __global__ void __launch_bounds__(kThreads)
     openes_ask_kernel(const float* __restrict__ center, const float* __restrict__ noise, const float* __restrict__ sigma_p,
                       long long pop, long long n, long long noise_rows, float* __restrict__ out, float* __restrict__ accum) {
   const float sigma = *sigma_p;
   const long long nv = n / VEC;
-  const bool mirrored = noise_rows < pop;  // row i + noise_rows is row i with the perturbation negated: one read, two writes
   for (long long i = blockIdx.y; i < noise_rows; i += gridDim.y) {
     const float* zrow = noise + i * n;
     for (long long c = (long long)blockIdx.x * blockDim.x + threadIdx.x; c < nv; c += (long long)gridDim.x * blockDim.x) {
@@ -221,12 +222,13 @@ __global__ void __launch_bounds__(kThreads)
         z[0] = zrow[c];
         ce[0] = center[c];
       }
-      for (int half = 0; half < (mirrored ? 2 : 1); ++half) {
+#pragma unroll
+      for (int half = 0; half < (MIRRORED ? 2 : 1); ++half) {
         const long long row = i + half * noise_rows;
         float* orow = out + row * n;
-        float* arow = accum ? accum + row * n : nullptr;
+        float* arow = ACCUM ? accum + row * n : nullptr;
         float ac[VEC], o[VEC];
-        if (arow) {
+        if constexpr (ACCUM) {
           if constexpr (VEC == 4) {
             const float4 q = __ldcs(reinterpret_cast<const float4*>(arow) + c);
             ac[0] = q.x; ac[1] = q.y; ac[2] = q.z; ac[3] = q.w;
@@ -238,14 +240,14 @@ __global__ void __launch_bounds__(kThreads)
         for (int j = 0; j < VEC; ++j) {
           const float pert = __fmul_rn(sigma, half ? -z[j] : z[j]);
           o[j] = __fadd_rn(ce[j], pert);
-          if (arow) ac[j] = __fadd_rn(ac[j], pert);
+          if constexpr (ACCUM) ac[j] = __fadd_rn(ac[j], pert);
         }
         if constexpr (VEC == 4) {
           __stcs(reinterpret_cast<float4*>(orow) + c, make_float4(o[0], o[1], o[2], o[3]));
-          if (arow) __stcs(reinterpret_cast<float4*>(arow) + c, make_float4(ac[0], ac[1], ac[2], ac[3]));
+          if constexpr (ACCUM) __stcs(reinterpret_cast<float4*>(arow) + c, make_float4(ac[0], ac[1], ac[2], ac[3]));
         } else {
           orow[c] = o[0];
-          if (arow) arow[c] = ac[0];
+          if constexpr (ACCUM) arow[c] = ac[0];
         }
       }
     }
@@ -547,10 +549,13 @@ extern "C" int evox_openes_ask(const float* center, const float* noise, const fl
   EVOX_REQUIRE(pop > 0 && dim > 0 && (noise_rows == pop || 2 * noise_rows == pop), EVOX_ERR_INVALID,
                "openes_ask: noise_rows must be pop or pop / 2");
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  if (dim % 4 == 0 && aligned16(center) && aligned16(noise) && aligned16(population))
-    openes_ask_kernel<4><<<rows_by_cols_grid(noise_rows, dim / 4), kThreads, 0, s>>>(center, noise, sigma, pop, dim, noise_rows, population, nullptr);
-  else
-    openes_ask_kernel<1><<<rows_by_cols_grid(noise_rows, dim), kThreads, 0, s>>>(center, noise, sigma, pop, dim, noise_rows, population, nullptr);
+  const bool vec = dim % 4 == 0 && aligned16(center) && aligned16(noise) && aligned16(population);
+  const bool mirrored = noise_rows < pop;
+  const dim3 grid = vec ? rows_by_cols_grid(noise_rows, dim / 4) : rows_by_cols_grid(noise_rows, dim);
+  if (vec && mirrored) openes_ask_kernel<4, true, false><<<grid, kThreads, 0, s>>>(center, noise, sigma, pop, dim, noise_rows, population, nullptr);
+  else if (vec) openes_ask_kernel<4, false, false><<<grid, kThreads, 0, s>>>(center, noise, sigma, pop, dim, noise_rows, population, nullptr);
+  else if (mirrored) openes_ask_kernel<1, true, false><<<grid, kThreads, 0, s>>>(center, noise, sigma, pop, dim, noise_rows, population, nullptr);
+  else openes_ask_kernel<1, false, false><<<grid, kThreads, 0, s>>>(center, noise, sigma, pop, dim, noise_rows, population, nullptr);
   EVOX_LAUNCH_CHECK();
   return EVOX_OK;
 }
@@ -561,9 +566,9 @@ extern "C" int evox_pes_ask(const float* center, const float* noise, const float
   EVOX_REQUIRE(pop > 0 && dim > 0 && pop % 2 == 0, EVOX_ERR_INVALID, "pes_ask: pop must be positive and even");
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (dim % 4 == 0 && aligned16(center) && aligned16(noise) && aligned16(population) && aligned16(pert_accum))
-    openes_ask_kernel<4><<<rows_by_cols_grid(pop / 2, dim / 4), kThreads, 0, s>>>(center, noise, sigma, pop, dim, pop / 2, population, pert_accum);
+    openes_ask_kernel<4, true, true><<<rows_by_cols_grid(pop / 2, dim / 4), kThreads, 0, s>>>(center, noise, sigma, pop, dim, pop / 2, population, pert_accum);
   else
-    openes_ask_kernel<1><<<rows_by_cols_grid(pop / 2, dim), kThreads, 0, s>>>(center, noise, sigma, pop, dim, pop / 2, population, pert_accum);
+    openes_ask_kernel<1, true, true><<<rows_by_cols_grid(pop / 2, dim), kThreads, 0, s>>>(center, noise, sigma, pop, dim, pop / 2, population, pert_accum);
   EVOX_LAUNCH_CHECK();
   return EVOX_OK;
 }
