@@ -165,11 +165,9 @@ __global__ void __launch_bounds__(kThreads)
 #pragma unroll
     for (int j = 0; j < VEC; ++j) acc[j] = 0.f;
     if (l < n) {
-#pragma unroll 4
-      for (long long i = warp; i < pop; i += kWarps) {
-        const bool mirrored = i >= noise_rows;
-        const float f = mirrored ? -fitness[i] : fitness[i];  // f * (-z) and (-f) * z round alike
-        const float* row = noise + (mirrored ? i - noise_rows : i) * n + l;
+      // the warp's rows in ascending order, written as two loops (own noise rows, then the mirrored ones: the same
+      // noise row with the fitness negated; f * (-z) and (-f) * z round alike) instead of one with a select per row
+      auto add_row = [&](float f, const float* row) {
         if constexpr (VEC == 4) {
           const float4 z = __ldg(reinterpret_cast<const float4*>(row));
           acc[0] = __fmaf_rn(f, z.x, acc[0]);
@@ -179,7 +177,13 @@ __global__ void __launch_bounds__(kThreads)
         } else {
           acc[0] = __fmaf_rn(f, __ldg(row), acc[0]);
         }
-      }
+      };
+      const long long plain_end = noise_rows < pop ? noise_rows : pop;
+      long long i = warp;
+#pragma unroll 4
+      for (; i < plain_end; i += kWarps) add_row(fitness[i], noise + i * n + l);
+#pragma unroll 4
+      for (; i < pop; i += kWarps) add_row(-fitness[i], noise + (i - noise_rows) * n + l);
     }
 #pragma unroll
     for (int j = 0; j < VEC; ++j) part[warp][lane * VEC + j] = acc[j];
