@@ -259,7 +259,11 @@ __device__ __forceinline__ float4 normal4(unsigned long long seed, unsigned long
   return make_float4(r0 * c0, r0 * s0, r1 * c1, r1 * s1);
 }
 
-template <bool PAIR, bool ACCUM>
+// EPI: what the layer epilogue does, known at compile time so that none of it is a condition inside the
+// per-element loops. 0: whatever the arguments say; 1: hidden layer of a virtual-LoRA network (rank-8 correction,
+// ReLU, bf16 output, next layer's projection; no bias, no bias noise); 2: its last layer (rank-8 correction, squared
+// error against the target; no bias, no bias noise, no ReLU). The accumulate variant ignores it.
+template <bool PAIR, bool ACCUM, int EPI = 0>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     lora_gemm_kernel(const __grid_constant__ CUtensorMap map_h, const __grid_constant__ CUtensorMap map_w, const GemmArgs a) {
   constexpr int STAGES = Ring<PAIR>::STAGES;
@@ -521,9 +525,17 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         continue;
       }
       const long long p_first = m0 / a.batch;
+      // what this epilogue does: compile-time constants for the two fixed shapes, the arguments otherwise
+      const bool has_t = EPI != 0 ? true : a.t != nullptr;
+      const bool has_bias = EPI != 0 ? false : a.bias != nullptr;
+      const bool has_noise = EPI != 0 ? false : a.has_bias_noise != 0;
+      const bool do_relu = EPI == 1 ? true : (EPI == 2 ? false : a.relu != 0);
+      const bool to_target = EPI == 2 ? true : (EPI == 1 ? false : a.target != nullptr);
+      const bool to_bf16 = EPI == 1 ? true : (EPI == 2 ? false : a.out_bf16 != nullptr);
+      const bool project = EPI == 1 ? true : (EPI == 2 ? false : a.t_partial != nullptr);
       // all epilogue threads are done with the previous tile's factors
       asm volatile("bar.sync 1, 256;" ::: "memory");
-      if (a.t != nullptr) {
+      if (has_t) {
         // B_p[n][q], q = 0..7: elements n * 8 + q of the stream -> Philox calls 2n and 2n + 1
         for (int idx = et; idx < inds_per_tile * BN * 2; idx += kEpilogueThreads) {
           const int ind = idx / (BN * 2), rest = idx - ind * (BN * 2);
@@ -533,7 +545,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           *reinterpret_cast<float4*>(bfac + ((size_t)(ind * BN + col) * RANK + half * 4)) = z;
         }
       }
-      if (a.has_bias_noise) {
+      if (has_noise) {
         for (int idx = et; idx < inds_per_tile * (BN / 4); idx += kEpilogueThreads) {
           const int ind = idx / (BN / 4), c4 = idx - ind * (BN / 4);
           const unsigned long long seed = (unsigned long long)a.seeds[p_first + ind];
@@ -541,7 +553,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           *reinterpret_cast<float4*>(bnoise + (size_t)ind * BN + c4 * 4) = z;
         }
       }
-      if (a.t_partial != nullptr) {
+      if (project) {
         // A'_p[q][n]: element q * N + n of the next block's stream; one call covers 4 columns of one q.
         // A task makes 4 calls (q = 4 half .. 4 half + 3) for columns 4 c4 .. 4 c4 + 3 and stores, per column,
         // the four q values as one float4 at [ind][half][column & 3][column >> 2]: neighbouring threads write
@@ -566,7 +578,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       float tr[RANK];
 #pragma unroll
       for (int q = 0; q < RANK; ++q) tr[q] = 0.f;
-      if (a.t != nullptr) {
+      if (has_t) {
         const float4 t0 = *reinterpret_cast<const float4*>(a.t + row * RANK);
         const float4 t1 = *reinterpret_cast<const float4*>(a.t + row * RANK + 4);
         tr[0] = t0.x; tr[1] = t0.y; tr[2] = t0.z; tr[3] = t0.w;
@@ -585,7 +597,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       float tp[RANK];
 #pragma unroll
       for (int q = 0; q < RANK; ++q) tp[q] = 0.f;
-      const float* target_row = a.target ? a.target + (row % a.batch) * a.N + n0 : nullptr;
+      const float* target_row = to_target ? a.target + (row % a.batch) * a.N + n0 : nullptr;
       float sq_sum = 0.f;
       for (int c = col_half * (BN / 2); c < (col_half + 1) * (BN / 2); c += 32) {
         uint32_t v[32];
@@ -595,8 +607,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
           float acc = __uint_as_float(v[j]) * a.out_scale;
-          if (a.bias) acc += __ldg(a.bias + n0 + c + j);
-          if (a.t != nullptr) {
+          if (has_bias) acc += __ldg(a.bias + n0 + c + j);
+          if (has_t) {
             const float4 b0 = *reinterpret_cast<const float4*>(bf + (size_t)(c + j) * RANK);
             const float4 b1 = *reinterpret_cast<const float4*>(bf + (size_t)(c + j) * RANK + 4);
             float dl = tr[0] * b0.x;
@@ -609,10 +621,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             dl = fmaf(tr[7], b1.w, dl);
             acc = fmaf(a.sigma, dl, acc);
           }
-          if (a.has_bias_noise) acc = fmaf(a.sigma, bn[c + j], acc);
-          y[j] = a.relu ? fmaxf(acc, 0.f) : acc;
+          if (has_noise) acc = fmaf(a.sigma, bn[c + j], acc);
+          y[j] = do_relu ? fmaxf(acc, 0.f) : acc;
         }
-        if (target_row) {
+        if (to_target) {
 #pragma unroll
           for (int j = 0; j < 32; j += 4) {
             const float4 tg = __ldg(reinterpret_cast<const float4*>(target_row + c + j));
@@ -622,8 +634,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             sq_sum = fmaf(d2, d2, sq_sum);
             sq_sum = fmaf(d3, d3, sq_sum);
           }
-        } else if (a.out_bf16) {
-          if (a.t_partial != nullptr) {
+        } else if (to_bf16) {
+          if (project) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
               const float yb = __bfloat162float(__float2bfloat16_rn(y[j]));  // what the next layer will read
@@ -660,8 +672,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           }
         }
       }
-      if (target_row) a.row_partial[(row * n_tiles_n + n_blk) * 2 + col_half] = sq_sum;
-      if (a.t_partial != nullptr && a.out_bf16 != nullptr) {
+      if (to_target) a.row_partial[(row * n_tiles_n + n_blk) * 2 + col_half] = sq_sum;
+      if (project && to_bf16) {
         float* o = a.t_partial + ((size_t)row * (size_t)(n_tiles_n * 2) + (size_t)(n_blk * 2 + col_half)) * RANK;
         *reinterpret_cast<float4*>(o) = make_float4(tp[0], tp[1], tp[2], tp[3]);
         *reinterpret_cast<float4*>(o + 4) = make_float4(tp[4], tp[5], tp[6], tp[7]);
@@ -965,10 +977,10 @@ int make_map(CUtensorMap* map, const void* base, long long rows, long long K, in
 }
 
 // A CTA pair per 256 x 256 tile when the rows allow it, one CTA per 128 x 256 tile otherwise.
-template <bool PAIR, bool ACCUM>
+template <bool PAIR, bool ACCUM, int EPI = 0>
 int launch_variant(cudaLaunchConfig_t& cfg, const CUtensorMap& map_a, const CUtensorMap& map_b, const GemmArgs& a) {
-  EVOX_CUDA(cudaFuncSetAttribute(lora_gemm_kernel<PAIR, ACCUM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
-  EVOX_CUDA(cudaLaunchKernelEx(&cfg, lora_gemm_kernel<PAIR, ACCUM>, map_a, map_b, a));
+  EVOX_CUDA(cudaFuncSetAttribute(lora_gemm_kernel<PAIR, ACCUM, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+  EVOX_CUDA(cudaLaunchKernelEx(&cfg, lora_gemm_kernel<PAIR, ACCUM, EPI>, map_a, map_b, a));
   return EVOX_OK;
 }
 
@@ -1013,11 +1025,19 @@ int launch_gemm(const void* a_base, long long a_rows, const void* b_base, long l
     cfg.attrs = attr;
     cfg.numAttrs = 1;
   }
+  // the two layer shapes of a virtual-LoRA network without biases get epilogues with nothing left to decide
+  const bool no_bias = a.bias == nullptr && !a.has_bias_noise && a.t != nullptr;
+  const bool hidden = no_bias && a.relu && a.out_bf16 != nullptr && a.t_partial != nullptr && a.target == nullptr;
+  const bool last = no_bias && !a.relu && a.target != nullptr && a.row_partial != nullptr;
   int rc;
-  if (pair)
-    rc = accumulate ? launch_variant<true, true>(cfg, map_a, map_b, a) : launch_variant<true, false>(cfg, map_a, map_b, a);
+  if (accumulate)
+    rc = pair ? launch_variant<true, true>(cfg, map_a, map_b, a) : launch_variant<false, true>(cfg, map_a, map_b, a);
+  else if (pair && hidden)
+    rc = launch_variant<true, false, 1>(cfg, map_a, map_b, a);
+  else if (pair && last)
+    rc = launch_variant<true, false, 2>(cfg, map_a, map_b, a);
   else
-    rc = accumulate ? launch_variant<false, true>(cfg, map_a, map_b, a) : launch_variant<false, false>(cfg, map_a, map_b, a);
+    rc = pair ? launch_variant<true, false>(cfg, map_a, map_b, a) : launch_variant<false, false>(cfg, map_a, map_b, a);
   if (rc) return rc;
   EVOX_LAUNCH_CHECK();
   return EVOX_OK;
