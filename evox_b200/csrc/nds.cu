@@ -695,10 +695,11 @@ __device__ __forceinline__ int first_nonzero(const uint4& v) {
 // scanned on, and never backwards: over all fronts a row of Dt is read once. Measured per front at
 // 100,000 rows: about 1.4 us for the barrier itself, the rest is the slowest block's scans (late fronts:
 // few unranked rows are left, so the next unranked dominator of a column is far away).
-template <int kPeelThreads>
+template <int kPeelThreads, bool kMaskInSmem>
 __global__ void __launch_bounds__(kPeelThreads)
     nds_peel_kernel(const uint32_t* __restrict__ Dt, int wp, long long n, uint32_t* U0, uint32_t* U1, int* ptr,
-                    int* rank, Ctrl* ctrl, int mask_in_smem, const uint32_t* __restrict__ perm, int tail_limit) {
+                    int* rank, Ctrl* ctrl, int, const uint32_t* __restrict__ perm, int tail_limit) {
+  constexpr int mask_in_smem = kMaskInSmem ? 1 : 0;  // a template argument: the mask is read inside every hot loop
   extern __shared__ __align__(16) uint32_t s_mask[];
   __shared__ unsigned s_cnt[kPeelThreads / 32];
   __shared__ unsigned s_newly[kPeelThreads / 32];  // per owning warp: columns ranked in this trip
@@ -1636,7 +1637,8 @@ int run_rank(const float* f, long long n, int m, int* rank, void* ws, const Layo
   const long long warps512 = (long long)sm_count() * (kPeelThreadsSmall / 32);
   const bool large = words > warps512 && words <= 2 * warps512;
   const int threads = large ? kPeelThreadsLarge : kPeelThreadsSmall;
-  const void* kernel = large ? (const void*)nds_peel_kernel<kPeelThreadsLarge> : (const void*)nds_peel_kernel<kPeelThreadsSmall>;
+  const void* kernel = large ? (mask_in_smem ? (const void*)nds_peel_kernel<kPeelThreadsLarge, true> : (const void*)nds_peel_kernel<kPeelThreadsLarge, false>)
+                             : (mask_in_smem ? (const void*)nds_peel_kernel<kPeelThreadsSmall, true> : (const void*)nds_peel_kernel<kPeelThreadsSmall, false>);
   if (mask_bytes > 40 * 1024) EVOX_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
   EVOX_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, mask_bytes));
   EVOX_REQUIRE(per_sm > 0, EVOX_ERR_CUDA, "nds_peel_kernel cannot be made resident");
